@@ -1,0 +1,686 @@
+// Block-scaled GEMM for sm_100a: D[M,N] (+)= A[M,K] . B[N,K]^T on tcgen05 tensor cores.
+//
+// One persistent kernel covers the reference's dense, M-grouped contiguous and M-grouped
+// masked GEMMs (api::gemm_nt / m_grouped_gemm_nt_contiguous / m_grouped_gemm_nt_masked,
+// deepgemm/src/api.rs:648-963, whose device side is gemm_sm100_impl in
+// deepgemm/kernels/gemm_sm100.cu:442-891), for three operand kinds:
+//   FP8  E4M3 x E4M3, UE8M0 scales per 32 or 128 K  -> tcgen05.mma kind::mxf8f6f4.block_scale
+//   FP4  E2M1 x E2M1 (packed), UE8M0 scales per 32 K -> tcgen05.mma kind::mxf4.block_scale.block32
+//   BF16                                              -> tcgen05.mma kind::f16
+// Numerical contract: gemm_ref of the reference's golden model (deepgemm/src/golden.rs:444-458)
+// within calc_diff <= 1e-3 (FP8) / 2e-3 (FP4).
+//
+// Structure of a CTA (256 threads, one CTA per SM, 128 x BLOCK_N output tiles):
+//   warp 0   TMA producer: A / B tiles (128B-swizzled, K-major) and packed-SF rows into a
+//            multi-stage shared-memory ring, one mbarrier per stage
+//   warp 1   MMA issuer: scale factors shared memory -> TMEM (tcgen05.cp), then 4 MMAs per
+//            k-block; tcgen05.commit frees the stage / publishes the accumulator
+//   warp 2   scale-factor transposer: rewrites each 128-word SF row from [4][32] to [32][4]
+//            order, the layout tcgen05.cp.32x128b.warpx4 needs; also owns TMEM alloc/free
+//   warps 4-7 epilogue: TMEM -> registers -> bf16/f32 -> global, double-buffered against the
+//            next tile's main loop (two accumulator stages in TMEM)
+// BLOCK_N, the stage count and the scale granularities are run-time parameters: the TMA boxes
+// come from the tensor maps and the MMA shape from a run-time instruction descriptor.
+#include "host.h"
+#include "ptx.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+
+namespace dg {
+
+constexpr uint32_t kBlockM = 128;
+constexpr uint32_t kMaxStages = 10;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kAccStageCols = 256;   // accumulator stage s starts at column s * 256
+constexpr uint32_t kSfaCol = 224;         // SF columns live above a <=224-wide accumulator
+constexpr uint32_t kSfbCol = 232;
+constexpr uint32_t kSmemBarrierBytes = 512;
+
+enum Kind : int { kFp8 = 0, kFp4 = 1, kBf16 = 2 };
+enum GType : int { kNormal = 0, kContiguous = 1, kMasked = 2 };
+
+struct GemmParams {
+    uint32_t m;            // rows of A/D (normal, contiguous); rows per group (masked)
+    uint32_t n;            // columns of D = rows of B per group
+    uint32_t num_groups;
+    uint32_t num_k_blocks;
+    uint32_t block_n;
+    uint32_t num_m_blocks; // normal / contiguous
+    uint32_t num_n_blocks;
+    uint32_t band;         // m-blocks per L2 band
+    uint32_t num_stages;
+    uint32_t stage_bytes;  // A + B + SFA + SFB, 1024-aligned
+    uint32_t off_b, off_sfa, off_sfb;
+    uint32_t sfa_period, sfb_period;  // k-blocks per SF row: 1 (gran 32) or 4 (gran 128)
+    uint32_t sfb_chunks;   // 128-row chunks of the B scale factors per tile
+    uint32_t sf_sub;       // SF rows per k-block: 1 (FP8) or 2 (FP4)
+    uint32_t tx_ab, tx_sfa, tx_sfb;
+    uint32_t out_f32, accumulate;
+    uint64_t ldd;          // D row pitch in elements
+    void* d;
+    const int32_t* layout; // m_indices (contiguous) or masked_m (masked)
+    uint32_t* status;
+};
+
+struct Tile {
+    uint32_t a_row;     // first row in A / SFA-column / D coordinates
+    uint32_t row_end;   // rows >= row_end are not stored
+    uint32_t n0;        // first column of D
+    uint32_t b_row;     // first row in (stacked) B / SFB-column coordinates
+    bool skip;
+};
+
+// Static persistent schedule: CTA c takes tiles c, c + grid, c + 2*grid, ...  Tile ids walk
+// bands of `band` m-blocks, m fastest inside a band, so that the ~148 tiles in flight share a
+// few A row-blocks and B column-blocks in L2.
+template <int GTYPE>
+struct Scheduler {
+    uint32_t next_id;
+    uint32_t g = 0, g_first_tile = 0;  // masked: current group and its first tile id
+    __device__ explicit Scheduler() : next_id(blockIdx.x) {}
+
+    __device__ bool next(const GemmParams& p, Tile& t) {
+        const uint32_t id = next_id;
+        next_id += gridDim.x;
+        t.skip = false;
+        if (GTYPE != kMasked) {
+            if (id >= p.num_m_blocks * p.num_n_blocks) return false;
+            const uint32_t per_band = p.band * p.num_n_blocks;
+            const uint32_t b = id / per_band, rem = id - b * per_band;
+            const uint32_t mb0 = b * p.band;
+            const uint32_t rows = min(p.band, p.num_m_blocks - mb0);
+            const uint32_t nb = rem / rows, mb = mb0 + (rem - nb * rows);
+            t.a_row = mb * kBlockM;
+            t.row_end = p.m;
+            t.n0 = nb * p.block_n;
+            t.b_row = t.n0;
+            if (GTYPE == kContiguous) {
+                const int32_t e = __ldg(p.layout + mb);
+                t.skip = e < 0 || (uint32_t)e >= p.num_groups;
+                t.b_row = (t.skip ? 0u : (uint32_t)e * p.n) + t.n0;
+            }
+            return true;
+        } else {
+            while (g < p.num_groups) {
+                const int32_t mm = __ldg(p.layout + g);
+                const uint32_t rows = mm <= 0 ? 0u : min((uint32_t)mm, p.m);
+                const uint32_t mbs = (rows + kBlockM - 1) / kBlockM;
+                const uint32_t cnt = mbs * p.num_n_blocks;
+                if (id < g_first_tile + cnt) {
+                    const uint32_t rem = id - g_first_tile;
+                    const uint32_t nb = rem / mbs, mb = rem - nb * mbs;
+                    t.a_row = g * p.m + mb * kBlockM;
+                    t.row_end = g * p.m + rows;
+                    t.n0 = nb * p.block_n;
+                    t.b_row = g * p.n + t.n0;
+                    return true;
+                }
+                g_first_tile += cnt;
+                ++g;
+            }
+            return false;
+        }
+    }
+};
+
+struct __align__(8) Barriers {
+    uint64_t full[kMaxStages];
+    uint64_t sf_ready[kMaxStages];
+    uint64_t empty[kMaxStages];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort;
+};
+static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
+
+template <int KIND, int GTYPE>
+__global__ void __launch_bounds__(256, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+            const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
+            const GemmParams p) {
+    constexpr bool kHasSf = KIND != kBf16;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // Dynamic shared memory: [barriers (512 B, padded to 1024)] [stage 0] [stage 1] ...
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    Barriers* bars = reinterpret_cast<Barriers*>(smem_raw + (smem_base - smem_u32(smem_raw)));
+    const uint32_t stages_base = smem_base + 1024u;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const WaitCtx wc{p.status, &bars->abort};
+
+    if (threadIdx.x == 0) {
+        bars->abort = 0;
+        for (uint32_t s = 0; s < p.num_stages; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->sf_ready[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bars->tmem_full[s]), 1);
+            mbar_init(smem_u32(&bars->tmem_empty[s]), 4);
+        }
+        fence_barrier_init();
+        tma_prefetch_desc(&tm_a);
+        tma_prefetch_desc(&tm_b);
+        if (kHasSf) {
+            tma_prefetch_desc(&tm_sfa);
+            tma_prefetch_desc(&tm_sfb);
+        }
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+    auto stage_addr = [&](uint32_t s) { return stages_base + s * p.stage_bytes; };
+
+    if (warp == 0 && lane == 0) {
+        // ===================================================== TMA producer
+        Scheduler<GTYPE> sched;
+        Tile t;
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        while (ok && sched.next(p, t)) {
+            if (t.skip) continue;
+            for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+                if (!(ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
+                const uint32_t bar = smem_u32(&bars->full[stage]);
+                const uint32_t sa = stage_addr(stage);
+                const bool ld_sfa = kHasSf && (kb % p.sfa_period == 0);
+                const bool ld_sfb = kHasSf && (kb % p.sfb_period == 0);
+                mbar_arrive_expect_tx(bar, p.tx_ab + (ld_sfa ? p.tx_sfa : 0u) + (ld_sfb ? p.tx_sfb : 0u));
+                if (ld_sfa) tma_load_2d(&tm_sfa, bar, sa + p.off_sfa, (int32_t)t.a_row, (int32_t)((kb / p.sfa_period) * p.sf_sub));
+                if (ld_sfb) tma_load_2d(&tm_sfb, bar, sa + p.off_sfb, (int32_t)t.b_row, (int32_t)((kb / p.sfb_period) * p.sf_sub));
+                // Inner coordinate in elements: 128 bytes per k-block (128 FP8, 256 FP4 = 128 B, 64 BF16).
+                const int32_t kx = (int32_t)(kb * (KIND == kBf16 ? 64u : 128u));
+                tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
+                tma_load_2d(&tm_b, bar, sa + p.off_b, kx, (int32_t)t.b_row);
+                if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ===================================================== MMA issuer
+        Scheduler<GTYPE> sched;
+        Tile t;
+        uint32_t stage = 0, phase = 0, tile_count = 0;
+        const uint32_t idesc = KIND == kBf16 ? make_idesc_bf16(kBlockM, p.block_n)
+                                             : make_idesc_bs(KIND == kFp4 ? 1u : 0u, kBlockM, p.block_n);
+        bool ok = true;
+        while (ok && sched.next(p, t)) {
+            if (t.skip) continue;
+            const uint32_t as = tile_count & 1u, aphase = (tile_count >> 1) & 1u;
+            ++tile_count;
+            if (!(ok = mbar_wait(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem + as * kAccStageCols;
+            for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+                if (!(ok = mbar_wait(smem_u32(&bars->full[stage]), phase, wc, kWaitFull))) break;
+                if (kHasSf) {
+                    if (!(ok = mbar_wait(smem_u32(&bars->sf_ready[stage]), phase, wc, kWaitSfReady))) break;
+                }
+                tc_fence_after();
+                const uint32_t sa = stage_addr(stage);
+                if (kHasSf) {
+                    if (kb % p.sfa_period == 0) {
+                        for (uint32_t j = 0; j < p.sf_sub; ++j)
+                            tc_cp_32x128b_warpx4(tmem + kSfaCol + j * 4u, make_sf_desc(sa + p.off_sfa + j * 512u));
+                    }
+                    if (kb % p.sfb_period == 0) {
+                        for (uint32_t j = 0; j < p.sf_sub; ++j)
+                            for (uint32_t c = 0; c < p.sfb_chunks; ++c)
+                                tc_cp_32x128b_warpx4(tmem + kSfbCol + (j * p.sfb_chunks + c) * 4u,
+                                                     make_sf_desc(sa + p.off_sfb + (j * p.sfb_chunks + c) * 512u));
+                    }
+                }
+                const uint64_t a_desc = make_kmajor_sw128_desc(sa);
+                const uint64_t b_desc = make_kmajor_sw128_desc(sa + p.off_b);
+#pragma unroll
+                for (uint32_t k = 0; k < 4; ++k) {
+                    // 32 bytes of K per MMA (32 FP8, 64 FP4, 16 BF16): +2 in the >>4 address field.
+                    const uint64_t ad = a_desc + 2u * k, bd = b_desc + 2u * k;
+                    const uint32_t acc = (kb | k) != 0u ? 1u : 0u;
+                    if (KIND == kBf16) {
+                        tc_mma_bf16(d_tmem, ad, bd, idesc, acc);
+                    } else if (KIND == kFp8) {
+                        // one SF byte per row per MMA: byte k of the word (gran 32), or the
+                        // byte of this k-block within its 512-wide SF row (gran 128)
+                        const uint32_t ida = p.sfa_period == 1 ? k : (kb & 3u);
+                        const uint32_t idb = p.sfb_period == 1 ? k : (kb & 3u);
+                        tc_mma_mxf8(d_tmem, ad, bd, idesc_with_sf_ids(idesc, ida, idb), acc, tmem + kSfaCol, tmem + kSfbCol);
+                    } else {
+                        // two SF bytes per row per MMA (64 elements): half-word (k & 1) of SF row (k >> 1)
+                        const uint32_t sub = k >> 1, id = (k & 1u) * 2u;
+                        tc_mma_mxf4(d_tmem, ad, bd, idesc_with_sf_ids(idesc, id, id), acc,
+                                    tmem + kSfaCol + sub * 4u, tmem + kSfbCol + sub * p.sfb_chunks * 4u);
+                    }
+                }
+                tc_commit(smem_u32(&bars->empty[stage]));
+                if (kb + 1 == p.num_k_blocks) tc_commit(smem_u32(&bars->tmem_full[as]));
+                if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 2 && kHasSf) {
+        // ===================================================== SF transposer
+        Scheduler<GTYPE> sched;
+        Tile t;
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        while (ok && sched.next(p, t)) {
+            if (t.skip) continue;
+            for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->full[stage]), phase, wc, kWaitFull));
+                if (!ok) break;
+                const bool has_a = kb % p.sfa_period == 0, has_b = kb % p.sfb_period == 0;
+                uint32_t* sfa = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfa - smem_u32(smem_raw)));
+                uint32_t* sfb = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfb - smem_u32(smem_raw)));
+                const uint32_t na = has_a ? p.sf_sub : 0u, nb = has_b ? p.sf_sub * p.sfb_chunks : 0u;
+                for (uint32_t c = 0; c < na + nb; ++c) {
+                    uint32_t* q = c < na ? sfa + c * 128u : sfb + (c - na) * 128u;
+                    // word of row 32*i + lane  ->  position lane*4 + i
+                    const uint32_t v0 = q[lane], v1 = q[32 + lane], v2 = q[64 + lane], v3 = q[96 + lane];
+                    __syncwarp();
+                    *reinterpret_cast<uint4*>(q + lane * 4u) = make_uint4(v0, v1, v2, v3);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
+                if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp >= 4) {
+        // ===================================================== epilogue
+        Scheduler<GTYPE> sched;
+        Tile t;
+        const uint32_t q = warp - 4u;  // TMEM lane quarter == warp index % 4
+        uint32_t tile_count = 0;
+        bool ok = true;
+        const bool vec_ok = (p.ldd * (p.out_f32 ? 4u : 2u)) % 16u == 0 && (reinterpret_cast<uintptr_t>(p.d) & 15u) == 0;
+        while (ok && sched.next(p, t)) {
+            if (t.skip) continue;
+            const uint32_t as = tile_count & 1u, aphase = (tile_count >> 1) & 1u;
+            ++tile_count;
+            ok = mbar_wait(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t row = t.a_row + q * 32u + lane;
+            const bool row_ok = row < t.row_end;
+            const uint32_t taddr = tmem + ((q * 32u) << 16) + as * kAccStageCols;
+            const uint32_t chunks = p.block_n / 32u;
+            for (uint32_t c = 0; c < chunks; ++c) {
+                uint32_t r[32];
+                __syncwarp();
+                tmem_ld_x32(taddr + c * 32u, r);
+                tmem_ld_wait();
+                if (c + 1 == chunks) {
+                    // accumulator drained into registers: hand the TMEM stage back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+                }
+                const uint32_t col0 = t.n0 + c * 32u;
+                if (!row_ok || col0 >= p.n) continue;
+                if (p.out_f32) {
+                    float* dst = reinterpret_cast<float*>(p.d) + (size_t)row * p.ldd + col0;
+                    if (vec_ok && col0 + 32u <= p.n) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) {
+                            float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                   __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                            if (p.accumulate) {
+                                const float4 o = *reinterpret_cast<const float4*>(dst + 4 * i);
+                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                            }
+                            *reinterpret_cast<float4*>(dst + 4 * i) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i)
+                            if (col0 + i < p.n) dst[i] = __uint_as_float(r[i]) + (p.accumulate ? dst[i] : 0.f);
+                    }
+                } else {
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + (size_t)row * p.ldd + col0;
+                    if (vec_ok && col0 + 32u <= p.n) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) {
+                            uint32_t w[4];
+#pragma unroll
+                            for (uint32_t j = 0; j < 4; ++j)
+                                w[j] = pack_bf16x2(__uint_as_float(r[8 * i + 2 * j]), __uint_as_float(r[8 * i + 2 * j + 1]));
+                            if (p.accumulate) {
+                                // D += bf16(acc), the add itself rounded to bf16 (the reference
+                                // accumulates with a bf16 reduce-add, gemm_sm100.cu:309-315)
+                                const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * i);
+                                const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                                for (uint32_t j = 0; j < 4; ++j) {
+                                    const float lo = __uint_as_float(ow[j] << 16) + __uint_as_float(w[j] << 16);
+                                    const float hi = __uint_as_float(ow[j] & 0xffff0000u) + __uint_as_float(w[j] & 0xffff0000u);
+                                    w[j] = pack_bf16x2(lo, hi);
+                                }
+                            }
+                            *reinterpret_cast<uint4*>(dst + 8 * i) = make_uint4(w[0], w[1], w[2], w[3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) {
+                            if (col0 + i < p.n) {
+                                __nv_bfloat16 v = __float2bfloat16_rn(__uint_as_float(r[i]));
+                                if (p.accumulate) v = __float2bfloat16_rn(__bfloat162float(dst[i]) + __bfloat162float(v));
+                                dst[i] = v;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// ============================================================================ host side
+struct Plan {
+    GemmParams p;
+    uint32_t smem_bytes;
+    uint32_t grid;
+    uint32_t num_tiles;
+};
+
+static uint32_t env_u32(const char* name, uint32_t dflt) {
+    const char* v = getenv(name);
+    return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
+}
+
+// Tile choice.  BLOCK_M is fixed at 128 (one UMMA M); BLOCK_N in {32..224 step 32} (256 for
+// BF16, which needs no SF columns) is chosen to minimise waves x per-tile cost, where a tile's
+// cost is the larger of its MMA time (~BLOCK_N) and its operand traffic (~128 + BLOCK_N).
+// DG_BLOCK_N / DG_NUM_STAGES override (the reference's DG_* overrides: heuristics.rs:41-58).
+static uint32_t pick_block_n(int kind, uint32_t m_blocks_total, uint32_t n, uint32_t sms) {
+    const uint32_t max_bn = kind == kBf16 ? 256u : 224u;
+    const uint32_t forced = env_u32("DG_BLOCK_N", 0);
+    if (forced >= 32 && forced <= max_bn && forced % 32 == 0) return forced;
+    uint32_t best = 32;
+    double best_cost = 1e30;
+    for (uint32_t bn = 32; bn <= max_bn; bn += 32) {
+        const uint64_t tiles = (uint64_t)m_blocks_total * ceil_div(n, bn);
+        const uint64_t waves = (tiles + sms - 1) / sms;
+        const double per_tile = (double)bn + 0.25 * (128.0 + bn) + 24.0;
+        const double cost = (double)waves * per_tile;
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
+static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k, uint32_t num_groups,
+                         uint32_t expected_m, uint32_t gran_a, uint32_t gran_b, const DeviceInfo* dev, Plan* plan) {
+    GemmParams& p = plan->p;
+    p = GemmParams{};
+    const uint32_t sms = (uint32_t)dev->sm_count;
+    const uint32_t block_k = kind == kFp4 ? 256u : (kind == kFp8 ? 128u : 64u);
+    p.m = m; p.n = n; p.num_groups = num_groups;
+    p.num_k_blocks = k / block_k;
+    uint32_t m_blocks_total;
+    if (gtype == kMasked) m_blocks_total = num_groups * ceil_div(expected_m ? expected_m : m, kBlockM);
+    else m_blocks_total = ceil_div(m, kBlockM);
+    p.block_n = pick_block_n(kind, m_blocks_total, n, sms);
+    p.num_m_blocks = gtype == kMasked ? ceil_div(m, kBlockM) : ceil_div(m, kBlockM);
+    p.num_n_blocks = ceil_div(n, p.block_n);
+    p.band = env_u32("DG_BAND", 8);
+    if (p.band == 0) p.band = 8;
+    const bool has_sf = kind != kBf16;
+    p.sf_sub = kind == kFp4 ? 2u : 1u;
+    p.sfb_chunks = ceil_div(p.block_n, 128u);
+    p.sfa_period = gran_a == 128 ? 4u : 1u;
+    p.sfb_period = gran_b == 128 ? 4u : 1u;
+    const uint32_t a_bytes = kBlockM * 128u, b_bytes = p.block_n * 128u;
+    const uint32_t sfa_bytes = has_sf ? p.sf_sub * 512u : 0u;
+    const uint32_t sfb_bytes = has_sf ? p.sf_sub * p.sfb_chunks * 512u : 0u;
+    p.off_b = a_bytes;
+    p.off_sfa = a_bytes + b_bytes;
+    p.off_sfb = p.off_sfa + sfa_bytes;
+    p.stage_bytes = align_up(p.off_sfb + sfb_bytes, 1024u);
+    p.tx_ab = a_bytes + b_bytes;
+    p.tx_sfa = sfa_bytes;
+    p.tx_sfb = sfb_bytes;
+    const uint32_t budget = (uint32_t)dev->smem_optin;
+    const uint32_t fixed = 1024u /*alignment slack*/ + 1024u /*barriers*/;
+    uint32_t stages = (budget - fixed) / p.stage_bytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    const uint32_t forced = env_u32("DG_NUM_STAGES", 0);
+    if (forced >= 2 && forced <= stages) stages = forced;
+    if (stages < 2) return fail(DG_ERR_RUNTIME, "shared memory budget %u B too small for a %u-wide tile", budget, p.block_n);
+    p.num_stages = stages;
+    plan->smem_bytes = fixed + stages * p.stage_bytes;
+    plan->num_tiles = gtype == kMasked ? m_blocks_total * p.num_n_blocks : p.num_m_blocks * p.num_n_blocks;
+    uint32_t grid = sms;
+    if (gtype != kMasked && plan->num_tiles < grid) grid = plan->num_tiles;
+    if (gtype == kMasked) {
+        const uint32_t worst = num_groups * ceil_div(m, kBlockM) * p.num_n_blocks;
+        if (worst < grid) grid = worst;
+    }
+    plan->grid = grid ? grid : 1;
+    p.status = dev->status;
+    if (env_u32("DG_PRINT_CONFIGS", 0))
+        fprintf(stderr, "[deepgemm_b200] kind=%d gtype=%d m=%u n=%u k=%u groups=%u -> block 128x%ux%u stages=%u smem=%u grid=%u tiles=%u\n",
+                kind, gtype, m, n, k, num_groups, p.block_n, block_k, stages, plan->smem_bytes, plan->grid, plan->num_tiles);
+    return DG_OK;
+}
+
+template <int KIND, int GTYPE>
+static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
+                      const CUtensorMap& tsb, cudaStream_t s) {
+    auto* fn = gemm_kernel<KIND, GTYPE>;
+    static thread_local uint32_t configured[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (configured[dev & 63] < plan.smem_bytes) {
+        DG_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
+        configured[dev & 63] = plan.smem_bytes;
+    }
+    fn<<<plan.grid, 256, plan.smem_bytes, s>>>(ta, tb, tsa, tsb, plan.p);
+    DG_CUDA_CHECK(cudaGetLastError());
+    return DG_OK;
+}
+
+static const char* dtype_name(int32_t d) {
+    switch (d) { case DG_FP8: return "FP8"; case DG_FP4: return "FP4"; case DG_BF16: return "BF16"; case DG_F32: return "F32"; }
+    return "?";
+}
+
+// Checks of deepgemm/src/api.rs:995-1022 (K multiples) and :175-185 (SF presence, majors).
+static int32_t validate_operand(const dg_operand_t* op, const char* name) {
+    if (!op || !op->data) return fail(DG_ERR_INVALID_ARG, "%s: null operand", name);
+    const uint32_t k = op->k;
+    switch (op->dtype) {
+        case DG_FP4: if (k % 256 != 0) return fail(DG_ERR_INVALID_ARG, "%s: FP4 K (%u) must be a multiple of 256", name, k); break;
+        case DG_FP8: if (k % 128 != 0) return fail(DG_ERR_INVALID_ARG, "%s: FP8 K (%u) must be a multiple of 128", name, k); break;
+        case DG_BF16: if (k % 64 != 0) return fail(DG_ERR_INVALID_ARG, "%s: BF16 K (%u) must be a multiple of 64", name, k); break;
+        default: return fail(DG_ERR_INVALID_ARG, "%s: operand dtype must be FP8, FP4 or BF16", name);
+    }
+    if (k == 0 || op->rows == 0) return fail(DG_ERR_INVALID_ARG, "%s: empty operand (%u x %u)", name, op->rows, k);
+    if (op->outer_stride < k) return fail(DG_ERR_INVALID_ARG, "%s: outer_stride (%u) smaller than K (%u)", name, op->outer_stride, k);
+    return DG_OK;
+}
+
+static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int gtype, const int32_t* layout,
+                        uint32_t layout_len, uint32_t num_groups, uint32_t expected_m, int32_t accumulate, void* stream) {
+    int32_t st;
+    if ((st = validate_operand(a, "A")) != DG_OK) return st;
+    if ((st = validate_operand(b, "B")) != DG_OK) return st;
+    if (!out || !out->data) return fail(DG_ERR_INVALID_ARG, "null output");
+    if (a->k != b->k) return fail(DG_ERR_INVALID_ARG, "A/B K mismatch");
+    if (out->cols != b->rows || out->rows != a->rows) return fail(DG_ERR_INVALID_ARG, "output shape mismatch");
+    if (out->dtype != DG_BF16 && out->dtype != DG_F32) return fail(DG_ERR_INVALID_ARG, "output must be BF16 or FP32");
+    if (out->stride < out->cols) return fail(DG_ERR_INVALID_ARG, "output stride (%u) smaller than its columns (%u)", out->stride, out->cols);
+    if (a->dtype != b->dtype)
+        return fail(DG_ERR_UNSUPPORTED, "mixed operand dtypes (%s x %s) are not built", dtype_name(a->dtype), dtype_name(b->dtype));
+    if (a->major != DG_MAJOR_K || b->major != DG_MAJOR_K) {
+        if (a->dtype == DG_FP4) return fail(DG_ERR_INVALID_ARG, "MXF4 MMA requires K-major operands");
+        return fail(DG_ERR_UNSUPPORTED, "MN-major operand views are not built; pass K-major A and B");
+    }
+    const int kind = a->dtype == DG_FP8 ? kFp8 : (a->dtype == DG_FP4 ? kFp4 : kBf16);
+    const bool has_sf = kind != kBf16;
+    if (has_sf && (!a->sf.data || !b->sf.data)) return fail(DG_ERR_INVALID_ARG, "FP8/FP4 operands require scale factors");
+    const uint32_t groups_a = gtype == kMasked ? num_groups : 1u;
+    const uint32_t groups_b = gtype == kNormal ? 1u : num_groups;
+    if (gtype != kNormal) {
+        if (num_groups == 0) return fail(DG_ERR_INVALID_ARG, "num_groups must be positive");
+        if (!layout) return fail(DG_ERR_INVALID_ARG, "grouped GEMM requires a layout buffer");
+        if (accumulate) return fail(DG_ERR_INVALID_ARG, "grouped GEMM does not accumulate");
+    }
+    if (gtype == kContiguous) {
+        if (a->rows % 128 != 0)
+            return fail(DG_ERR_INVALID_ARG, "contiguous layout requires M (%u) to be a multiple of 128", a->rows);
+        if (layout_len != a->rows / 128)
+            return fail(DG_ERR_INVALID_ARG, "m_indices must hold M/128 = %u entries (one per 128-row block), got %u", a->rows / 128, layout_len);
+    }
+    const uint32_t m = a->rows, n = b->rows, k = a->k;
+    if ((uint64_t)groups_a * m >= (1ull << 31) || (uint64_t)groups_b * n >= (1ull << 31))
+        return fail(DG_ERR_INVALID_ARG, "stacked row count exceeds 2^31");
+    uint32_t gran_a = 32, gran_b = 32;
+    if (has_sf) {
+        gran_a = a->sf.gran; gran_b = b->sf.gran;
+        if ((gran_a != 32 && gran_a != 128) || (gran_b != 32 && gran_b != 128))
+            return fail(DG_ERR_INVALID_ARG, "SF granularity must be 32 or 128");
+        if (kind == kFp4 && (gran_a != 32 || gran_b != 32)) return fail(DG_ERR_INVALID_ARG, "FP4 requires SF granularity 32");
+        if (a->sf.rows < ceil_div(k, gran_a * 4) || a->sf.cols < align_up(groups_a * m, 4))
+            return fail(DG_ERR_INVALID_ARG, "A scale-factor tensor is %u x %u, need at least %u x %u", a->sf.rows, a->sf.cols,
+                        ceil_div(k, gran_a * 4), align_up(groups_a * m, 4));
+        if (b->sf.rows < ceil_div(k, gran_b * 4) || b->sf.cols < align_up(groups_b * n, 4))
+            return fail(DG_ERR_INVALID_ARG, "B scale-factor tensor is %u x %u, need at least %u x %u", b->sf.rows, b->sf.cols,
+                        ceil_div(k, gran_b * 4), align_up(groups_b * n, 4));
+        // TMA starts SF boxes at column group*rows + tile offset: keep that 16-byte aligned.
+        if (gtype != kNormal && n % 4 != 0) return fail(DG_ERR_INVALID_ARG, "grouped GEMM requires N (%u) %% 4 == 0", n);
+        if (gtype == kMasked && m % 4 != 0) return fail(DG_ERR_INVALID_ARG, "masked GEMM requires per-group M (%u) %% 4 == 0", m);
+    }
+
+    // Arguments are checked first so that a bad call reports InvalidArg on any machine; the
+    // device gate follows (deepgemm/src/api.rs:168-173).
+    const DeviceInfo* dev;
+    if ((st = current_device(&dev)) != DG_OK) return st;
+    Plan plan;
+    if ((st = make_plan(kind, gtype, m, n, k, num_groups, expected_m, gran_a, gran_b, dev, &plan)) != DG_OK) return st;
+    GemmParams& p = plan.p;
+    p.out_f32 = out->dtype == DG_F32;
+    p.accumulate = accumulate ? 1u : 0u;
+    p.ldd = out->stride;
+    p.d = out->data;
+    p.layout = layout;
+
+    CUtensorMap ta, tb, tsa, tsb;
+    const uint32_t ebytes = kind == kBf16 ? 2u : 1u;
+    // FP4 rows are k/2 bytes and are moved as bytes (two codes per byte stay packed in shared memory).
+    const uint64_t inner = kind == kFp4 ? k / 2 : k;
+    const uint64_t pitch_a = kind == kFp4 ? a->outer_stride / 2 : (uint64_t)a->outer_stride * ebytes;
+    const uint64_t pitch_b = kind == kFp4 ? b->outer_stride / 2 : (uint64_t)b->outer_stride * ebytes;
+    const CUtensorMapDataType dt = kind == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const uint32_t box_inner = kind == kBf16 ? 64u : 128u;
+    if ((st = make_tmap_2d(&ta, dt, ebytes, a->data, inner, (uint64_t)groups_a * m, pitch_a, box_inner, kBlockM,
+                           CU_TENSOR_MAP_SWIZZLE_128B, "A")) != DG_OK) return st;
+    if ((st = make_tmap_2d(&tb, dt, ebytes, b->data, inner, (uint64_t)groups_b * n, pitch_b, box_inner, p.block_n,
+                           CU_TENSOR_MAP_SWIZZLE_128B, "B")) != DG_OK) return st;
+    if (has_sf) {
+        if ((st = make_tmap_2d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a->sf.data, a->sf.cols, a->sf.rows,
+                               (uint64_t)a->sf.cols * 4, 128u, p.sf_sub, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA")) != DG_OK) return st;
+        if ((st = make_tmap_2d(&tsb, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, b->sf.data, b->sf.cols, b->sf.rows,
+                               (uint64_t)b->sf.cols * 4, p.sfb_chunks * 128u, p.sf_sub, CU_TENSOR_MAP_SWIZZLE_NONE, "SFB")) != DG_OK) return st;
+    } else {
+        tsa = ta; tsb = tb;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define DG_DISPATCH(K, G) if (kind == K && gtype == G) return launch<K, G>(plan, ta, tb, tsa, tsb, s)
+    DG_DISPATCH(kFp8, kNormal); DG_DISPATCH(kFp8, kContiguous); DG_DISPATCH(kFp8, kMasked);
+    DG_DISPATCH(kFp4, kNormal); DG_DISPATCH(kFp4, kContiguous); DG_DISPATCH(kFp4, kMasked);
+    DG_DISPATCH(kBf16, kNormal); DG_DISPATCH(kBf16, kContiguous); DG_DISPATCH(kBf16, kMasked);
+#undef DG_DISPATCH
+    return fail(DG_ERR_RUNTIME, "no kernel for kind %d / type %d", kind, gtype);
+}
+
+}  // namespace dg
+
+extern "C" {
+
+int32_t dg_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream) {
+    return dg::run_gemm(a, b, out, dg::kNormal, nullptr, 0, 1, a ? a->rows : 0, accumulate, stream);
+}
+static int32_t typed(const dg_operand_t* a, const dg_operand_t* b, int32_t want, const char* fn) {
+    if (!a || !b) return dg::fail(DG_ERR_INVALID_ARG, "%s: null operand", fn);
+    if (a->dtype != want || b->dtype != want)
+        return dg::fail(DG_ERR_INVALID_ARG, "%s: operands must be %s", fn, dg::dtype_name(want));
+    return DG_OK;
+}
+int32_t dg_fp8_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream) {
+    int32_t st = typed(a, b, DG_FP8, "fp8_gemm_nt");
+    return st != DG_OK ? st : dg_gemm_nt(a, b, out, accumulate, stream);
+}
+int32_t dg_fp4_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream) {
+    int32_t st = typed(a, b, DG_FP4, "fp4_gemm_nt");
+    return st != DG_OK ? st : dg_gemm_nt(a, b, out, accumulate, stream);
+}
+int32_t dg_bf16_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream) {
+    int32_t st = typed(a, b, DG_BF16, "bf16_gemm_nt");
+    return st != DG_OK ? st : dg_gemm_nt(a, b, out, accumulate, stream);
+}
+
+int32_t dg_m_grouped_gemm_nt_contiguous(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                        const int32_t* m_indices, uint32_t m_indices_len, uint32_t num_groups, void* stream) {
+    if (a && a->major != DG_MAJOR_K) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous requires K-major A");
+    return dg::run_gemm(a, b, out, dg::kContiguous, m_indices, m_indices_len, num_groups, a ? a->rows : 0, 0, stream);
+}
+int32_t dg_m_grouped_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, const int32_t* masked_m,
+                                    uint32_t num_groups, uint32_t expected_m, void* stream) {
+    if (a && b && (a->major != DG_MAJOR_K || b->major != DG_MAJOR_K))
+        return dg::fail(DG_ERR_INVALID_ARG, "m-grouped masked requires K-major A/B");
+    return dg::run_gemm(a, b, out, dg::kMasked, masked_m, num_groups, num_groups, expected_m, 0, stream);
+}
+
+#define DG_TYPED_GROUPED(NAME, DT)                                                                                         \
+    int32_t dg_m_grouped_##NAME##_gemm_nt_contiguous(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,        \
+                                                     const int32_t* mi, uint32_t len, uint32_t g, void* stream) {          \
+        int32_t st = typed(a, b, DT, "m_grouped_" #NAME "_gemm_nt_contiguous");                                            \
+        return st != DG_OK ? st : dg_m_grouped_gemm_nt_contiguous(a, b, out, mi, len, g, stream);                          \
+    }                                                                                                                      \
+    int32_t dg_m_grouped_##NAME##_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,            \
+                                                 const int32_t* mm, uint32_t g, uint32_t em, void* stream) {               \
+        int32_t st = typed(a, b, DT, "m_grouped_" #NAME "_gemm_nt_masked");                                                \
+        return st != DG_OK ? st : dg_m_grouped_gemm_nt_masked(a, b, out, mm, g, em, stream);                               \
+    }
+DG_TYPED_GROUPED(fp8, DG_FP8)
+DG_TYPED_GROUPED(fp4, DG_FP4)
+DG_TYPED_GROUPED(bf16, DG_BF16)
+#undef DG_TYPED_GROUPED
+
+int32_t dg_get_gemm_config(int32_t dtype, int32_t kind, uint32_t m, uint32_t n, uint32_t k, uint32_t num_groups,
+                           dg_gemm_config_t* cfg) {
+    const dg::DeviceInfo* dev;
+    int32_t st = dg::current_device(&dev);
+    if (st != DG_OK) return st;
+    if (!cfg || kind < 0 || kind > 2 || dtype < 0 || dtype > 2) return dg::fail(DG_ERR_INVALID_ARG, "get_gemm_config: bad argument");
+    dg::Plan plan;
+    st = dg::make_plan(dtype == DG_FP8 ? dg::kFp8 : dtype == DG_FP4 ? dg::kFp4 : dg::kBf16, kind, m, n, k,
+                       num_groups ? num_groups : 1, m, 32, 32, dev, &plan);
+    if (st != DG_OK) return st;
+    cfg->block_m = dg::kBlockM;
+    cfg->block_n = plan.p.block_n;
+    cfg->block_k = dtype == DG_FP4 ? 256 : dtype == DG_FP8 ? 128 : 64;
+    cfg->num_stages = plan.p.num_stages;
+    cfg->smem_bytes = plan.smem_bytes;
+    cfg->num_tiles = plan.num_tiles;
+    cfg->grid = plan.grid;
+    cfg->cluster = 1;
+    return DG_OK;
+}
+
+}  // extern "C"

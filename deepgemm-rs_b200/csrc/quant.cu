@@ -1,0 +1,328 @@
+// quant_mx, dequant_mx and transform_sf for sm_100a: HBM-streaming kernels (128-bit loads,
+// warp-shuffle amax, whole-word scale-factor stores, no atomics, no pre-cleared outputs).
+//
+// Contract (bit-exact): the reference's CPU golden model, deepgemm/src/golden.rs:211-396;
+// the kernels they replace are quant_mx_impl / dequant_mx_impl / transform_sf_impl in
+// deepgemm/kernels/layout_quant.cu:43-252 behind api::quant_mx / dequant_mx / transform_sf
+// (deepgemm/src/api.rs:1031-1135, 1480-1601).
+#include <cuda_fp16.h>
+
+#include "host.h"
+
+namespace dg {
+
+// ------------------------------------------------------------------------- device helpers
+// amax -> biased UE8M0 exponent (golden.rs:211-241): round amax/qmax up to a power of two.
+template <bool FP4>
+__device__ __forceinline__ uint32_t ue8m0_exp(float amax) {
+    constexpr uint32_t kQMaxMant = FP4 ? (0x40u << 16) : (0x60u << 16);
+    constexpr uint32_t kQExp = FP4 ? 2u : 8u;
+    constexpr uint32_t kMinExp = FP4 ? 1u : 105u;
+    uint32_t rounded = (__float_as_uint(amax) + 0x7fffffu - kQMaxMant) >> 23;
+    return max(rounded, kMinExp + kQExp) - kQExp;
+}
+
+// Four scaled floats -> four E4M3 bytes (element 0 in the low byte), RNE, saturating.
+// NaN encodes as a signed zero code, like the golden model's grid search (golden.rs:142-189).
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+    uint16_t lo, hi;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
+    uint32_t r = (uint32_t)lo | ((uint32_t)hi << 16);
+    if (a != a) r = (r & 0xffffff00u) | ((__float_as_uint(a) >> 31) << 7);
+    if (b != b) r = (r & 0xffff00ffu) | ((__float_as_uint(b) >> 31) << 15);
+    if (c != c) r = (r & 0xff00ffffu) | ((__float_as_uint(c) >> 31) << 23);
+    if (d != d) r = (r & 0x00ffffffu) | ((__float_as_uint(d) >> 31) << 31);
+    return r;
+}
+// Two scaled floats -> one byte of two E2M1 nibbles (first element in the low nibble).
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float a, float b) {
+    uint16_t r;
+    asm("{ .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %2, %1;\n mov.b16 %0, {t, 0}; }" : "=h"(r) : "f"(a), "f"(b));
+    uint32_t v = r;
+    if (a != a) v = (v & 0xf0u) | ((__float_as_uint(a) >> 31) << 3);
+    if (b != b) v = (v & 0x0fu) | ((__float_as_uint(b) >> 31) << 7);
+    return v;
+}
+
+__device__ __forceinline__ float amax4(const float4& v) {
+    return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+
+// ------------------------------------------------------------------------- quant_mx
+// One warp owns 32 consecutive rows x one "span" of 4 scale groups (4*G floats), so that it
+// produces whole SF words: lane r keeps the word of row r and the warp stores 128 contiguous
+// bytes of the SF row.  G = 32: one float4 per lane covers the span (8 lanes per group);
+// G = 128: four float4 per lane, load j is group j.
+template <uint32_t G, bool FP4>
+__global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__ x, uint32_t m, uint32_t k,
+                                                      uint8_t* __restrict__ data, uint32_t* __restrict__ sf,
+                                                      uint32_t sf_cols, uint32_t num_spans, uint32_t num_row_blocks) {
+    constexpr uint32_t kLoads = G / 32;                   // float4 loads per lane per row
+    constexpr uint32_t kRowsPerIter = G == 32 ? 8 : 2;    // rows in flight per warp
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (warp_global >= num_spans * num_row_blocks) return;
+    // Consecutive warps walk the spans of one row block, so a block of 8 warps reads
+    // 8 * 4G contiguous floats of each row.
+    const uint32_t span = warp_global % num_spans;
+    const uint32_t row0 = (warp_global / num_spans) * 32u;
+    const uint32_t num_groups = k / G;
+    const uint32_t groups_here = min(4u, num_groups - span * 4u);
+    const uint32_t col0 = span * 4u * G;
+    uint32_t my_word = 0;
+
+    for (uint32_t rb = 0; rb < 32u; rb += kRowsPerIter) {
+        float4 v[kRowsPerIter][kLoads];
+#pragma unroll
+        for (uint32_t i = 0; i < kRowsPerIter; ++i) {
+            const uint32_t row = row0 + rb + i;
+#pragma unroll
+            for (uint32_t j = 0; j < kLoads; ++j) {
+                const uint32_t grp = G == 32 ? (lane >> 3) : j;
+                const bool ok = row < m && grp < groups_here;
+                v[i][j] = ok ? __ldcs(reinterpret_cast<const float4*>(x + (size_t)row * k + col0 + j * 128u + lane * 4u))
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < kRowsPerIter; ++i) {
+            const uint32_t row = row0 + rb + i;
+            uint32_t word = 0;
+#pragma unroll
+            for (uint32_t j = 0; j < kLoads; ++j) {
+                float a = amax4(v[i][j]);
+                if (G == 32) {
+#pragma unroll
+                    for (uint32_t s = 1; s < 8; s <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, s));
+                } else {
+#pragma unroll
+                    for (uint32_t s = 1; s < 32; s <<= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, s));
+                }
+                a = fmaxf(a, 1e-30f);
+                const uint32_t e = ue8m0_exp<FP4>(a);
+                const float inv = __uint_as_float((254u - e) << 23);
+                const uint32_t grp = G == 32 ? (lane >> 3) : j;
+                const bool ok = row < m && grp < groups_here;
+                const float4 q = make_float4(v[i][j].x * inv, v[i][j].y * inv, v[i][j].z * inv, v[i][j].w * inv);
+                const size_t col = col0 + j * 128u + lane * 4u;
+                if (FP4) {
+                    const uint32_t b = cvt_e2m1x2(q.x, q.y) | (cvt_e2m1x2(q.z, q.w) << 8);
+                    if (ok) *reinterpret_cast<uint16_t*>(data + ((size_t)row * k + col) / 2) = (uint16_t)b;
+                } else {
+                    const uint32_t b = cvt_e4m3x4(q.x, q.y, q.z, q.w);
+                    if (ok) *reinterpret_cast<uint32_t*>(data + (size_t)row * k + col) = b;
+                }
+                if (G == 32) {
+                    // group leaders are lanes 0, 8, 16, 24
+                    const uint32_t e0 = __shfl_sync(0xffffffffu, e, 0), e1 = __shfl_sync(0xffffffffu, e, 8);
+                    const uint32_t e2 = __shfl_sync(0xffffffffu, e, 16), e3 = __shfl_sync(0xffffffffu, e, 24);
+                    word = e0 | (groups_here > 1 ? e1 << 8 : 0u) | (groups_here > 2 ? e2 << 16 : 0u) |
+                           (groups_here > 3 ? e3 << 24 : 0u);
+                } else {
+                    if (j < groups_here) word |= e << (8u * j);
+                }
+            }
+            if (lane == rb + i) my_word = row < m ? word : 0u;
+        }
+    }
+    // One SF word per (span, row); columns m .. sf_cols-1 are padding and get zeros.
+    const uint32_t row = row0 + lane;
+    if (row < sf_cols) sf[(size_t)span * sf_cols + row] = my_word;
+}
+
+// ------------------------------------------------------------------------- dequant_mx
+// One thread decodes 8 consecutive elements (8 or 4 code bytes) and stores two float4.
+template <bool FP4>
+__global__ void __launch_bounds__(256) dequant_mx_kernel(const uint8_t* __restrict__ data, const uint32_t* __restrict__ sf,
+                                                        uint32_t sf_cols, uint32_t m, uint32_t k, uint32_t gran,
+                                                        float* __restrict__ out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t per_row = k / 8u;
+    if (idx >= (size_t)m * per_row) return;
+    const uint32_t row = (uint32_t)(idx / per_row);
+    const uint32_t col = (uint32_t)(idx % per_row) * 8u;
+    const uint32_t slot = col / gran;  // 8 | gran, so all 8 elements share one scale
+    const uint32_t word = __ldg(sf + (size_t)(slot >> 2) * sf_cols + row);
+    const uint32_t e = (word >> (8u * (slot & 3u))) & 0xffu;
+    const float scale = __uint_as_float(e == 0u ? 0x00400000u : e << 23);  // 2^(e-127); e = 0 is subnormal
+    float r[8];
+    if (FP4) {
+        const uint32_t c = *reinterpret_cast<const uint32_t*>(data + ((size_t)row * k + col) / 2);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t h2;
+            const uint16_t b = (uint16_t)((c >> (8 * i)) & 0xffu);
+            asm("{ .reg .b8 t, z;\n mov.b16 {t, z}, %1;\n cvt.rn.f16x2.e2m1x2 %0, t; }" : "=r"(h2) : "h"(b));
+            const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h2));
+            r[2 * i] = f.x * scale;
+            r[2 * i + 1] = f.y * scale;
+        }
+    } else {
+        const uint2 c = *reinterpret_cast<const uint2*>(data + (size_t)row * k + col);
+        const uint32_t w[2] = {c.x, c.y};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t h2;
+            const uint16_t b = (uint16_t)((w[i >> 1] >> (16 * (i & 1))) & 0xffffu);
+            asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(b));
+            const float2 f = __half22float2(*reinterpret_cast<__half2*>(&h2));
+            r[2 * i] = f.x * scale;
+            r[2 * i + 1] = f.y * scale;
+        }
+    }
+    float4* o = reinterpret_cast<float4*>(out + (size_t)row * k + col);
+    __stcs(o, make_float4(r[0], r[1], r[2], r[3]));
+    __stcs(o + 1, make_float4(r[4], r[5], r[6], r[7]));
+}
+
+// ------------------------------------------------------------------------- transform_sf
+// f32 [mn, sf_k] -> u32 [ceil(sf_k/4), align4(mn)].  A block stages 64 rows x 64 scales in
+// shared memory with row-contiguous loads, then writes words with mn-contiguous stores.
+__global__ void __launch_bounds__(256) transform_sf_kernel(const float* __restrict__ sf, uint32_t mn, uint32_t sf_k,
+                                                          uint32_t* __restrict__ out, uint32_t out_cols) {
+    __shared__ uint32_t tile[64][65];
+    const uint32_t m0 = blockIdx.x * 64u, k0 = blockIdx.y * 64u;
+    for (uint32_t i = threadIdx.x; i < 64u * 64u; i += 256u) {
+        const uint32_t r = i >> 6, c = i & 63u;
+        const uint32_t m = m0 + r, kk = k0 + c;
+        // exponent byte of the f32 (golden.rs:115-117); rows / scales outside the tensor give 0
+        tile[r][c] = (m < mn && kk < sf_k) ? ((__float_as_uint(__ldg(sf + (size_t)m * sf_k + kk)) >> 23) & 0xffu) : 0u;
+    }
+    __syncthreads();
+    // 16 word rows x 64 columns per block
+    for (uint32_t i = threadIdx.x; i < 16u * 64u; i += 256u) {
+        const uint32_t wr = i >> 6, c = i & 63u;
+        const uint32_t m = m0 + c, word_row = (k0 >> 2) + wr;
+        if (m < out_cols && word_row * 4u < sf_k) {
+            const uint32_t w = tile[c][4 * wr] | (tile[c][4 * wr + 1] << 8) | (tile[c][4 * wr + 2] << 16) |
+                               (tile[c][4 * wr + 3] << 24);
+            out[(size_t)word_row * out_cols + m] = w;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------- host side
+static int32_t check_quant_args(const void* x, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran,
+                                const void* data_out, const void* sf_out) {
+    if (!x || !data_out || !sf_out) return fail(DG_ERR_INVALID_ARG, "quant_mx: null buffer");
+    if (m == 0 || k == 0) return fail(DG_ERR_INVALID_ARG, "quant_mx: empty shape %u x %u", m, k);
+    if (dtype != DG_FP8 && dtype != DG_FP4) return fail(DG_ERR_INVALID_ARG, "quant_mx: dtype must be FP8 or FP4");
+    if (gran != 32 && gran != 128) return fail(DG_ERR_INVALID_ARG, "quant_mx: granularity must be 32 or 128");
+    // deepgemm/src/api.rs:1489-1498
+    if (dtype == DG_FP4 && (gran != 32 || k % 32 != 0))
+        return fail(DG_ERR_INVALID_ARG, "quant_mx: FP4 requires granularity 32 and K (%u) %% 32 == 0", k);
+    if (k % gran != 0) return fail(DG_ERR_INVALID_ARG, "quant_mx: K (%u) must be a multiple of the SF granularity %u", k, gran);
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(data_out) & 3u))
+        return fail(DG_ERR_INVALID_ARG, "quant_mx: x must be 16-byte aligned and the code buffer 4-byte aligned");
+    return DG_OK;
+}
+
+static int32_t launch_quant(const float* x, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran, void* data_out,
+                            uint32_t* sf_out, cudaStream_t s) {
+    const uint32_t sf_cols = align_up(m, 4);
+    const uint32_t num_spans = ceil_div(k / gran, 4);
+    const uint32_t num_row_blocks = ceil_div(sf_cols, 32);
+    const uint64_t warps = (uint64_t)num_spans * num_row_blocks;
+    const uint32_t blocks = (uint32_t)((warps + 7) / 8);
+    uint8_t* d = static_cast<uint8_t*>(data_out);
+    if (dtype == DG_FP4)
+        quant_mx_kernel<32, true><<<blocks, 256, 0, s>>>(x, m, k, d, sf_out, sf_cols, num_spans, num_row_blocks);
+    else if (gran == 32)
+        quant_mx_kernel<32, false><<<blocks, 256, 0, s>>>(x, m, k, d, sf_out, sf_cols, num_spans, num_row_blocks);
+    else
+        quant_mx_kernel<128, false><<<blocks, 256, 0, s>>>(x, m, k, d, sf_out, sf_cols, num_spans, num_row_blocks);
+    DG_CUDA_CHECK(cudaGetLastError());
+    return DG_OK;
+}
+
+}  // namespace dg
+
+extern "C" {
+
+int32_t dg_quant_mx(const float* x, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran, void* data_out,
+                    uint32_t* sf_out, void* stream) {
+    int32_t st = dg::check_quant_args(x, m, k, dtype, gran, data_out, sf_out);
+    if (st != DG_OK) return st;
+    const dg::DeviceInfo* dev;
+    if ((st = dg::current_device(&dev)) != DG_OK) return st;
+    return dg::launch_quant(x, m, k, dtype, gran, data_out, sf_out, static_cast<cudaStream_t>(stream));
+}
+
+int32_t dg_quant_mx_host(const float* x_host, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran, void* data_out,
+                         uint32_t* sf_out, void* stream) {
+    int32_t st = dg::check_quant_args(x_host, m, k, dtype, gran, data_out, sf_out);
+    if (st != DG_OK) return st;
+    const dg::DeviceInfo* dev;
+    if ((st = dg::current_device(&dev)) != DG_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* staging = nullptr;
+    const size_t bytes = (size_t)m * k * sizeof(float);
+    DG_CUDA_CHECK(cudaMallocAsync(&staging, bytes, s));
+    cudaError_t e = cudaMemcpyAsync(staging, x_host, bytes, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) st = dg::launch_quant(staging, m, k, dtype, gran, data_out, sf_out, s);
+    cudaFreeAsync(staging, s);
+    if (e != cudaSuccess) return dg::fail(DG_ERR_DRIVER, "quant_mx: host to device copy failed: %s", cudaGetErrorString(e));
+    return st;
+}
+
+int32_t dg_dequant_mx(const void* data, const dg_sf_tensor_t* sf, uint32_t m, uint32_t k, int32_t dtype, float* out,
+                      void* stream) {
+    int32_t st;
+    if (!data || !sf || !sf->data || !out) return dg::fail(DG_ERR_INVALID_ARG, "dequant_mx: null buffer");
+    if (dtype != DG_FP8 && dtype != DG_FP4) return dg::fail(DG_ERR_INVALID_ARG, "dequant_mx: dtype must be FP8 or FP4");
+    if (sf->gran != 32 && sf->gran != 128) return dg::fail(DG_ERR_INVALID_ARG, "dequant_mx: granularity must be 32 or 128");
+    if (m == 0 || k == 0 || k % sf->gran != 0)
+        return dg::fail(DG_ERR_INVALID_ARG, "dequant_mx: K (%u) must be a positive multiple of the SF granularity %u", k, sf->gran);
+    if (sf->cols < m || sf->rows < dg::ceil_div(k, sf->gran * 4))
+        return dg::fail(DG_ERR_INVALID_ARG, "dequant_mx: SF tensor %u x %u too small for %u x %u", sf->rows, sf->cols, m, k);
+    if ((reinterpret_cast<uintptr_t>(data) & 7u) || (reinterpret_cast<uintptr_t>(out) & 15u))
+        return dg::fail(DG_ERR_INVALID_ARG, "dequant_mx: buffers must be 8/16-byte aligned");
+    const dg::DeviceInfo* dev;
+    if ((st = dg::current_device(&dev)) != DG_OK) return st;
+    const uint64_t threads = (uint64_t)m * (k / 8);
+    const uint32_t blocks = (uint32_t)((threads + 255) / 256);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == DG_FP4)
+        dg::dequant_mx_kernel<true><<<blocks, 256, 0, s>>>(static_cast<const uint8_t*>(data), sf->data, sf->cols, m, k, sf->gran, out);
+    else
+        dg::dequant_mx_kernel<false><<<blocks, 256, 0, s>>>(static_cast<const uint8_t*>(data), sf->data, sf->cols, m, k, sf->gran, out);
+    DG_CUDA_CHECK(cudaGetLastError());
+    return DG_OK;
+}
+
+static int32_t transform_sf_impl(const float* sf, uint32_t mn, uint32_t sf_k, uint32_t* out, cudaStream_t s) {
+    const uint32_t cols = dg::align_up(mn, 4);
+    dim3 grid(dg::ceil_div(cols, 64), dg::ceil_div(sf_k, 64));
+    dg::transform_sf_kernel<<<grid, 256, 0, s>>>(sf, mn, sf_k, out, cols);
+    DG_CUDA_CHECK(cudaGetLastError());
+    return DG_OK;
+}
+
+int32_t dg_transform_sf(const float* sf, uint32_t mn, uint32_t sf_k, uint32_t* out, void* stream) {
+    if (!sf || !out) return dg::fail(DG_ERR_INVALID_ARG, "transform_sf: null buffer");
+    if (mn == 0 || sf_k == 0) return dg::fail(DG_ERR_INVALID_ARG, "sf length must be mn * sf_k");
+    const dg::DeviceInfo* dev;
+    int32_t st = dg::current_device(&dev);
+    if (st != DG_OK) return st;
+    return transform_sf_impl(sf, mn, sf_k, out, static_cast<cudaStream_t>(stream));
+}
+
+int32_t dg_transform_sf_host(const float* sf_host, uint32_t mn, uint32_t sf_k, uint32_t* out, void* stream) {
+    if (!sf_host || !out) return dg::fail(DG_ERR_INVALID_ARG, "transform_sf: null buffer");
+    if (mn == 0 || sf_k == 0) return dg::fail(DG_ERR_INVALID_ARG, "sf length must be mn * sf_k");
+    const dg::DeviceInfo* dev;
+    int32_t st = dg::current_device(&dev);
+    if (st != DG_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    float* staging = nullptr;
+    const size_t bytes = (size_t)mn * sf_k * sizeof(float);
+    DG_CUDA_CHECK(cudaMallocAsync(&staging, bytes, s));
+    cudaError_t e = cudaMemcpyAsync(staging, sf_host, bytes, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) st = transform_sf_impl(staging, mn, sf_k, out, s);
+    cudaFreeAsync(staging, s);
+    if (e != cudaSuccess) return dg::fail(DG_ERR_DRIVER, "transform_sf: host to device copy failed: %s", cudaGetErrorString(e));
+    return st;
+}
+
+}  // extern "C"

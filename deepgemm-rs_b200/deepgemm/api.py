@@ -1,0 +1,191 @@
+"""Operator API with the names and argument meaning of the reference's `deepgemm::api`
+(deepgemm/src/api.rs), bound to the C ABI of libdeepgemm_b200.so.
+
+torch is used for device memory and streams only.  `dev` / `stream` of the reference
+signatures collapse into an optional `stream` (a torch.cuda.Stream or None = current stream).
+Errors surface as the DgError subclasses of .types.  There is no CPU path: without the
+library or without an sm_100 GPU every operator raises.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+from .types import Dtype, Major, Operand, Output, SfGran, SfTensor, error_for
+
+
+def _stream_ptr(stream):
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return C.c_void_p(stream.cuda_stream)
+
+
+def _check(code):
+    if code != 0:
+        raise error_for(code, _lib.load().dg_last_error().decode())
+
+
+def _sf_c(sf):
+    if sf is None:
+        return _lib.SfTensorC(0, 0, 0, None)
+    return _lib.SfTensorC(sf.rows, sf.cols, int(sf.gran), sf.buf.data_ptr())
+
+
+def _op_c(op):
+    return _lib.OperandC(int(op.dtype), int(op.major), op.rows, op.k, op.outer_stride, _sf_c(op.sf), op.data.data_ptr())
+
+
+def _out_c(out):
+    return _lib.OutputC(int(out.dtype), out.rows, out.cols, out.stride, out.data.data_ptr())
+
+
+def device_check():
+    _check(_lib.load().dg_device_check())
+
+
+def poll_device_status(stream=None):
+    """Synchronises the stream and raises DeviceTimeout if a kernel gave up on a wait."""
+    _check(_lib.load().dg_poll_device_status(_stream_ptr(stream)))
+
+
+def sf_shape(mn, k, gran):
+    r, c = C.c_uint32(), C.c_uint32()
+    _lib.load().dg_sf_shape(mn, k, int(gran), C.byref(r), C.byref(c))
+    return r.value, c.value
+
+
+# ---- dense GEMM (api.rs:648-657, 762-771, 829-850) -------------------------------------
+def _gemm(fn, a, b, out, accumulate, stream):
+    ac, bc, oc = _op_c(a), _op_c(b), _out_c(out)
+    _check(fn(C.byref(ac), C.byref(bc), C.byref(oc), 1 if accumulate else 0, _stream_ptr(stream)))
+
+
+def gemm_nt(a, b, out, accumulate=False, stream=None):
+    _gemm(_lib.load().dg_gemm_nt, a, b, out, accumulate, stream)
+
+
+def fp8_gemm_nt(a, b, out, accumulate=False, stream=None):
+    _gemm(_lib.load().dg_fp8_gemm_nt, a, b, out, accumulate, stream)
+
+
+def fp4_gemm_nt(a, b, out, accumulate=False, stream=None):
+    _gemm(_lib.load().dg_fp4_gemm_nt, a, b, out, accumulate, stream)
+
+
+def bf16_gemm_nt(a, b, out, accumulate=False, stream=None):
+    _gemm(_lib.load().dg_bf16_gemm_nt, a, b, out, accumulate, stream)
+
+
+# ---- grouped GEMM (api.rs:859-963) -----------------------------------------------------
+def _contig(fn, a, b, out, m_indices, num_groups, stream):
+    ac, bc, oc = _op_c(a), _op_c(b), _out_c(out)
+    _check(fn(C.byref(ac), C.byref(bc), C.byref(oc), m_indices.data_ptr(), m_indices.numel(), num_groups,
+              _stream_ptr(stream)))
+
+
+def _masked(fn, a, b, out, masked_m, num_groups, expected_m, stream):
+    ac, bc, oc = _op_c(a), _op_c(b), _out_c(out)
+    _check(fn(C.byref(ac), C.byref(bc), C.byref(oc), masked_m.data_ptr(), num_groups, expected_m, _stream_ptr(stream)))
+
+
+def m_grouped_gemm_nt_contiguous(a, b, out, m_indices, num_groups, stream=None):
+    _contig(_lib.load().dg_m_grouped_gemm_nt_contiguous, a, b, out, m_indices, num_groups, stream)
+
+
+def m_grouped_gemm_nt_masked(a, b, out, masked_m, num_groups, expected_m, stream=None):
+    _masked(_lib.load().dg_m_grouped_gemm_nt_masked, a, b, out, masked_m, num_groups, expected_m, stream)
+
+
+def m_grouped_fp8_gemm_nt_contiguous(a, b, out, m_indices, num_groups, stream=None):
+    _contig(_lib.load().dg_m_grouped_fp8_gemm_nt_contiguous, a, b, out, m_indices, num_groups, stream)
+
+
+def m_grouped_fp4_gemm_nt_contiguous(a, b, out, m_indices, num_groups, stream=None):
+    _contig(_lib.load().dg_m_grouped_fp4_gemm_nt_contiguous, a, b, out, m_indices, num_groups, stream)
+
+
+def m_grouped_bf16_gemm_nt_contiguous(a, b, out, m_indices, num_groups, stream=None):
+    _contig(_lib.load().dg_m_grouped_bf16_gemm_nt_contiguous, a, b, out, m_indices, num_groups, stream)
+
+
+def m_grouped_fp8_gemm_nt_masked(a, b, out, masked_m, num_groups, expected_m, stream=None):
+    _masked(_lib.load().dg_m_grouped_fp8_gemm_nt_masked, a, b, out, masked_m, num_groups, expected_m, stream)
+
+
+def m_grouped_fp4_gemm_nt_masked(a, b, out, masked_m, num_groups, expected_m, stream=None):
+    _masked(_lib.load().dg_m_grouped_fp4_gemm_nt_masked, a, b, out, masked_m, num_groups, expected_m, stream)
+
+
+def m_grouped_bf16_gemm_nt_masked(a, b, out, masked_m, num_groups, expected_m, stream=None):
+    _masked(_lib.load().dg_m_grouped_bf16_gemm_nt_masked, a, b, out, masked_m, num_groups, expected_m, stream)
+
+
+# ---- quantisation (api.rs:1480-1601) ---------------------------------------------------
+def quant_mx(x, m, k, dtype, gran, stream=None):
+    """x: f32 [m, k], a device tensor or a host tensor/ndarray (the reference takes a host
+    slice, api.rs:1480-1488).  Returns (codes u8 device tensor, SfTensor)."""
+    L = _lib.load()
+    gran = SfGran(int(gran))
+    host = not (isinstance(x, torch.Tensor) and x.is_cuda)
+    if host:
+        x = torch.as_tensor(x, dtype=torch.float32).contiguous()
+    if x.numel() != m * k:
+        raise error_for(3, "x must be [m, k] row-major")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rows, cols = sf_shape(m, k, gran)
+    data = torch.empty((m, k // 2 if dtype == Dtype.Fp4 else k), dtype=torch.uint8, device=dev)
+    sf = torch.empty((rows, cols), dtype=torch.int32, device=dev)
+    fn = L.dg_quant_mx_host if host else L.dg_quant_mx
+    _check(fn(x.data_ptr(), m, k, int(dtype), int(gran), data.data_ptr(), sf.data_ptr(), _stream_ptr(stream)))
+    if host:
+        torch.cuda.current_stream().synchronize() if stream is None else stream.synchronize()
+    return data, SfTensor(rows, cols, gran, sf)
+
+
+def dequant_mx(data, sf, m, k, dtype, stream=None):
+    out = torch.empty((m, k), dtype=torch.float32, device=data.device)
+    sc = _sf_c(sf)
+    _check(_lib.load().dg_dequant_mx(data.data_ptr(), C.byref(sc), m, k, int(dtype), out.data_ptr(), _stream_ptr(stream)))
+    return out
+
+
+def transform_sf(sf, mn, gran, stream=None):
+    """sf: f32 [mn, sf_k] powers of two, device tensor or host tensor/ndarray (api.rs:1031-1037).
+    Returns the packed SfTensor."""
+    L = _lib.load()
+    host = not (isinstance(sf, torch.Tensor) and sf.is_cuda)
+    if host:
+        sf = torch.as_tensor(sf, dtype=torch.float32).contiguous()
+    if mn == 0 or sf.numel() % mn != 0:
+        raise error_for(3, "sf length must be mn * sf_k")
+    sf_k = sf.numel() // mn
+    dev = torch.device("cuda", torch.cuda.current_device())
+    rows, cols = (sf_k + 3) // 4, (mn + 3) // 4 * 4
+    out = torch.empty((rows, cols), dtype=torch.int32, device=dev)
+    fn = L.dg_transform_sf_host if host else L.dg_transform_sf
+    _check(fn(sf.data_ptr(), mn, sf_k, out.data_ptr(), _stream_ptr(stream)))
+    if host:
+        torch.cuda.current_stream().synchronize() if stream is None else stream.synchronize()
+    return SfTensor(rows, cols, SfGran(int(gran)), out)
+
+
+# ---- MQA logits ------------------------------------------------------------------------
+def mqa_logits_f32(q, kv, kv_scale, weights, cu_k_start, cu_k_end, num_tokens, num_kv_tokens, num_heads, head_dim,
+                   logits, logits_stride, stream=None):
+    _check(_lib.load().dg_mqa_logits_f32(q.data_ptr(), kv.data_ptr(), kv_scale.data_ptr(), weights.data_ptr(),
+                                         cu_k_start.data_ptr(), cu_k_end.data_ptr(), num_tokens, num_kv_tokens,
+                                         num_heads, head_dim, logits.data_ptr(), logits_stride, _stream_ptr(stream)))
+
+
+def mqa_logits(q, kv, weights, cu_k_start, cu_k_end, num_tokens, num_kv_tokens, num_heads, head_dim, logits,
+               logits_stride, stream=None):
+    qc, kc = _op_c(q), _op_c(kv)
+    _check(_lib.load().dg_mqa_logits(C.byref(qc), C.byref(kc), weights.data_ptr(), cu_k_start.data_ptr(),
+                                     cu_k_end.data_ptr(), num_tokens, num_kv_tokens, num_heads, head_dim,
+                                     logits.data_ptr(), logits_stride, _stream_ptr(stream)))
+
+
+def get_gemm_config(dtype, kind, m, n, k, num_groups=1):
+    cfg = _lib.GemmConfigC()
+    _check(_lib.load().dg_get_gemm_config(int(dtype), kind, m, n, k, num_groups, C.byref(cfg)))
+    return {f: getattr(cfg, f) for f, _ in cfg._fields_}

@@ -1,0 +1,194 @@
+/*
+ * deepgemm_b200 -- C ABI of the B200 (sm_100a) block-scaled GEMM path.
+ *
+ * One entry point per operator of the reference crate's `deepgemm::api` hot path
+ * (re-exported by deepgemm/src/lib.rs:55-61).  Every function
+ *   - takes plain pointers and sizes (device pointers unless the name ends in `_host`),
+ *   - enqueues on the caller's stream (`stream` is a cudaStream_t / CUstream; NULL = default
+ *     stream) and returns without synchronising, like the reference
+ *     (docs/PRODUCTION.md:84-86),
+ *   - validates its arguments and returns a status instead of aborting
+ *     (docs/PRODUCTION.md:103-107); the message is available from dg_last_error().
+ * There is no CPU fallback: without an sm_100 device every compute entry returns
+ * DG_ERR_UNSUPPORTED (deepgemm/src/api.rs:168-173).
+ */
+#ifndef DEEPGEMM_B200_H
+#define DEEPGEMM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define DG_API __attribute__((visibility("default")))
+#else
+#define DG_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes; the names follow the reference's DgError variants (deepgemm/src/error.rs:6-15).
+ * DG_ERR_DEVICE_TIMEOUT is new: a bounded device-side wait gave up (the reference's waits are
+ * unbounded, deepgemm/kernels/prelude.h:252-262). */
+typedef enum dg_status {
+    DG_OK = 0,
+    DG_ERR_DRIVER = 1,
+    DG_ERR_NVRTC = 2,        /* never returned: kernels are compiled ahead of time */
+    DG_ERR_INVALID_ARG = 3,
+    DG_ERR_UNSUPPORTED = 4,
+    DG_ERR_MISMATCH = 5,
+    DG_ERR_RUNTIME = 6,
+    DG_ERR_IO = 7,           /* never returned: nothing is read from or written to disk */
+    DG_ERR_DEVICE_TIMEOUT = 8
+} dg_status_t;
+
+/* deepgemm/src/types.rs:5-11 (Dtype), :33-37 (Major), :55-68 (SfGran). */
+typedef enum dg_dtype { DG_FP8 = 0, DG_FP4 = 1, DG_BF16 = 2, DG_F32 = 3 } dg_dtype_t;
+typedef enum dg_major { DG_MAJOR_K = 0, DG_MAJOR_MN = 1 } dg_major_t;
+
+/* Packed UE8M0 scale factors, deepgemm/src/types.rs:87-96: u32 [rows = ceil(K/(gran*4)),
+ * cols = align4(MN)], MN contiguous; byte j of word [r][m] scales k-group 4r+j of row m. */
+typedef struct dg_sf_tensor {
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t gran;            /* 32 or 128 */
+    const uint32_t* data;     /* device */
+} dg_sf_tensor_t;
+
+/* deepgemm/src/types.rs:98-111 (Operand).  K-major [rows, k]: element (r, k) at
+ * r * outer_stride + k; FP4 counts logical elements (the buffer holds k/2 bytes per row,
+ * even k in the low nibble). `sf.data == NULL` means "no scale factors" (Option::None). */
+typedef struct dg_operand {
+    int32_t dtype;            /* dg_dtype_t */
+    int32_t major;            /* dg_major_t */
+    uint32_t rows;
+    uint32_t k;
+    uint32_t outer_stride;    /* elements */
+    dg_sf_tensor_t sf;
+    const void* data;         /* device */
+} dg_operand_t;
+
+/* deepgemm/src/types.rs:113-121 (Output): row-major [rows, cols], BF16 or F32. */
+typedef struct dg_output {
+    int32_t dtype;            /* DG_BF16 or DG_F32 */
+    uint32_t rows;
+    uint32_t cols;
+    uint32_t stride;          /* elements */
+    void* data;               /* device */
+} dg_output_t;
+
+/* ---- library ------------------------------------------------------------------------ */
+DG_API const char* dg_last_error(void);          /* thread-local message of the last failing call */
+DG_API const char* dg_version(void);
+/* Returns DG_OK when the current device is sm_100 and the kernels can be launched there
+ * (replaces the arch gate of deepgemm/src/api.rs:168-173). */
+DG_API int32_t dg_device_check(void);
+/* Synchronises `stream`, then reports DG_ERR_DEVICE_TIMEOUT if any kernel launched by this
+ * library on the current device gave up on a wait since the last call, and clears the flag. */
+DG_API int32_t dg_poll_device_status(void* stream);
+
+/* Shape of the packed SF tensor of an [mn, k] operand: rows = ceil(k/(gran*4)),
+ * cols = align4(mn) (deepgemm/src/heuristics.rs:617-624, deepgemm/src/golden.rs:71-73). */
+DG_API void dg_sf_shape(uint32_t mn, uint32_t k, uint32_t gran, uint32_t* rows, uint32_t* cols);
+
+/* ---- dense GEMM: D[M,N] (+)= A[M,K] . B[N,K]^T ---------------------------------------
+ * replaces api::gemm_nt / fp8_gemm_nt / fp4_gemm_nt / bf16_gemm_nt
+ * (deepgemm/src/api.rs:648-657, 762-771, 829-838, 841-850). */
+DG_API int32_t dg_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
+DG_API int32_t dg_fp8_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
+DG_API int32_t dg_fp4_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
+DG_API int32_t dg_bf16_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
+
+/* ---- grouped GEMM (MoE) ----------------------------------------------------------------
+ * replaces api::m_grouped_gemm_nt_contiguous (deepgemm/src/api.rs:859-903).  a.rows must be
+ * a multiple of 128; m_indices (device, int32, a.rows/128 entries) holds the expert of each
+ * 128-row block, negative = skip the block; b is the stacked [num_groups * b.rows, K] weight
+ * whose SF tensor is that of the stacked matrix (deepgemm/tests/e2e_gpu.rs:421). */
+DG_API int32_t dg_m_grouped_gemm_nt_contiguous(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                        const int32_t* m_indices, uint32_t m_indices_len,
+                                        uint32_t num_groups, void* stream);
+/* replaces api::m_grouped_gemm_nt_masked (deepgemm/src/api.rs:930-963).  a, b and out are
+ * stacked per group ([num_groups * rows, ...]); masked_m (device, int32, num_groups entries)
+ * holds the valid rows of each group; rows beyond it are neither computed nor written.
+ * expected_m only steers the tile choice. */
+DG_API int32_t dg_m_grouped_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                    const int32_t* masked_m, uint32_t num_groups, uint32_t expected_m,
+                                    void* stream);
+/* dtype-named spellings of the two grouped entries (deepgemm/src/api.rs:907, README.md:26-27);
+ * they additionally check the operand dtype. */
+DG_API int32_t dg_m_grouped_fp8_gemm_nt_contiguous(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                            const int32_t* m_indices, uint32_t m_indices_len,
+                                            uint32_t num_groups, void* stream);
+DG_API int32_t dg_m_grouped_fp4_gemm_nt_contiguous(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                            const int32_t* m_indices, uint32_t m_indices_len,
+                                            uint32_t num_groups, void* stream);
+DG_API int32_t dg_m_grouped_bf16_gemm_nt_contiguous(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                             const int32_t* m_indices, uint32_t m_indices_len,
+                                             uint32_t num_groups, void* stream);
+DG_API int32_t dg_m_grouped_fp8_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                        const int32_t* masked_m, uint32_t num_groups, uint32_t expected_m,
+                                        void* stream);
+DG_API int32_t dg_m_grouped_fp4_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                        const int32_t* masked_m, uint32_t num_groups, uint32_t expected_m,
+                                        void* stream);
+DG_API int32_t dg_m_grouped_bf16_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                         const int32_t* masked_m, uint32_t num_groups, uint32_t expected_m,
+                                         void* stream);
+
+/* ---- quantisation / scale-factor layout ------------------------------------------------
+ * replaces api::quant_mx (deepgemm/src/api.rs:1480-1553): x f32 [m,k] -> codes (E4M3 [m,k]
+ * bytes, or packed E2M1 [m,k/2] bytes) + packed UE8M0 SF words [ceil(k/gran/4), align4(m)].
+ * Every output word is written (padding columns and missing k bytes are zero), so the
+ * outputs need not be cleared.  FP4 requires gran 32.  The reference takes a host slice and
+ * returns owned device buffers; here the caller owns the buffers.  `_host` takes x in host
+ * memory and copies it to the device on `stream` first. */
+DG_API int32_t dg_quant_mx(const float* x, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran,
+                    void* data_out, uint32_t* sf_out, void* stream);
+DG_API int32_t dg_quant_mx_host(const float* x_host, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran,
+                         void* data_out, uint32_t* sf_out, void* stream);
+/* replaces api::dequant_mx (deepgemm/src/api.rs:1556-1601): codes + SF -> f32 [m,k]. */
+DG_API int32_t dg_dequant_mx(const void* data, const dg_sf_tensor_t* sf, uint32_t m, uint32_t k, int32_t dtype,
+                      float* out, void* stream);
+/* replaces api::transform_sf (deepgemm/src/api.rs:1031-1064): f32 power-of-two scales
+ * [mn, sf_k] row-major -> packed words [ceil(sf_k/4), align4(mn)]. */
+DG_API int32_t dg_transform_sf(const float* sf, uint32_t mn, uint32_t sf_k, uint32_t* out, void* stream);
+DG_API int32_t dg_transform_sf_host(const float* sf_host, uint32_t mn, uint32_t sf_k, uint32_t* out, void* stream);
+
+/* ---- MQA logits (lightning indexer) ----------------------------------------------------
+ * logits[i, j] = sum_h w[i,h] * relu(<q[i,h,:], kv[j,:]>) for j in [ks[i], min(ke[i], S)).
+ * fp32 contract (deepgemm/src/api_sm90_mqa.rs:5-31): q raw E4M3 [T,H,D]; kv E4M3 [S,D]
+ * with one f32 scale per kv token applied after the head sum; weights f32 [T,H]; logits f32
+ * with row pitch `logits_stride` elements, written at the absolute column j; columns outside
+ * the range are not written. */
+DG_API int32_t dg_mqa_logits_f32(const void* q, const void* kv, const float* kv_scale, const float* weights,
+                          const uint32_t* cu_k_start, const uint32_t* cu_k_end,
+                          uint32_t num_tokens, uint32_t num_kv_tokens, uint32_t num_heads, uint32_t head_dim,
+                          float* logits, uint32_t logits_stride, void* stream);
+/* reference SM100 contract, api::mqa_logits (deepgemm/src/api.rs:1614-1745): q and kv carry
+ * packed UE8M0 per-32 scales, weights are bf16 [T,H], logits are bf16 and stored compressed
+ * at column j - ks[i] (deepgemm/kernels/mqa_logits_sm100.cu:1014-1020). */
+DG_API int32_t dg_mqa_logits(const dg_operand_t* q, const dg_operand_t* kv, const void* weights_bf16,
+                      const uint32_t* cu_k_start, const uint32_t* cu_k_end,
+                      uint32_t num_tokens, uint32_t num_kv_tokens, uint32_t num_heads, uint32_t head_dim,
+                      void* logits_bf16, uint32_t logits_stride, void* stream);
+
+/* ---- tuning / introspection -------------------------------------------------------------
+ * Describes the tile configuration the library would use for a dense / grouped GEMM
+ * (counterpart of heuristics::get_best_config, deepgemm/src/heuristics.rs:559-608, and of
+ * DG_PRINT_CONFIGS, :23-27).  kind: 0 normal, 1 contiguous, 2 masked. */
+typedef struct dg_gemm_config {
+    uint32_t block_m, block_n, block_k;
+    uint32_t num_stages;
+    uint32_t smem_bytes;
+    uint32_t num_tiles;
+    uint32_t grid;
+    uint32_t cluster;
+} dg_gemm_config_t;
+DG_API int32_t dg_get_gemm_config(int32_t dtype, int32_t kind, uint32_t m, uint32_t n, uint32_t k,
+                           uint32_t num_groups, dg_gemm_config_t* cfg);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEEPGEMM_B200_H */

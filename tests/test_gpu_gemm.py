@@ -1,0 +1,256 @@
+"""GPU parity of the dense and grouped GEMMs against the oracle's gemm_ref, through the C ABI.
+Tolerance: calc_diff = 1 - 2*sum(xy)/sum(x^2+y^2) <= 1e-3 (FP8) / 2e-3 (FP4), the stated
+contract, on identical oracle-quantised inputs (helpers.TOL), plus an element-wise bound."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle as o
+from deepgemm import (Dtype, Operand, bf16_gemm_nt, fp4_gemm_nt, fp8_gemm_nt, gemm_nt, get_gemm_config,
+                      m_grouped_fp8_gemm_nt_contiguous, m_grouped_fp8_gemm_nt_masked, m_grouped_gemm_nt_contiguous,
+                      m_grouped_gemm_nt_masked, poll_device_status)
+from helpers import (assert_close_to_oracle, bf16_operand, bf16_round, dev, new_output, quantised_operand, randn,
+                     to_f32)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _clean_env():
+    yield
+    for v in ("DG_BLOCK_N", "DG_NUM_STAGES", "DG_BAND"):
+        os.environ.pop(v, None)
+
+
+def run_dense(kind, m, n, k, gran_a=32, gran_b=32, block128_b=False, f32=False, seed=0, block_n=None, stages=None):
+    if block_n:
+        os.environ["DG_BLOCK_N"] = str(block_n)
+    if stages:
+        os.environ["DG_NUM_STAGES"] = str(stages)
+    xa, xb = randn((m, k), seed), randn((n, k), seed + 1)
+    if kind == "bf16":
+        a, fa = bf16_operand(xa)
+        b, fb = bf16_operand(xb)
+        ref = o.gemm_f32_ref(fa, fb)
+        fn = bf16_gemm_nt
+    else:
+        a, ga = quantised_operand(xa, kind, gran_a)
+        b, gb = quantised_operand(xb, kind, gran_b, block128=block128_b)
+        ref = o.gemm_ref(ga, gb, m=m, n=n)
+        fn = fp8_gemm_nt if kind == "fp8" else fp4_gemm_nt
+    out = new_output(m, n, f32=f32)
+    fn(a, b, out)
+    poll_device_status()
+    got = to_f32(out)
+    assert_close_to_oracle(got, ref if f32 else bf16_round(ref), kind, f"{kind} {m}x{n}x{k}")
+    return got, ref
+
+
+# ---- the reference's own CPU-runnable configuration: FP8 M128 N256 K512, 1x128 / 128x128 scales
+def test_fp8_config_golden_case():
+    run_dense("fp8", 128, 256, 512, gran_a=128, gran_b=128, block128_b=True, seed=0)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8", "fp4"])
+def test_single_tile(kind):
+    run_dense(kind, 128, 128, 512, seed=3, block_n=128)
+
+
+@pytest.mark.parametrize("gran_a,gran_b", [(32, 32), (128, 128), (128, 32), (32, 128)])
+def test_fp8_granularities(gran_a, gran_b):
+    run_dense("fp8", 256, 384, 1536, gran_a=gran_a, gran_b=gran_b, seed=5)
+
+
+@pytest.mark.parametrize("block_n", [32, 64, 96, 128, 160, 192, 224])
+def test_fp8_every_block_n(block_n):
+    run_dense("fp8", 256, 512, 1024, gran_a=128, gran_b=128, seed=block_n, block_n=block_n)
+
+
+@pytest.mark.parametrize("block_n", [32, 128, 224])
+def test_fp4_block_n(block_n):
+    run_dense("fp4", 256, 512, 1024, seed=block_n, block_n=block_n)
+
+
+@pytest.mark.parametrize("block_n", [64, 256])
+def test_bf16_block_n(block_n):
+    run_dense("bf16", 256, 512, 512, seed=block_n, block_n=block_n)
+
+
+@pytest.mark.parametrize("kind,m,n,k", [
+    ("fp8", 100, 200, 256),     # ragged M and N (N % 8 == 0)
+    ("fp8", 1, 8, 128),         # smallest
+    ("fp8", 300, 1000, 640),
+    ("fp8", 129, 260, 128),     # N % 8 != 0: scalar store path
+    ("fp4", 100, 200, 512),
+    ("bf16", 70, 136, 192),
+])
+def test_ragged_shapes(kind, m, n, k):
+    run_dense(kind, m, n, k, seed=m + n)
+
+
+@pytest.mark.parametrize("stages", [2, 3])
+def test_pipeline_wraps_with_few_stages(stages):
+    run_dense("fp8", 384, 640, 4096, gran_a=128, gran_b=128, seed=11, stages=stages)
+
+
+def test_many_tiles_per_cta_and_long_k():
+    """More tiles than CTAs (persistent loop, both accumulator stages) and a deep K loop."""
+    run_dense("fp8", 2048, 4096, 2048, gran_a=128, gran_b=128, block128_b=True, seed=21)
+    run_dense("fp8", 128, 256, 16384, gran_a=128, gran_b=128, seed=22)
+
+
+def test_f32_output_and_strided_output():
+    got, ref = run_dense("fp8", 256, 256, 512, f32=True, seed=31)
+    xa, xb = randn((200, 256), 32), randn((96, 256), 33)
+    a, ga = quantised_operand(xa, "fp8", 32)
+    b, gb = quantised_operand(xb, "fp8", 32)
+    out = new_output(200, 96, stride=136, fill=7.0)
+    gemm_nt(a, b, out)
+    poll_device_status()
+    assert_close_to_oracle(to_f32(out), bf16_round(o.gemm_ref(ga, gb, m=200, n=96)), "fp8", "strided D")
+    assert bool((out.data[:, 96:] == 7.0).all()), "columns beyond N were touched"
+
+
+def test_accumulate_adds_the_rounded_tile():
+    """D0 + bf16(acc), rounded to bf16 (the oracle has no accumulate model; the reference adds
+    the cast tile in D's dtype, deepgemm/kernels/gemm_sm100.cu:309-315)."""
+    m, n, k = 256, 256, 512
+    xa, xb = randn((m, k), 41), randn((n, k), 42)
+    a, ga = quantised_operand(xa, "fp8", 128)
+    b, gb = quantised_operand(xb, "fp8", 128)
+    d0 = bf16_round(randn((m, n), 43) * 10)
+    out = new_output(m, n)
+    out.data.copy_(torch.from_numpy(d0))
+    plain = new_output(m, n)
+    gemm_nt(a, b, plain)
+    gemm_nt(a, b, out, accumulate=True)
+    poll_device_status()
+    want = bf16_round(d0 + to_f32(plain))
+    assert np.array_equal(to_f32(out), want)
+    outf = new_output(m, n, f32=True, fill=1.5)
+    plainf = new_output(m, n, f32=True)
+    gemm_nt(a, b, plainf)
+    gemm_nt(a, b, outf, accumulate=True)
+    assert np.array_equal(to_f32(outf), to_f32(plainf) + np.float32(1.5))
+
+
+def test_bitwise_determinism():
+    xa, xb = randn((512, 1024), 51), randn((768, 1024), 52)
+    a, _ = quantised_operand(xa, "fp8", 128)
+    b, _ = quantised_operand(xb, "fp8", 128)
+    o1, o2 = new_output(512, 768), new_output(512, 768)
+    fp8_gemm_nt(a, b, o1)
+    fp8_gemm_nt(a, b, o2)
+    poll_device_status()
+    assert torch.equal(o1.data, o2.data)
+
+
+# ---- grouped --------------------------------------------------------------------------------
+def _stacked_b(kind, groups, n, k, seed, gran=32):
+    xb = randn((groups * n, k), seed)
+    if kind == "bf16":
+        op, f = bf16_operand(xb)
+        op.rows = n
+        return op, f
+    op, g = quantised_operand(xb, kind, gran)
+    op.rows = n
+    return op, g
+
+
+@pytest.mark.parametrize("kind", ["fp8", "fp4", "bf16"])
+def test_m_grouped_contiguous(kind):
+    groups, n, k = 4, 256, 512
+    blocks = [0, 0, 2, -1, 3, 1, 1, -1, 2]            # expert of each 128-row block, -1 = padding
+    m = 128 * len(blocks)
+    xa = randn((m, k), 61)
+    xa[128 * 5 + 70: 128 * 6] = 0.0                   # zero padding rows inside a block
+    b, gb = _stacked_b(kind, groups, n, k, 62)
+    if kind == "bf16":
+        a, fa = bf16_operand(xa)
+    else:
+        a, ga = quantised_operand(xa, kind, 32)
+    out = new_output(m, n, fill=3.0)
+    m_indices = dev(np.array(blocks, dtype=np.int32))
+    m_grouped_gemm_nt_contiguous(a, b, out, m_indices, groups)
+    poll_device_status()
+    got = to_f32(out)
+    for i, e in enumerate(blocks):
+        rows = np.arange(128 * i, 128 * (i + 1))
+        if e < 0:
+            assert (got[rows] == 3.0).all(), "a padding block was written"
+            continue
+        if kind == "bf16":
+            ref = o.gemm_f32_ref(fa[rows], gb[e * n:(e + 1) * n])
+        else:
+            ref = o.gemm_ref(ga, gb, rows=rows, n=n, b_row0=e * n)
+        assert_close_to_oracle(got[rows], bf16_round(ref), kind, f"block {i} expert {e}")
+
+
+def test_m_grouped_contiguous_reference_test_shape():
+    """deepgemm/tests/e2e_gpu.rs:403-484 with a well-formed m_indices: 4 groups, N 128, K 512."""
+    groups, n, k = 4, 128, 512
+    m = groups * 128
+    a, ga = quantised_operand(randn((m, k), 9), "fp8", 32)
+    b, gb = _stacked_b("fp8", groups, n, k, 10)
+    out = new_output(m, n)
+    m_grouped_fp8_gemm_nt_contiguous(a, b, out, dev(np.arange(groups, dtype=np.int32)), groups)
+    poll_device_status()
+    got = to_f32(out)
+    for g in range(groups):
+        rows = np.arange(128 * g, 128 * (g + 1))
+        assert_close_to_oracle(got[rows], bf16_round(o.gemm_ref(ga, gb, rows=rows, n=n, b_row0=g * n)), "fp8")
+
+
+@pytest.mark.parametrize("kind", ["fp8", "fp4", "bf16"])
+def test_m_grouped_masked(kind):
+    groups, max_m, n, k = 6, 256, 384, 512
+    masked = [256, 0, 1, 128, 129, 77]
+    xa = randn((groups * max_m, k), 71)
+    b, gb = _stacked_b(kind, groups, n, k, 72)
+    if kind == "bf16":
+        a, fa = bf16_operand(xa)
+    else:
+        a, ga = quantised_operand(xa, kind, 32)
+    a.rows = max_m
+    out = new_output(groups * max_m, n, fill=5.0)
+    out.rows = max_m
+    m_grouped_gemm_nt_masked(a, b, out, dev(np.array(masked, dtype=np.int32)), groups, 128)
+    poll_device_status()
+    got = out.data.float().cpu().numpy()
+    for g, mm in enumerate(masked):
+        base = g * max_m
+        assert (got[base + mm: base + max_m] == 5.0).all(), f"group {g}: rows beyond masked_m were written"
+        if mm == 0:
+            continue
+        rows = np.arange(base, base + mm)
+        if kind == "bf16":
+            ref = o.gemm_f32_ref(fa[rows], gb[g * n:(g + 1) * n])
+        else:
+            ref = o.gemm_ref(ga, gb, rows=rows, n=n, b_row0=g * n)
+        assert_close_to_oracle(got[rows], bf16_round(ref), kind, f"group {g}")
+
+
+def test_m_grouped_masked_reference_test_shape():
+    """deepgemm/tests/e2e_gpu.rs:328-401: 4 groups, M 64 per group, N 128, K 512, all rows valid."""
+    groups, m, n, k = 4, 64, 128, 512
+    a, ga = quantised_operand(randn((groups * m, k), 7), "fp8", 32)
+    b, gb = _stacked_b("fp8", groups, n, k, 8)
+    a.rows = m
+    out = new_output(groups * m, n)
+    out.rows = m
+    m_grouped_fp8_gemm_nt_masked(a, b, out, dev(np.full(groups, m, dtype=np.int32)), groups, m)
+    poll_device_status()
+    got = out.data.float().cpu().numpy()
+    for g in range(groups):
+        rows = np.arange(g * m, (g + 1) * m)
+        assert_close_to_oracle(got[rows], bf16_round(o.gemm_ref(ga, gb, rows=rows, n=n, b_row0=g * n)), "fp8")
+
+
+def test_config_introspection():
+    cfg = get_gemm_config(Dtype.Fp8, 0, 4096, 7168, 16384)
+    assert cfg["block_m"] == 128 and cfg["block_k"] == 128 and cfg["block_n"] % 32 == 0
+    assert cfg["smem_bytes"] <= 232448 and cfg["num_stages"] >= 2
+    assert get_gemm_config(Dtype.Fp4, 0, 8192, 8192, 8192)["block_k"] == 256
+    assert get_gemm_config(Dtype.Bf16, 0, 2048, 2048, 2048)["block_k"] == 64
