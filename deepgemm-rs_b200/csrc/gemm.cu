@@ -125,8 +125,9 @@ struct Scheduler {
 };
 
 struct __align__(8) Barriers {
-    uint64_t full[kMaxStages];
-    uint64_t sf_ready[kMaxStages];
+    uint64_t full[kMaxStages];      // A and B tiles landed
+    uint64_t sf_full[kMaxStages];   // SF rows landed (only on k-blocks that load SF)
+    uint64_t sf_ready[kMaxStages];  // SF rows transposed
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
@@ -154,6 +155,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         bars->abort = 0;
         for (uint32_t s = 0; s < p.num_stages; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->sf_full[s]), 1);
             mbar_init(smem_u32(&bars->sf_ready[s]), 1);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
@@ -194,9 +196,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 const uint32_t sa = stage_addr(stage);
                 const bool ld_sfa = kHasSf && (kb % p.sfa_period == 0);
                 const bool ld_sfb = kHasSf && (kb % p.sfb_period == 0);
-                mbar_arrive_expect_tx(bar, p.tx_ab + (ld_sfa ? p.tx_sfa : 0u) + (ld_sfb ? p.tx_sfb : 0u));
-                if (ld_sfa) tma_load_2d(&tm_sfa, bar, sa + p.off_sfa, (int32_t)t.a_row, (int32_t)((kb / p.sfa_period) * p.sf_sub));
-                if (ld_sfb) tma_load_2d(&tm_sfb, bar, sa + p.off_sfb, (int32_t)t.b_row, (int32_t)((kb / p.sfb_period) * p.sf_sub));
+                // Scale factors go first and complete on their own barrier, so that their
+                // transposition overlaps the (much larger) A/B transfer.
+                if (ld_sfa || ld_sfb) {
+                    const uint32_t sbar = smem_u32(&bars->sf_full[stage]);
+                    mbar_arrive_expect_tx(sbar, (ld_sfa ? p.tx_sfa : 0u) + (ld_sfb ? p.tx_sfb : 0u));
+                    if (ld_sfa) tma_load_2d(&tm_sfa, sbar, sa + p.off_sfa, (int32_t)t.a_row, (int32_t)((kb / p.sfa_period) * p.sf_sub));
+                    if (ld_sfb) tma_load_2d(&tm_sfb, sbar, sa + p.off_sfb, (int32_t)t.b_row, (int32_t)((kb / p.sfb_period) * p.sf_sub));
+                }
+                mbar_arrive_expect_tx(bar, p.tx_ab);
                 // Inner coordinate in elements: 128 bytes per k-block (128 FP8, 256 FP4 = 128 B, 64 BF16).
                 const int32_t kx = (int32_t)(kb * (KIND == kBf16 ? 64u : 128u));
                 tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
@@ -209,6 +217,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         Scheduler<GTYPE> sched;
         Tile t;
         uint32_t stage = 0, phase = 0, tile_count = 0;
+        uint32_t sf_bits = 0;  // per-stage parity of sf_ready (it completes only on SF k-blocks)
         const uint32_t idesc = KIND == kBf16 ? make_idesc_bf16(kBlockM, p.block_n)
                                              : make_idesc_bs(KIND == kFp4 ? 1u : 0u, kBlockM, p.block_n);
         bool ok = true;
@@ -221,8 +230,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const uint32_t d_tmem = tmem + as * kAccStageCols;
             for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
                 if (!(ok = mbar_wait(smem_u32(&bars->full[stage]), phase, wc, kWaitFull))) break;
-                if (kHasSf) {
-                    if (!(ok = mbar_wait(smem_u32(&bars->sf_ready[stage]), phase, wc, kWaitSfReady))) break;
+                if (kHasSf && (kb % p.sfa_period == 0 || kb % p.sfb_period == 0)) {
+                    if (!(ok = mbar_wait(smem_u32(&bars->sf_ready[stage]), (sf_bits >> stage) & 1u, wc, kWaitSfReady))) break;
+                    sf_bits ^= 1u << stage;
                 }
                 tc_fence_after();
                 const uint32_t sa = stage_addr(stage);
@@ -269,28 +279,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         // ===================================================== SF transposer
         Scheduler<GTYPE> sched;
         Tile t;
-        uint32_t stage = 0, phase = 0;
+        uint32_t stage = 0, sf_bits = 0;
         bool ok = true;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
             for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
-                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->full[stage]), phase, wc, kWaitFull));
-                if (!ok) break;
                 const bool has_a = kb % p.sfa_period == 0, has_b = kb % p.sfb_period == 0;
-                uint32_t* sfa = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfa - smem_u32(smem_raw)));
-                uint32_t* sfb = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfb - smem_u32(smem_raw)));
-                const uint32_t na = has_a ? p.sf_sub : 0u, nb = has_b ? p.sf_sub * p.sfb_chunks : 0u;
-                for (uint32_t c = 0; c < na + nb; ++c) {
-                    uint32_t* q = c < na ? sfa + c * 128u : sfb + (c - na) * 128u;
-                    // word of row 32*i + lane  ->  position lane*4 + i
-                    const uint32_t v0 = q[lane], v1 = q[32 + lane], v2 = q[64 + lane], v3 = q[96 + lane];
+                if (has_a || has_b) {
+                    const uint32_t parity = (sf_bits >> stage) & 1u;
+                    sf_bits ^= 1u << stage;
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->sf_full[stage]), parity, wc, kWaitFull));
+                    if (!ok) break;
+                    uint32_t* sfa = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfa - smem_u32(smem_raw)));
+                    uint32_t* sfb = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfb - smem_u32(smem_raw)));
+                    const uint32_t na = has_a ? p.sf_sub : 0u, nb = has_b ? p.sf_sub * p.sfb_chunks : 0u;
+                    // Up to 6 chunks of 128 words: word of row 32*i + lane -> position lane*4 + i.
+                    // All loads are issued before the first store.
+                    uint4 v[6];
+#pragma unroll
+                    for (uint32_t c = 0; c < 6; ++c) {
+                        if (c < na + nb) {
+                            const uint32_t* q = c < na ? sfa + c * 128u : sfb + (c - na) * 128u;
+                            v[c] = make_uint4(q[lane], q[32 + lane], q[64 + lane], q[96 + lane]);
+                        }
+                    }
                     __syncwarp();
-                    *reinterpret_cast<uint4*>(q + lane * 4u) = make_uint4(v0, v1, v2, v3);
+#pragma unroll
+                    for (uint32_t c = 0; c < 6; ++c) {
+                        if (c < na + nb) {
+                            uint32_t* q = c < na ? sfa + c * 128u : sfb + (c - na) * 128u;
+                            *reinterpret_cast<uint4*>(q + lane * 4u) = v[c];
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
-                if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+                if (++stage == p.num_stages) stage = 0;
             }
         }
     } else if (warp >= 4) {

@@ -1,0 +1,450 @@
+// MQA logits (MLA lightning indexer) for sm_100a:
+//   logits[i, j] = s_kv[j] * sum_h w[i,h] * relu(<q[i,h,:], kv[j,:]>),  j in [ks[i], min(ke[i], S))
+// stored compressed at column j - ks[i] of row i.
+//
+// Two contracts of the reference share this kernel:
+//   fp32  (deepgemm/src/api_sm90_mqa.rs:5-31): raw E4M3 q, E4M3 kv with one f32 scale per kv
+//         token, f32 weights, f32 logits           -> tcgen05.mma kind::f8f6f4
+//   ue8m0 (api::mqa_logits, deepgemm/src/api.rs:1614-1745; device side
+//         deepgemm/kernels/mqa_logits_sm100.cu:514-1084): UE8M0 scales per 32 along head_dim on
+//         q and kv, bf16 weights, bf16 logits      -> tcgen05.mma kind::mxf8f6f4.block_scale
+// Numerical contract: mqa_logits_ref of the golden model (deepgemm/src/golden.rs:469-501).
+//
+// The contraction runs with the 128 kv tokens of a block on the UMMA M side (TMEM lanes) and
+// the (query, head) pairs of a query block on the N side, so one epilogue thread owns one kv
+// token, reduces over heads with weights broadcast from shared memory and the warp stores 32
+// consecutive columns of a logits row.
+//   warp 0      TMA producer (Q tile per query block, KV tiles streamed through a ring)
+//   warp 1      MMA issuer (head_dim/32 MMAs per kv block, two accumulator stages in TMEM)
+//   warp 2      TMEM owner; ue8m0 contract: scale-factor transposer
+//   warps 4-11  two epilogue warpgroups, each reducing half of the query block's columns
+#include "host.h"
+#include "ptx.cuh"
+
+namespace dg {
+
+constexpr uint32_t kMqaBlockKv = 128;
+constexpr uint32_t kMqaMaxKvStages = 10;
+constexpr uint32_t kMqaThreads = 384;
+constexpr uint32_t kMqaSfaCol = 448;   // ue8m0 contract only: accumulators are <= 192 wide
+constexpr uint32_t kMqaSfbCol = 452;
+
+struct MqaParams {
+    uint32_t num_tokens, num_kv, num_heads, head_dim;
+    uint32_t block_q, n;          // n = block_q * num_heads (UMMA N)
+    uint32_t num_q_blocks;
+    uint32_t kv_stages, kv_stage_bytes, q_stage_bytes;
+    uint32_t off_w, off_q, off_kv;  // offsets from the 1024-aligned base
+    uint32_t kv_sf_off, q_sf_off;   // SF words inside a kv / q stage (ue8m0 contract)
+    uint32_t sbo;                   // 8-row group pitch of the swizzled tiles
+    uint32_t layout;                // UMMA layout type of the tiles
+    uint32_t logits_stride;
+    const uint32_t* ks;
+    const uint32_t* ke;
+    const float* kv_scale;          // fp32 contract
+    const void* weights;            // f32 (fp32 contract) or bf16 (ue8m0 contract)
+    void* logits;
+    uint32_t* status;
+};
+
+struct __align__(8) MqaBarriers {
+    uint64_t kv_full[kMqaMaxKvStages];
+    uint64_t kv_ready[kMqaMaxKvStages];   // ue8m0: SF transposed
+    uint64_t kv_empty[kMqaMaxKvStages];
+    uint64_t q_full[2], q_ready[2], q_empty[2];
+    uint64_t tmem_full[2], tmem_empty[2];
+    uint64_t w_full[2];                   // weights of a query block staged by the 8 epilogue warps
+    uint32_t tmem_base;
+    uint32_t abort;
+};
+
+// kv-block range [b0, b1) that a query block touches; identical in every role.
+struct QRange { uint32_t b0, b1; };
+__device__ __forceinline__ QRange q_block_range(const MqaParams& p, uint32_t qb) {
+    uint32_t lo = 0xffffffffu, hi = 0;
+    for (uint32_t i = 0; i < p.block_q; ++i) {
+        const uint32_t q = qb * p.block_q + i;
+        if (q < p.num_tokens) {
+            const uint32_t s = __ldg(p.ks + q), e = min(__ldg(p.ke + q), p.num_kv);
+            if (s < e) { lo = min(lo, s); hi = max(hi, e); }
+        }
+    }
+    QRange r;
+    r.b0 = hi > lo ? lo / kMqaBlockKv : 0;
+    r.b1 = hi > lo ? (hi + kMqaBlockKv - 1) / kMqaBlockKv : 0;
+    return r;
+}
+
+__device__ __forceinline__ void tc_mma_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc_f8(uint32_t m, uint32_t n) {
+    return (1u << 4) /*D=f32*/ | ((n >> 3) << 17) | ((m >> 4) << 24);  // A, B = E4M3 (format 0), K-major
+}
+
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ float sum_f32x2(uint64_t v) {
+    float lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+    return lo + hi;
+}
+
+template <bool SCALED>
+__global__ void __launch_bounds__(kMqaThreads, 1)
+mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
+                  const __grid_constant__ CUtensorMap tm_qsf, const __grid_constant__ CUtensorMap tm_kvsf,
+                  const MqaParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t raw_u32 = smem_u32(smem_raw);
+    const uint32_t base = (raw_u32 + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_u32);
+    MqaBarriers* bars = reinterpret_cast<MqaBarriers*>(base_ptr);
+    float* w_smem = reinterpret_cast<float*>(base_ptr + p.off_w);   // [2][n]
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const WaitCtx wc{p.status, &bars->abort};
+
+    if (threadIdx.x == 0) {
+        bars->abort = 0;
+        for (uint32_t s = 0; s < p.kv_stages; ++s) {
+            mbar_init(smem_u32(&bars->kv_full[s]), 1);
+            mbar_init(smem_u32(&bars->kv_ready[s]), 1);
+            mbar_init(smem_u32(&bars->kv_empty[s]), 1);
+        }
+        for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bars->q_full[s]), 1);
+            mbar_init(smem_u32(&bars->q_ready[s]), 1);
+            mbar_init(smem_u32(&bars->q_empty[s]), 1);
+            mbar_init(smem_u32(&bars->tmem_full[s]), 1);
+            mbar_init(smem_u32(&bars->tmem_empty[s]), 8);
+            mbar_init(smem_u32(&bars->w_full[s]), 8);
+        }
+        fence_barrier_init();
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_kv);
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(&bars->tmem_base), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+    const uint32_t acc_stride = SCALED ? 192u : 256u;
+    const uint32_t num_mma = p.head_dim / 32u;
+
+    if (warp == 0 && lane == 0) {
+        // ===================================================== producer
+        uint32_t stage = 0, phase = 0, qcount = 0;
+        bool ok = true;
+        for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
+            const QRange r = q_block_range(p, qb);
+            if (r.b1 <= r.b0) continue;
+            const uint32_t qs = qcount & 1u, qphase = (qcount >> 1) & 1u;
+            ++qcount;
+            if (!(ok = mbar_wait(smem_u32(&bars->q_empty[qs]), qphase ^ 1u, wc, kWaitEmpty))) break;
+            const uint32_t qbar = smem_u32(&bars->q_full[qs]);
+            const uint32_t qdst = base + p.off_q + qs * p.q_stage_bytes;
+            mbar_arrive_expect_tx(qbar, p.n * p.head_dim + (SCALED ? p.n * 4u : 0u));
+            tma_load_2d(&tm_q, qbar, qdst, 0, (int32_t)(qb * p.n));
+            if (SCALED) tma_load_2d(&tm_qsf, qbar, qdst + p.q_sf_off, (int32_t)(qb * p.n), 0);
+            for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
+                if (!(ok = mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
+                const uint32_t bar = smem_u32(&bars->kv_full[stage]);
+                const uint32_t dst = base + p.off_kv + stage * p.kv_stage_bytes;
+                mbar_arrive_expect_tx(bar, kMqaBlockKv * p.head_dim + (SCALED ? kMqaBlockKv * 4u : 0u));
+                tma_load_2d(&tm_kv, bar, dst, 0, (int32_t)(kb * kMqaBlockKv));
+                if (SCALED) tma_load_2d(&tm_kvsf, bar, dst + p.kv_sf_off, (int32_t)(kb * kMqaBlockKv), 0);
+                if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ===================================================== MMA issuer
+        uint32_t stage = 0, phase = 0, qcount = 0, acount = 0;
+        const uint32_t idesc = SCALED ? make_idesc_bs(0u, kMqaBlockKv, p.n) : make_idesc_f8(kMqaBlockKv, p.n);
+        bool ok = true;
+        for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
+            const QRange r = q_block_range(p, qb);
+            if (r.b1 <= r.b0) continue;
+            const uint32_t qs = qcount & 1u, qphase = (qcount >> 1) & 1u;
+            ++qcount;
+            if (!(ok = mbar_wait(smem_u32(&bars->q_full[qs]), qphase, wc, kWaitFull))) break;
+            if (SCALED && !(ok = mbar_wait(smem_u32(&bars->q_ready[qs]), qphase, wc, kWaitSfReady))) break;
+            tc_fence_after();
+            const uint32_t qaddr = base + p.off_q + qs * p.q_stage_bytes;
+            const uint64_t q_desc = make_smem_desc(qaddr, p.sbo, 0, p.layout);
+            if (SCALED) {
+                for (uint32_t c = 0; c < (p.n + 127u) / 128u; ++c)
+                    tc_cp_32x128b_warpx4(tmem + kMqaSfbCol + c * 4u, make_sf_desc(qaddr + p.q_sf_off + c * 512u));
+            }
+            for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
+                const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
+                ++acount;
+                if (!(ok = mbar_wait(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull))) break;
+                if (SCALED && !(ok = mbar_wait(smem_u32(&bars->kv_ready[stage]), phase, wc, kWaitSfReady))) break;
+                if (!(ok = mbar_wait(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
+                tc_fence_after();
+                const uint32_t kaddr = base + p.off_kv + stage * p.kv_stage_bytes;
+                const uint64_t kv_desc = make_smem_desc(kaddr, p.sbo, 0, p.layout);
+                if (SCALED) tc_cp_32x128b_warpx4(tmem + kMqaSfaCol, make_sf_desc(kaddr + p.kv_sf_off));
+                const uint32_t d_tmem = tmem + as * acc_stride;
+                for (uint32_t k = 0; k < num_mma; ++k) {
+                    if (SCALED)
+                        tc_mma_mxf8(d_tmem, kv_desc + 2u * k, q_desc + 2u * k, idesc_with_sf_ids(idesc, k, k), k != 0u,
+                                    tmem + kMqaSfaCol, tmem + kMqaSfbCol);
+                    else
+                        tc_mma_f8(d_tmem, kv_desc + 2u * k, q_desc + 2u * k, idesc, k != 0u);
+                }
+                tc_commit(smem_u32(&bars->kv_empty[stage]));
+                tc_commit(smem_u32(&bars->tmem_full[as]));
+                if (kb + 1 == r.b1) tc_commit(smem_u32(&bars->q_empty[qs]));
+                if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp == 2 && SCALED) {
+        // ===================================================== SF transposer (ue8m0 contract)
+        uint32_t stage = 0, phase = 0, qcount = 0;
+        bool ok = true;
+        auto transpose128 = [&](uint32_t* q) {
+            const uint32_t v0 = q[lane], v1 = q[32 + lane], v2 = q[64 + lane], v3 = q[96 + lane];
+            __syncwarp();
+            *reinterpret_cast<uint4*>(q + lane * 4u) = make_uint4(v0, v1, v2, v3);
+        };
+        for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
+            const QRange r = q_block_range(p, qb);
+            if (r.b1 <= r.b0) continue;
+            const uint32_t qs = qcount & 1u, qphase = (qcount >> 1) & 1u;
+            ++qcount;
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->q_full[qs]), qphase, wc, kWaitFull));
+            if (!ok) break;
+            uint32_t* qsf = reinterpret_cast<uint32_t*>(base_ptr + p.off_q + qs * p.q_stage_bytes + p.q_sf_off);
+            for (uint32_t c = 0; c < (p.n + 127u) / 128u; ++c) transpose128(qsf + c * 128u);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->q_ready[qs]));
+            for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull));
+                if (!ok) break;
+                transpose128(reinterpret_cast<uint32_t*>(base_ptr + p.off_kv + stage * p.kv_stage_bytes + p.kv_sf_off));
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->kv_ready[stage]));
+                if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp >= 4) {
+        // ===================================================== epilogue (2 warpgroups)
+        const uint32_t et = threadIdx.x - 128u;       // 0..255
+        const uint32_t wg = et >> 7;                  // which half of the query block
+        const uint32_t quarter = warp & 3u;           // TMEM lane quarter of this warp
+        const uint32_t q_per_wg = p.block_q >> 1;
+        uint32_t qcount = 0, acount = 0;
+        bool ok = true;
+        for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
+            const QRange r = q_block_range(p, qb);
+            if (r.b1 <= r.b0) continue;
+            const uint32_t wb = qcount & 1u, wphase = (qcount >> 1) & 1u;
+            float* w = w_smem + wb * p.n;
+            ++qcount;
+            if (et < p.n) {
+                const uint32_t q = qb * p.block_q + et / p.num_heads;
+                float v = 0.f;
+                if (q < p.num_tokens) {
+                    const size_t idx = (size_t)q * p.num_heads + et % p.num_heads;
+                    v = SCALED ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.weights)[idx])
+                               : reinterpret_cast<const float*>(p.weights)[idx];
+                }
+                w[et] = v;
+            }
+            // The two buffers alternate, and no warp can run more than one query block ahead of
+            // the slowest one (it waits here), so a buffer is never rewritten while still read.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->w_full[wb]));
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->w_full[wb]), wphase, wc, kWaitPeer));
+            if (!ok) break;
+            for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
+                const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
+                ++acount;
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t j = kb * kMqaBlockKv + quarter * 32u + lane;
+                float scale = 1.f;
+                if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
+                const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride;
+                for (uint32_t qi = 0; qi < q_per_wg; ++qi) {
+                    const uint32_t ql = wg * q_per_wg + qi;          // query within the block
+                    const uint32_t col0 = ql * p.num_heads;
+                    uint64_t acc0 = 0, acc1 = 0;                     // two f32x2 accumulators
+                    for (uint32_t c = 0; c < p.num_heads; c += 32u) {
+                        uint32_t v[32];
+                        __syncwarp();
+                        tmem_ld_x32(taddr + col0 + c, v);
+                        tmem_ld_wait();
+                        if (qi + 1 == q_per_wg && c + 32u == p.num_heads) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+                        }
+                        const float4* w4 = reinterpret_cast<const float4*>(w + col0 + c);
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) {
+                            const float4 ww = w4[i];
+                            const float x0 = fmaxf(__uint_as_float(v[4 * i]), 0.f), x1 = fmaxf(__uint_as_float(v[4 * i + 1]), 0.f);
+                            const float x2 = fmaxf(__uint_as_float(v[4 * i + 2]), 0.f), x3 = fmaxf(__uint_as_float(v[4 * i + 3]), 0.f);
+                            acc0 = fma_f32x2(pack_f32x2(x0, x1), pack_f32x2(ww.x, ww.y), acc0);
+                            acc1 = fma_f32x2(pack_f32x2(x2, x3), pack_f32x2(ww.z, ww.w), acc1);
+                        }
+                    }
+                    const uint32_t q = qb * p.block_q + ql;
+                    if (q < p.num_tokens) {
+                        const uint32_t s = __ldg(p.ks + q), e = min(__ldg(p.ke + q), p.num_kv);
+                        if (j >= s && j < e) {
+                            const float val = (sum_f32x2(acc0) + sum_f32x2(acc1)) * scale;
+                            const size_t o = (size_t)q * p.logits_stride + (j - s);
+                            if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
+                            else reinterpret_cast<float*>(p.logits)[o] = val;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// ============================================================================ host side
+static int32_t check_mqa_common(uint32_t num_tokens, uint32_t num_kv, uint32_t num_heads, uint32_t head_dim,
+                                uint32_t logits_stride, const void* ks, const void* ke, const void* w, const void* logits) {
+    if (!ks || !ke || !w || !logits) return fail(DG_ERR_INVALID_ARG, "mqa_logits: null buffer");
+    if (num_tokens == 0 || num_kv == 0) return fail(DG_ERR_INVALID_ARG, "mqa_logits: empty problem");
+    // deepgemm/src/api.rs:1639-1650
+    if (head_dim % 32 != 0 || head_dim > 128 || head_dim == 96 || head_dim == 0)
+        return fail(DG_ERR_INVALID_ARG, "head_dim must be 32/64/128");
+    if (num_heads % 4 != 0 || num_heads > 256 || num_heads == 0)
+        return fail(DG_ERR_INVALID_ARG, "num_heads must be a multiple of 4 (<= 256)");
+    if (logits_stride == 0) return fail(DG_ERR_INVALID_ARG, "mqa_logits: logits_stride must be positive");
+    return DG_OK;
+}
+
+template <bool SCALED>
+static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint32_t q_sf_cols, const uint32_t* kv_sf,
+                       uint32_t kv_sf_cols, const float* kv_scale, const void* weights, const uint32_t* ks,
+                       const uint32_t* ke, uint32_t num_tokens, uint32_t num_kv, uint32_t num_heads, uint32_t head_dim,
+                       void* logits, uint32_t logits_stride, void* stream) {
+    // Tiling: the query block holds an even number of queries so that the two epilogue
+    // warpgroups split it; heads must come in whole 32-column TMEM loads.
+    const uint32_t max_n = SCALED ? 192u : 256u;
+    if (num_heads % 32 != 0 || 2 * num_heads > max_n)
+        return fail(DG_ERR_UNSUPPORTED, "mqa_logits: this build handles num_heads in {32, 64%s}, got %u",
+                    SCALED ? ", 96" : ", 96, 128", num_heads);
+    const DeviceInfo* dev;
+    int32_t st = current_device(&dev);
+    if (st != DG_OK) return st;
+    MqaParams p{};
+    p.num_tokens = num_tokens; p.num_kv = num_kv; p.num_heads = num_heads; p.head_dim = head_dim;
+    p.block_q = 2 * (max_n / 2 / num_heads);
+    p.n = p.block_q * num_heads;
+    p.num_q_blocks = ceil_div(num_tokens, p.block_q);
+    p.sbo = 8 * head_dim;
+    p.layout = head_dim == 128 ? 2u : head_dim == 64 ? 4u : 6u;
+    const CUtensorMapSwizzle sw = head_dim == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : head_dim == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    p.off_w = 1024;
+    p.off_q = 1024 + 2048;
+    p.q_sf_off = align_up(p.n * head_dim, 1024);
+    p.q_stage_bytes = p.q_sf_off + (SCALED ? 1024u : 0u);
+    p.off_kv = p.off_q + 2 * p.q_stage_bytes;
+    p.kv_sf_off = kMqaBlockKv * head_dim;
+    p.kv_stage_bytes = align_up(p.kv_sf_off + (SCALED ? 512u : 0u), 1024);
+    const uint32_t budget = (uint32_t)dev->smem_optin - 1024u;
+    uint32_t stages = (budget - p.off_kv) / p.kv_stage_bytes;
+    if (stages > kMqaMaxKvStages) stages = kMqaMaxKvStages;
+    if (stages < 2) return fail(DG_ERR_RUNTIME, "mqa_logits: shared memory budget too small");
+    p.kv_stages = stages;
+    const uint32_t smem_bytes = 1024u + p.off_kv + stages * p.kv_stage_bytes;
+    p.logits_stride = logits_stride;
+    p.ks = ks; p.ke = ke; p.kv_scale = kv_scale; p.weights = weights; p.logits = logits;
+    p.status = dev->status;
+
+    CUtensorMap tq, tkv, tqsf, tkvsf;
+    if ((st = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, head_dim, (uint64_t)num_tokens * num_heads, head_dim,
+                           head_dim, p.n, sw, "q")) != DG_OK) return st;
+    if ((st = make_tmap_2d(&tkv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, kv, head_dim, num_kv, head_dim, head_dim, kMqaBlockKv,
+                           sw, "kv")) != DG_OK) return st;
+    if (SCALED) {
+        if ((st = make_tmap_2d(&tqsf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, q_sf, q_sf_cols, 1, (uint64_t)q_sf_cols * 4, p.n, 1,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, "q_sf")) != DG_OK) return st;
+        if ((st = make_tmap_2d(&tkvsf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, kv_sf, kv_sf_cols, 1, (uint64_t)kv_sf_cols * 4,
+                               kMqaBlockKv, 1, CU_TENSOR_MAP_SWIZZLE_NONE, "kv_sf")) != DG_OK) return st;
+    } else {
+        tqsf = tq; tkvsf = tkv;
+    }
+    auto* fn = mqa_logits_kernel<SCALED>;
+    DG_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    uint32_t grid = (uint32_t)dev->sm_count;
+    if (p.num_q_blocks < grid) grid = p.num_q_blocks;
+    fn<<<grid, kMqaThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tq, tkv, tqsf, tkvsf, p);
+    DG_CUDA_CHECK(cudaGetLastError());
+    return DG_OK;
+}
+
+}  // namespace dg
+
+extern "C" {
+
+int32_t dg_mqa_logits_f32(const void* q, const void* kv, const float* kv_scale, const float* weights,
+                          const uint32_t* cu_k_start, const uint32_t* cu_k_end, uint32_t num_tokens,
+                          uint32_t num_kv_tokens, uint32_t num_heads, uint32_t head_dim, float* logits,
+                          uint32_t logits_stride, void* stream) {
+    if (!q || !kv || !kv_scale) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: null buffer");
+    int32_t st = dg::check_mqa_common(num_tokens, num_kv_tokens, num_heads, head_dim, logits_stride, cu_k_start, cu_k_end,
+                                      weights, logits);
+    if (st != DG_OK) return st;
+    return dg::run_mqa<false>(q, kv, nullptr, 0, nullptr, 0, kv_scale, weights, cu_k_start, cu_k_end, num_tokens,
+                              num_kv_tokens, num_heads, head_dim, logits, logits_stride, stream);
+}
+
+int32_t dg_mqa_logits(const dg_operand_t* q, const dg_operand_t* kv, const void* weights_bf16, const uint32_t* cu_k_start,
+                      const uint32_t* cu_k_end, uint32_t num_tokens, uint32_t num_kv_tokens, uint32_t num_heads,
+                      uint32_t head_dim, void* logits_bf16, uint32_t logits_stride, void* stream) {
+    if (!q || !kv || !q->data || !kv->data) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: null operand");
+    if (q->dtype != kv->dtype) return dg::fail(DG_ERR_INVALID_ARG, "Q/KV dtype mismatch");
+    int32_t st = dg::check_mqa_common(num_tokens, num_kv_tokens, num_heads, head_dim, logits_stride, cu_k_start, cu_k_end,
+                                      weights_bf16, logits_bf16);
+    if (st != DG_OK) return st;
+    if (q->dtype == DG_FP4) {
+        if (head_dim != 64 && head_dim != 128) return dg::fail(DG_ERR_INVALID_ARG, "MXFP4 requires head_dim 64/128");
+        return dg::fail(DG_ERR_UNSUPPORTED, "mqa_logits: the MXFP4 flavour is not built");
+    }
+    if (q->dtype != DG_FP8) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q/kv must be FP8 or FP4");
+    if (!q->sf.data || !kv->sf.data) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q and kv require scale factors");
+    if (q->sf.gran != 32 || kv->sf.gran != 32) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: scale granularity must be 32");
+    if (q->rows != num_tokens * num_heads || q->k != head_dim || kv->rows != num_kv_tokens || kv->k != head_dim)
+        return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q must be [num_tokens*num_heads, head_dim] and kv [num_kv_tokens, head_dim]");
+    if (q->sf.cols < dg::align_up(q->rows, 4) || kv->sf.cols < dg::align_up(kv->rows, 4) || q->sf.rows < 1 || kv->sf.rows < 1)
+        return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: scale-factor tensors too small");
+    return dg::run_mqa<true>(q->data, kv->data, q->sf.data, q->sf.cols, kv->sf.data, kv->sf.cols, nullptr, weights_bf16,
+                             cu_k_start, cu_k_end, num_tokens, num_kv_tokens, num_heads, head_dim, logits_bf16,
+                             logits_stride, stream);
+}
+
+}  // extern "C"

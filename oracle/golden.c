@@ -92,6 +92,13 @@ uint8_t dgo_quant_e4m3(float v) {
     return (uint8_t)((signbit(v) ? 0x80 : 0) | code);
 }
 
+/* quant_e4m3 over an array (input generator for raw-E4M3 tensors such as the MQA query). */
+void dgo_quant_e4m3_vec(const float* x, size_t n, uint8_t* out) {
+    grids_init();
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) out[i] = dgo_quant_e4m3(x[i]);
+}
+
 /* golden.rs:193-202 */
 uint8_t dgo_quant_e2m1(float v) {
     int code = rne_on_grid((double)fabsf(v), g_e2m1_grid, 8);

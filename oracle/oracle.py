@@ -50,6 +50,7 @@ def lib():
         L.dgo_tma_aligned.argtypes = [u32, u32]
         L.dgo_f32_to_bf16_bits.restype = C.c_uint16
         L.dgo_f32_to_bf16_bits.argtypes = [C.c_float]
+        L.dgo_quant_e4m3_vec.argtypes = [f32p, C.c_size_t, u8p]
         L.dgo_transform_sf_host.argtypes = [f32p, u32, u32, u32p]
         L.dgo_quant_mx_host.argtypes = [f32p, u32, u32, C.c_int, u32, u8p, u32p]
         L.dgo_quant_fp8_block128_host.argtypes = [f32p, u32, u32, u8p, u32p]
@@ -200,6 +201,14 @@ def f32_to_bf16_bits_np(x):
     b = _c(x, np.float32).view(np.uint32).astype(np.uint64)
     r = 0x7FFF + ((b >> 16) & 1)
     return ((((b + r) >> 16) & 0x7FFF) | ((b >> 31) << 15)).astype(np.uint16)
+
+
+def quant_e4m3_array(x):
+    """Element-wise quant_e4m3 (golden.rs:180-189): f32 array -> E4M3 bytes of the same shape."""
+    x = _c(x, np.float32)
+    out = np.zeros(x.shape, dtype=np.uint8)
+    lib().dgo_quant_e4m3_vec(_p(x, C.c_float), x.size, _p(out, C.c_uint8))
+    return out
 
 
 def e4m3_table():
