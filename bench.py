@@ -1,0 +1,370 @@
+#!/usr/bin/env python
+"""Benchmark of the block-scaled GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-extra]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Headline workload (every N): the grouped-MoE prefill step of the benchmark configuration --
+256 experts, top-8 routing, 16384 tokens per GPU, hidden K = 7168, gate+up N = 4096, FP8 E4M3
+with UE8M0 scales at granularity 128.  Experts are sharded over the N GPUs (256/N each, weights
+resident); one step = routing plan -> dispatch (all-to-all over NCCL when N > 1) -> 128-row
+padded contiguous layout -> m_grouped_fp8_gemm_nt_contiguous -> return all-to-all -> top-k
+combine.  `value` = valid-row FLOPs of all ranks / max-over-ranks device time (TFLOPS, weak
+scaling: per-GPU work is fixed).  At N = 1 the same line carries, under "extra", the dense FP8 /
+FP4 GEMMs, the masked grouped GEMM, mqa_logits and quant_mx of the other configurations.
+
+`--impl reference` times the reference's CPU golden model of the same path (the C
+restatement under oracle/, all host threads) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "deepgemm-rs_b200"))
+
+CFG = dict(num_experts=256, topk=8, tokens_per_gpu=16384, hidden=7168, n_out=4096, gran=128)
+METRIC = "grouped-MoE FP8 GEMM throughput (m_grouped_fp8_gemm_nt_contiguous, expert-parallel)"
+NOMINAL_FP8_TFLOPS = 4500.0
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled during the timed region."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------ reference arm
+def cpu_gemm_sample(rows, cols, k, seed=0):
+    """Times the oracle's gemm_ref (quantised inputs prepared outside the timed region) on a
+    rows x cols x k sample of the grouped workload; returns (TFLOPS, seconds, threads)."""
+    import numpy as np
+    import oracle as o
+    rng = np.random.default_rng(seed)
+    xa = rng.standard_normal((rows, k)).astype(np.float32)
+    xb = rng.standard_normal((cols, k)).astype(np.float32)
+    qa, sa = o.quant_mx_host(xa, o.FP8, 128)
+    qb, sb = o.quant_fp8_block128_host(xb) if cols % 128 == 0 else o.quant_mx_host(xb, o.FP8, 128)
+    a, b = o.GoldenOperand(qa, sa, o.FP8, 128, k), o.GoldenOperand(qb, sb, o.FP8, 128, k)
+    t0 = time.perf_counter()
+    o.gemm_ref(a, b, m=rows, n=cols)
+    dt = time.perf_counter() - t0
+    return 2.0 * rows * cols * k / dt / 1e12, dt, os.cpu_count()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows, cols, k = 512, 512, CFG["hidden"]
+    for _ in range(args.warmup):
+        cpu_gemm_sample(rows, cols, k)
+    t0 = time.perf_counter()
+    for s in range(args.steps):
+        cpu_gemm_sample(rows, cols, k, seed=s)
+    # only the gemm_ref calls count: re-time them precisely
+    times = [cpu_gemm_sample(rows, cols, k, seed=s)[1] for s in range(args.steps)]
+    dt = sum(times) / len(times)
+    val = 2.0 * rows * cols * k / dt / 1e12
+    sample = f"{rows} token rows x {cols} weight rows x K={k} of one expert (gemm_ref, f64 accumulation), per step"
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOPS", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp8_e4m3 (f64 accumulate on CPU)", "data": "synthetic", "config": workload_config(args.gpus),
+            "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(n):
+    c = dict(CFG)
+    return {"workload": "moe_prefill_m_grouped_fp8_gemm_nt_contiguous", "experts": c["num_experts"], "topk": c["topk"],
+            "tokens_per_gpu": c["tokens_per_gpu"], "hidden_k": c["hidden"], "n": c["n_out"], "sf_granularity": c["gran"],
+            "experts_per_gpu": c["num_experts"] // n, "parallelism": f"ep{n}",
+            "l2": "inputs (>= 1 GB of weights touched per step) exceed the 126 MB L2; no flush needed"}
+
+
+# ------------------------------------------------------------------------------ our arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the additional single-GPU workloads")
+    ap.add_argument("--tokens", type=int, default=CFG["tokens_per_gpu"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    CFG["tokens_per_gpu"] = args.tokens
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    import deepgemm as dg
+    from deepgemm import moe, synth, _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
+    dg.device_check()
+    peaks, peak_kind = load_peaks()
+
+    E, topk, T, K, N = CFG["num_experts"], CFG["topk"], CFG["tokens_per_gpu"], CFG["hidden"], CFG["n_out"]
+    e_local = E // world
+    weights = synth.random_expert_weights(e_local, N, K, seed=1000 + rank, device=dev)
+    layer = moe.ExpertParallelMoE(weights, E, group)
+    gx = torch.Generator(device=dev).manual_seed(rank)
+    x_host = torch.empty((T, K), dtype=torch.float32).pin_memory()
+    x_dev = torch.randn((T, K), device=dev, generator=gx)
+    x_host.copy_(x_dev)
+    topk_idx, topk_w = synth.random_topk_routing(T, E, topk, seed=7 + rank, device=dev)
+    idx_host = topk_idx.cpu().pin_memory()
+    w_host = topk_w.cpu().pin_memory()
+    x8, x_sf = synth.quantised_tokens(x_dev)
+    out_host = torch.empty((T, N), dtype=torch.bfloat16).pin_memory()
+
+    gemm_events = []
+    orig_gemm = moe.m_grouped_gemm_nt_contiguous
+
+    def timed_gemm(*a, **kw):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        orig_gemm(*a, **kw)
+        e1.record()
+        gemm_events.append((e0, e1))
+
+    def step_resident():
+        return layer.forward(x8, x_sf, topk_idx, topk_w)
+
+    def step_e2e():
+        xd = x_host.to(dev, non_blocking=True)
+        idx = idx_host.to(dev, non_blocking=True)
+        w = w_host.to(dev, non_blocking=True)
+        c, sf = synth.quantised_tokens(xd)
+        out = layer.forward(c, sf, idx, w)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup, launches_of=None):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0 = _lib.launch_count()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() / steps, (_lib.launch_count() - c0)
+
+    # valid rows of all ranks = tokens * topk per rank (every copy is computed exactly once)
+    flops_per_step = 2.0 * T * topk * N * K * world
+
+    sampler = ClockSampler(local)
+    moe.m_grouped_gemm_nt_contiguous = timed_gemm
+    if rank == 0:
+        sampler.start()
+    ms_step, launches = timed(step_resident, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    dg.poll_device_status()
+    ev = gemm_events[-args.steps:]
+    gemm_ms = sum(a.elapsed_time(b) for a, b in ev) / len(ev)
+    moe.m_grouped_gemm_nt_contiguous = orig_gemm
+    ms_e2e, _ = timed(step_e2e, max(2, min(args.steps, 5)), 1)
+
+    value = flops_per_step / (ms_step * 1e-3) / 1e12
+    e2e_value = flops_per_step / (ms_e2e * 1e-3) / 1e12
+    gemm_tflops = 2.0 * T * topk * N * K / (gemm_ms * 1e-3) / 1e12       # this rank's launch
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
+        "data": "synthetic", "config": workload_config(world),
+        "e2e": {"value": e2e_value, "unit": "TFLOPS", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": x_host.numel() * 4 + idx_host.numel() * 4 + w_host.numel() * 4,
+                "d2h_bytes_per_step": out_host.numel() * 2,
+                "path": "pinned host f32 tokens -> quant_mx -> expert-parallel grouped GEMM -> combine -> pinned host bf16"},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "tensor", "kernel": "gemm_kernel<fp8, contiguous>", "achieved": gemm_tflops, "peak": fp8_peak,
+                     "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": None,
+                     "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_kind}); FP8 runs at twice the bf16 rate",
+                     "frac_of_nominal_4500": gemm_tflops / NOMINAL_FP8_TFLOPS, "launch_ms": gemm_ms,
+                     "algorithmic_flops_per_launch": 2.0 * T * topk * N * K},
+    }
+    if rank == 0 and world == 1:
+        v, dt, cores = cpu_gemm_sample(1024, 1024, K)
+        line["cpu_baseline"] = {"value": v, "unit": "TFLOPS", "cores": cores, "kind": "port", "seconds": dt,
+                                "sample": f"1024 token rows x 1024 weight rows x K={K} of one expert through the oracle's gemm_ref"}
+        if not args.no_extra:
+            try:
+                line["extra"] = extra_workloads(torch, dg, synth, dev, peaks)
+            except Exception as ex:  # the headline number stands on its own
+                line["extra"] = {"error": repr(ex)}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def extra_workloads(torch, dg, synth, dev, peaks):
+    """Single-GPU numbers of the other benchmark configurations (CUDA events, >= 3 warm-ups,
+    inputs larger than L2 or rotated)."""
+    from deepgemm import Dtype, Operand, Output
+
+    def timeit(fn, iters=10, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    g = torch.Generator(device=dev).manual_seed(0)
+    res = {}
+
+    def dense(kind, m, n, k):
+        if kind == "fp8":
+            da, sa = dg.quant_mx(torch.randn((m, k), device=dev, generator=g), m, k, Dtype.Fp8, 128)
+            wb = torch.randn((-(-n // 128) * 128, k), device=dev, generator=g)
+            cb, sb = synth.block128_quant_fp8(wb) if k % 512 == 0 else (None, None)
+            if cb is None:
+                cb, sfb = dg.quant_mx(wb[:n], n, k, Dtype.Fp8, 128)
+            else:
+                from deepgemm import SfGran, SfTensor
+                sfb = SfTensor(k // 512, wb.shape[0], SfGran.G128, sb)
+            a, b = Operand.k_major(Dtype.Fp8, m, k, k, sa, da), Operand.k_major(Dtype.Fp8, n, k, k, sfb, cb)
+            peak = 2 * peaks["bf16_tflops"]
+        else:
+            da, sa = dg.quant_mx(torch.randn((m, k), device=dev, generator=g), m, k, Dtype.Fp4, 32)
+            db, sb = dg.quant_mx(torch.randn((n, k), device=dev, generator=g), n, k, Dtype.Fp4, 32)
+            a, b = Operand.k_major(Dtype.Fp4, m, k, k, sa, da), Operand.k_major(Dtype.Fp4, n, k, k, sb, db)
+            peak = 4 * peaks["bf16_tflops"]
+        out = Output(Dtype.Bf16, m, n, n, torch.empty((m, n), dtype=torch.bfloat16, device=dev))
+        ms = timeit(lambda: dg.gemm_nt(a, b, out))
+        tf = 2.0 * m * n * k / ms / 1e9
+        byts = (m * k + n * k) * (1 if kind == "fp8" else 0.5) + m * n * 2
+        return {"ms": ms, "tflops": tf, "frac_of_measured_tensor_peak": tf / peak, "hbm_gbs": byts / ms / 1e6,
+                "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
+
+    for m in (128, 4096):
+        for n, k in ((24576, 1536), (7168, 16384), (4096, 7168)):
+            res[f"fp8_gemm_nt_M{m}_N{n}_K{k}"] = dense("fp8", m, n, k)
+    res["fp4_gemm_nt_M8192_N8192_K8192"] = dense("fp4", 8192, 8192, 8192)
+    res["fp4_gemm_nt_M4096_N7168_K7168"] = dense("fp4", 4096, 7168, 7168)
+
+    # masked decode: 32 experts, expected_m 128, masked_m uniform in [0, 256]
+    G, max_m, n, k = 32, 256, 4096, 7168
+    w = synth.random_expert_weights(G, n, k, seed=5, device=dev)
+    da, sa = dg.quant_mx(torch.randn((G * max_m, k), device=dev, generator=g), G * max_m, k, Dtype.Fp8, 128)
+    a = Operand.k_major(Dtype.Fp8, max_m, k, k, sa, da)
+    masked = torch.randint(0, 257, (G,), device=dev, generator=g, dtype=torch.int32)
+    out = Output(Dtype.Bf16, max_m, n, n, torch.empty((G * max_m, n), dtype=torch.bfloat16, device=dev))
+    ms = timeit(lambda: dg.m_grouped_fp8_gemm_nt_masked(a, w, out, masked, G, 128))
+    sm = int(masked.sum().item())
+    byts = sm * k + G * n * k + sm * n * 2
+    res["m_grouped_fp8_gemm_nt_masked_G32"] = {"ms": ms, "sum_masked_m": sm, "tflops": 2.0 * sm * n * k / ms / 1e9,
+                                               "hbm_gbs": byts / ms / 1e6, "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
+
+    # mqa_logits, fp32 contract
+    T, S, H, D = 4096, 32768, 64, 128
+    q = torch.randn((T, H, D), device=dev, generator=g).to(torch.float8_e4m3fn).view(torch.uint8)
+    kvf = torch.randn((S, D), device=dev, generator=g)
+    scale = kvf.abs().amax(dim=1) / 448.0
+    kv = (kvf / scale[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+    wq = torch.randn((T, H), device=dev, generator=g)
+    ks = torch.zeros(T, dtype=torch.int32, device=dev)
+    ke = (S - T + torch.arange(T, device=dev) + 1).to(torch.int32)
+    logits = torch.empty((T, S), dtype=torch.float32, device=dev)
+    ms = timeit(lambda: dg.mqa_logits_f32(q, kv, scale, wq, ks, ke, T, S, H, D, logits, S), iters=5)
+    pairs = int(ke.sum().item())
+    res["mqa_logits_T4096_S32768_H64_D128"] = {"ms": ms, "tflops": 2.0 * H * D * pairs / ms / 1e9,
+                                               "frac_of_measured_tensor_peak": 2.0 * H * D * pairs / ms / 1e9 / (2 * peaks["bf16_tflops"])}
+
+    # quant_mx bandwidth
+    for (m, k, dt, gran, name) in ((16384, 7168, Dtype.Fp8, 128, "fp8_g128"), (16384, 7168, Dtype.Fp8, 32, "fp8_g32"),
+                                   (16384, 7168, Dtype.Fp4, 32, "fp4_g32"), (4096, 16384, Dtype.Fp8, 128, "fp8_g128")):
+        x = torch.randn((m, k), device=dev, generator=g)
+        ms = timeit(lambda: dg.quant_mx(x, m, k, dt, gran))
+        byts = 4 * m * k + (m * k if dt == Dtype.Fp8 else m * k // 2) + 4 * (-(-(k // gran) // 4)) * m
+        res[f"quant_mx_{name}_{m}x{k}"] = {"ms": ms, "gbs": byts / ms / 1e6, "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
+    dg.poll_device_status()
+    return res
+
+
+if __name__ == "__main__":
+    main()

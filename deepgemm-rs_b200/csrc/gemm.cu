@@ -61,6 +61,7 @@ struct GemmParams {
     void* d;
     const int32_t* layout; // m_indices (contiguous) or masked_m (masked)
     uint32_t* status;
+    unsigned long long* trace;  // debug: per-k-block clock64 stamps of CTA 0's first tile (or null)
 };
 
 struct Tile {
@@ -182,8 +183,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
     auto stage_addr = [&](uint32_t s) { return stages_base + s * p.stage_bytes; };
 
-    if (warp == 0 && lane == 0) {
-        // ===================================================== TMA producer
+    if (warp == 0) {
+        // ===================================================== TMA producer (warp-converged, one lane issues)
         Scheduler<GTYPE> sched;
         Tile t;
         uint32_t stage = 0, phase = 0;
@@ -191,11 +192,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
             for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
-                if (!(ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
+                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
+                if (p.trace && blockIdx.x == 0 && kb < 256 && sched.next_id == gridDim.x && lane == 0) p.trace[kb] = clock64();
                 const uint32_t bar = smem_u32(&bars->full[stage]);
                 const uint32_t sa = stage_addr(stage);
                 const bool ld_sfa = kHasSf && (kb % p.sfa_period == 0);
                 const bool ld_sfb = kHasSf && (kb % p.sfb_period == 0);
+                const int32_t kx = (int32_t)(kb * (KIND == kBf16 ? 64u : 128u));
+                if (elect_one()) {
                 // Scale factors go first and complete on their own barrier, so that their
                 // transposition overlaps the (much larger) A/B transfer.
                 if (ld_sfa || ld_sfb) {
@@ -205,15 +209,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     if (ld_sfb) tma_load_2d(&tm_sfb, sbar, sa + p.off_sfb, (int32_t)t.b_row, (int32_t)((kb / p.sfb_period) * p.sf_sub));
                 }
                 mbar_arrive_expect_tx(bar, p.tx_ab);
-                // Inner coordinate in elements: 128 bytes per k-block (128 FP8, 256 FP4 = 128 B, 64 BF16).
-                const int32_t kx = (int32_t)(kb * (KIND == kBf16 ? 64u : 128u));
+                // Inner coordinate kx in elements: 128 bytes per k-block (128 FP8, 256 FP4 = 128 B, 64 BF16).
                 tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
                 tma_load_2d(&tm_b, bar, sa + p.off_b, kx, (int32_t)t.b_row);
+                }
+                __syncwarp();
+                if (p.trace && blockIdx.x == 0 && kb < 256 && sched.next_id == gridDim.x && lane == 0) p.trace[256 + kb] = clock64();
                 if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ===================================================== MMA issuer
+    } else if (warp == 1) {
+        // ===================================================== MMA issuer (warp-converged, one lane issues)
         Scheduler<GTYPE> sched;
         Tile t;
         uint32_t stage = 0, phase = 0, tile_count = 0;
@@ -225,17 +231,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             if (t.skip) continue;
             const uint32_t as = tile_count & 1u, aphase = (tile_count >> 1) & 1u;
             ++tile_count;
-            if (!(ok = mbar_wait(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
+            if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem + as * kAccStageCols;
             for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
-                if (!(ok = mbar_wait(smem_u32(&bars->full[stage]), phase, wc, kWaitFull))) break;
+                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->full[stage]), phase, wc, kWaitFull))) break;
                 if (kHasSf && (kb % p.sfa_period == 0 || kb % p.sfb_period == 0)) {
-                    if (!(ok = mbar_wait(smem_u32(&bars->sf_ready[stage]), (sf_bits >> stage) & 1u, wc, kWaitSfReady))) break;
+                    if (!(ok = DG_WARP_WAIT(smem_u32(&bars->sf_ready[stage]), (sf_bits >> stage) & 1u, wc, kWaitSfReady))) break;
                     sf_bits ^= 1u << stage;
                 }
                 tc_fence_after();
+                if (p.trace && blockIdx.x == 0 && kb < 256 && sched.next_id == gridDim.x && lane == 0) p.trace[512 + kb] = clock64();
                 const uint32_t sa = stage_addr(stage);
+                if (elect_one()) {
                 if (kHasSf) {
                     if (kb % p.sfa_period == 0) {
                         for (uint32_t j = 0; j < p.sf_sub; ++j)
@@ -272,6 +280,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 tc_commit(smem_u32(&bars->empty[stage]));
                 if (kb + 1 == p.num_k_blocks) tc_commit(smem_u32(&bars->tmem_full[as]));
+                }
+                __syncwarp();
+                if (p.trace && blockIdx.x == 0 && kb < 256 && sched.next_id == gridDim.x && lane == 0) p.trace[768 + kb] = clock64();
                 if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -423,6 +434,8 @@ struct Plan {
     uint32_t num_tiles;
 };
 
+static unsigned long long* g_trace = nullptr;  // set by dg_debug_set_trace (development aid)
+
 static uint32_t env_u32(const char* name, uint32_t dflt) {
     const char* v = getenv(name);
     return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
@@ -497,6 +510,7 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     }
     plan->grid = grid ? grid : 1;
     p.status = dev->status;
+    p.trace = g_trace;
     if (env_u32("DG_PRINT_CONFIGS", 0))
         fprintf(stderr, "[deepgemm_b200] kind=%d gtype=%d m=%u n=%u k=%u groups=%u -> block 128x%ux%u stages=%u smem=%u grid=%u tiles=%u\n",
                 kind, gtype, m, n, k, num_groups, p.block_n, block_k, stages, plan->smem_bytes, plan->grid, plan->num_tiles);
@@ -515,6 +529,7 @@ static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap
         configured[dev & 63] = plan.smem_bytes;
     }
     fn<<<plan.grid, 256, plan.smem_bytes, s>>>(ta, tb, tsa, tsb, plan.p);
+    dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;
 }
@@ -686,6 +701,11 @@ DG_TYPED_GROUPED(fp8, DG_FP8)
 DG_TYPED_GROUPED(fp4, DG_FP4)
 DG_TYPED_GROUPED(bf16, DG_BF16)
 #undef DG_TYPED_GROUPED
+
+// Development aid, not part of the public header: a device buffer of 1024 u64 that receives
+// clock64 stamps of CTA 0's first tile (producer: stage free / loads issued; MMA issuer:
+// stage full / MMAs issued), or NULL to switch tracing off.
+__attribute__((visibility("default"))) void dg_debug_set_trace(void* buf) { dg::g_trace = static_cast<unsigned long long*>(buf); }
 
 int32_t dg_get_gemm_config(int32_t dtype, int32_t kind, uint32_t m, uint32_t n, uint32_t k, uint32_t num_groups,
                            dg_gemm_config_t* cfg) {

@@ -3,6 +3,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <atomic>
 #include <mutex>
 
 namespace dg {
@@ -16,6 +17,9 @@ int32_t fail(int32_t code, const char* fmt, ...) {
     va_end(ap);
     return code;
 }
+
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 static std::mutex g_mu;
 static DeviceInfo g_dev[64];
@@ -115,6 +119,8 @@ int32_t dg_poll_device_status(void* stream) {
     }
     return DG_OK;
 }
+
+unsigned long long dg_launch_count(void) { return dg::g_launches.load(); }
 
 void dg_sf_shape(uint32_t mn, uint32_t k, uint32_t gran, uint32_t* rows, uint32_t* cols) {
     if (rows) *rows = gran ? dg::ceil_div(k, gran * 4) : 0;

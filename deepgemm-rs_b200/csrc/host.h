@@ -44,6 +44,9 @@ int32_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, uint32_t elem_byt
                      uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner,
                      uint32_t box_outer, CUtensorMapSwizzle swizzle, const char* what);
 
+// Counts kernel launches made by this library (dg_launch_count reports it).
+void note_launch();
+
 inline uint32_t ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
 inline uint32_t align_up(uint32_t a, uint32_t b) { return ceil_div(a, b) * b; }
 

@@ -145,8 +145,8 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t acc_stride = SCALED ? 192u : 256u;
     const uint32_t num_mma = p.head_dim / 32u;
 
-    if (warp == 0 && lane == 0) {
-        // ===================================================== producer
+    if (warp == 0) {
+        // ===================================================== producer (warp-converged, one lane issues)
         uint32_t stage = 0, phase = 0, qcount = 0;
         bool ok = true;
         for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
@@ -154,24 +154,30 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (r.b1 <= r.b0) continue;
             const uint32_t qs = qcount & 1u, qphase = (qcount >> 1) & 1u;
             ++qcount;
-            if (!(ok = mbar_wait(smem_u32(&bars->q_empty[qs]), qphase ^ 1u, wc, kWaitEmpty))) break;
+            if (!(ok = DG_WARP_WAIT(smem_u32(&bars->q_empty[qs]), qphase ^ 1u, wc, kWaitEmpty))) break;
             const uint32_t qbar = smem_u32(&bars->q_full[qs]);
             const uint32_t qdst = base + p.off_q + qs * p.q_stage_bytes;
-            mbar_arrive_expect_tx(qbar, p.n * p.head_dim + (SCALED ? p.n * 4u : 0u));
-            tma_load_2d(&tm_q, qbar, qdst, 0, (int32_t)(qb * p.n));
-            if (SCALED) tma_load_2d(&tm_qsf, qbar, qdst + p.q_sf_off, (int32_t)(qb * p.n), 0);
+            if (elect_one()) {
+                mbar_arrive_expect_tx(qbar, p.n * p.head_dim + (SCALED ? p.n * 4u : 0u));
+                tma_load_2d(&tm_q, qbar, qdst, 0, (int32_t)(qb * p.n));
+                if (SCALED) tma_load_2d(&tm_qsf, qbar, qdst + p.q_sf_off, (int32_t)(qb * p.n), 0);
+            }
+            __syncwarp();
             for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
-                if (!(ok = mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
+                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
                 const uint32_t bar = smem_u32(&bars->kv_full[stage]);
                 const uint32_t dst = base + p.off_kv + stage * p.kv_stage_bytes;
-                mbar_arrive_expect_tx(bar, kMqaBlockKv * p.head_dim + (SCALED ? kMqaBlockKv * 4u : 0u));
-                tma_load_2d(&tm_kv, bar, dst, 0, (int32_t)(kb * kMqaBlockKv));
-                if (SCALED) tma_load_2d(&tm_kvsf, bar, dst + p.kv_sf_off, (int32_t)(kb * kMqaBlockKv), 0);
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(bar, kMqaBlockKv * p.head_dim + (SCALED ? kMqaBlockKv * 4u : 0u));
+                    tma_load_2d(&tm_kv, bar, dst, 0, (int32_t)(kb * kMqaBlockKv));
+                    if (SCALED) tma_load_2d(&tm_kvsf, bar, dst + p.kv_sf_off, (int32_t)(kb * kMqaBlockKv), 0);
+                }
+                __syncwarp();
                 if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ===================================================== MMA issuer
+    } else if (warp == 1) {
+        // ===================================================== MMA issuer (warp-converged, one lane issues)
         uint32_t stage = 0, phase = 0, qcount = 0, acount = 0;
         const uint32_t idesc = SCALED ? make_idesc_bs(0u, kMqaBlockKv, p.n) : make_idesc_f8(kMqaBlockKv, p.n);
         bool ok = true;
@@ -180,26 +186,30 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (r.b1 <= r.b0) continue;
             const uint32_t qs = qcount & 1u, qphase = (qcount >> 1) & 1u;
             ++qcount;
-            if (!(ok = mbar_wait(smem_u32(&bars->q_full[qs]), qphase, wc, kWaitFull))) break;
-            if (SCALED && !(ok = mbar_wait(smem_u32(&bars->q_ready[qs]), qphase, wc, kWaitSfReady))) break;
+            if (!(ok = DG_WARP_WAIT(smem_u32(&bars->q_full[qs]), qphase, wc, kWaitFull))) break;
+            if (SCALED && !(ok = DG_WARP_WAIT(smem_u32(&bars->q_ready[qs]), qphase, wc, kWaitSfReady))) break;
             tc_fence_after();
             const uint32_t qaddr = base + p.off_q + qs * p.q_stage_bytes;
             const uint64_t q_desc = make_smem_desc(qaddr, p.sbo, 0, p.layout);
             if (SCALED) {
-                for (uint32_t c = 0; c < (p.n + 127u) / 128u; ++c)
-                    tc_cp_32x128b_warpx4(tmem + kMqaSfbCol + c * 4u, make_sf_desc(qaddr + p.q_sf_off + c * 512u));
+                if (elect_one()) {
+                    for (uint32_t c = 0; c < (p.n + 127u) / 128u; ++c)
+                        tc_cp_32x128b_warpx4(tmem + kMqaSfbCol + c * 4u, make_sf_desc(qaddr + p.q_sf_off + c * 512u));
+                }
+                __syncwarp();
             }
             for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
                 const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
                 ++acount;
-                if (!(ok = mbar_wait(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull))) break;
-                if (SCALED && !(ok = mbar_wait(smem_u32(&bars->kv_ready[stage]), phase, wc, kWaitSfReady))) break;
-                if (!(ok = mbar_wait(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
+                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull))) break;
+                if (SCALED && !(ok = DG_WARP_WAIT(smem_u32(&bars->kv_ready[stage]), phase, wc, kWaitSfReady))) break;
+                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
                 tc_fence_after();
                 const uint32_t kaddr = base + p.off_kv + stage * p.kv_stage_bytes;
                 const uint64_t kv_desc = make_smem_desc(kaddr, p.sbo, 0, p.layout);
-                if (SCALED) tc_cp_32x128b_warpx4(tmem + kMqaSfaCol, make_sf_desc(kaddr + p.kv_sf_off));
                 const uint32_t d_tmem = tmem + as * acc_stride;
+                if (elect_one()) {
+                if (SCALED) tc_cp_32x128b_warpx4(tmem + kMqaSfaCol, make_sf_desc(kaddr + p.kv_sf_off));
                 for (uint32_t k = 0; k < num_mma; ++k) {
                     if (SCALED)
                         tc_mma_mxf8(d_tmem, kv_desc + 2u * k, q_desc + 2u * k, idesc_with_sf_ids(idesc, k, k), k != 0u,
@@ -210,6 +220,8 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tc_commit(smem_u32(&bars->kv_empty[stage]));
                 tc_commit(smem_u32(&bars->tmem_full[as]));
                 if (kb + 1 == r.b1) tc_commit(smem_u32(&bars->q_empty[qs]));
+                }
+                __syncwarp();
                 if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -403,6 +415,7 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     uint32_t grid = (uint32_t)dev->sm_count;
     if (p.num_q_blocks < grid) grid = p.num_q_blocks;
     fn<<<grid, kMqaThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tq, tkv, tqsf, tkvsf, p);
+    dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;
 }

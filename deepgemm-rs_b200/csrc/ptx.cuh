@@ -30,6 +30,16 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
     return t;
 }
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
+// One lane of a fully converged warp.  The single-thread roles (TMA producer, MMA issuer) run
+// their loops warp-converged and predicate only the issuing instructions with this, so that
+// descriptors, coordinates and barrier addresses stay warp-uniform values.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+// Bounded wait by every lane of a converged warp; the result is warp-uniform.
+#define DG_WARP_WAIT(bar, parity, wc, site) __all_sync(0xffffffffu, ::dg::mbar_wait((bar), (parity), (wc), (site)))
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {

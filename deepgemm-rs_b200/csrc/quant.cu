@@ -232,6 +232,7 @@ static int32_t launch_quant(const float* x, uint32_t m, uint32_t k, int32_t dtyp
         quant_mx_kernel<32, false><<<blocks, 256, 0, s>>>(x, m, k, d, sf_out, sf_cols, num_spans, num_row_blocks);
     else
         quant_mx_kernel<128, false><<<blocks, 256, 0, s>>>(x, m, k, d, sf_out, sf_cols, num_spans, num_row_blocks);
+    dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;
 }
@@ -287,6 +288,7 @@ int32_t dg_dequant_mx(const void* data, const dg_sf_tensor_t* sf, uint32_t m, ui
         dg::dequant_mx_kernel<true><<<blocks, 256, 0, s>>>(static_cast<const uint8_t*>(data), sf->data, sf->cols, m, k, sf->gran, out);
     else
         dg::dequant_mx_kernel<false><<<blocks, 256, 0, s>>>(static_cast<const uint8_t*>(data), sf->data, sf->cols, m, k, sf->gran, out);
+    dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;
 }
@@ -295,6 +297,7 @@ static int32_t transform_sf_impl(const float* sf, uint32_t mn, uint32_t sf_k, ui
     const uint32_t cols = dg::align_up(mn, 4);
     dim3 grid(dg::ceil_div(cols, 64), dg::ceil_div(sf_k, 64));
     dg::transform_sf_kernel<<<grid, 256, 0, s>>>(sf, mn, sf_k, out, cols);
+    dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;
 }

@@ -37,6 +37,11 @@ def declared_symbols():
 _lib = None
 
 
+def launch_count():
+    """Kernels launched by the library so far in this process."""
+    return int(load().dg_launch_count())
+
+
 def load(build_if_missing=True):
     """Returns the loaded library.  There is no fallback: if the shared object is missing and
     cannot be built, this raises."""
@@ -57,6 +62,7 @@ def load(build_if_missing=True):
     L.dg_last_error.restype = C.c_char_p
     L.dg_version.restype = C.c_char_p
     L.dg_device_check.restype = i32
+    L.dg_launch_count.restype = C.c_ulonglong
     L.dg_poll_device_status.argtypes = [vp]
     L.dg_sf_shape.argtypes = [u32, u32, u32, C.POINTER(u32), C.POINTER(u32)]
     L.dg_sf_shape.restype = None
@@ -77,8 +83,10 @@ def load(build_if_missing=True):
         L.dg_mqa_logits_f32.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, vp, u32, vp]
     if hasattr(L, "dg_mqa_logits"):
         L.dg_mqa_logits.argtypes = [opp, opp, vp, vp, vp, u32, u32, u32, u32, vp, u32, vp]
+    u64 = C.c_uint64
+    L.dg_gather_rows.argtypes = [vp, u64, vp, vp, u64, u32, u32, vp]
+    L.dg_gather_sf.argtypes = [vp, u64, u64, vp, vp, u64, u64, u32, u32, vp]
+    L.dg_moe_combine.argtypes = [vp, u64, vp, vp, vp, u64, u32, u32, u32, vp]
     L.dg_get_gemm_config.argtypes = [i32, i32, u32, u32, u32, u32, C.POINTER(GemmConfigC)]
-    for name in dir(L):
-        pass
     _lib = L
     return L

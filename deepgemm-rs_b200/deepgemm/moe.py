@@ -1,0 +1,207 @@
+"""Expert-parallel MoE layer step around `m_grouped_gemm_nt_contiguous`.
+
+One process per GPU; rank r owns experts [r*E/n, (r+1)*E/n) with their FP8 weights resident.
+A step is: route -> dispatch (all-to-all of FP8 token rows and their scale factors over
+NCCL) -> build the 128-row-padded contiguous layout and `m_indices` -> grouped GEMM ->
+return (all-to-all of bf16 output rows) -> combine the top-k copies of every token.
+The reference has no host-side communication layer (its only expert-parallel code is the
+device-side MegaMoE protocol, deepgemm/src/api_mega_moe.rs:1154-1221); the layout conventions
+are those of api::m_grouped_gemm_nt_contiguous (deepgemm/src/api.rs:852-903): `m_indices[b]` is
+the expert of the b-th 128-row block, negative for padding blocks.
+
+The index arithmetic (plain torch, device-agnostic) is separated from the data movement
+(the library's gather / GEMM / combine kernels) so that it can be checked on CPU ranks.
+"""
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .api import _check, _stream_ptr, m_grouped_gemm_nt_contiguous
+from .types import Dtype, Operand, Output, SfGran, SfTensor
+
+BLOCK = 128  # rows per m_indices entry (heuristics::mk_alignment_for_contiguous_layout)
+
+
+@dataclass
+class ContiguousLayout:
+    """Placement of `rows` grouped rows into the padded contiguous layout."""
+    m_cap: int                  # allocated rows (a multiple of 128; trailing blocks are padding)
+    src_row: torch.Tensor       # int32 [m_cap]: source row of every slot, -1 = padding row
+    slot_of_row: torch.Tensor   # int32 [rows]: slot of every source row
+    m_indices: torch.Tensor     # int32 [m_cap / 128]: expert of each block, -1 = skip
+    counts: torch.Tensor        # int64 [num_experts]
+
+
+def contiguous_capacity(rows, num_experts):
+    """Rows that are always enough: every expert may waste up to 127 padding rows."""
+    return (rows + num_experts * (BLOCK - 1) + BLOCK - 1) // BLOCK * BLOCK
+
+
+def build_contiguous_layout(expert_of_row, num_experts, m_cap=None):
+    """expert_of_row: int tensor [rows] (any device).  Rows keep their relative order inside an
+    expert's group; each group is padded to a multiple of 128 rows.  No host synchronisation."""
+    e = expert_of_row.to(torch.int64)
+    rows = e.numel()
+    dev = e.device
+    if m_cap is None:
+        m_cap = contiguous_capacity(rows, num_experts)
+    counts = torch.bincount(e, minlength=num_experts)
+    padded = (counts + BLOCK - 1) // BLOCK * BLOCK
+    pad_end = torch.cumsum(padded, 0)
+    pad_off = pad_end - padded
+    off = torch.cumsum(counts, 0) - counts
+    order = torch.argsort(e, stable=True)
+    e_sorted = e[order]
+    slot_sorted = pad_off[e_sorted] + (torch.arange(rows, device=dev) - off[e_sorted])
+    src_row = torch.full((m_cap,), -1, dtype=torch.int32, device=dev)
+    src_row[slot_sorted] = order.to(torch.int32)
+    slot_of_row = torch.empty(rows, dtype=torch.int32, device=dev)
+    slot_of_row[order] = slot_sorted.to(torch.int32)
+    blocks = torch.arange(m_cap // BLOCK, device=dev)
+    owner = torch.searchsorted(pad_end // BLOCK, blocks, right=True)
+    m_indices = torch.where(blocks < pad_end[-1] // BLOCK, owner, torch.full_like(owner, -1)).to(torch.int32)
+    return ContiguousLayout(m_cap, src_row, slot_of_row, m_indices, counts)
+
+
+@dataclass
+class DispatchPlan:
+    """Everything a rank needs to ship its token copies to the expert owners and back."""
+    order: torch.Tensor          # int64 [T*k]: copies sorted by global expert (= by destination rank)
+    send_token: torch.Tensor     # int32 [T*k]: token row of every sorted copy
+    copy_pos: torch.Tensor       # int32 [T, k]: position of copy (t, j) in the sorted order
+    send_splits: list            # rows to every rank
+    recv_splits: list            # rows from every rank
+    recv_expert: torch.Tensor    # int64 [R]: local expert of every received row
+    layout: ContiguousLayout     # placement of the R received rows
+
+
+def plan_dispatch(topk_idx, num_experts, group=None):
+    """topk_idx: int tensor [T, k] of global expert ids.  Exchanges the per-expert counts (one
+    all-to-all of world*E_local integers, plus one device-to-host copy of the split sizes)."""
+    world = dist.get_world_size(group) if group is not None else 1
+    e_local = num_experts // world
+    flat = topk_idx.reshape(-1).to(torch.int64)
+    dev = flat.device
+    order = torch.argsort(flat, stable=True)
+    send_token = (order // topk_idx.shape[1]).to(torch.int32)
+    copy_pos = torch.empty_like(order)
+    copy_pos[order] = torch.arange(order.numel(), device=dev)
+    send_counts = torch.bincount(flat, minlength=num_experts).reshape(world, e_local)
+    if world > 1:
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=group)
+    else:
+        recv_counts = send_counts
+    both = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()
+    send_splits, recv_splits = both[0].tolist(), both[1].tolist()
+    # received rows arrive ordered by (source rank, local expert)
+    recv_expert = torch.repeat_interleave(torch.arange(e_local, device=dev).repeat(world), recv_counts.reshape(-1),
+                                          output_size=sum(recv_splits))
+    # capacity from the received row count only (known on the host), so every rank allocates alike per step
+    layout = build_contiguous_layout(recv_expert, e_local, contiguous_capacity(sum(recv_splits), e_local))
+    return DispatchPlan(order, send_token, copy_pos.reshape(topk_idx.shape).to(torch.int32), send_splits, recv_splits,
+                        recv_expert, layout)
+
+
+# ---- data movement (library kernels) -----------------------------------------------------------
+def gather_rows(src, idx, out=None):
+    """out[i] = src[idx[i]] (zeros for idx < 0) for 2-D byte / bf16 tensors with 16-byte rows."""
+    n = idx.numel()
+    row_bytes = src.shape[1] * src.element_size()
+    if out is None:
+        out = torch.empty((n, src.shape[1]), dtype=src.dtype, device=src.device)
+    _check(_lib.load().dg_gather_rows(src.data_ptr(), src.stride(0) * src.element_size(), idx.data_ptr(), out.data_ptr(),
+                                      out.stride(0) * out.element_size(), n, row_bytes, _stream_ptr(None)))
+    return out
+
+
+def _gather_sf(src, src_rs, src_cs, idx, dst, dst_rs, dst_cs, sf_rows):
+    _check(_lib.load().dg_gather_sf(src.data_ptr(), src_rs, src_cs, idx.data_ptr(), dst.data_ptr(), dst_rs, dst_cs,
+                                    sf_rows, idx.numel(), _stream_ptr(None)))
+
+
+def sf_to_wire(sf, idx):
+    """Packed SF [sf_rows, cols] -> row-per-token words [len(idx), sf_rows]."""
+    wire = torch.empty((idx.numel(), sf.rows), dtype=torch.int32, device=sf.buf.device)
+    _gather_sf(sf.buf, sf.cols, 1, idx, wire, 1, sf.rows, sf.rows)
+    return wire
+
+
+def sf_from_wire(wire, idx, gran):
+    """Row-per-token words [R, sf_rows] -> packed SF tensor whose column i is wire row idx[i]."""
+    sf_rows = wire.shape[1]
+    cols = idx.numel()
+    buf = torch.empty((sf_rows, cols), dtype=torch.int32, device=wire.device)
+    _gather_sf(wire, 1, sf_rows, idx, buf, cols, 1, sf_rows)
+    return SfTensor(sf_rows, cols, SfGran(int(gran)), buf)
+
+
+def sf_permute(sf, idx):
+    buf = torch.empty((sf.rows, idx.numel()), dtype=torch.int32, device=sf.buf.device)
+    _gather_sf(sf.buf, sf.cols, 1, idx, buf, idx.numel(), 1, sf.rows)
+    return SfTensor(sf.rows, idx.numel(), sf.gran, buf)
+
+
+def combine(src, pos, weights, out=None):
+    """out[t] = sum_j weights[t, j] * src[pos[t, j]] (bf16 rows, f32 accumulation)."""
+    tokens, topk = pos.shape
+    if out is None:
+        out = torch.empty((tokens, src.shape[1]), dtype=torch.bfloat16, device=src.device)
+    _check(_lib.load().dg_moe_combine(src.data_ptr(), src.stride(0), pos.data_ptr(),
+                                      weights.data_ptr() if weights is not None else None, out.data_ptr(), out.stride(0),
+                                      tokens, topk, src.shape[1], _stream_ptr(None)))
+    return out
+
+
+class ExpertParallelMoE:
+    """Grouped-GEMM MoE projection with experts sharded over the ranks of `group`.
+
+    weights: Operand of the stacked local experts [E_local * n_out, K] (rows = n_out), resident.
+    forward(x, x_sf, topk_idx, topk_w): x = FP8 codes [T, K] of this rank's tokens, x_sf their
+    packed SF; returns bf16 [T, n_out] = sum_j topk_w[t, j] * (x[t] . W[topk_idx[t, j]]^T).
+    """
+
+    def __init__(self, weights: Operand, num_experts: int, group=None):
+        self.w = weights
+        self.num_experts = num_experts
+        self.group = group
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.e_local = num_experts // self.world
+        self.last_plan: Optional[DispatchPlan] = None
+
+    def forward(self, x, x_sf, topk_idx, topk_w=None):
+        plan = plan_dispatch(topk_idx, self.num_experts, self.group)
+        self.last_plan = plan
+        k, n_out = x.shape[1], self.w.rows
+        lay = plan.layout
+        if self.world == 1:
+            # no wire: place token copies straight into the contiguous layout
+            src_token = torch.where(lay.src_row >= 0, plan.send_token[lay.src_row.clamp(min=0).long()],
+                                    torch.full_like(lay.src_row, -1))
+            a = gather_rows(x, src_token)
+            a_sf = sf_permute(x_sf, src_token)
+        else:
+            rows = gather_rows(x, plan.send_token)
+            wire = sf_to_wire(x_sf, plan.send_token)
+            r = sum(plan.recv_splits)
+            recv_rows = torch.empty((r, k), dtype=x.dtype, device=x.device)
+            recv_wire = torch.empty((r, wire.shape[1]), dtype=wire.dtype, device=x.device)
+            dist.all_to_all_single(recv_rows, rows, plan.recv_splits, plan.send_splits, group=self.group)
+            dist.all_to_all_single(recv_wire, wire, plan.recv_splits, plan.send_splits, group=self.group)
+            a = gather_rows(recv_rows, lay.src_row)
+            a_sf = sf_from_wire(recv_wire, lay.src_row, x_sf.gran)
+        d = torch.empty((lay.m_cap, n_out), dtype=torch.bfloat16, device=x.device)
+        a_op = Operand.k_major(self.w.dtype, lay.m_cap, k if self.w.dtype != Dtype.Fp4 else k * 2,
+                               k if self.w.dtype != Dtype.Fp4 else k * 2, a_sf, a)
+        m_grouped_gemm_nt_contiguous(a_op, self.w, Output(Dtype.Bf16, lay.m_cap, n_out, n_out, d), lay.m_indices, self.e_local)
+        if self.world == 1:
+            pos = lay.slot_of_row[plan.copy_pos.long()]
+            return combine(d, pos, topk_w)
+        back = gather_rows(d, lay.slot_of_row)                       # received order
+        ret = torch.empty((plan.order.numel(), n_out), dtype=torch.bfloat16, device=x.device)
+        dist.all_to_all_single(ret, back, plan.send_splits, plan.recv_splits, group=self.group)
+        return combine(ret, plan.copy_pos, topk_w)

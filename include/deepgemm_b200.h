@@ -88,6 +88,9 @@ DG_API int32_t dg_device_check(void);
  * library on the current device gave up on a wait since the last call, and clears the flag. */
 DG_API int32_t dg_poll_device_status(void* stream);
 
+/* Number of kernels this library has launched in this process (all devices, all threads). */
+DG_API unsigned long long dg_launch_count(void);
+
 /* Shape of the packed SF tensor of an [mn, k] operand: rows = ceil(k/(gran*4)),
  * cols = align4(mn) (deepgemm/src/heuristics.rs:617-624, deepgemm/src/golden.rs:71-73). */
 DG_API void dg_sf_shape(uint32_t mn, uint32_t k, uint32_t gran, uint32_t* rows, uint32_t* cols);
@@ -172,6 +175,26 @@ DG_API int32_t dg_mqa_logits(const dg_operand_t* q, const dg_operand_t* kv, cons
                       const uint32_t* cu_k_start, const uint32_t* cu_k_end,
                       uint32_t num_tokens, uint32_t num_kv_tokens, uint32_t num_heads, uint32_t head_dim,
                       void* logits_bf16, uint32_t logits_stride, void* stream);
+
+/* ---- MoE row movement around the grouped GEMM -----------------------------------------------
+ * The steps the reference leaves to the caller of Serving::moe_grouped_layer
+ * (deepgemm/src/api_serving.rs:293-377): gather token rows (and the MN columns of their packed
+ * scale factors) into the 128-row-padded contiguous layout, and combine expert outputs per token.
+ * dg_gather_rows: dst[i,:] = src[idx[i],:], zeros when idx[i] < 0; rows and pitches in bytes,
+ * multiples of 16. */
+DG_API int32_t dg_gather_rows(const void* src, uint64_t src_pitch_bytes, const int32_t* idx, void* dst,
+                              uint64_t dst_pitch_bytes, uint32_t n_rows, uint32_t row_bytes, void* stream);
+/* dst[r*dst_row_stride + i*dst_col_stride] = src[r*src_row_stride + idx[i]*src_col_stride] for r < sf_rows,
+ * i < n (strides in words; 0 when idx[i] < 0): permutes the MN columns of a packed SF tensor, or converts
+ * it to / from a row-per-token wire format. */
+DG_API int32_t dg_gather_sf(const uint32_t* src, uint64_t src_row_stride, uint64_t src_col_stride, const int32_t* idx,
+                            uint32_t* dst, uint64_t dst_row_stride, uint64_t dst_col_stride, uint32_t sf_rows, uint32_t n,
+                            void* stream);
+/* out[t,:] = sum_j weights[t,j] * src[pos[t,j],:] over the topk copies of token t (bf16 rows, f32 sum in
+ * the order j = 0..topk-1); pos < 0 skips a copy; weights == NULL means 1; pitches in elements. */
+DG_API int32_t dg_moe_combine(const void* src_bf16, uint64_t src_pitch, const int32_t* pos, const float* weights,
+                              void* out_bf16, uint64_t out_pitch, uint32_t tokens, uint32_t topk, uint32_t cols,
+                              void* stream);
 
 /* ---- tuning / introspection -------------------------------------------------------------
  * Describes the tile configuration the library would use for a dense / grouped GEMM
