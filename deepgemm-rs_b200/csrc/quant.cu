@@ -267,6 +267,47 @@ int32_t dg_quant_mx_host(const float* x_host, uint32_t m, uint32_t k, int32_t dt
     return st;
 }
 
+// ---- quant_mx from host memory without any allocation --------------------------------------
+// Staging area for the host tensor, owned by the library image: every GPU that loads the
+// library holds these bytes until the process exits.
+constexpr size_t kStaticStagingBytes = 16u << 20;   // 16 MiB = 4 Mi f32 elements
+static __device__ __align__(256) unsigned char g_quant_staging[kStaticStagingBytes];
+// g_quant_staging names a host-side handle in host code, not a device address: the address the
+// kernel and the copy engine need comes from cudaGetSymbolAddress, once per device.
+static float* g_quant_staging_addr[64] = {nullptr};
+
+int32_t dg_quant_mx_host_static(const float* x_host, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran,
+                                void* data_out, uint32_t* sf_out, void* stream) {
+    int32_t st = dg::check_quant_args(x_host, m, k, dtype, gran, data_out, sf_out);
+    if (st != DG_OK) return st;
+    const size_t bytes = (size_t)m * k * sizeof(float);
+    if (bytes > kStaticStagingBytes)
+        return dg::fail(DG_ERR_INVALID_ARG,
+                        "quant_mx (static staging): %u x %u f32 = %zu bytes exceeds the %zu-byte built-in staging area; "
+                        "use dg_quant_mx_host or split the rows",
+                        m, k, bytes, (size_t)kStaticStagingBytes);
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return dg::fail(DG_ERR_UNSUPPORTED, "no usable CUDA device; the kernels require SM100 (Blackwell)");
+    }
+    if (!g_quant_staging_addr[dev]) {
+        // one-time set-up on this device (it is the current one)
+        int major = 0;
+        DG_CUDA_CHECK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        if (major != 10) return dg::fail(DG_ERR_UNSUPPORTED, "the kernels require SM100 (Blackwell); this device is sm_%d*", major);
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_quant_staging);
+        if (e != cudaSuccess || !p)
+            return dg::fail(DG_ERR_DRIVER, "cudaGetSymbolAddress(static staging area) failed: %s", cudaGetErrorString(e));
+        g_quant_staging_addr[dev] = static_cast<float*>(p);
+    }
+    float* staging = g_quant_staging_addr[dev];
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DG_CUDA_CHECK(cudaMemcpyAsync(staging, x_host, bytes, cudaMemcpyHostToDevice, s));
+    return dg::launch_quant(staging, m, k, dtype, gran, data_out, sf_out, s);
+}
+
 int32_t dg_dequant_mx(const void* data, const dg_sf_tensor_t* sf, uint32_t m, uint32_t k, int32_t dtype, float* out,
                       void* stream) {
     int32_t st;

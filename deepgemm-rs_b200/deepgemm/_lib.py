@@ -76,6 +76,7 @@ def load(build_if_missing=True):
         getattr(L, n).argtypes = [opp, opp, outp, vp, u32, u32, vp]
     L.dg_quant_mx.argtypes = [vp, u32, u32, i32, u32, vp, vp, vp]
     L.dg_quant_mx_host.argtypes = [vp, u32, u32, i32, u32, vp, vp, vp]
+    L.dg_quant_mx_host_static.argtypes = [vp, u32, u32, i32, u32, vp, vp, vp]
     L.dg_dequant_mx.argtypes = [vp, C.POINTER(SfTensorC), u32, u32, i32, vp, vp]
     L.dg_transform_sf.argtypes = [vp, u32, u32, vp, vp]
     L.dg_transform_sf_host.argtypes = [vp, u32, u32, vp, vp]

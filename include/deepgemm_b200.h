@@ -150,6 +150,20 @@ DG_API int32_t dg_quant_mx(const float* x, uint32_t m, uint32_t k, int32_t dtype
                     void* data_out, uint32_t* sf_out, void* stream);
 DG_API int32_t dg_quant_mx_host(const float* x_host, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran,
                          void* data_out, uint32_t* sf_out, void* stream);
+/* No counterpart in the reference.  Same result as dg_quant_mx_host, for callers that must not
+ * allocate device memory while they run: code inside a region where cudaMalloc / cudaMallocAsync is
+ * forbidden or would stall (a latency-critical serving loop, a process whose memory is entirely
+ * handed to another allocator, a plugin host that audits allocations).  The host tensor is staged
+ * in a 16 MiB array built into the library image (held by every GPU that loads the library, until
+ * exit), so m * k * 4 bytes must not exceed 16 MiB; larger inputs are rejected with
+ * DG_ERR_INVALID_ARG.  The call makes no cudaMalloc / cudaFree / pool allocation.  Its first call
+ * on a device looks up the array's device address once: make that first call outside any stream
+ * capture.  All calls share the one staging array and it keeps the previous call's contents (each
+ * call overwrites exactly the bytes it then reads, nothing needs clearing): calls whose work can
+ * overlap on the GPU -- different streams, or several host threads -- race on it and must be
+ * serialised by the caller. */
+DG_API int32_t dg_quant_mx_host_static(const float* x_host, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran,
+                                       void* data_out, uint32_t* sf_out, void* stream);
 /* replaces api::dequant_mx (deepgemm/src/api.rs:1556-1601): codes + SF -> f32 [m,k]. */
 DG_API int32_t dg_dequant_mx(const void* data, const dg_sf_tensor_t* sf, uint32_t m, uint32_t k, int32_t dtype,
                       float* out, void* stream);
