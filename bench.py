@@ -142,11 +142,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the additional single-GPU workloads")
-    ap.add_argument("--tokens", type=int, default=CFG["tokens_per_gpu"])
+    ap.add_argument("--tokens", type=int, default=CFG["tokens_per_gpu"], help="tokens per GPU (smaller cases for profiling)")
+    ap.add_argument("--experts", type=int, default=CFG["num_experts"], help="total experts (smaller cases for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
     CFG["tokens_per_gpu"] = args.tokens
+    CFG["num_experts"] = args.experts
 
     import torch
     import torch.distributed as dist
