@@ -69,9 +69,105 @@ __global__ void __launch_bounds__(256) combine_kernel(const __nv_bfloat16* __res
     }
 }
 
+// ---- grouping plan: rows -> expert-contiguous slots ---------------------------------------------
+// plan_count: counts[e] = number of rows routed to expert e (counts zeroed by the caller's stream).
+__global__ void __launch_bounds__(256) plan_count_kernel(const int32_t* __restrict__ expert_of_row, uint32_t n_rows,
+                                                        uint32_t num_experts, int32_t* __restrict__ counts) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    const int32_t e = __ldg(expert_of_row + r);
+    if (e >= 0 && (uint32_t)e < num_experts) atomicAdd(counts + e, 1);
+}
+
+// plan_scan (one block): offsets[e] = first slot of expert e with every group padded to `align`
+// rows, offsets[E] = total; block_expert[b] = expert owning the b-th `align`-row block or -1;
+// cursors reset to 0.
+__global__ void __launch_bounds__(1024) plan_scan_kernel(const int32_t* __restrict__ counts, uint32_t num_experts,
+                                                        uint32_t align, uint32_t capacity, int32_t* __restrict__ offsets,
+                                                        int32_t* __restrict__ cursors, int32_t* __restrict__ block_expert) {
+    extern __shared__ int32_t sh_off[];  // [num_experts + 1]
+    if (threadIdx.x == 0) {
+        int32_t acc = 0;
+        for (uint32_t e = 0; e < num_experts; ++e) {
+            sh_off[e] = acc;
+            acc += (int32_t)(((uint32_t)counts[e] + align - 1) / align * align);
+        }
+        sh_off[num_experts] = acc;
+    }
+    __syncthreads();
+    for (uint32_t e = threadIdx.x; e <= num_experts; e += blockDim.x) {
+        offsets[e] = sh_off[e];
+        if (e < num_experts) cursors[e] = 0;
+    }
+    if (block_expert) {
+        const uint32_t total = (uint32_t)sh_off[num_experts];
+        for (uint32_t b = threadIdx.x; b < capacity / align; b += blockDim.x) {
+            const uint32_t row = b * align;
+            int32_t owner = -1;
+            if (row < total) {
+                uint32_t lo = 0, hi = num_experts;      // last e with sh_off[e] <= row
+                while (hi - lo > 1) {
+                    const uint32_t mid = (lo + hi) >> 1;
+                    if ((uint32_t)sh_off[mid] <= row) lo = mid; else hi = mid;
+                }
+                owner = (int32_t)lo;
+            }
+            block_expert[b] = owner;
+        }
+    }
+}
+
+// plan_place: every row takes the next free slot of its expert.  slot_src[slot] = r / div (the
+// token of copy r when div = top-k), slot_of_row[r] = slot.  The order of rows inside a group is
+// not fixed from run to run; no result depends on it (a GEMM row does not see its neighbours).
+__global__ void __launch_bounds__(256) plan_place_kernel(const int32_t* __restrict__ expert_of_row, uint32_t n_rows,
+                                                        uint32_t num_experts, uint32_t div, const int32_t* __restrict__ offsets,
+                                                        int32_t* __restrict__ cursors, int32_t* __restrict__ slot_src,
+                                                        int32_t* __restrict__ slot_of_row) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    const int32_t e = __ldg(expert_of_row + r);
+    if (e < 0 || (uint32_t)e >= num_experts) { slot_of_row[r] = -1; return; }
+    const int32_t slot = offsets[e] + atomicAdd(cursors + e, 1);
+    slot_src[slot] = (int32_t)(r / div);
+    slot_of_row[r] = slot;
+}
+
 }  // namespace dg
 
 extern "C" {
+
+int32_t dg_moe_plan(const int32_t* expert_of_row, uint32_t n_rows, uint32_t num_experts, uint32_t align, uint32_t div,
+                    uint32_t capacity, int32_t* counts, int32_t* offsets, int32_t* cursors, int32_t* slot_src,
+                    int32_t* slot_of_row, int32_t* block_expert, void* stream) {
+    if (!expert_of_row || !counts || !offsets || !cursors || !slot_src || !slot_of_row)
+        return dg::fail(DG_ERR_INVALID_ARG, "moe_plan: null buffer");
+    if (num_experts == 0 || num_experts > 8192 || align == 0 || div == 0 || capacity % align != 0)
+        return dg::fail(DG_ERR_INVALID_ARG, "moe_plan: need 1..8192 experts, align > 0, div > 0 and capacity %% align == 0");
+    if ((uint64_t)capacity < (uint64_t)n_rows + (uint64_t)num_experts * (align - 1))
+        return dg::fail(DG_ERR_INVALID_ARG, "moe_plan: capacity %u cannot hold %u rows in %u groups padded to %u", capacity,
+                        n_rows, num_experts, align);
+    const dg::DeviceInfo* dev;
+    int32_t st = dg::current_device(&dev);
+    if (st != DG_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    DG_CUDA_CHECK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * num_experts, s));
+    DG_CUDA_CHECK(cudaMemsetAsync(slot_src, 0xff, sizeof(int32_t) * (size_t)capacity, s));
+    if (n_rows) {
+        dg::plan_count_kernel<<<dg::ceil_div(n_rows, 256), 256, 0, s>>>(expert_of_row, n_rows, num_experts, counts);
+        dg::note_launch();
+    }
+    dg::plan_scan_kernel<<<1, 1024, sizeof(int32_t) * (num_experts + 1), s>>>(counts, num_experts, align, capacity, offsets,
+                                                                              cursors, block_expert);
+    dg::note_launch();
+    if (n_rows) {
+        dg::plan_place_kernel<<<dg::ceil_div(n_rows, 256), 256, 0, s>>>(expert_of_row, n_rows, num_experts, div, offsets,
+                                                                        cursors, slot_src, slot_of_row);
+        dg::note_launch();
+    }
+    DG_CUDA_CHECK(cudaGetLastError());
+    return DG_OK;
+}
 
 int32_t dg_gather_rows(const void* src, uint64_t src_pitch_bytes, const int32_t* idx, void* dst, uint64_t dst_pitch_bytes,
                        uint32_t n_rows, uint32_t row_bytes, void* stream) {

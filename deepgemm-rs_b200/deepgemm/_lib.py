@@ -87,6 +87,7 @@ def load(build_if_missing=True):
     u64 = C.c_uint64
     L.dg_gather_rows.argtypes = [vp, u64, vp, vp, u64, u32, u32, vp]
     L.dg_gather_sf.argtypes = [vp, u64, u64, vp, vp, u64, u64, u32, u32, vp]
+    L.dg_moe_plan.argtypes = [vp, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, vp]
     L.dg_moe_combine.argtypes = [vp, u64, vp, vp, vp, u64, u32, u32, u32, vp]
     L.dg_get_gemm_config.argtypes = [i32, i32, u32, u32, u32, u32, C.POINTER(GemmConfigC)]
     _lib = L

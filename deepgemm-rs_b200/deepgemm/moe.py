@@ -9,8 +9,10 @@ device-side MegaMoE protocol, deepgemm/src/api_mega_moe.rs:1154-1221); the layou
 are those of api::m_grouped_gemm_nt_contiguous (deepgemm/src/api.rs:852-903): `m_indices[b]` is
 the expert of the b-th 128-row block, negative for padding blocks.
 
-The index arithmetic (plain torch, device-agnostic) is separated from the data movement
-(the library's gather / GEMM / combine kernels) so that it can be checked on CPU ranks.
+The step's index arithmetic exists twice with one contract: in plain torch (`plan_dispatch`,
+`build_contiguous_layout`: device-agnostic, checked on CPU ranks over gloo) and as library
+kernels (`device_plan`, used by `ExpertParallelMoE` so that a step needs no host
+synchronisation on one GPU and exactly one on several).
 """
 import ctypes as C
 from dataclasses import dataclass
@@ -107,6 +109,38 @@ def plan_dispatch(topk_idx, num_experts, group=None):
                         recv_expert, layout)
 
 
+# ---- device-side plan (library kernels; same contract as build_contiguous_layout) ---------------
+@dataclass
+class DevicePlan:
+    counts: torch.Tensor        # int32 [E]
+    offsets: torch.Tensor       # int32 [E + 1]
+    slot_src: torch.Tensor      # int32 [capacity]: row // div of each slot, -1 = padding
+    slot_of_row: torch.Tensor   # int32 [rows]
+    block_expert: torch.Tensor  # int32 [capacity / align]
+    capacity: int
+
+
+def device_plan(expert_of_row, num_experts, align, div=1, capacity=None):
+    """Groups rows by expert on the device without any host synchronisation (dg_moe_plan).
+    Unlike build_contiguous_layout the order of rows inside a group is not fixed; nothing
+    downstream depends on it."""
+    e = expert_of_row.reshape(-1)
+    if e.dtype != torch.int32 or not e.is_contiguous():
+        e = e.to(torch.int32).contiguous()
+    rows = e.numel()
+    if capacity is None:
+        capacity = (rows + num_experts * (align - 1) + align - 1) // align * align
+    dev = e.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    counts, offsets, cursors = torch.empty(num_experts, **i32), torch.empty(num_experts + 1, **i32), torch.empty(num_experts, **i32)
+    slot_src, slot_of_row = torch.empty(max(capacity, 1), **i32), torch.empty(max(rows, 1), **i32)
+    block_expert = torch.empty(max(capacity // align, 1), **i32)
+    _check(_lib.load().dg_moe_plan(e.data_ptr(), rows, num_experts, align, div, capacity, counts.data_ptr(), offsets.data_ptr(),
+                                   cursors.data_ptr(), slot_src.data_ptr(), slot_of_row.data_ptr(), block_expert.data_ptr(),
+                                   _stream_ptr(None)))
+    return DevicePlan(counts, offsets, slot_src[:capacity], slot_of_row[:rows], block_expert[:capacity // align], capacity)
+
+
 # ---- data movement (library kernels) -----------------------------------------------------------
 def gather_rows(src, idx, out=None):
     """out[i] = src[idx[i]] (zeros for idx < 0) for 2-D byte / bf16 tensors with 16-byte rows."""
@@ -171,37 +205,49 @@ class ExpertParallelMoE:
         self.group = group
         self.world = dist.get_world_size(group) if group is not None else 1
         self.e_local = num_experts // self.world
-        self.last_plan: Optional[DispatchPlan] = None
+        self.last_m_indices: Optional[torch.Tensor] = None
 
     def forward(self, x, x_sf, topk_idx, topk_w=None):
-        plan = plan_dispatch(topk_idx, self.num_experts, self.group)
-        self.last_plan = plan
+        tokens, topk = topk_idx.shape
         k, n_out = x.shape[1], self.w.rows
-        lay = plan.layout
+        k_elems = k if self.w.dtype != Dtype.Fp4 else k * 2
         if self.world == 1:
-            # no wire: place token copies straight into the contiguous layout
-            src_token = torch.where(lay.src_row >= 0, plan.send_token[lay.src_row.clamp(min=0).long()],
-                                    torch.full_like(lay.src_row, -1))
-            a = gather_rows(x, src_token)
-            a_sf = sf_permute(x_sf, src_token)
-        else:
-            rows = gather_rows(x, plan.send_token)
-            wire = sf_to_wire(x_sf, plan.send_token)
-            r = sum(plan.recv_splits)
-            recv_rows = torch.empty((r, k), dtype=x.dtype, device=x.device)
-            recv_wire = torch.empty((r, wire.shape[1]), dtype=wire.dtype, device=x.device)
-            dist.all_to_all_single(recv_rows, rows, plan.recv_splits, plan.send_splits, group=self.group)
-            dist.all_to_all_single(recv_wire, wire, plan.recv_splits, plan.send_splits, group=self.group)
-            a = gather_rows(recv_rows, lay.src_row)
-            a_sf = sf_from_wire(recv_wire, lay.src_row, x_sf.gran)
-        d = torch.empty((lay.m_cap, n_out), dtype=torch.bfloat16, device=x.device)
-        a_op = Operand.k_major(self.w.dtype, lay.m_cap, k if self.w.dtype != Dtype.Fp4 else k * 2,
-                               k if self.w.dtype != Dtype.Fp4 else k * 2, a_sf, a)
-        m_grouped_gemm_nt_contiguous(a_op, self.w, Output(Dtype.Bf16, lay.m_cap, n_out, n_out, d), lay.m_indices, self.e_local)
-        if self.world == 1:
-            pos = lay.slot_of_row[plan.copy_pos.long()]
-            return combine(d, pos, topk_w)
-        back = gather_rows(d, lay.slot_of_row)                       # received order
-        ret = torch.empty((plan.order.numel(), n_out), dtype=torch.bfloat16, device=x.device)
-        dist.all_to_all_single(ret, back, plan.send_splits, plan.recv_splits, group=self.group)
-        return combine(ret, plan.copy_pos, topk_w)
+            # one device-side plan straight into the padded layout; no host synchronisation
+            p = device_plan(topk_idx, self.num_experts, BLOCK, div=topk)
+            a = gather_rows(x, p.slot_src)
+            a_sf = sf_permute(x_sf, p.slot_src)
+            d = torch.empty((p.capacity, n_out), dtype=torch.bfloat16, device=x.device)
+            a_op = Operand.k_major(self.w.dtype, p.capacity, k_elems, k_elems, a_sf, a)
+            m_grouped_gemm_nt_contiguous(a_op, self.w, Output(Dtype.Bf16, p.capacity, n_out, n_out, d), p.block_expert,
+                                         self.e_local)
+            self.last_m_indices = p.block_expert
+            return combine(d, p.slot_of_row.view(tokens, topk), topk_w)
+        # sort copies by global expert (= by destination rank), exchange the per-expert counts
+        sp = device_plan(topk_idx, self.num_experts, 1, div=topk, capacity=tokens * topk)
+        send_counts = sp.counts.view(self.world, self.e_local)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        both = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()      # the one host sync of the step
+        send_splits, recv_splits = both[0].tolist(), both[1].tolist()
+        r = sum(recv_splits)
+        rows = gather_rows(x, sp.slot_src)
+        wire = sf_to_wire(x_sf, sp.slot_src)
+        recv_rows = torch.empty((r, k), dtype=x.dtype, device=x.device)
+        recv_wire = torch.empty((r, wire.shape[1]), dtype=wire.dtype, device=x.device)
+        dist.all_to_all_single(recv_rows, rows, recv_splits, send_splits, group=self.group)
+        dist.all_to_all_single(recv_wire, wire, recv_splits, send_splits, group=self.group)
+        # received rows are ordered by (source rank, local expert)
+        recv_expert = torch.repeat_interleave(torch.arange(self.e_local, device=x.device, dtype=torch.int32).repeat(self.world),
+                                              recv_counts.reshape(-1), output_size=r)
+        rp = device_plan(recv_expert, self.e_local, BLOCK, div=1, capacity=contiguous_capacity(r, self.e_local))
+        a = gather_rows(recv_rows, rp.slot_src)
+        a_sf = sf_from_wire(recv_wire, rp.slot_src, x_sf.gran)
+        d = torch.empty((rp.capacity, n_out), dtype=torch.bfloat16, device=x.device)
+        a_op = Operand.k_major(self.w.dtype, rp.capacity, k_elems, k_elems, a_sf, a)
+        m_grouped_gemm_nt_contiguous(a_op, self.w, Output(Dtype.Bf16, rp.capacity, n_out, n_out, d), rp.block_expert,
+                                     self.e_local)
+        self.last_m_indices = rp.block_expert
+        back = gather_rows(d, rp.slot_of_row)                                    # received order
+        ret = torch.empty((tokens * topk, n_out), dtype=torch.bfloat16, device=x.device)
+        dist.all_to_all_single(ret, back, send_splits, recv_splits, group=self.group)
+        return combine(ret, sp.slot_of_row.view(tokens, topk), topk_w)

@@ -204,6 +204,17 @@ DG_API int32_t dg_gather_rows(const void* src, uint64_t src_pitch_bytes, const i
 DG_API int32_t dg_gather_sf(const uint32_t* src, uint64_t src_row_stride, uint64_t src_col_stride, const int32_t* idx,
                             uint32_t* dst, uint64_t dst_row_stride, uint64_t dst_col_stride, uint32_t sf_rows, uint32_t n,
                             void* stream);
+/* Grouping plan on the device (no host synchronisation): rows with expert ids expert_of_row[r]
+ * (negative = drop) are assigned slots so that each expert's rows are contiguous and every group
+ * is padded to `align` rows (128 for the grouped GEMM, 1 for a plain sort by expert).
+ *   counts[E]        rows per expert            offsets[E+1]   first slot of each group, total
+ *   slot_src[cap]    r / div of the row in each slot, -1 = padding (div = top-k maps a copy to its token)
+ *   slot_of_row[n]   slot of every row          block_expert[cap/align]  expert of each block, -1 = none
+ *                    (may be NULL); with align = 128 this is `m_indices` (deepgemm/src/api.rs:852-853)
+ * cursors[E] is caller-provided scratch.  capacity >= n_rows + E*(align-1), a multiple of align. */
+DG_API int32_t dg_moe_plan(const int32_t* expert_of_row, uint32_t n_rows, uint32_t num_experts, uint32_t align,
+                           uint32_t div, uint32_t capacity, int32_t* counts, int32_t* offsets, int32_t* cursors,
+                           int32_t* slot_src, int32_t* slot_of_row, int32_t* block_expert, void* stream);
 /* out[t,:] = sum_j weights[t,j] * src[pos[t,j],:] over the topk copies of token t (bf16 rows, f32 sum in
  * the order j = 0..topk-1); pos < 0 skips a copy; weights == NULL means 1; pitches in elements. */
 DG_API int32_t dg_moe_combine(const void* src_bf16, uint64_t src_pitch, const int32_t* pos, const float* weights,

@@ -70,5 +70,32 @@ def test_moe_forward_single_rank_matches_oracle():
     assert o.calc_diff(got, ref) <= 1e-3
     assert np.abs(got - ref).max() <= 0.05 * np.sqrt((ref ** 2).mean())
     # padding blocks of the layout were skipped, real blocks carry their expert
-    lay = layer.last_plan.layout
-    assert (lay.m_indices >= -1).all() and int((lay.m_indices >= 0).sum()) >= E
+    mi = layer.last_m_indices
+    assert (mi >= -1).all() and int((mi >= 0).sum()) >= E
+
+
+def test_device_plan_matches_torch_plan_contract():
+    """dg_moe_plan against build_contiguous_layout: same counts, block owners and padding; the
+    same set of rows in every group (the order inside a group is free)."""
+    E, rows = 16, 5000
+    g = torch.Generator(device="cuda").manual_seed(4)
+    e = torch.randint(0, E, (rows,), device="cuda", generator=g, dtype=torch.int32)
+    e[::50] = 3                                  # a heavy expert
+    e[e == 7] = 8                                # an empty expert
+    ref = moe.build_contiguous_layout(e, E)
+    p = moe.device_plan(e, E, 128, div=1, capacity=ref.m_cap)
+    torch.cuda.synchronize()
+    assert torch.equal(p.counts.long(), ref.counts)
+    assert torch.equal(p.block_expert, ref.m_indices)
+    assert torch.equal(p.slot_src >= 0, ref.src_row >= 0)
+    src, slot = p.slot_src.cpu().numpy(), p.slot_of_row.cpu().numpy()
+    assert (src[slot] == np.arange(rows)).all()
+    eh, be = e.cpu().numpy(), p.block_expert.cpu().numpy()
+    assert (be[slot // 128] == eh).all()
+    # sort-only form (align 1, div = top-k): slots are exactly the rows, ordered by expert
+    q = moe.device_plan(e, E, 1, div=4, capacity=rows)
+    torch.cuda.synchronize()
+    order = q.slot_src.cpu().numpy()
+    assert sorted(order.tolist()) == sorted((np.arange(rows) // 4).tolist())
+    es = eh[np.argsort(q.slot_of_row.cpu().numpy(), kind="stable")]
+    assert (np.diff(es) >= 0).all()
