@@ -72,18 +72,21 @@ struct Tile {
     bool skip;
 };
 
-// Static persistent schedule: CTA c takes tiles c, c + grid, c + 2*grid, ...  Tile ids walk
-// bands of `band` m-blocks, m fastest inside a band, so that the ~148 tiles in flight share a
-// few A row-blocks and B column-blocks in L2.
-template <int GTYPE>
+// Static persistent schedule: cluster c (one CTA, or a CTA pair) takes tiles c, c + C, c + 2C, ...
+// A tile is (128 * CL) x BLOCK_N; CTA `rank` of a pair owns rows [rank*128, rank*128 + 128) of it.
+// Tile ids walk bands of `band` m-tiles, m fastest inside a band, so that the tiles in flight
+// share a few A row-blocks and B column-blocks in L2.
+template <int GTYPE, int CL>
 struct Scheduler {
-    uint32_t next_id;
+    uint32_t next_id, stride, rank;
     uint32_t g = 0, g_first_tile = 0;  // masked: current group and its first tile id
-    __device__ explicit Scheduler() : next_id(blockIdx.x) {}
+    __device__ explicit Scheduler(uint32_t rank_) : next_id(blockIdx.x / CL), stride(gridDim.x / CL), rank(rank_) {}
+    __device__ bool first_tile_pending() const { return next_id == blockIdx.x / CL + stride; }
 
     __device__ bool next(const GemmParams& p, Tile& t) {
+        constexpr uint32_t kTileM = kBlockM * CL;
         const uint32_t id = next_id;
-        next_id += gridDim.x;
+        next_id += stride;
         t.skip = false;
         if (GTYPE != kMasked) {
             if (id >= p.num_m_blocks * p.num_n_blocks) return false;
@@ -92,7 +95,7 @@ struct Scheduler {
             const uint32_t mb0 = b * p.band;
             const uint32_t rows = min(p.band, p.num_m_blocks - mb0);
             const uint32_t nb = rem / rows, mb = mb0 + (rem - nb * rows);
-            t.a_row = mb * kBlockM;
+            t.a_row = mb * kTileM + rank * kBlockM;
             t.row_end = p.m;
             t.n0 = nb * p.block_n;
             t.b_row = t.n0;
@@ -106,12 +109,12 @@ struct Scheduler {
             while (g < p.num_groups) {
                 const int32_t mm = __ldg(p.layout + g);
                 const uint32_t rows = mm <= 0 ? 0u : min((uint32_t)mm, p.m);
-                const uint32_t mbs = (rows + kBlockM - 1) / kBlockM;
+                const uint32_t mbs = (rows + kTileM - 1) / kTileM;
                 const uint32_t cnt = mbs * p.num_n_blocks;
                 if (id < g_first_tile + cnt) {
                     const uint32_t rem = id - g_first_tile;
                     const uint32_t nb = rem / mbs, mb = rem - nb * mbs;
-                    t.a_row = g * p.m + mb * kBlockM;
+                    t.a_row = g * p.m + mb * kTileM + rank * kBlockM;
                     t.row_end = g * p.m + rows;
                     t.n0 = nb * p.block_n;
                     t.b_row = g * p.n + t.n0;
@@ -126,18 +129,21 @@ struct Scheduler {
 };
 
 struct __align__(8) Barriers {
-    uint64_t full[kMaxStages];      // A and B tiles landed
-    uint64_t sf_full[kMaxStages];   // SF rows landed (only on k-blocks that load SF)
-    uint64_t sf_ready[kMaxStages];  // SF rows transposed
+    uint64_t full[kMaxStages];      // A and B tiles landed (pair: both CTAs' tiles, on the leader's barrier)
+    uint64_t sf_full[kMaxStages];   // this CTA's SF rows landed (only on k-blocks that load SF)
+    uint64_t sf_ready[kMaxStages];  // SF rows transposed (pair: both CTAs arrive on the leader's barrier)
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
-    uint64_t tmem_empty[2];
+    uint64_t tmem_empty[2];         // pair: the leader's barrier collects both CTAs' epilogue warps
     uint32_t tmem_base;
     uint32_t abort;
 };
 static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 
-template <int KIND, int GTYPE>
+// CL = 1: one CTA per tile.  CL = 2: a CTA pair per 256-row tile (tcgen05 cta_group::2): each CTA
+// loads its own 128 rows of A and its own half of the B tile, the leader CTA issues MMAs that read
+// both CTAs' shared memory and write both CTAs' TMEM, each CTA drains its own accumulator.
+template <int KIND, int GTYPE, int CL>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -145,11 +151,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     constexpr bool kHasSf = KIND != kBf16;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // Dynamic shared memory: [barriers (512 B, padded to 1024)] [stage 0] [stage 1] ...
+    // (identical offsets in both CTAs of a pair: the launch gives every CTA the same window offset)
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     Barriers* bars = reinterpret_cast<Barriers*>(smem_raw + (smem_base - smem_u32(smem_raw)));
     const uint32_t stages_base = smem_base + 1024u;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t rank = CL == 2 ? cluster_ctarank() : 0u;
+    const bool leader = rank == 0;
     const WaitCtx wc{p.status, &bars->abort};
 
     if (threadIdx.x == 0) {
@@ -157,12 +166,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         for (uint32_t s = 0; s < p.num_stages; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
             mbar_init(smem_u32(&bars->sf_full[s]), 1);
-            mbar_init(smem_u32(&bars->sf_ready[s]), 1);
+            mbar_init(smem_u32(&bars->sf_ready[s]), CL);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         for (uint32_t s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&bars->tmem_full[s]), 1);
-            mbar_init(smem_u32(&bars->tmem_empty[s]), 4);
+            mbar_init(smem_u32(&bars->tmem_empty[s]), 4 * CL);
         }
         fence_barrier_init();
         tma_prefetch_desc(&tm_a);
@@ -173,59 +182,69 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     }
     if (warp == 2) {
-        tmem_alloc(smem_u32(&bars->tmem_base), kTmemCols);
-        tmem_relinquish();
+        tmem_alloc<CL>(smem_u32(&bars->tmem_base), kTmemCols);
+        tmem_relinquish<CL>();
     }
     tc_fence_before();
-    __syncthreads();
+    if (CL == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
 
     auto stage_addr = [&](uint32_t s) { return stages_base + s * p.stage_bytes; };
+    const bool tracing = p.trace != nullptr && blockIdx.x == 0;
 
     if (warp == 0) {
         // ===================================================== TMA producer (warp-converged, one lane issues)
-        Scheduler<GTYPE> sched;
+        Scheduler<GTYPE, CL> sched(rank);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
+        const uint32_t b_rows_per_cta = p.block_n / CL;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
             for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
-                if (p.trace && blockIdx.x == 0 && kb < 256 && sched.next_id == gridDim.x && lane == 0) p.trace[kb] = clock64();
-                const uint32_t bar = smem_u32(&bars->full[stage]);
+                if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[kb] = clock64();
                 const uint32_t sa = stage_addr(stage);
                 const bool ld_sfa = kHasSf && (kb % p.sfa_period == 0);
                 const bool ld_sfb = kHasSf && (kb % p.sfb_period == 0);
+                // Inner coordinate kx in elements: 128 bytes per k-block (128 FP8, 256 FP4 = 128 B, 64 BF16).
                 const int32_t kx = (int32_t)(kb * (KIND == kBf16 ? 64u : 128u));
                 if (elect_one()) {
-                // Scale factors go first and complete on their own barrier, so that their
-                // transposition overlaps the (much larger) A/B transfer.
-                if (ld_sfa || ld_sfb) {
-                    const uint32_t sbar = smem_u32(&bars->sf_full[stage]);
-                    mbar_arrive_expect_tx(sbar, (ld_sfa ? p.tx_sfa : 0u) + (ld_sfb ? p.tx_sfb : 0u));
-                    if (ld_sfa) tma_load_2d(&tm_sfa, sbar, sa + p.off_sfa, (int32_t)t.a_row, (int32_t)((kb / p.sfa_period) * p.sf_sub));
-                    if (ld_sfb) tma_load_2d(&tm_sfb, sbar, sa + p.off_sfb, (int32_t)t.b_row, (int32_t)((kb / p.sfb_period) * p.sf_sub));
-                }
-                mbar_arrive_expect_tx(bar, p.tx_ab);
-                // Inner coordinate kx in elements: 128 bytes per k-block (128 FP8, 256 FP4 = 128 B, 64 BF16).
-                tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
-                tma_load_2d(&tm_b, bar, sa + p.off_b, kx, (int32_t)t.b_row);
+                    // Scale factors go first and complete on this CTA's own barrier, so that their
+                    // transposition overlaps the (much larger) A/B transfer.
+                    if (ld_sfa || ld_sfb) {
+                        const uint32_t sbar = smem_u32(&bars->sf_full[stage]);
+                        mbar_arrive_expect_tx(sbar, (ld_sfa ? p.tx_sfa : 0u) + (ld_sfb ? p.tx_sfb : 0u));
+                        if (ld_sfa) tma_load_2d(&tm_sfa, sbar, sa + p.off_sfa, (int32_t)t.a_row, (int32_t)((kb / p.sfa_period) * p.sf_sub));
+                        if (ld_sfb) tma_load_2d(&tm_sfb, sbar, sa + p.off_sfb, (int32_t)t.b_row, (int32_t)((kb / p.sfb_period) * p.sf_sub));
+                    }
+                    if (CL == 1) {
+                        const uint32_t bar = smem_u32(&bars->full[stage]);
+                        mbar_arrive_expect_tx(bar, p.tx_ab);
+                        tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
+                        tma_load_2d(&tm_b, bar, sa + p.off_b, kx, (int32_t)t.b_row);
+                    } else {
+                        // both CTAs' tiles complete on the leader's barrier; the leader announces the bytes of both
+                        if (leader) mbar_arrive_expect_tx(smem_u32(&bars->full[stage]), 2u * p.tx_ab);
+                        const uint32_t bar = mapa(smem_u32(&bars->full[stage]), 0);
+                        tma_load_2d_pair(&tm_a, bar, sa, kx, (int32_t)t.a_row);
+                        tma_load_2d_pair(&tm_b, bar, sa + p.off_b, kx, (int32_t)(t.b_row + rank * b_rows_per_cta));
+                    }
                 }
                 __syncwarp();
-                if (p.trace && blockIdx.x == 0 && kb < 256 && sched.next_id == gridDim.x && lane == 0) p.trace[256 + kb] = clock64();
+                if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[256 + kb] = clock64();
                 if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 && leader) {
         // ===================================================== MMA issuer (warp-converged, one lane issues)
-        Scheduler<GTYPE> sched;
+        Scheduler<GTYPE, CL> sched(rank);
         Tile t;
         uint32_t stage = 0, phase = 0, tile_count = 0;
         uint32_t sf_bits = 0;  // per-stage parity of sf_ready (it completes only on SF k-blocks)
-        const uint32_t idesc = KIND == kBf16 ? make_idesc_bf16(kBlockM, p.block_n)
-                                             : make_idesc_bs(KIND == kFp4 ? 1u : 0u, kBlockM, p.block_n);
+        const uint32_t idesc = KIND == kBf16 ? make_idesc_bf16(kBlockM * CL, p.block_n)
+                                             : make_idesc_bs(KIND == kFp4 ? 1u : 0u, kBlockM * CL, p.block_n);
         bool ok = true;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
@@ -241,54 +260,59 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     sf_bits ^= 1u << stage;
                 }
                 tc_fence_after();
-                if (p.trace && blockIdx.x == 0 && kb < 256 && sched.next_id == gridDim.x && lane == 0) p.trace[512 + kb] = clock64();
+                if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[512 + kb] = clock64();
                 const uint32_t sa = stage_addr(stage);
                 if (elect_one()) {
-                if (kHasSf) {
-                    if (kb % p.sfa_period == 0) {
-                        for (uint32_t j = 0; j < p.sf_sub; ++j)
-                            tc_cp_32x128b_warpx4(tmem + kSfaCol + j * 4u, make_sf_desc(sa + p.off_sfa + j * 512u));
+                    if (kHasSf) {
+                        if (kb % p.sfa_period == 0) {
+                            for (uint32_t j = 0; j < p.sf_sub; ++j)
+                                tc_cp_32x128b_warpx4<CL>(tmem + kSfaCol + j * 4u, make_sf_desc(sa + p.off_sfa + j * 512u));
+                        }
+                        if (kb % p.sfb_period == 0) {
+                            for (uint32_t j = 0; j < p.sf_sub; ++j)
+                                for (uint32_t c = 0; c < p.sfb_chunks; ++c)
+                                    tc_cp_32x128b_warpx4<CL>(tmem + kSfbCol + (j * p.sfb_chunks + c) * 4u,
+                                                             make_sf_desc(sa + p.off_sfb + (j * p.sfb_chunks + c) * 512u));
+                        }
                     }
-                    if (kb % p.sfb_period == 0) {
-                        for (uint32_t j = 0; j < p.sf_sub; ++j)
-                            for (uint32_t c = 0; c < p.sfb_chunks; ++c)
-                                tc_cp_32x128b_warpx4(tmem + kSfbCol + (j * p.sfb_chunks + c) * 4u,
-                                                     make_sf_desc(sa + p.off_sfb + (j * p.sfb_chunks + c) * 512u));
-                    }
-                }
-                const uint64_t a_desc = make_kmajor_sw128_desc(sa);
-                const uint64_t b_desc = make_kmajor_sw128_desc(sa + p.off_b);
+                    const uint64_t a_desc = make_kmajor_sw128_desc(sa);
+                    const uint64_t b_desc = make_kmajor_sw128_desc(sa + p.off_b);
 #pragma unroll
-                for (uint32_t k = 0; k < 4; ++k) {
-                    // 32 bytes of K per MMA (32 FP8, 64 FP4, 16 BF16): +2 in the >>4 address field.
-                    const uint64_t ad = a_desc + 2u * k, bd = b_desc + 2u * k;
-                    const uint32_t acc = (kb | k) != 0u ? 1u : 0u;
-                    if (KIND == kBf16) {
-                        tc_mma_bf16(d_tmem, ad, bd, idesc, acc);
-                    } else if (KIND == kFp8) {
-                        // one SF byte per row per MMA: byte k of the word (gran 32), or the
-                        // byte of this k-block within its 512-wide SF row (gran 128)
-                        const uint32_t ida = p.sfa_period == 1 ? k : (kb & 3u);
-                        const uint32_t idb = p.sfb_period == 1 ? k : (kb & 3u);
-                        tc_mma_mxf8(d_tmem, ad, bd, idesc_with_sf_ids(idesc, ida, idb), acc, tmem + kSfaCol, tmem + kSfbCol);
-                    } else {
-                        // two SF bytes per row per MMA (64 elements): half-word (k & 1) of SF row (k >> 1)
-                        const uint32_t sub = k >> 1, id = (k & 1u) * 2u;
-                        tc_mma_mxf4(d_tmem, ad, bd, idesc_with_sf_ids(idesc, id, id), acc,
-                                    tmem + kSfaCol + sub * 4u, tmem + kSfbCol + sub * p.sfb_chunks * 4u);
+                    for (uint32_t k = 0; k < 4; ++k) {
+                        // 32 bytes of K per MMA (32 FP8, 64 FP4, 16 BF16): +2 in the >>4 address field.
+                        const uint64_t ad = a_desc + 2u * k, bd = b_desc + 2u * k;
+                        const uint32_t acc = (kb | k) != 0u ? 1u : 0u;
+                        if (KIND == kBf16) {
+                            tc_mma_bf16<CL>(d_tmem, ad, bd, idesc, acc);
+                        } else if (KIND == kFp8) {
+                            // one SF byte per row per MMA: byte k of the word (gran 32), or the
+                            // byte of this k-block within its 512-wide SF row (gran 128)
+                            const uint32_t ida = p.sfa_period == 1 ? k : (kb & 3u);
+                            const uint32_t idb = p.sfb_period == 1 ? k : (kb & 3u);
+                            tc_mma_mxf8<CL>(d_tmem, ad, bd, idesc_with_sf_ids(idesc, ida, idb), acc, tmem + kSfaCol, tmem + kSfbCol);
+                        } else {
+                            // two SF bytes per row per MMA (64 elements): half-word (k & 1) of SF row (k >> 1)
+                            const uint32_t sub = k >> 1, id = (k & 1u) * 2u;
+                            tc_mma_mxf4<CL>(d_tmem, ad, bd, idesc_with_sf_ids(idesc, id, id), acc,
+                                            tmem + kSfaCol + sub * 4u, tmem + kSfbCol + sub * p.sfb_chunks * 4u);
+                        }
                     }
-                }
-                tc_commit(smem_u32(&bars->empty[stage]));
-                if (kb + 1 == p.num_k_blocks) tc_commit(smem_u32(&bars->tmem_full[as]));
+                    // free the stage in both CTAs / publish the accumulator to both epilogues
+                    tc_commit<CL>(smem_u32(&bars->empty[stage]));
+                    if (CL == 2) tc_commit<CL>(mapa(smem_u32(&bars->empty[stage]), 1));
+                    if (kb + 1 == p.num_k_blocks) {
+                        tc_commit<CL>(smem_u32(&bars->tmem_full[as]));
+                        if (CL == 2) tc_commit<CL>(mapa(smem_u32(&bars->tmem_full[as]), 1));
+                    }
                 }
                 __syncwarp();
-                if (p.trace && blockIdx.x == 0 && kb < 256 && sched.next_id == gridDim.x && lane == 0) p.trace[768 + kb] = clock64();
+                if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[768 + kb] = clock64();
                 if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 2 && kHasSf) {
         // ===================================================== SF transposer
-        Scheduler<GTYPE> sched;
+        Scheduler<GTYPE, CL> sched(rank);
         Tile t;
         uint32_t stage = 0, sf_bits = 0;
         bool ok = true;
@@ -299,7 +323,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (has_a || has_b) {
                     const uint32_t parity = (sf_bits >> stage) & 1u;
                     sf_bits ^= 1u << stage;
-                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->sf_full[stage]), parity, wc, kWaitFull));
+                    ok = DG_WARP_WAIT(smem_u32(&bars->sf_full[stage]), parity, wc, kWaitFull);
                     if (!ok) break;
                     uint32_t* sfa = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfa - smem_u32(smem_raw)));
                     uint32_t* sfb = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfb - smem_u32(smem_raw)));
@@ -324,14 +348,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
+                    if (lane == 0) {
+                        if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
+                        else mbar_arrive_cluster(mapa(smem_u32(&bars->sf_ready[stage]), 0));
+                    }
                 }
                 if (++stage == p.num_stages) stage = 0;
             }
         }
     } else if (warp >= 4) {
         // ===================================================== epilogue
-        Scheduler<GTYPE> sched;
+        Scheduler<GTYPE, CL> sched(rank);
         Tile t;
         const uint32_t q = warp - 4u;  // TMEM lane quarter == warp index % 4
         uint32_t tile_count = 0;
@@ -341,8 +368,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             if (t.skip) continue;
             const uint32_t as = tile_count & 1u, aphase = (tile_count >> 1) & 1u;
             ++tile_count;
-            ok = mbar_wait(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull);
-            ok = __all_sync(0xffffffffu, ok);
+            ok = DG_WARP_WAIT(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull);
             if (!ok) break;
             tc_fence_after();
             const uint32_t row = t.a_row + q * 32u + lane;
@@ -355,10 +381,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 tmem_ld_x32(taddr + c * 32u, r);
                 tmem_ld_wait();
                 if (c + 1 == chunks) {
-                    // accumulator drained into registers: hand the TMEM stage back
+                    // accumulator drained into registers: hand the TMEM stage back to the MMA issuer
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+                    if (lane == 0) {
+                        if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+                        else mbar_arrive_cluster(mapa(smem_u32(&bars->tmem_empty[as]), 0));
+                    }
                 }
                 const uint32_t col0 = t.n0 + c * 32u;
                 if (!row_ok || col0 >= p.n) continue;
@@ -418,11 +447,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     }
 
+    // The peer's shared memory and barriers are in use until the leader's last MMA and commit have
+    // completed, which every epilogue has observed by now: both CTAs leave together.
     tc_fence_before();
-    __syncthreads();
+    if (CL == 2) cluster_sync_all(); else __syncthreads();
     if (warp == 2) {
         tc_fence_after();
-        tmem_dealloc(tmem, kTmemCols);
+        tmem_dealloc<CL>(tmem, kTmemCols);
     }
 }
 
@@ -432,6 +463,7 @@ struct Plan {
     uint32_t smem_bytes;
     uint32_t grid;
     uint32_t num_tiles;
+    uint32_t cluster;   // CTAs per tile: 1, or 2 (CTA pair)
 };
 
 static unsigned long long* g_trace = nullptr;  // set by dg_debug_set_trace (development aid)
@@ -441,19 +473,19 @@ static uint32_t env_u32(const char* name, uint32_t dflt) {
     return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
 }
 
-// Tile choice.  BLOCK_M is fixed at 128 (one UMMA M); BLOCK_N in {32..224 step 32} (256 for
-// BF16, which needs no SF columns) is chosen to minimise waves x per-tile cost, where a tile's
-// cost is the larger of its MMA time (~BLOCK_N) and its operand traffic (~128 + BLOCK_N).
-// DG_BLOCK_N / DG_NUM_STAGES override (the reference's DG_* overrides: heuristics.rs:41-58).
-static uint32_t pick_block_n(int kind, uint32_t m_blocks_total, uint32_t n, uint32_t sms) {
+// Tile choice.  A tile is (128 * cluster) x BLOCK_N with BLOCK_N in {32..224 step 32} (256 for
+// BF16, which needs no SF columns in TMEM), chosen to minimise waves x per-tile cost, where a
+// tile's cost is its MMA time (~BLOCK_N) plus a share of its operand traffic and a fixed part.
+// DG_BLOCK_N / DG_NUM_STAGES / DG_CLUSTER override (the reference's DG_* overrides: heuristics.rs:41-58).
+static uint32_t pick_block_n(int kind, uint32_t m_tiles_total, uint32_t n, uint32_t units) {
     const uint32_t max_bn = kind == kBf16 ? 256u : 224u;
     const uint32_t forced = env_u32("DG_BLOCK_N", 0);
     if (forced >= 32 && forced <= max_bn && forced % 32 == 0) return forced;
     uint32_t best = 32;
     double best_cost = 1e30;
     for (uint32_t bn = 32; bn <= max_bn; bn += 32) {
-        const uint64_t tiles = (uint64_t)m_blocks_total * ceil_div(n, bn);
-        const uint64_t waves = (tiles + sms - 1) / sms;
+        const uint64_t tiles = (uint64_t)m_tiles_total * ceil_div(n, bn);
+        const uint64_t waves = (tiles + units - 1) / units;
         const double per_tile = (double)bn + 0.25 * (128.0 + bn) + 24.0;
         const double cost = (double)waves * per_tile;
         if (cost < best_cost - 1e-9) { best_cost = cost; best = bn; }
@@ -469,24 +501,34 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     const uint32_t block_k = kind == kFp4 ? 256u : (kind == kFp8 ? 128u : 64u);
     p.m = m; p.n = n; p.num_groups = num_groups;
     p.num_k_blocks = k / block_k;
-    uint32_t m_blocks_total;
-    if (gtype == kMasked) m_blocks_total = num_groups * ceil_div(expected_m ? expected_m : m, kBlockM);
-    else m_blocks_total = ceil_div(m, kBlockM);
-    p.block_n = pick_block_n(kind, m_blocks_total, n, sms);
-    p.num_m_blocks = gtype == kMasked ? ceil_div(m, kBlockM) : ceil_div(m, kBlockM);
+    // CTA pairs (256-row tiles) halve the B traffic per SM; they need at least two row blocks
+    // that share B.  The contiguous grouped layout switches expert every 128 rows, so it stays on
+    // single CTAs.
+    const uint32_t rows_per_group = gtype == kMasked ? (expected_m ? expected_m : m) : m;
+    uint32_t cl = (gtype != kContiguous && rows_per_group > kBlockM) ? 2u : 1u;
+    const uint32_t forced_cl = env_u32("DG_CLUSTER", 0);
+    if ((forced_cl == 1 || forced_cl == 2) && gtype != kContiguous) cl = forced_cl;
+    plan->cluster = cl;
+    const uint32_t tile_m = kBlockM * cl;
+    const uint32_t units = sms / cl;
+    uint32_t m_tiles_total;
+    if (gtype == kMasked) m_tiles_total = num_groups * ceil_div(rows_per_group, tile_m);
+    else m_tiles_total = ceil_div(m, tile_m);
+    p.block_n = pick_block_n(kind, m_tiles_total, n, units);
+    p.num_m_blocks = ceil_div(m, tile_m);
     p.num_n_blocks = ceil_div(n, p.block_n);
-    p.band = env_u32("DG_BAND", 8);
-    if (p.band == 0) p.band = 8;
+    p.band = env_u32("DG_BAND", 8 / cl);
+    if (p.band == 0) p.band = 8 / cl;
     const bool has_sf = kind != kBf16;
     p.sf_sub = kind == kFp4 ? 2u : 1u;
     p.sfb_chunks = ceil_div(p.block_n, 128u);
     p.sfa_period = gran_a == 128 ? 4u : 1u;
     p.sfb_period = gran_b == 128 ? 4u : 1u;
-    const uint32_t a_bytes = kBlockM * 128u, b_bytes = p.block_n * 128u;
+    const uint32_t a_bytes = kBlockM * 128u, b_bytes = p.block_n / cl * 128u;   // per CTA
     const uint32_t sfa_bytes = has_sf ? p.sf_sub * 512u : 0u;
     const uint32_t sfb_bytes = has_sf ? p.sf_sub * p.sfb_chunks * 512u : 0u;
     p.off_b = a_bytes;
-    p.off_sfa = a_bytes + b_bytes;
+    p.off_sfa = align_up(a_bytes + b_bytes, 1024u);
     p.off_sfb = p.off_sfa + sfa_bytes;
     p.stage_bytes = align_up(p.off_sfb + sfb_bytes, 1024u);
     p.tx_ab = a_bytes + b_bytes;
@@ -501,26 +543,24 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     if (stages < 2) return fail(DG_ERR_RUNTIME, "shared memory budget %u B too small for a %u-wide tile", budget, p.block_n);
     p.num_stages = stages;
     plan->smem_bytes = fixed + stages * p.stage_bytes;
-    plan->num_tiles = gtype == kMasked ? m_blocks_total * p.num_n_blocks : p.num_m_blocks * p.num_n_blocks;
-    uint32_t grid = sms;
-    if (gtype != kMasked && plan->num_tiles < grid) grid = plan->num_tiles;
-    if (gtype == kMasked) {
-        const uint32_t worst = num_groups * ceil_div(m, kBlockM) * p.num_n_blocks;
-        if (worst < grid) grid = worst;
-    }
-    plan->grid = grid ? grid : 1;
+    plan->num_tiles = gtype == kMasked ? m_tiles_total * p.num_n_blocks : p.num_m_blocks * p.num_n_blocks;
+    uint32_t clusters = units;
+    const uint32_t worst = gtype == kMasked ? num_groups * ceil_div(m, tile_m) * p.num_n_blocks : plan->num_tiles;
+    if (worst < clusters) clusters = worst;
+    if (clusters == 0) clusters = 1;
+    plan->grid = clusters * cl;
     p.status = dev->status;
     p.trace = g_trace;
     if (env_u32("DG_PRINT_CONFIGS", 0))
-        fprintf(stderr, "[deepgemm_b200] kind=%d gtype=%d m=%u n=%u k=%u groups=%u -> block 128x%ux%u stages=%u smem=%u grid=%u tiles=%u\n",
-                kind, gtype, m, n, k, num_groups, p.block_n, block_k, stages, plan->smem_bytes, plan->grid, plan->num_tiles);
+        fprintf(stderr, "[deepgemm_b200] kind=%d gtype=%d m=%u n=%u k=%u groups=%u -> tile %ux%ux%u cluster=%u stages=%u smem=%u grid=%u tiles=%u\n",
+                kind, gtype, m, n, k, num_groups, tile_m, p.block_n, block_k, cl, stages, plan->smem_bytes, plan->grid, plan->num_tiles);
     return DG_OK;
 }
 
-template <int KIND, int GTYPE>
+template <int KIND, int GTYPE, int CL>
 static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                       const CUtensorMap& tsb, cudaStream_t s) {
-    auto* fn = gemm_kernel<KIND, GTYPE>;
+    auto* fn = gemm_kernel<KIND, GTYPE, CL>;
     static thread_local uint32_t configured[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -528,9 +568,20 @@ static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap
         DG_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem_bytes));
         configured[dev & 63] = plan.smem_bytes;
     }
-    fn<<<plan.grid, 256, plan.smem_bytes, s>>>(ta, tb, tsa, tsb, plan.p);
-    dg::note_launch();
-    DG_CUDA_CHECK(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(plan.grid);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = plan.smem_bytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, ta, tb, tsa, tsb, plan.p));
+    note_launch();
     return DG_OK;
 }
 
@@ -629,7 +680,7 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     const uint32_t box_inner = kind == kBf16 ? 64u : 128u;
     if ((st = make_tmap_2d(&ta, dt, ebytes, a->data, inner, (uint64_t)groups_a * m, pitch_a, box_inner, kBlockM,
                            CU_TENSOR_MAP_SWIZZLE_128B, "A")) != DG_OK) return st;
-    if ((st = make_tmap_2d(&tb, dt, ebytes, b->data, inner, (uint64_t)groups_b * n, pitch_b, box_inner, p.block_n,
+    if ((st = make_tmap_2d(&tb, dt, ebytes, b->data, inner, (uint64_t)groups_b * n, pitch_b, box_inner, p.block_n / plan.cluster,
                            CU_TENSOR_MAP_SWIZZLE_128B, "B")) != DG_OK) return st;
     if (has_sf) {
         if ((st = make_tmap_2d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a->sf.data, a->sf.cols, a->sf.rows,
@@ -640,10 +691,14 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
         tsa = ta; tsb = tb;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-#define DG_DISPATCH(K, G) if (kind == K && gtype == G) return launch<K, G>(plan, ta, tb, tsa, tsb, s)
-    DG_DISPATCH(kFp8, kNormal); DG_DISPATCH(kFp8, kContiguous); DG_DISPATCH(kFp8, kMasked);
-    DG_DISPATCH(kFp4, kNormal); DG_DISPATCH(kFp4, kContiguous); DG_DISPATCH(kFp4, kMasked);
-    DG_DISPATCH(kBf16, kNormal); DG_DISPATCH(kBf16, kContiguous); DG_DISPATCH(kBf16, kMasked);
+#define DG_DISPATCH(K, G)                                                                  \
+    if (kind == K && gtype == G) {                                                         \
+        if (plan.cluster == 2) return launch<K, G, 2>(plan, ta, tb, tsa, tsb, s);          \
+        return launch<K, G, 1>(plan, ta, tb, tsa, tsb, s);                                 \
+    }
+    DG_DISPATCH(kFp8, kNormal) DG_DISPATCH(kFp8, kContiguous) DG_DISPATCH(kFp8, kMasked)
+    DG_DISPATCH(kFp4, kNormal) DG_DISPATCH(kFp4, kContiguous) DG_DISPATCH(kFp4, kMasked)
+    DG_DISPATCH(kBf16, kNormal) DG_DISPATCH(kBf16, kContiguous) DG_DISPATCH(kBf16, kMasked)
 #undef DG_DISPATCH
     return fail(DG_ERR_RUNTIME, "no kernel for kind %d / type %d", kind, gtype);
 }
@@ -724,7 +779,8 @@ int32_t dg_get_gemm_config(int32_t dtype, int32_t kind, uint32_t m, uint32_t n, 
     cfg->smem_bytes = plan.smem_bytes;
     cfg->num_tiles = plan.num_tiles;
     cfg->grid = plan.grid;
-    cfg->cluster = 1;
+    cfg->cluster = plan.cluster;
+    cfg->block_m = dg::kBlockM * plan.cluster;
     return DG_OK;
 }
 

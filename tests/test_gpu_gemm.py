@@ -20,11 +20,14 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def _clean_env():
     yield
-    for v in ("DG_BLOCK_N", "DG_NUM_STAGES", "DG_BAND"):
+    for v in ("DG_BLOCK_N", "DG_NUM_STAGES", "DG_BAND", "DG_CLUSTER"):
         os.environ.pop(v, None)
 
 
-def run_dense(kind, m, n, k, gran_a=32, gran_b=32, block128_b=False, f32=False, seed=0, block_n=None, stages=None):
+def run_dense(kind, m, n, k, gran_a=32, gran_b=32, block128_b=False, f32=False, seed=0, block_n=None, stages=None,
+              cluster=None):
+    if cluster:
+        os.environ["DG_CLUSTER"] = str(cluster)
     if block_n:
         os.environ["DG_BLOCK_N"] = str(block_n)
     if stages:
@@ -88,6 +91,22 @@ def test_bf16_block_n(block_n):
 ])
 def test_ragged_shapes(kind, m, n, k):
     run_dense(kind, m, n, k, seed=m + n)
+
+
+@pytest.mark.parametrize("cluster", [1, 2])
+@pytest.mark.parametrize("kind,m,n,k", [
+    ("fp8", 512, 896, 1024), ("fp8", 100, 200, 256), ("fp8", 300, 1000, 640), ("fp8", 1, 8, 128),
+    ("fp4", 384, 448, 1024), ("bf16", 384, 512, 512), ("bf16", 130, 72, 192),
+])
+def test_single_cta_and_cta_pair_tiles(cluster, kind, m, n, k):
+    """Both tilings on the same shapes: one CTA per 128-row tile, and a CTA pair per 256-row tile
+    (including shapes where the second CTA of the last pair has no valid row)."""
+    run_dense(kind, m, n, k, gran_a=128 if kind == "fp8" else 32, gran_b=32, seed=m + cluster, cluster=cluster)
+
+
+@pytest.mark.parametrize("cluster,block_n", [(2, 32), (2, 96), (2, 224), (1, 224)])
+def test_cta_pair_block_n(cluster, block_n):
+    run_dense("fp8", 512, 1344, 2048, gran_a=128, gran_b=128, seed=block_n, block_n=block_n, cluster=cluster)
 
 
 @pytest.mark.parametrize("stages", [2, 3])
@@ -250,7 +269,7 @@ def test_m_grouped_masked_reference_test_shape():
 
 def test_config_introspection():
     cfg = get_gemm_config(Dtype.Fp8, 0, 4096, 7168, 16384)
-    assert cfg["block_m"] == 128 and cfg["block_k"] == 128 and cfg["block_n"] % 32 == 0
+    assert cfg["block_m"] == 128 * cfg["cluster"] and cfg["block_k"] == 128 and cfg["block_n"] % 32 == 0
     assert cfg["smem_bytes"] <= 232448 and cfg["num_stages"] >= 2
     assert get_gemm_config(Dtype.Fp4, 0, 8192, 8192, 8192)["block_k"] == 256
     assert get_gemm_config(Dtype.Bf16, 0, 2048, 2048, 2048)["block_k"] == 64
