@@ -36,6 +36,8 @@ constexpr uint32_t kAccStageCols = 256;   // accumulator stage s starts at colum
 constexpr uint32_t kSfaCol = 224;         // SF columns live above a <=224-wide accumulator
 constexpr uint32_t kSfbCol = 232;
 constexpr uint32_t kSmemBarrierBytes = 512;
+constexpr uint32_t kMaxPairedBlocks = 4096;   // contiguous layout on CTA pairs: m_indices entries the in-kernel tile list holds
+constexpr uint32_t kPairedListBytes = 17 * 1024;  // tile list + run list (u16 each), 1024-aligned
 
 enum Kind : int { kFp8 = 0, kFp4 = 1, kBf16 = 2 };
 enum GType : int { kNormal = 0, kContiguous = 1, kMasked = 2 };
@@ -60,7 +62,10 @@ struct GemmParams {
     uint64_t ldd;          // D row pitch in elements
     void* d;
     const int32_t* layout; // m_indices (contiguous) or masked_m (masked)
+    const int32_t* d_row_map;  // optional: D row of every A row (negative = drop the row); NULL = identity
     uint32_t* status;
+    uint32_t pf_chunk;          // k-blocks per L2 prefetch of B (0 = off)
+    uint32_t dbg;               // development switches (timing experiments only; results become wrong)
     unsigned long long* trace;  // debug: per-k-block clock64 stamps of CTA 0's first tile (or null)
 };
 
@@ -80,7 +85,12 @@ template <int GTYPE, int CL>
 struct Scheduler {
     uint32_t next_id, stride, rank;
     uint32_t g = 0, g_first_tile = 0;  // masked: current group and its first tile id
+    const uint16_t* mtiles = nullptr;  // contiguous on CTA pairs: first block of every m-tile, bit 15 = both blocks share the expert
+    const uint16_t* run_first = nullptr;  // first m-tile of every run of equal experts, [n_runs + 1]
+    uint32_t n_mtiles = 0, n_runs = 0;
     __device__ explicit Scheduler(uint32_t rank_) : next_id(blockIdx.x / CL), stride(gridDim.x / CL), rank(rank_) {}
+    __device__ Scheduler(uint32_t rank_, const uint16_t* mt, uint32_t n, const uint16_t* rf, uint32_t nr)
+        : next_id(blockIdx.x / CL), stride(gridDim.x / CL), rank(rank_), mtiles(mt), run_first(rf), n_mtiles(n), n_runs(nr) {}
     __device__ bool first_tile_pending() const { return next_id == blockIdx.x / CL + stride; }
 
     __device__ bool next(const GemmParams& p, Tile& t) {
@@ -88,7 +98,30 @@ struct Scheduler {
         const uint32_t id = next_id;
         next_id += stride;
         t.skip = false;
-        if (GTYPE != kMasked) {
+        if (GTYPE == kContiguous && CL == 2) {
+            // m-tiles come from the list built at kernel start: a pair of 128-row blocks of one
+            // expert, or a single block whose partner rows (the next block, another expert's) are
+            // computed by the second CTA and dropped.
+            // Tile order: one expert after the other; inside an expert its m-tiles are fastest, so
+            // the tiles that share a weight tile run next to each other and the expert's few A
+            // blocks are reused across all its n-blocks.
+            if (id >= n_mtiles * p.num_n_blocks) return false;
+            uint32_t lo = 0, hi = n_runs;   // last run with run_first[run] * num_n_blocks <= id
+            while (hi - lo > 1) {
+                const uint32_t mid = (lo + hi) >> 1;
+                if ((uint32_t)run_first[mid] * p.num_n_blocks <= id) lo = mid; else hi = mid;
+            }
+            const uint32_t mt0 = run_first[lo], rows = run_first[lo + 1] - mt0;
+            const uint32_t rem = id - mt0 * p.num_n_blocks;
+            const uint32_t nb = rem / rows, mt = mt0 + (rem - nb * rows);
+            const uint32_t entry = mtiles[mt], blk = entry & 0x7fffu;
+            const bool paired = (entry & 0x8000u) != 0;
+            t.a_row = (blk + rank) * kBlockM;
+            t.row_end = (rank == 0 || paired) ? p.m : 0u;
+            t.n0 = nb * p.block_n;
+            t.b_row = (uint32_t)__ldg(p.layout + blk) * p.n + t.n0;
+            return true;
+        } else if (GTYPE != kMasked) {
             if (id >= p.num_m_blocks * p.num_n_blocks) return false;
             const uint32_t per_band = p.band * p.num_n_blocks;
             const uint32_t b = id / per_band, rem = id - b * per_band;
@@ -137,6 +170,7 @@ struct __align__(8) Barriers {
     uint64_t tmem_empty[2];         // pair: the leader's barrier collects both CTAs' epilogue warps
     uint32_t tmem_base;
     uint32_t abort;
+    uint32_t n_mtiles, n_runs;
 };
 static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 
@@ -147,14 +181,18 @@ template <int KIND, int GTYPE, int CL>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap tm_bpf, const GemmParams p) {
     constexpr bool kHasSf = KIND != kBf16;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // Dynamic shared memory: [barriers (512 B, padded to 1024)] [stage 0] [stage 1] ...
     // (identical offsets in both CTAs of a pair: the launch gives every CTA the same window offset)
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     Barriers* bars = reinterpret_cast<Barriers*>(smem_raw + (smem_base - smem_u32(smem_raw)));
-    const uint32_t stages_base = smem_base + 1024u;
+    constexpr bool kPairedContig = GTYPE == kContiguous && CL == 2;
+    // [tile list, 16 KB] only for the contiguous layout on CTA pairs
+    uint16_t* mtiles = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(bars) + 1024);
+    uint16_t* run_first = mtiles + kMaxPairedBlocks;    // [kMaxPairedBlocks + 1], padded to 17 KB
+    const uint32_t stages_base = smem_base + 1024u + (kPairedContig ? kPairedListBytes : 0u);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t rank = CL == 2 ? cluster_ctarank() : 0u;
@@ -185,17 +223,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         tmem_alloc<CL>(smem_u32(&bars->tmem_base), kTmemCols);
         tmem_relinquish<CL>();
     }
+    if (kPairedContig && warp == 3) {
+        // Tile list of the contiguous layout: walk m_indices 32 blocks at a time.  Inside a run of
+        // equal experts every second block starts a tile; it is a pair when the next block has
+        // the same expert.  Both CTAs of a pair build the same list.
+        const uint32_t nblk = p.m / kBlockM;
+        uint32_t ntiles = 0, nruns = 0, carry_start = 0;
+        int32_t carry_e = -2;
+        for (uint32_t base = 0; base < nblk; base += 32u) {
+            const uint32_t b = base + lane;
+            int32_t e = -3;
+            if (b < nblk) {
+                e = __ldg(p.layout + b);
+                if (e < 0 || (uint32_t)e >= p.num_groups) e = -1;
+            }
+            int32_t e_prev = __shfl_up_sync(0xffffffffu, e, 1);
+            if (lane == 0) e_prev = carry_e;
+            const uint32_t bnd = __ballot_sync(0xffffffffu, e != e_prev);
+            const uint32_t upto = bnd & (0xffffffffu >> (31u - lane));
+            const uint32_t run_start = upto ? base + (31u - (uint32_t)__clz((int)upto)) : carry_start;
+            int32_t e_next = __shfl_down_sync(0xffffffffu, e, 1);
+            if (lane == 31) {
+                e_next = -3;
+                if (b + 1 < nblk) {
+                    e_next = __ldg(p.layout + b + 1);
+                    if (e_next < 0 || (uint32_t)e_next >= p.num_groups) e_next = -1;
+                }
+            }
+            const bool is_start = b < nblk && e >= 0 && ((b - run_start) & 1u) == 0;
+            const uint32_t starts = __ballot_sync(0xffffffffu, is_start);
+            const uint32_t my_tile = ntiles + __popc(starts & ((1u << lane) - 1u));
+            if (is_start) mtiles[my_tile] = (uint16_t)(b | (e_next == e ? 0x8000u : 0u));
+            // a run of a valid expert begins where the expert changes
+            const bool run_begin = b < nblk && e >= 0 && e != e_prev;
+            const uint32_t begins = __ballot_sync(0xffffffffu, run_begin);
+            if (run_begin) run_first[nruns + __popc(begins & ((1u << lane) - 1u))] = (uint16_t)my_tile;
+            nruns += __popc(begins);
+            ntiles += __popc(starts);
+            carry_start = __shfl_sync(0xffffffffu, run_start, 31);
+            carry_e = __shfl_sync(0xffffffffu, e, 31);
+        }
+        if (lane == 0) {
+            run_first[nruns] = (uint16_t)ntiles;
+            bars->n_mtiles = ntiles;
+            bars->n_runs = nruns;
+        }
+    }
     tc_fence_before();
     if (CL == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+    const uint32_t n_mtiles = kPairedContig ? *reinterpret_cast<volatile uint32_t*>(&bars->n_mtiles) : 0u;
+    const uint32_t n_runs = kPairedContig ? *reinterpret_cast<volatile uint32_t*>(&bars->n_runs) : 0u;
 
     auto stage_addr = [&](uint32_t s) { return stages_base + s * p.stage_bytes; };
     const bool tracing = p.trace != nullptr && blockIdx.x == 0;
 
     if (warp == 0) {
         // ===================================================== TMA producer (warp-converged, one lane issues)
-        Scheduler<GTYPE, CL> sched(rank);
+        Scheduler<GTYPE, CL> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
@@ -211,6 +297,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 // Inner coordinate kx in elements: 128 bytes per k-block (128 FP8, 256 FP4 = 128 B, 64 BF16).
                 const int32_t kx = (int32_t)(kb * (KIND == kBf16 ? 64u : 128u));
                 if (elect_one()) {
+                    // Weights stream from HBM in 128-byte row pieces, one piece per k-block; asking
+                    // L2 for `pf_chunk` k-blocks of every row at once (two chunks ahead) turns that
+                    // into long contiguous DRAM reads.
+                    if (p.pf_chunk && kb % p.pf_chunk == 0) {
+                        const int32_t brow = (int32_t)(t.b_row + rank * b_rows_per_cta);
+                        if (kb == 0) {
+                            tma_prefetch_2d(&tm_bpf, 0, brow);
+                            if (p.pf_chunk < p.num_k_blocks) tma_prefetch_2d(&tm_bpf, (int32_t)(p.pf_chunk * 16u), brow);
+                        }
+                        if (kb + 2 * p.pf_chunk < p.num_k_blocks) tma_prefetch_2d(&tm_bpf, (int32_t)((kb + 2 * p.pf_chunk) * 16u), brow);
+                    }
                     // Scale factors go first and complete on this CTA's own barrier, so that their
                     // transposition overlaps the (much larger) A/B transfer.
                     if (ld_sfa || ld_sfb) {
@@ -239,7 +336,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else if (warp == 1 && leader) {
         // ===================================================== MMA issuer (warp-converged, one lane issues)
-        Scheduler<GTYPE, CL> sched(rank);
+        Scheduler<GTYPE, CL> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         Tile t;
         uint32_t stage = 0, phase = 0, tile_count = 0;
         uint32_t sf_bits = 0;  // per-stage parity of sf_ready (it completes only on SF k-blocks)
@@ -263,7 +360,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[512 + kb] = clock64();
                 const uint32_t sa = stage_addr(stage);
                 if (elect_one()) {
-                    if (kHasSf) {
+                    if (kHasSf && !(p.dbg & 1u)) {
                         if (kb % p.sfa_period == 0) {
                             for (uint32_t j = 0; j < p.sf_sub; ++j)
                                 tc_cp_32x128b_warpx4<CL>(tmem + kSfaCol + j * 4u, make_sf_desc(sa + p.off_sfa + j * 512u));
@@ -279,6 +376,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     const uint64_t b_desc = make_kmajor_sw128_desc(sa + p.off_b);
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {
+                        if ((p.dbg & 4u) && k) break;
                         // 32 bytes of K per MMA (32 FP8, 64 FP4, 16 BF16): +2 in the >>4 address field.
                         const uint64_t ad = a_desc + 2u * k, bd = b_desc + 2u * k;
                         const uint32_t acc = (kb | k) != 0u ? 1u : 0u;
@@ -312,7 +410,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else if (warp == 2 && kHasSf) {
         // ===================================================== SF transposer
-        Scheduler<GTYPE, CL> sched(rank);
+        Scheduler<GTYPE, CL> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         Tile t;
         uint32_t stage = 0, sf_bits = 0;
         bool ok = true;
@@ -325,12 +423,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     sf_bits ^= 1u << stage;
                     ok = DG_WARP_WAIT(smem_u32(&bars->sf_full[stage]), parity, wc, kWaitFull);
                     if (!ok) break;
+                    if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[1024 + kb] = clock64();
                     uint32_t* sfa = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfa - smem_u32(smem_raw)));
                     uint32_t* sfb = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfb - smem_u32(smem_raw)));
                     const uint32_t na = has_a ? p.sf_sub : 0u, nb = has_b ? p.sf_sub * p.sfb_chunks : 0u;
                     // Up to 6 chunks of 128 words: word of row 32*i + lane -> position lane*4 + i.
                     // All loads are issued before the first store.
                     uint4 v[6];
+                    if (!(p.dbg & 2u)) {
 #pragma unroll
                     for (uint32_t c = 0; c < 6; ++c) {
                         if (c < na + nb) {
@@ -346,19 +446,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             *reinterpret_cast<uint4*>(q + lane * 4u) = v[c];
                         }
                     }
-                    fence_proxy_async_smem();
+                    }
+                    if (!(p.dbg & 8u)) fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
                         if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
                         else mbar_arrive_cluster(mapa(smem_u32(&bars->sf_ready[stage]), 0));
                     }
+                    if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[1280 + kb] = clock64();
                 }
                 if (++stage == p.num_stages) stage = 0;
             }
         }
     } else if (warp >= 4) {
         // ===================================================== epilogue
-        Scheduler<GTYPE, CL> sched(rank);
+        Scheduler<GTYPE, CL> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         Tile t;
         const uint32_t q = warp - 4u;  // TMEM lane quarter == warp index % 4
         uint32_t tile_count = 0;
@@ -371,8 +473,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             ok = DG_WARP_WAIT(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t row = t.a_row + q * 32u + lane;
-            const bool row_ok = row < t.row_end;
+            uint32_t row = t.a_row + q * 32u + lane;
+            bool row_ok = row < t.row_end;
+            if (p.d_row_map && row_ok) {
+                const int32_t mapped = __ldg(p.d_row_map + row);
+                row_ok = mapped >= 0;
+                row = (uint32_t)mapped;
+            }
             const uint32_t taddr = tmem + ((q * 32u) << 16) + as * kAccStageCols;
             const uint32_t chunks = p.block_n / 32u;
             for (uint32_t c = 0; c < chunks; ++c) {
@@ -502,12 +609,16 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     p.m = m; p.n = n; p.num_groups = num_groups;
     p.num_k_blocks = k / block_k;
     // CTA pairs (256-row tiles) halve the B traffic per SM; they need at least two row blocks
-    // that share B.  The contiguous grouped layout switches expert every 128 rows, so it stays on
-    // single CTAs.
+    // that share B.  In the contiguous grouped layout the kernel pairs neighbouring blocks of one
+    // expert and runs an odd last block with an idle partner.
     const uint32_t rows_per_group = gtype == kMasked ? (expected_m ? expected_m : m) : m;
-    uint32_t cl = (gtype != kContiguous && rows_per_group > kBlockM) ? 2u : 1u;
+    // Measured on B200: pairs win for FP8 / BF16 dense and masked GEMMs; FP4 (scale factors on
+    // every k-block, twice the UTCCP traffic) and the contiguous layout (an expert's weights are
+    // shared by only a few row blocks) run faster on single CTAs.
+    uint32_t cl = (rows_per_group > kBlockM && kind != kFp4 && gtype != kContiguous) ? 2u : 1u;
     const uint32_t forced_cl = env_u32("DG_CLUSTER", 0);
-    if ((forced_cl == 1 || forced_cl == 2) && gtype != kContiguous) cl = forced_cl;
+    if (forced_cl == 1 || forced_cl == 2) cl = forced_cl;
+    if (gtype == kContiguous && m / kBlockM > kMaxPairedBlocks) cl = 1;   // the in-kernel tile list is bounded
     plan->cluster = cl;
     const uint32_t tile_m = kBlockM * cl;
     const uint32_t units = sms / cl;
@@ -535,7 +646,8 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     p.tx_sfa = sfa_bytes;
     p.tx_sfb = sfb_bytes;
     const uint32_t budget = (uint32_t)dev->smem_optin;
-    const uint32_t fixed = 1024u /*alignment slack*/ + 1024u /*barriers*/;
+    const uint32_t fixed = 1024u /*alignment slack*/ + 1024u /*barriers*/ +
+                           ((gtype == kContiguous && cl == 2) ? kPairedListBytes : 0u) /*tile and run lists*/;
     uint32_t stages = (budget - fixed) / p.stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     const uint32_t forced = env_u32("DG_NUM_STAGES", 0);
@@ -545,12 +657,16 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     plan->smem_bytes = fixed + stages * p.stage_bytes;
     plan->num_tiles = gtype == kMasked ? m_tiles_total * p.num_n_blocks : p.num_m_blocks * p.num_n_blocks;
     uint32_t clusters = units;
-    const uint32_t worst = gtype == kMasked ? num_groups * ceil_div(m, tile_m) * p.num_n_blocks : plan->num_tiles;
+    uint32_t worst = gtype == kMasked ? num_groups * ceil_div(m, tile_m) * p.num_n_blocks : plan->num_tiles;
+    if (gtype == kContiguous && cl == 2) worst = (m / kBlockM) * p.num_n_blocks;   // every block may be a tile of its own
     if (worst < clusters) clusters = worst;
     if (clusters == 0) clusters = 1;
     plan->grid = clusters * cl;
     p.status = dev->status;
     p.trace = g_trace;
+    p.dbg = env_u32("DG_DEBUG_SKIP", 0);
+    p.pf_chunk = env_u32("DG_PREFETCH", 0);
+    if (p.pf_chunk > 16) p.pf_chunk = 16;
     if (env_u32("DG_PRINT_CONFIGS", 0))
         fprintf(stderr, "[deepgemm_b200] kind=%d gtype=%d m=%u n=%u k=%u groups=%u -> tile %ux%ux%u cluster=%u stages=%u smem=%u grid=%u tiles=%u\n",
                 kind, gtype, m, n, k, num_groups, tile_m, p.block_n, block_k, cl, stages, plan->smem_bytes, plan->grid, plan->num_tiles);
@@ -559,7 +675,7 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
 
 template <int KIND, int GTYPE, int CL>
 static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
-                      const CUtensorMap& tsb, cudaStream_t s) {
+                      const CUtensorMap& tsb, const CUtensorMap& tbpf, cudaStream_t s) {
     auto* fn = gemm_kernel<KIND, GTYPE, CL>;
     static thread_local uint32_t configured[64] = {0};
     int dev = 0;
@@ -580,7 +696,7 @@ static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, ta, tb, tsa, tsb, plan.p));
+    DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, ta, tb, tsa, tsb, tbpf, plan.p));
     note_launch();
     return DG_OK;
 }
@@ -606,13 +722,14 @@ static int32_t validate_operand(const dg_operand_t* op, const char* name) {
 }
 
 static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int gtype, const int32_t* layout,
-                        uint32_t layout_len, uint32_t num_groups, uint32_t expected_m, int32_t accumulate, void* stream) {
+                        uint32_t layout_len, uint32_t num_groups, uint32_t expected_m, int32_t accumulate, void* stream,
+                        const int32_t* d_row_map = nullptr) {
     int32_t st;
     if ((st = validate_operand(a, "A")) != DG_OK) return st;
     if ((st = validate_operand(b, "B")) != DG_OK) return st;
     if (!out || !out->data) return fail(DG_ERR_INVALID_ARG, "null output");
     if (a->k != b->k) return fail(DG_ERR_INVALID_ARG, "A/B K mismatch");
-    if (out->cols != b->rows || out->rows != a->rows) return fail(DG_ERR_INVALID_ARG, "output shape mismatch");
+    if (out->cols != b->rows || (!d_row_map && out->rows != a->rows)) return fail(DG_ERR_INVALID_ARG, "output shape mismatch");
     if (out->dtype != DG_BF16 && out->dtype != DG_F32) return fail(DG_ERR_INVALID_ARG, "output must be BF16 or FP32");
     if (out->stride < out->cols) return fail(DG_ERR_INVALID_ARG, "output stride (%u) smaller than its columns (%u)", out->stride, out->cols);
     if (a->dtype != b->dtype)
@@ -669,6 +786,7 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     p.ldd = out->stride;
     p.d = out->data;
     p.layout = layout;
+    p.d_row_map = d_row_map;
 
     CUtensorMap ta, tb, tsa, tsb;
     const uint32_t ebytes = kind == kBf16 ? 2u : 1u;
@@ -690,11 +808,18 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     } else {
         tsa = ta; tsb = tb;
     }
+    // Prefetch view of B: 8-byte elements, `pf_chunk` k-blocks (128 B each) x the CTA's rows per box.
+    CUtensorMap tbpf = tb;
+    if (p.pf_chunk) {
+        const uint64_t row_bytes = kind == kBf16 ? (uint64_t)k * 2 : inner;
+        if ((st = make_tmap_2d(&tbpf, CU_TENSOR_MAP_DATA_TYPE_INT64, 8, b->data, row_bytes / 8, (uint64_t)groups_b * n, pitch_b,
+                               p.pf_chunk * 16u, p.block_n / plan.cluster, CU_TENSOR_MAP_SWIZZLE_NONE, "B prefetch")) != DG_OK) return st;
+    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define DG_DISPATCH(K, G)                                                                  \
     if (kind == K && gtype == G) {                                                         \
-        if (plan.cluster == 2) return launch<K, G, 2>(plan, ta, tb, tsa, tsb, s);          \
-        return launch<K, G, 1>(plan, ta, tb, tsa, tsb, s);                                 \
+        if (plan.cluster == 2) return launch<K, G, 2>(plan, ta, tb, tsa, tsb, tbpf, s);    \
+        return launch<K, G, 1>(plan, ta, tb, tsa, tsb, tbpf, s);                           \
     }
     DG_DISPATCH(kFp8, kNormal) DG_DISPATCH(kFp8, kContiguous) DG_DISPATCH(kFp8, kMasked)
     DG_DISPATCH(kFp4, kNormal) DG_DISPATCH(kFp4, kContiguous) DG_DISPATCH(kFp4, kMasked)
@@ -734,6 +859,13 @@ int32_t dg_m_grouped_gemm_nt_contiguous(const dg_operand_t* a, const dg_operand_
     if (a && a->major != DG_MAJOR_K) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous requires K-major A");
     return dg::run_gemm(a, b, out, dg::kContiguous, m_indices, m_indices_len, num_groups, a ? a->rows : 0, 0, stream);
 }
+int32_t dg_m_grouped_gemm_nt_contiguous_scatter(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
+                                                const int32_t* m_indices, uint32_t m_indices_len, uint32_t num_groups,
+                                                const int32_t* d_row_map, void* stream) {
+    if (!d_row_map) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous scatter requires a row map");
+    if (a && a->major != DG_MAJOR_K) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous requires K-major A");
+    return dg::run_gemm(a, b, out, dg::kContiguous, m_indices, m_indices_len, num_groups, a ? a->rows : 0, 0, stream, d_row_map);
+}
 int32_t dg_m_grouped_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, const int32_t* masked_m,
                                     uint32_t num_groups, uint32_t expected_m, void* stream) {
     if (a && b && (a->major != DG_MAJOR_K || b->major != DG_MAJOR_K))
@@ -757,7 +889,7 @@ DG_TYPED_GROUPED(fp4, DG_FP4)
 DG_TYPED_GROUPED(bf16, DG_BF16)
 #undef DG_TYPED_GROUPED
 
-// Development aid, not part of the public header: a device buffer of 1024 u64 that receives
+// Development aid, not part of the public header: a device buffer of 2048 u64 that receives
 // clock64 stamps of CTA 0's first tile (producer: stage free / loads issued; MMA issuer:
 // stage full / MMAs issued), or NULL to switch tracing off.
 __attribute__((visibility("default"))) void dg_debug_set_trace(void* buf) { dg::g_trace = static_cast<unsigned long long*>(buf); }

@@ -22,7 +22,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .api import _check, _stream_ptr, m_grouped_gemm_nt_contiguous
+from .api import _check, _stream_ptr, m_grouped_gemm_nt_contiguous, m_grouped_gemm_nt_contiguous_scatter
 from .types import Dtype, Operand, Output, SfGran, SfTensor
 
 BLOCK = 128  # rows per m_indices entry (heuristics::mk_alignment_for_contiguous_layout)
@@ -199,7 +199,8 @@ class ExpertParallelMoE:
     packed SF; returns bf16 [T, n_out] = sum_j topk_w[t, j] * (x[t] . W[topk_idx[t, j]]^T).
     """
 
-    def __init__(self, weights: Operand, num_experts: int, group=None):
+    def __init__(self, weights: Operand, num_experts: int, group=None, chunks: int = 4):
+        self.chunks = chunks
         self.w = weights
         self.num_experts = num_experts
         self.group = group
@@ -222,32 +223,76 @@ class ExpertParallelMoE:
                                          self.e_local)
             self.last_m_indices = p.block_expert
             return combine(d, p.slot_of_row.view(tokens, topk), topk_w)
-        # sort copies by global expert (= by destination rank), exchange the per-expert counts
-        sp = device_plan(topk_idx, self.num_experts, 1, div=topk, capacity=tokens * topk)
-        send_counts = sp.counts.view(self.world, self.e_local)
-        recv_counts = torch.empty_like(send_counts)
+        # Several GPUs: the tokens are cut into `chunks` slices that flow through
+        # dispatch -> GEMM -> return as a pipeline, so that NCCL traffic of one slice overlaps the
+        # grouped GEMM of another.  All count exchanges happen first (one all-to-all, one host sync).
+        # Every slice re-reads this rank's expert weights, so slices must stay large: about
+        # 1024 rows per local expert and slice.
+        rows_per_expert = tokens * topk * self.world // self.num_experts
+        chunks = max(1, min(self.chunks, rows_per_expert // 1024, tokens // 64 or 1))
+        bounds = [tokens * c // chunks for c in range(chunks + 1)]
+        sps = [device_plan(topk_idx[bounds[c]:bounds[c + 1]], self.num_experts, 1, div=topk,
+                           capacity=(bounds[c + 1] - bounds[c]) * topk) for c in range(chunks)]
+        send_counts = torch.stack([sp.counts for sp in sps]).view(chunks, self.world, self.e_local)
+        send_counts = send_counts.permute(1, 0, 2).contiguous()                       # [dst, chunk, expert]
+        recv_counts = torch.empty_like(send_counts)                                   # [src, chunk, expert]
         dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        both = torch.stack([send_counts.sum(1), recv_counts.sum(1)]).cpu()      # the one host sync of the step
-        send_splits, recv_splits = both[0].tolist(), both[1].tolist()
-        r = sum(recv_splits)
-        rows = gather_rows(x, sp.slot_src)
-        wire = sf_to_wire(x_sf, sp.slot_src)
-        recv_rows = torch.empty((r, k), dtype=x.dtype, device=x.device)
-        recv_wire = torch.empty((r, wire.shape[1]), dtype=wire.dtype, device=x.device)
-        dist.all_to_all_single(recv_rows, rows, recv_splits, send_splits, group=self.group)
-        dist.all_to_all_single(recv_wire, wire, recv_splits, send_splits, group=self.group)
-        # received rows are ordered by (source rank, local expert)
-        recv_expert = torch.repeat_interleave(torch.arange(self.e_local, device=x.device, dtype=torch.int32).repeat(self.world),
-                                              recv_counts.reshape(-1), output_size=r)
-        rp = device_plan(recv_expert, self.e_local, BLOCK, div=1, capacity=contiguous_capacity(r, self.e_local))
-        a = gather_rows(recv_rows, rp.slot_src)
-        a_sf = sf_from_wire(recv_wire, rp.slot_src, x_sf.gran)
-        d = torch.empty((rp.capacity, n_out), dtype=torch.bfloat16, device=x.device)
-        a_op = Operand.k_major(self.w.dtype, rp.capacity, k_elems, k_elems, a_sf, a)
-        m_grouped_gemm_nt_contiguous(a_op, self.w, Output(Dtype.Bf16, rp.capacity, n_out, n_out, d), rp.block_expert,
-                                     self.e_local)
-        self.last_m_indices = rp.block_expert
-        back = gather_rows(d, rp.slot_of_row)                                    # received order
-        ret = torch.empty((tokens * topk, n_out), dtype=torch.bfloat16, device=x.device)
-        dist.all_to_all_single(ret, back, send_splits, recv_splits, group=self.group)
-        return combine(ret, sp.slot_of_row.view(tokens, topk), topk_w)
+        both = torch.stack([send_counts.sum(2), recv_counts.sum(2)]).cpu()            # the one host sync of the step
+        out = torch.empty((tokens, n_out), dtype=torch.bfloat16, device=x.device)
+        experts = torch.arange(self.e_local, device=x.device, dtype=torch.int32).repeat(self.world)
+        self.last_m_indices = []
+
+        def dispatch(c):
+            send_splits, recv_splits = both[0][:, c].tolist(), both[1][:, c].tolist()
+            xs = x[bounds[c]:bounds[c + 1]]
+            rows = gather_rows(xs, sps[c].slot_src)
+            # scale factors of the slice: columns bounds[c].. of the packed tensor
+            sf_view = SfTensor(x_sf.rows, x_sf.cols, x_sf.gran, x_sf.buf[:, bounds[c]:])
+            wire = torch.empty((rows.shape[0], x_sf.rows), dtype=torch.int32, device=x.device)
+            _gather_sf(sf_view.buf, x_sf.cols, 1, sps[c].slot_src, wire, 1, x_sf.rows, x_sf.rows)
+            r = sum(recv_splits)
+            recv_rows = torch.empty((r, k), dtype=x.dtype, device=x.device)
+            recv_wire = torch.empty((r, x_sf.rows), dtype=torch.int32, device=x.device)
+            w1 = dist.all_to_all_single(recv_rows, rows, recv_splits, send_splits, group=self.group, async_op=True)
+            w2 = dist.all_to_all_single(recv_wire, wire, recv_splits, send_splits, group=self.group, async_op=True)
+            return dict(send_splits=send_splits, recv_splits=recv_splits, recv_rows=recv_rows, recv_wire=recv_wire,
+                        works=(w1, w2), keep=(rows, wire), r=r)
+
+        def compute_and_return(c, st):
+            for w in st["works"]:
+                w.wait()
+            r = st["r"]
+            # received rows are ordered by (source rank, local expert)
+            recv_expert = torch.repeat_interleave(experts, recv_counts[:, c, :].reshape(-1), output_size=r)
+            rp = device_plan(recv_expert, self.e_local, BLOCK, div=1, capacity=contiguous_capacity(r, self.e_local))
+            a = gather_rows(st["recv_rows"], rp.slot_src)
+            a_sf = sf_from_wire(st["recv_wire"], rp.slot_src, x_sf.gran)
+            # the GEMM epilogue stores every slot's row at its position in the received order,
+            # which is the order the return all-to-all needs
+            back = torch.empty((max(r, 1), n_out), dtype=torch.bfloat16, device=x.device)
+            a_op = Operand.k_major(self.w.dtype, rp.capacity, k_elems, k_elems, a_sf, a)
+            m_grouped_gemm_nt_contiguous_scatter(a_op, self.w, Output(Dtype.Bf16, max(r, 1), n_out, n_out, back),
+                                                 rp.block_expert, self.e_local, rp.slot_src)
+            back = back[:r]
+            self.last_m_indices.append(rp.block_expert)
+            ret = torch.empty(((bounds[c + 1] - bounds[c]) * topk, n_out), dtype=torch.bfloat16, device=x.device)
+            st["ret"], st["back"] = ret, back
+            st["ret_work"] = dist.all_to_all_single(ret, back, st["send_splits"], st["recv_splits"], group=self.group,
+                                                    async_op=True)
+
+        def finish(c, st):
+            st["ret_work"].wait()
+            tw = topk_w[bounds[c]:bounds[c + 1]] if topk_w is not None else None
+            combine(st["ret"], sps[c].slot_of_row.view(-1, topk), tw, out=out[bounds[c]:bounds[c + 1]])
+
+        # issue order on the NCCL stream: d0, d1, r0, d2, r1, ..., r_last
+        states = [None] * chunks
+        states[0] = dispatch(0)
+        for c in range(chunks):
+            if c + 1 < chunks:
+                states[c + 1] = dispatch(c + 1)
+            compute_and_return(c, states[c])
+            if c >= 1:
+                finish(c - 1, states[c - 1])
+        finish(chunks - 1, states[chunks - 1])
+        return out

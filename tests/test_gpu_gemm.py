@@ -178,10 +178,13 @@ def _stacked_b(kind, groups, n, k, seed, gran=32):
     return op, g
 
 
+@pytest.mark.parametrize("cluster", [1, 2])
 @pytest.mark.parametrize("kind", ["fp8", "fp4", "bf16"])
-def test_m_grouped_contiguous(kind):
+def test_m_grouped_contiguous(kind, cluster):
+    os.environ["DG_CLUSTER"] = str(cluster)
     groups, n, k = 4, 256, 512
-    blocks = [0, 0, 2, -1, 3, 1, 1, -1, 2]            # expert of each 128-row block, -1 = padding
+    # expert of each 128-row block, -1 = padding: pairs, odd runs, a run of 3, a trailing single
+    blocks = [0, 0, 2, -1, 3, 1, 1, -1, 2, 2, 2, 0, 3, 3, 3, 3, 1]
     m = 128 * len(blocks)
     xa = randn((m, k), 61)
     xa[128 * 5 + 70: 128 * 6] = 0.0                   # zero padding rows inside a block
@@ -207,6 +210,31 @@ def test_m_grouped_contiguous(kind):
         assert_close_to_oracle(got[rows], bf16_round(ref), kind, f"block {i} expert {e}")
 
 
+def test_m_grouped_contiguous_many_blocks_random_runs():
+    """A long random m_indices (runs of 1..5 blocks, padding blocks in between) on CTA pairs:
+    exercises the in-kernel tile list over several 32-block chunks."""
+    rng = np.random.default_rng(5)
+    groups, n, k = 8, 128, 256
+    blocks = []
+    while len(blocks) < 90:
+        blocks += [int(rng.integers(0, groups))] * int(rng.integers(1, 6))
+        if rng.random() < 0.3:
+            blocks.append(-1)
+    m = 128 * len(blocks)
+    a, ga = quantised_operand(randn((m, k), 1), "fp8", 128)
+    b, gb = _stacked_b("fp8", groups, n, k, 2, gran=128)
+    out = new_output(m, n, fill=3.0)
+    m_grouped_gemm_nt_contiguous(a, b, out, dev(np.array(blocks, dtype=np.int32)), groups)
+    poll_device_status()
+    got = to_f32(out)
+    for i, e in enumerate(blocks):
+        rows = np.arange(128 * i, 128 * (i + 1))
+        if e < 0:
+            assert (got[rows] == 3.0).all()
+        else:
+            assert_close_to_oracle(got[rows], bf16_round(o.gemm_ref(ga, gb, rows=rows, n=n, b_row0=e * n)), "fp8", f"block {i}")
+
+
 def test_m_grouped_contiguous_reference_test_shape():
     """deepgemm/tests/e2e_gpu.rs:403-484 with a well-formed m_indices: 4 groups, N 128, K 512."""
     groups, n, k = 4, 128, 512
@@ -222,8 +250,10 @@ def test_m_grouped_contiguous_reference_test_shape():
         assert_close_to_oracle(got[rows], bf16_round(o.gemm_ref(ga, gb, rows=rows, n=n, b_row0=g * n)), "fp8")
 
 
+@pytest.mark.parametrize("cluster", [1, 2])
 @pytest.mark.parametrize("kind", ["fp8", "fp4", "bf16"])
-def test_m_grouped_masked(kind):
+def test_m_grouped_masked(kind, cluster):
+    os.environ["DG_CLUSTER"] = str(cluster)
     groups, max_m, n, k = 6, 256, 384, 512
     masked = [256, 0, 1, 128, 129, 77]
     xa = randn((groups * max_m, k), 71)
