@@ -64,6 +64,8 @@ struct GemmParams {
     const int32_t* layout; // m_indices (contiguous) or masked_m (masked)
     const int32_t* d_row_map;  // optional: D row of every A row (negative = drop the row); NULL = identity
     uint32_t* status;
+    uint32_t b_group_rows;      // rows of B per group (grouped GEMMs); >= n when only a column range is computed
+    uint32_t b_row_offset;      // first B row inside every group
     uint32_t pf_chunk;          // k-blocks per L2 prefetch of B (0 = off)
     uint32_t dbg;               // development switches (timing experiments only; results become wrong)
     unsigned long long* trace;  // debug: per-k-block clock64 stamps of CTA 0's first tile (or null)
@@ -119,7 +121,7 @@ struct Scheduler {
             t.a_row = (blk + rank) * kBlockM;
             t.row_end = (rank == 0 || paired) ? p.m : 0u;
             t.n0 = nb * p.block_n;
-            t.b_row = (uint32_t)__ldg(p.layout + blk) * p.n + t.n0;
+            t.b_row = (uint32_t)__ldg(p.layout + blk) * p.b_group_rows + p.b_row_offset + t.n0;
             return true;
         } else if (GTYPE != kMasked) {
             if (id >= p.num_m_blocks * p.num_n_blocks) return false;
@@ -131,11 +133,11 @@ struct Scheduler {
             t.a_row = mb * kTileM + rank * kBlockM;
             t.row_end = p.m;
             t.n0 = nb * p.block_n;
-            t.b_row = t.n0;
+            t.b_row = p.b_row_offset + t.n0;
             if (GTYPE == kContiguous) {
                 const int32_t e = __ldg(p.layout + mb);
                 t.skip = e < 0 || (uint32_t)e >= p.num_groups;
-                t.b_row = (t.skip ? 0u : (uint32_t)e * p.n) + t.n0;
+                t.b_row = (t.skip ? 0u : (uint32_t)e * p.b_group_rows + p.b_row_offset) + t.n0;
             }
             return true;
         } else {
@@ -150,7 +152,7 @@ struct Scheduler {
                     t.a_row = g * p.m + mb * kTileM + rank * kBlockM;
                     t.row_end = g * p.m + rows;
                     t.n0 = nb * p.block_n;
-                    t.b_row = g * p.n + t.n0;
+                    t.b_row = g * p.b_group_rows + p.b_row_offset + t.n0;
                     return true;
                 }
                 g_first_tile += cnt;
@@ -723,13 +725,17 @@ static int32_t validate_operand(const dg_operand_t* op, const char* name) {
 
 static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int gtype, const int32_t* layout,
                         uint32_t layout_len, uint32_t num_groups, uint32_t expected_m, int32_t accumulate, void* stream,
-                        const int32_t* d_row_map = nullptr) {
+                        const int32_t* d_row_map = nullptr, uint32_t n_begin = 0, uint32_t n_count = 0) {
     int32_t st;
     if ((st = validate_operand(a, "A")) != DG_OK) return st;
     if ((st = validate_operand(b, "B")) != DG_OK) return st;
     if (!out || !out->data) return fail(DG_ERR_INVALID_ARG, "null output");
     if (a->k != b->k) return fail(DG_ERR_INVALID_ARG, "A/B K mismatch");
-    if (out->cols != b->rows || (!d_row_map && out->rows != a->rows)) return fail(DG_ERR_INVALID_ARG, "output shape mismatch");
+    if (n_count == 0) { n_begin = 0; n_count = b ? b->rows : 0; }
+    if (n_begin + n_count > b->rows || n_begin % 4 != 0)
+        return fail(DG_ERR_INVALID_ARG, "column range [%u, %u) must lie inside N = %u and start on a multiple of 4", n_begin,
+                    n_begin + n_count, b->rows);
+    if (out->cols != n_count || (!d_row_map && out->rows != a->rows)) return fail(DG_ERR_INVALID_ARG, "output shape mismatch");
     if (out->dtype != DG_BF16 && out->dtype != DG_F32) return fail(DG_ERR_INVALID_ARG, "output must be BF16 or FP32");
     if (out->stride < out->cols) return fail(DG_ERR_INVALID_ARG, "output stride (%u) smaller than its columns (%u)", out->stride, out->cols);
     if (a->dtype != b->dtype)
@@ -754,8 +760,8 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
         if (layout_len != a->rows / 128)
             return fail(DG_ERR_INVALID_ARG, "m_indices must hold M/128 = %u entries (one per 128-row block), got %u", a->rows / 128, layout_len);
     }
-    const uint32_t m = a->rows, n = b->rows, k = a->k;
-    if ((uint64_t)groups_a * m >= (1ull << 31) || (uint64_t)groups_b * n >= (1ull << 31))
+    const uint32_t m = a->rows, n = n_count, n_full = b->rows, k = a->k;
+    if ((uint64_t)groups_a * m >= (1ull << 31) || (uint64_t)groups_b * n_full >= (1ull << 31))
         return fail(DG_ERR_INVALID_ARG, "stacked row count exceeds 2^31");
     uint32_t gran_a = 32, gran_b = 32;
     if (has_sf) {
@@ -766,11 +772,11 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
         if (a->sf.rows < ceil_div(k, gran_a * 4) || a->sf.cols < align_up(groups_a * m, 4))
             return fail(DG_ERR_INVALID_ARG, "A scale-factor tensor is %u x %u, need at least %u x %u", a->sf.rows, a->sf.cols,
                         ceil_div(k, gran_a * 4), align_up(groups_a * m, 4));
-        if (b->sf.rows < ceil_div(k, gran_b * 4) || b->sf.cols < align_up(groups_b * n, 4))
+        if (b->sf.rows < ceil_div(k, gran_b * 4) || b->sf.cols < align_up(groups_b * n_full, 4))
             return fail(DG_ERR_INVALID_ARG, "B scale-factor tensor is %u x %u, need at least %u x %u", b->sf.rows, b->sf.cols,
-                        ceil_div(k, gran_b * 4), align_up(groups_b * n, 4));
+                        ceil_div(k, gran_b * 4), align_up(groups_b * n_full, 4));
         // TMA starts SF boxes at column group*rows + tile offset: keep that 16-byte aligned.
-        if (gtype != kNormal && n % 4 != 0) return fail(DG_ERR_INVALID_ARG, "grouped GEMM requires N (%u) %% 4 == 0", n);
+        if (gtype != kNormal && n_full % 4 != 0) return fail(DG_ERR_INVALID_ARG, "grouped GEMM requires N (%u) %% 4 == 0", n_full);
         if (gtype == kMasked && m % 4 != 0) return fail(DG_ERR_INVALID_ARG, "masked GEMM requires per-group M (%u) %% 4 == 0", m);
     }
 
@@ -787,6 +793,8 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     p.d = out->data;
     p.layout = layout;
     p.d_row_map = d_row_map;
+    p.b_group_rows = n_full;
+    p.b_row_offset = n_begin;
 
     CUtensorMap ta, tb, tsa, tsb;
     const uint32_t ebytes = kind == kBf16 ? 2u : 1u;
@@ -798,7 +806,7 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     const uint32_t box_inner = kind == kBf16 ? 64u : 128u;
     if ((st = make_tmap_2d(&ta, dt, ebytes, a->data, inner, (uint64_t)groups_a * m, pitch_a, box_inner, kBlockM,
                            CU_TENSOR_MAP_SWIZZLE_128B, "A")) != DG_OK) return st;
-    if ((st = make_tmap_2d(&tb, dt, ebytes, b->data, inner, (uint64_t)groups_b * n, pitch_b, box_inner, p.block_n / plan.cluster,
+    if ((st = make_tmap_2d(&tb, dt, ebytes, b->data, inner, (uint64_t)groups_b * n_full, pitch_b, box_inner, p.block_n / plan.cluster,
                            CU_TENSOR_MAP_SWIZZLE_128B, "B")) != DG_OK) return st;
     if (has_sf) {
         if ((st = make_tmap_2d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a->sf.data, a->sf.cols, a->sf.rows,
@@ -812,7 +820,7 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     CUtensorMap tbpf = tb;
     if (p.pf_chunk) {
         const uint64_t row_bytes = kind == kBf16 ? (uint64_t)k * 2 : inner;
-        if ((st = make_tmap_2d(&tbpf, CU_TENSOR_MAP_DATA_TYPE_INT64, 8, b->data, row_bytes / 8, (uint64_t)groups_b * n, pitch_b,
+        if ((st = make_tmap_2d(&tbpf, CU_TENSOR_MAP_DATA_TYPE_INT64, 8, b->data, row_bytes / 8, (uint64_t)groups_b * n_full, pitch_b,
                                p.pf_chunk * 16u, p.block_n / plan.cluster, CU_TENSOR_MAP_SWIZZLE_NONE, "B prefetch")) != DG_OK) return st;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -861,10 +869,12 @@ int32_t dg_m_grouped_gemm_nt_contiguous(const dg_operand_t* a, const dg_operand_
 }
 int32_t dg_m_grouped_gemm_nt_contiguous_scatter(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
                                                 const int32_t* m_indices, uint32_t m_indices_len, uint32_t num_groups,
-                                                const int32_t* d_row_map, void* stream) {
+                                                const int32_t* d_row_map, uint32_t n_begin, uint32_t n_count, void* stream) {
     if (!d_row_map) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous scatter requires a row map");
-    if (a && a->major != DG_MAJOR_K) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous requires K-major A");
-    return dg::run_gemm(a, b, out, dg::kContiguous, m_indices, m_indices_len, num_groups, a ? a->rows : 0, 0, stream, d_row_map);
+    if (!a || !b) return dg::fail(DG_ERR_INVALID_ARG, "null operand");
+    if (a->major != DG_MAJOR_K) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous requires K-major A");
+    return dg::run_gemm(a, b, out, dg::kContiguous, m_indices, m_indices_len, num_groups, a->rows, 0, stream, d_row_map,
+                        n_begin, n_count);
 }
 int32_t dg_m_grouped_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, const int32_t* masked_m,
                                     uint32_t num_groups, uint32_t expected_m, void* stream) {

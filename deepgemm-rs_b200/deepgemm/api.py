@@ -92,12 +92,13 @@ def m_grouped_gemm_nt_contiguous(a, b, out, m_indices, num_groups, stream=None):
     _contig(_lib.load().dg_m_grouped_gemm_nt_contiguous, a, b, out, m_indices, num_groups, stream)
 
 
-def m_grouped_gemm_nt_contiguous_scatter(a, b, out, m_indices, num_groups, d_row_map, stream=None):
-    """Extension: row r of the result is stored at row d_row_map[r] of `out` (negative = dropped)."""
+def m_grouped_gemm_nt_contiguous_scatter(a, b, out, m_indices, num_groups, d_row_map, n_begin=0, n_count=0, stream=None):
+    """Extension: row r of the result is stored at row d_row_map[r] of `out` (negative = dropped);
+    only the output columns [n_begin, n_begin + n_count) of every expert are computed (0 = all)."""
     ac, bc, oc = _op_c(a), _op_c(b), _out_c(out)
     _check(_lib.load().dg_m_grouped_gemm_nt_contiguous_scatter(C.byref(ac), C.byref(bc), C.byref(oc), m_indices.data_ptr(),
                                                                m_indices.numel(), num_groups, d_row_map.data_ptr(),
-                                                               _stream_ptr(stream)))
+                                                               n_begin, n_count, _stream_ptr(stream)))
 
 
 def m_grouped_gemm_nt_masked(a, b, out, masked_m, num_groups, expected_m, stream=None):

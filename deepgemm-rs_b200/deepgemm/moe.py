@@ -15,6 +15,7 @@ kernels (`device_plan`, used by `ExpertParallelMoE` so that a step needs no host
 synchronisation on one GPU and exactly one on several).
 """
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -199,8 +200,13 @@ class ExpertParallelMoE:
     packed SF; returns bf16 [T, n_out] = sum_j topk_w[t, j] * (x[t] . W[topk_idx[t, j]]^T).
     """
 
-    def __init__(self, weights: Operand, num_experts: int, group=None, chunks: int = 4):
+    def __init__(self, weights: Operand, num_experts: int, group=None, chunks: int = 1, return_parts: int = 1):
+        # chunks > 1: token slices pipelined through dispatch / GEMM / return; return_parts > 1: the
+        # GEMM of a slice runs in column ranges whose return transfers overlap the next range.  Both
+        # overlap NCCL kernels with a GEMM that wants every SM; measured on 2 GPUs they lost more
+        # than they hid, so the default is the plain sequence.
         self.chunks = chunks
+        self.return_parts = int(os.environ.get("DG_EP_RETURN_PARTS", return_parts))
         self.w = weights
         self.num_experts = num_experts
         self.group = group
@@ -230,6 +236,8 @@ class ExpertParallelMoE:
         # 1024 rows per local expert and slice.
         rows_per_expert = tokens * topk * self.world // self.num_experts
         chunks = max(1, min(self.chunks, rows_per_expert // 1024, tokens // 64 or 1))
+        if os.environ.get("DG_EP_CHUNKS"):
+            chunks = max(1, int(os.environ["DG_EP_CHUNKS"]))
         bounds = [tokens * c // chunks for c in range(chunks + 1)]
         sps = [device_plan(topk_idx[bounds[c]:bounds[c + 1]], self.num_experts, 1, div=topk,
                            capacity=(bounds[c + 1] - bounds[c]) * topk) for c in range(chunks)]
@@ -267,23 +275,33 @@ class ExpertParallelMoE:
             rp = device_plan(recv_expert, self.e_local, BLOCK, div=1, capacity=contiguous_capacity(r, self.e_local))
             a = gather_rows(st["recv_rows"], rp.slot_src)
             a_sf = sf_from_wire(st["recv_wire"], rp.slot_src, x_sf.gran)
-            # the GEMM epilogue stores every slot's row at its position in the received order,
-            # which is the order the return all-to-all needs
-            back = torch.empty((max(r, 1), n_out), dtype=torch.bfloat16, device=x.device)
+            # The GEMM epilogue stores every slot's row at its position in the received order, the
+            # order the return all-to-all needs.  With a single slice the GEMM runs in column
+            # halves, so that the first half travels back while the second is computed.
             a_op = Operand.k_major(self.w.dtype, rp.capacity, k_elems, k_elems, a_sf, a)
-            m_grouped_gemm_nt_contiguous_scatter(a_op, self.w, Output(Dtype.Bf16, max(r, 1), n_out, n_out, back),
-                                                 rp.block_expert, self.e_local, rp.slot_src)
-            back = back[:r]
             self.last_m_indices.append(rp.block_expert)
-            ret = torch.empty(((bounds[c + 1] - bounds[c]) * topk, n_out), dtype=torch.bfloat16, device=x.device)
-            st["ret"], st["back"] = ret, back
-            st["ret_work"] = dist.all_to_all_single(ret, back, st["send_splits"], st["recv_splits"], group=self.group,
-                                                    async_op=True)
+            rows_back = (bounds[c + 1] - bounds[c]) * topk
+            parts = self.return_parts if n_out % (64 * self.return_parts) == 0 else 1
+            st["ret"], st["back"], st["ret_work"] = [], [], []
+            for h in range(parts):
+                n0, nc = n_out // parts * h, n_out // parts
+                back = torch.empty((max(r, 1), nc), dtype=torch.bfloat16, device=x.device)
+                m_grouped_gemm_nt_contiguous_scatter(a_op, self.w, Output(Dtype.Bf16, max(r, 1), nc, nc, back),
+                                                     rp.block_expert, self.e_local, rp.slot_src, n0, nc)
+                ret = torch.empty((rows_back, nc), dtype=torch.bfloat16, device=x.device)
+                st["back"].append(back)
+                st["ret"].append(ret)
+                st["ret_work"].append(dist.all_to_all_single(ret, back[:r], st["send_splits"], st["recv_splits"],
+                                                             group=self.group, async_op=True))
 
         def finish(c, st):
-            st["ret_work"].wait()
             tw = topk_w[bounds[c]:bounds[c + 1]] if topk_w is not None else None
-            combine(st["ret"], sps[c].slot_of_row.view(-1, topk), tw, out=out[bounds[c]:bounds[c + 1]])
+            pos = sps[c].slot_of_row.view(-1, topk)
+            col = 0
+            for work, ret in zip(st["ret_work"], st["ret"]):
+                work.wait()
+                combine(ret, pos, tw, out=out[bounds[c]:bounds[c + 1], col:col + ret.shape[1]])
+                col += ret.shape[1]
 
         # issue order on the NCCL stream: d0, d1, r0, d2, r1, ..., r_last
         states = [None] * chunks

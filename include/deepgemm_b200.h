@@ -113,11 +113,15 @@ DG_API int32_t dg_m_grouped_gemm_nt_contiguous(const dg_operand_t* a, const dg_o
                                         uint32_t num_groups, void* stream);
 /* Extension (no counterpart in the reference): the contiguous grouped GEMM whose epilogue stores
  * row r of the result at row d_row_map[r] of `out` (device, int32, a.rows entries; negative = the
- * row is not stored).  out.rows is the number of destination rows and every valid map entry must be
- * below it.  Lets an expert-parallel layer write expert outputs straight into its return buffer. */
+ * row is not stored) and which computes only the output columns [n_begin, n_begin + n_count) of every
+ * expert (n_count = 0: all; out.cols = the number of computed columns, n_begin a multiple of 4).
+ * out.rows is the number of destination rows and every valid map entry must be below it.  Lets an
+ * expert-parallel layer write expert outputs straight into its return buffer, one column slice at a
+ * time so that the slices' return transfers overlap the remaining GEMM. */
 DG_API int32_t dg_m_grouped_gemm_nt_contiguous_scatter(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out,
                                                        const int32_t* m_indices, uint32_t m_indices_len,
-                                                       uint32_t num_groups, const int32_t* d_row_map, void* stream);
+                                                       uint32_t num_groups, const int32_t* d_row_map,
+                                                       uint32_t n_begin, uint32_t n_count, void* stream);
 /* replaces api::m_grouped_gemm_nt_masked (deepgemm/src/api.rs:930-963).  a, b and out are
  * stacked per group ([num_groups * rows, ...]); masked_m (device, int32, num_groups entries)
  * holds the valid rows of each group; rows beyond it are neither computed nor written.

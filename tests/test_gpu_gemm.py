@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import oracle as o
-from deepgemm import (Dtype, Operand, bf16_gemm_nt, fp4_gemm_nt, fp8_gemm_nt, gemm_nt, get_gemm_config,
+from deepgemm import (Dtype, Operand, Output, m_grouped_gemm_nt_contiguous_scatter, bf16_gemm_nt, fp4_gemm_nt, fp8_gemm_nt, gemm_nt, get_gemm_config,
                       m_grouped_fp8_gemm_nt_contiguous, m_grouped_fp8_gemm_nt_masked, m_grouped_gemm_nt_contiguous,
                       m_grouped_gemm_nt_masked, poll_device_status)
 from helpers import (assert_close_to_oracle, bf16_operand, bf16_round, dev, new_output, quantised_operand, randn,
@@ -233,6 +233,33 @@ def test_m_grouped_contiguous_many_blocks_random_runs():
             assert (got[rows] == 3.0).all()
         else:
             assert_close_to_oracle(got[rows], bf16_round(o.gemm_ref(ga, gb, rows=rows, n=n, b_row0=e * n)), "fp8", f"block {i}")
+
+
+def test_m_grouped_contiguous_scatter_and_column_range():
+    """Extension entry: rows stored through a row map (negative = dropped), only a column range of
+    every expert computed; must equal the same rows / columns of the plain grouped GEMM bit for bit."""
+    groups, n, k = 3, 384, 512
+    blocks = [2, 0, 0, -1, 1]
+    m = 128 * len(blocks)
+    a, _ = quantised_operand(randn((m, k), 3), "fp8", 128)
+    b, _ = _stacked_b("fp8", groups, n, k, 4, gran=128)
+    mi = dev(np.array(blocks, dtype=np.int32))
+    full = new_output(m, n, fill=0.0)
+    m_grouped_gemm_nt_contiguous(a, b, full, mi, groups)
+    rng = np.random.default_rng(0)
+    rmap = rng.permutation(m).astype(np.int32)
+    rmap[5::7] = -1
+    n0, nc = 128, 192
+    out = torch.full((m, nc), 9.0, dtype=torch.bfloat16, device="cuda")
+    m_grouped_gemm_nt_contiguous_scatter(a, b, Output(Dtype.Bf16, m, nc, nc, out), mi, groups, dev(rmap), n0, nc)
+    poll_device_status()
+    got, want = out.float().cpu().numpy(), to_f32(full)
+    written = np.zeros(m, dtype=bool)
+    for r in range(m):
+        if blocks[r // 128] >= 0 and rmap[r] >= 0:
+            assert np.array_equal(got[rmap[r]], want[r, n0:n0 + nc])
+            written[rmap[r]] = True
+    assert (got[~written] == 9.0).all()
 
 
 def test_m_grouped_contiguous_reference_test_shape():
