@@ -64,6 +64,9 @@ struct GemmParams {
     const int32_t* layout; // m_indices (contiguous) or masked_m (masked)
     const int32_t* d_row_map;  // optional: D row of every A row (negative = drop the row); NULL = identity
     uint32_t* status;
+    uint32_t k_splits;          // dense GEMM with few tiles: K is cut into this many ranges (1 = off)
+    uint32_t kb_per_split;      // k-blocks per range (a multiple of 4)
+    float* split_ws;            // f32 partial tiles [k_splits][m][n] when k_splits > 1
     uint32_t b_group_rows;      // rows of B per group (grouped GEMMs); >= n when only a column range is computed
     uint32_t b_row_offset;      // first B row inside every group
     uint32_t pf_chunk;          // k-blocks per L2 prefetch of B (0 = off)
@@ -76,6 +79,8 @@ struct Tile {
     uint32_t row_end;   // rows >= row_end are not stored
     uint32_t n0;        // first column of D
     uint32_t b_row;     // first row in (stacked) B / SFB-column coordinates
+    uint32_t kb0, kb1;  // k-block range of this work item
+    uint32_t split;     // index of the K range (0 without split-K)
     bool skip;
 };
 
@@ -100,6 +105,7 @@ struct Scheduler {
         const uint32_t id = next_id;
         next_id += stride;
         t.skip = false;
+        t.kb0 = 0; t.kb1 = p.num_k_blocks; t.split = 0;
         if (GTYPE == kContiguous && CL == 2) {
             // m-tiles come from the list built at kernel start: a pair of 128-row blocks of one
             // expert, or a single block whose partner rows (the next block, another expert's) are
@@ -124,9 +130,19 @@ struct Scheduler {
             t.b_row = (uint32_t)__ldg(p.layout + blk) * p.b_group_rows + p.b_row_offset + t.n0;
             return true;
         } else if (GTYPE != kMasked) {
-            if (id >= p.num_m_blocks * p.num_n_blocks) return false;
+            uint32_t tile = id;
+            if (GTYPE == kNormal && p.k_splits > 1) {
+                // work item = (tile, K range); ranges of one tile are neighbours in the order
+                if (id >= p.num_m_blocks * p.num_n_blocks * p.k_splits) return false;
+                tile = id / p.k_splits;
+                t.split = id - tile * p.k_splits;
+                t.kb0 = t.split * p.kb_per_split;
+                t.kb1 = min(p.num_k_blocks, t.kb0 + p.kb_per_split);
+            } else if (id >= p.num_m_blocks * p.num_n_blocks) {
+                return false;
+            }
             const uint32_t per_band = p.band * p.num_n_blocks;
-            const uint32_t b = id / per_band, rem = id - b * per_band;
+            const uint32_t b = tile / per_band, rem = tile - b * per_band;
             const uint32_t mb0 = b * p.band;
             const uint32_t rows = min(p.band, p.num_m_blocks - mb0);
             const uint32_t nb = rem / rows, mb = mb0 + (rem - nb * rows);
@@ -290,7 +306,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         const uint32_t b_rows_per_cta = p.block_n / CL;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
-            for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+            for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
                 if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[kb] = clock64();
                 const uint32_t sa = stage_addr(stage);
@@ -352,7 +368,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem + as * kAccStageCols;
-            for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+            for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->full[stage]), phase, wc, kWaitFull))) break;
                 if (kHasSf && (kb % p.sfa_period == 0 || kb % p.sfb_period == 0)) {
                     if (!(ok = DG_WARP_WAIT(smem_u32(&bars->sf_ready[stage]), (sf_bits >> stage) & 1u, wc, kWaitSfReady))) break;
@@ -381,7 +397,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         if ((p.dbg & 4u) && k) break;
                         // 32 bytes of K per MMA (32 FP8, 64 FP4, 16 BF16): +2 in the >>4 address field.
                         const uint64_t ad = a_desc + 2u * k, bd = b_desc + 2u * k;
-                        const uint32_t acc = (kb | k) != 0u ? 1u : 0u;
+                        const uint32_t acc = (kb != t.kb0 || k != 0u) ? 1u : 0u;
                         if (KIND == kBf16) {
                             tc_mma_bf16<CL>(d_tmem, ad, bd, idesc, acc);
                         } else if (KIND == kFp8) {
@@ -400,7 +416,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     // free the stage in both CTAs / publish the accumulator to both epilogues
                     tc_commit<CL>(smem_u32(&bars->empty[stage]));
                     if (CL == 2) tc_commit<CL>(mapa(smem_u32(&bars->empty[stage]), 1));
-                    if (kb + 1 == p.num_k_blocks) {
+                    if (kb + 1 == t.kb1) {
                         tc_commit<CL>(smem_u32(&bars->tmem_full[as]));
                         if (CL == 2) tc_commit<CL>(mapa(smem_u32(&bars->tmem_full[as]), 1));
                     }
@@ -418,7 +434,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         bool ok = true;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
-            for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+            for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
                 const bool has_a = kb % p.sfa_period == 0, has_b = kb % p.sfb_period == 0;
                 if (has_a || has_b) {
                     const uint32_t parity = (sf_bits >> stage) & 1u;
@@ -500,6 +516,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 const uint32_t col0 = t.n0 + c * 32u;
                 if (!row_ok || col0 >= p.n) continue;
+                if (GTYPE == kNormal && p.k_splits > 1) {
+                    // partial sum of this K range; reduced in range order by split_reduce_kernel
+                    float* dst = p.split_ws + ((size_t)t.split * p.m + row) * p.n + col0;
+                    if (p.n % 4 == 0 && col0 + 32u <= p.n) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i)
+                            *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                                                  __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                    } else {
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i)
+                            if (col0 + i < p.n) dst[i] = __uint_as_float(r[i]);
+                    }
+                    continue;
+                }
                 if (p.out_f32) {
                     float* dst = reinterpret_cast<float*>(p.d) + (size_t)row * p.ldd + col0;
                     if (vec_ok && col0 + 32u <= p.n) {
@@ -563,6 +594,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (warp == 2) {
         tc_fence_after();
         tmem_dealloc<CL>(tmem, kTmemCols);
+    }
+}
+
+// D[r][c] (+)= sum over K ranges, added in range order (fixed, so results repeat bit for bit),
+// then rounded once to the output type.
+__global__ void __launch_bounds__(256) split_reduce_kernel(const float* __restrict__ ws, uint32_t splits, uint32_t m, uint32_t n,
+                                                          void* __restrict__ d, uint64_t ldd, uint32_t out_f32, uint32_t accumulate) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)m * n) return;
+    const uint32_t r = (uint32_t)(idx / n), c = (uint32_t)(idx % n);
+    float acc = 0.f;
+    for (uint32_t s = 0; s < splits; ++s) acc += ws[((size_t)s * m + r) * n + c];
+    if (out_f32) {
+        float* o = reinterpret_cast<float*>(d) + (size_t)r * ldd + c;
+        *o = accumulate ? *o + acc : acc;
+    } else {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(d) + (size_t)r * ldd + c;
+        __nv_bfloat16 v = __float2bfloat16_rn(acc);
+        if (accumulate) v = __float2bfloat16_rn(__bfloat162float(*o) + __bfloat162float(v));
+        *o = v;
     }
 }
 
@@ -630,6 +681,34 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     p.block_n = pick_block_n(kind, m_tiles_total, n, units);
     p.num_m_blocks = ceil_div(m, tile_m);
     p.num_n_blocks = ceil_div(n, p.block_n);
+    // Split-K for weight-streaming shapes (a single row block, long K): with one tile per SM at
+    // best, the k-loop latency of a tile bounds the run, so K is cut into ranges that run on
+    // otherwise idle SMs; partial tiles are summed in range order by a second kernel.
+    p.k_splits = 1;
+    p.kb_per_split = p.num_k_blocks;
+    if (gtype == kNormal && cl == 1 && m <= kBlockM && p.num_k_blocks >= 16 && env_u32("DG_SPLIT_K", 1)) {
+        const uint32_t forced_bn = env_u32("DG_BLOCK_N", 0);
+        uint32_t best_bn = p.block_n, best_splits = 1;
+        double best_cost = 1e30;
+        for (uint32_t bn = 64; bn <= 224; bn += 32) {
+            if (forced_bn && bn != forced_bn) continue;
+            const uint32_t tiles = ceil_div(n, bn);
+            for (uint32_t sp = 1; sp <= 16; ++sp) {
+                const uint32_t per = align_up(ceil_div(p.num_k_blocks, sp), 4);
+                if (ceil_div(p.num_k_blocks, per) != sp) continue;
+                const uint32_t waves = ceil_div(tiles * sp, sms);
+                // k-blocks of the longest chain + a fixed cost per work item + the reduce traffic
+                const double cost = (double)waves * (per * (0.35 + bn / 640.0) + 6.0) + (sp > 1 ? 2.0 + sp * 0.5 : 0.0);
+                if (cost < best_cost) { best_cost = cost; best_bn = bn; best_splits = sp; }
+            }
+        }
+        const uint32_t forced_sp = env_u32("DG_SPLIT_K", 1);
+        if (forced_sp > 1) best_splits = forced_sp;
+        p.block_n = best_bn;
+        p.num_n_blocks = ceil_div(n, p.block_n);
+        p.kb_per_split = align_up(ceil_div(p.num_k_blocks, best_splits), 4);
+        p.k_splits = ceil_div(p.num_k_blocks, p.kb_per_split);
+    }
     p.band = env_u32("DG_BAND", 8 / cl);
     if (p.band == 0) p.band = 8 / cl;
     const bool has_sf = kind != kBf16;
@@ -657,7 +736,7 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     if (stages < 2) return fail(DG_ERR_RUNTIME, "shared memory budget %u B too small for a %u-wide tile", budget, p.block_n);
     p.num_stages = stages;
     plan->smem_bytes = fixed + stages * p.stage_bytes;
-    plan->num_tiles = gtype == kMasked ? m_tiles_total * p.num_n_blocks : p.num_m_blocks * p.num_n_blocks;
+    plan->num_tiles = gtype == kMasked ? m_tiles_total * p.num_n_blocks : p.num_m_blocks * p.num_n_blocks * p.k_splits;
     uint32_t clusters = units;
     uint32_t worst = gtype == kMasked ? num_groups * ceil_div(m, tile_m) * p.num_n_blocks : plan->num_tiles;
     if (gtype == kContiguous && cl == 2) worst = (m / kBlockM) * p.num_n_blocks;   // every block may be a tile of its own
@@ -824,6 +903,24 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
                                p.pf_chunk * 16u, p.block_n / plan.cluster, CU_TENSOR_MAP_SWIZZLE_NONE, "B prefetch")) != DG_OK) return st;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (p.k_splits > 1) {
+        // stream-ordered scratch for the partial tiles; freed after the reduction below
+        DG_CUDA_CHECK(cudaMallocAsync(&p.split_ws, sizeof(float) * (size_t)p.k_splits * m * n, s));
+        int32_t lst = DG_OK;
+        if (kind == kFp8) lst = launch<kFp8, kNormal, 1>(plan, ta, tb, tsa, tsb, tbpf, s);
+        else if (kind == kFp4) lst = launch<kFp4, kNormal, 1>(plan, ta, tb, tsa, tsb, tbpf, s);
+        else lst = launch<kBf16, kNormal, 1>(plan, ta, tb, tsa, tsb, tbpf, s);
+        if (lst == DG_OK) {
+            const size_t total = (size_t)m * n;
+            split_reduce_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, s>>>(p.split_ws, p.k_splits, m, n, out->data, out->stride,
+                                                                                 p.out_f32, p.accumulate);
+            note_launch();
+        }
+        cudaFreeAsync(p.split_ws, s);
+        if (lst != DG_OK) return lst;
+        DG_CUDA_CHECK(cudaGetLastError());
+        return DG_OK;
+    }
 #define DG_DISPATCH(K, G)                                                                  \
     if (kind == K && gtype == G) {                                                         \
         if (plan.cluster == 2) return launch<K, G, 2>(plan, ta, tb, tsa, tsb, tbpf, s);    \

@@ -52,6 +52,10 @@ int32_t current_device(const DeviceInfo** out) {
     return DG_OK;
 }
 
+static int32_t encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, uint32_t elem_bytes, const void* base,
+                              uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner,
+                              uint32_t box_outer, CUtensorMapSwizzle swizzle, const char* what);
+
 int32_t get_encode_tiled(EncodeTiledFn* fn) {
     static EncodeTiledFn cached = nullptr;
     if (!cached) {
@@ -66,9 +70,48 @@ int32_t get_encode_tiled(EncodeTiledFn* fn) {
     return DG_OK;
 }
 
+// Encoding a tensor map costs about a microsecond of host time and a GEMM needs four or five; calls
+// in a serving loop repeat the same operands, so the last few encodings are kept per thread.
+struct TmapKey {
+    const void* base;
+    uint64_t inner, outer, pitch;
+    uint32_t dt, box_inner, box_outer, swizzle;
+    bool operator==(const TmapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && pitch == o.pitch && dt == o.dt &&
+               box_inner == o.box_inner && box_outer == o.box_outer && swizzle == o.swizzle;
+    }
+};
+struct TmapCache {
+    static constexpr int kSlots = 32;
+    TmapKey key[kSlots];
+    CUtensorMap map[kSlots];
+    int device[kSlots];
+    int used = 0, next = 0;
+};
+static thread_local TmapCache g_tmaps;
+
 int32_t make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, uint32_t elem_bytes, const void* base,
                      uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner,
                      uint32_t box_outer, CUtensorMapSwizzle swizzle, const char* what) {
+    const TmapKey key{base, inner, outer, row_pitch_bytes, (uint32_t)dt, box_inner, box_outer, (uint32_t)swizzle};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    for (int i = 0; i < g_tmaps.used; ++i)
+        if (g_tmaps.device[i] == dev && g_tmaps.key[i] == key) { *map = g_tmaps.map[i]; return DG_OK; }
+    int32_t st = encode_tmap_2d(map, dt, elem_bytes, base, inner, outer, row_pitch_bytes, box_inner, box_outer, swizzle, what);
+    if (st != DG_OK) return st;
+    const int slot = g_tmaps.next;
+    g_tmaps.next = (g_tmaps.next + 1) % TmapCache::kSlots;
+    if (g_tmaps.used < TmapCache::kSlots) ++g_tmaps.used;
+    g_tmaps.key[slot] = key;
+    g_tmaps.map[slot] = *map;
+    g_tmaps.device[slot] = dev;
+    return DG_OK;
+}
+
+static int32_t encode_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, uint32_t elem_bytes, const void* base,
+                       uint64_t inner, uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner,
+                       uint32_t box_outer, CUtensorMapSwizzle swizzle, const char* what) {
     EncodeTiledFn enc;
     int32_t st = get_encode_tiled(&enc);
     if (st != DG_OK) return st;

@@ -17,7 +17,8 @@
 //   warp 0      TMA producer (Q tile per query block, KV tiles streamed through a ring)
 //   warp 1      MMA issuer (head_dim/32 MMAs per kv block, two accumulator stages in TMEM)
 //   warp 2      TMEM owner; ue8m0 contract: scale-factor transposer
-//   warps 4-11  two epilogue warpgroups, each reducing half of the query block's columns
+//   warps 4-..  two or four epilogue warpgroups, each reducing its share of the query block's
+//               columns with the next TMEM load in flight while a chunk is consumed
 #include "host.h"
 #include "ptx.cuh"
 
@@ -25,13 +26,14 @@ namespace dg {
 
 constexpr uint32_t kMqaBlockKv = 128;
 constexpr uint32_t kMqaMaxKvStages = 10;
-constexpr uint32_t kMqaThreads = 384;
+constexpr uint32_t kMqaMaxThreads = 640;   // 4 role warps + up to 4 epilogue warpgroups
 constexpr uint32_t kMqaSfaCol = 448;   // ue8m0 contract only: accumulators are <= 192 wide
 constexpr uint32_t kMqaSfbCol = 452;
 
 struct MqaParams {
     uint32_t num_tokens, num_kv, num_heads, head_dim;
     uint32_t block_q, n;          // n = block_q * num_heads (UMMA N)
+    uint32_t ep_groups;           // epilogue warpgroups (2 or 4); each reduces block_q / ep_groups queries
     uint32_t num_q_blocks;
     uint32_t kv_stages, kv_stage_bytes, q_stage_bytes;
     uint32_t off_w, off_q, off_kv;  // offsets from the 1024-aligned base
@@ -102,7 +104,7 @@ __device__ __forceinline__ float sum_f32x2(uint64_t v) {
 }
 
 template <bool SCALED>
-__global__ void __launch_bounds__(kMqaThreads, 1)
+__global__ void __launch_bounds__(kMqaMaxThreads, 1)
 mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_qsf, const __grid_constant__ CUtensorMap tm_kvsf,
                   const MqaParams p) {
@@ -127,8 +129,8 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(smem_u32(&bars->q_ready[s]), 1);
             mbar_init(smem_u32(&bars->q_empty[s]), 1);
             mbar_init(smem_u32(&bars->tmem_full[s]), 1);
-            mbar_init(smem_u32(&bars->tmem_empty[s]), 8);
-            mbar_init(smem_u32(&bars->w_full[s]), 8);
+            mbar_init(smem_u32(&bars->tmem_empty[s]), 4 * p.ep_groups);
+            mbar_init(smem_u32(&bars->w_full[s]), 4 * p.ep_groups);
         }
         fence_barrier_init();
         tma_prefetch_desc(&tm_q);
@@ -257,11 +259,14 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
         }
     } else if (warp >= 4) {
-        // ===================================================== epilogue (2 warpgroups)
-        const uint32_t et = threadIdx.x - 128u;       // 0..255
-        const uint32_t wg = et >> 7;                  // which half of the query block
+        // ===================================================== epilogue (2 or 4 warpgroups)
+        const uint32_t et = threadIdx.x - 128u;
+        const uint32_t wg = et >> 7;                  // which share of the query block
         const uint32_t quarter = warp & 3u;           // TMEM lane quarter of this warp
-        const uint32_t q_per_wg = p.block_q >> 1;
+        const uint32_t q_per_wg = p.block_q / p.ep_groups;
+        const uint32_t chunks_per_q = p.num_heads / 32u;
+        const uint32_t nchunks = q_per_wg * chunks_per_q;      // 32-column TMEM loads per kv block
+        const uint32_t col_base = wg * q_per_wg * p.num_heads;
         uint32_t qcount = 0, acount = 0;
         bool ok = true;
         for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
@@ -295,40 +300,54 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 const uint32_t j = kb * kMqaBlockKv + quarter * 32u + lane;
                 float scale = 1.f;
                 if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
-                const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride;
-                for (uint32_t qi = 0; qi < q_per_wg; ++qi) {
-                    const uint32_t ql = wg * q_per_wg + qi;          // query within the block
-                    const uint32_t col0 = ql * p.num_heads;
-                    uint64_t acc0 = 0, acc1 = 0;                     // two f32x2 accumulators
-                    for (uint32_t c = 0; c < p.num_heads; c += 32u) {
-                        uint32_t v[32];
-                        __syncwarp();
-                        tmem_ld_x32(taddr + col0 + c, v);
-                        tmem_ld_wait();
-                        if (qi + 1 == q_per_wg && c + 32u == p.num_heads) {
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
-                        }
-                        const float4* w4 = reinterpret_cast<const float4*>(w + col0 + c);
+                const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride + col_base;
+                uint64_t acc0 = 0, acc1 = 0;                     // two f32x2 accumulators of the current query
+
+                // One 32-column chunk: weighted ReLU into the accumulators; on a query's last
+                // chunk, scale and store its logit.
+                auto consume = [&](const uint32_t (&v)[32], uint32_t c) {
+                    const float4* w4 = reinterpret_cast<const float4*>(w + col_base + c * 32u);
 #pragma unroll
-                        for (uint32_t i = 0; i < 8; ++i) {
-                            const float4 ww = w4[i];
-                            const float x0 = fmaxf(__uint_as_float(v[4 * i]), 0.f), x1 = fmaxf(__uint_as_float(v[4 * i + 1]), 0.f);
-                            const float x2 = fmaxf(__uint_as_float(v[4 * i + 2]), 0.f), x3 = fmaxf(__uint_as_float(v[4 * i + 3]), 0.f);
-                            acc0 = fma_f32x2(pack_f32x2(x0, x1), pack_f32x2(ww.x, ww.y), acc0);
-                            acc1 = fma_f32x2(pack_f32x2(x2, x3), pack_f32x2(ww.z, ww.w), acc1);
-                        }
+                    for (uint32_t i = 0; i < 8; ++i) {
+                        const float4 ww = w4[i];
+                        const float x0 = fmaxf(__uint_as_float(v[4 * i]), 0.f), x1 = fmaxf(__uint_as_float(v[4 * i + 1]), 0.f);
+                        const float x2 = fmaxf(__uint_as_float(v[4 * i + 2]), 0.f), x3 = fmaxf(__uint_as_float(v[4 * i + 3]), 0.f);
+                        acc0 = fma_f32x2(pack_f32x2(x0, x1), pack_f32x2(ww.x, ww.y), acc0);
+                        acc1 = fma_f32x2(pack_f32x2(x2, x3), pack_f32x2(ww.z, ww.w), acc1);
                     }
-                    const uint32_t q = qb * p.block_q + ql;
-                    if (q < p.num_tokens) {
-                        const uint32_t s = __ldg(p.ks + q), e = min(__ldg(p.ke + q), p.num_kv);
-                        if (j >= s && j < e) {
-                            const float val = (sum_f32x2(acc0) + sum_f32x2(acc1)) * scale;
-                            const size_t o = (size_t)q * p.logits_stride + (j - s);
-                            if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
-                            else reinterpret_cast<float*>(p.logits)[o] = val;
+                    if ((c + 1) % chunks_per_q == 0) {
+                        const uint32_t q = qb * p.block_q + wg * q_per_wg + c / chunks_per_q;
+                        if (q < p.num_tokens) {
+                            const uint32_t s = __ldg(p.ks + q), e = min(__ldg(p.ke + q), p.num_kv);
+                            if (j >= s && j < e) {
+                                const float val = (sum_f32x2(acc0) + sum_f32x2(acc1)) * scale;
+                                const size_t o = (size_t)q * p.logits_stride + (j - s);
+                                if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
+                                else reinterpret_cast<float*>(p.logits)[o] = val;
+                            }
                         }
+                        acc0 = 0; acc1 = 0;
+                    }
+                };
+                auto release = [&]() {
+                    // every column of this stage is in registers: hand the TMEM stage back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+                };
+                // Two register buffers: the load of chunk c+1 is in flight while chunk c is consumed.
+                uint32_t va[32], vb[32];
+                __syncwarp();
+                tmem_ld_x32(taddr, va);
+                tmem_ld_wait();
+                for (uint32_t c = 0; c < nchunks; c += 2) {
+                    if (c + 1 < nchunks) tmem_ld_x32(taddr + (c + 1) * 32u, vb); else release();
+                    consume(va, c);
+                    if (c + 1 < nchunks) {
+                        tmem_ld_wait();
+                        if (c + 2 < nchunks) tmem_ld_x32(taddr + (c + 2) * 32u, va); else release();
+                        consume(vb, c + 1);
+                        if (c + 2 < nchunks) tmem_ld_wait();
                     }
                 }
             }
@@ -375,6 +394,7 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     p.num_tokens = num_tokens; p.num_kv = num_kv; p.num_heads = num_heads; p.head_dim = head_dim;
     p.block_q = 2 * (max_n / 2 / num_heads);
     p.n = p.block_q * num_heads;
+    p.ep_groups = p.block_q % 4 == 0 ? 4u : 2u;
     p.num_q_blocks = ceil_div(num_tokens, p.block_q);
     p.sbo = 8 * head_dim;
     p.layout = head_dim == 128 ? 2u : head_dim == 64 ? 4u : 6u;
@@ -414,7 +434,7 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     DG_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     uint32_t grid = (uint32_t)dev->sm_count;
     if (p.num_q_blocks < grid) grid = p.num_q_blocks;
-    fn<<<grid, kMqaThreads, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tq, tkv, tqsf, tkvsf, p);
+    fn<<<grid, 128u + 128u * p.ep_groups, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tq, tkv, tqsf, tkvsf, p);
     dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;

@@ -32,11 +32,27 @@ def _sf_c(sf):
 
 
 def _op_c(op):
-    return _lib.OperandC(int(op.dtype), int(op.major), op.rows, op.k, op.outer_stride, _sf_c(op.sf), op.data.data_ptr())
+    """C view of an Operand, cached on the object while its fields are unchanged (building the
+    ctypes structures costs more host time than a small GEMM takes on the GPU)."""
+    sf = op.sf
+    key = (int(op.dtype), int(op.major), op.rows, op.k, op.outer_stride, op.data.data_ptr(),
+           None if sf is None else (sf.rows, sf.cols, int(sf.gran), sf.buf.data_ptr()))
+    cached = op.__dict__.get("_c")
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    c = _lib.OperandC(key[0], key[1], op.rows, op.k, op.outer_stride, _sf_c(sf), key[5])
+    op.__dict__["_c"] = (key, c)
+    return c
 
 
 def _out_c(out):
-    return _lib.OutputC(int(out.dtype), out.rows, out.cols, out.stride, out.data.data_ptr())
+    key = (int(out.dtype), out.rows, out.cols, out.stride, out.data.data_ptr())
+    cached = out.__dict__.get("_c")
+    if cached is not None and cached[0] == key:
+        return cached[1]
+    c = _lib.OutputC(*key)
+    out.__dict__["_c"] = (key, c)
+    return c
 
 
 def device_check():

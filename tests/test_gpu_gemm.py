@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def _clean_env():
     yield
-    for v in ("DG_BLOCK_N", "DG_NUM_STAGES", "DG_BAND", "DG_CLUSTER"):
+    for v in ("DG_BLOCK_N", "DG_NUM_STAGES", "DG_BAND", "DG_CLUSTER", "DG_SPLIT_K"):
         os.environ.pop(v, None)
 
 
@@ -118,6 +118,40 @@ def test_many_tiles_per_cta_and_long_k():
     """More tiles than CTAs (persistent loop, both accumulator stages) and a deep K loop."""
     run_dense("fp8", 2048, 4096, 2048, gran_a=128, gran_b=128, block128_b=True, seed=21)
     run_dense("fp8", 128, 256, 16384, gran_a=128, gran_b=128, seed=22)
+
+
+@pytest.mark.parametrize("kind,m,n,k,splits", [
+    ("fp8", 128, 512, 4096, 0), ("fp8", 128, 512, 4096, 4), ("fp8", 77, 200, 8192, 8), ("fp8", 128, 260, 2048, 2),
+    ("fp4", 100, 384, 8192, 4), ("bf16", 128, 256, 2048, 4),
+])
+def test_split_k_for_single_row_block(kind, m, n, k, splits):
+    """Weight-streaming shapes (one row block, long K) run split over K ranges with a fixed-order
+    reduction; splits = 0 lets the library choose."""
+    if splits:
+        os.environ["DG_SPLIT_K"] = str(splits)
+    run_dense(kind, m, n, k, gran_a=128 if kind == "fp8" else 32, gran_b=128 if kind == "fp8" else 32, seed=k + splits)
+
+
+def test_split_k_accumulate_f32_and_determinism():
+    os.environ["DG_SPLIT_K"] = "4"
+    m, n, k = 128, 384, 4096
+    a, ga = quantised_operand(randn((m, k), 1), "fp8", 128)
+    b, gb = quantised_operand(randn((n, k), 2), "fp8", 128)
+    o1, o2 = new_output(m, n), new_output(m, n)
+    fp8_gemm_nt(a, b, o1)
+    fp8_gemm_nt(a, b, o2)
+    assert torch.equal(o1.data, o2.data)
+    of = new_output(m, n, f32=True, fill=2.0)
+    pf = new_output(m, n, f32=True)
+    gemm_nt(a, b, pf)
+    gemm_nt(a, b, of, accumulate=True)
+    poll_device_status()
+    assert np.array_equal(to_f32(of), to_f32(pf) + np.float32(2.0))
+    assert_close_to_oracle(to_f32(pf), o.gemm_ref(ga, gb, m=m, n=n), "fp8", "split-K f32")
+    os.environ["DG_SPLIT_K"] = "0"      # switched off: same contract
+    p1 = new_output(m, n, f32=True)
+    gemm_nt(a, b, p1)
+    assert_close_to_oracle(to_f32(p1), o.gemm_ref(ga, gb, m=m, n=n), "fp8", "no split")
 
 
 def test_f32_output_and_strided_output():
