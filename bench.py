@@ -144,6 +144,8 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the additional single-GPU workloads")
     ap.add_argument("--tokens", type=int, default=CFG["tokens_per_gpu"], help="tokens per GPU (smaller cases for profiling)")
     ap.add_argument("--experts", type=int, default=CFG["num_experts"], help="total experts (smaller cases for profiling)")
+    ap.add_argument("--only", default=None, help="run only the extra single-GPU workloads whose name starts with this "
+                                                 "(e.g. mqa_logits, fp4_gemm_nt_M4096, quant_mx_fp8_g32) and print them; for profiling")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -170,6 +172,9 @@ def main():
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
     dg.device_check()
     peaks, peak_kind = load_peaks()
+    if args.only:
+        print(json.dumps({"only": args.only, "results": extra_workloads(torch, dg, synth, dev, peaks, only=args.only)}))
+        return
 
     E, topk, T, K, N = CFG["num_experts"], CFG["topk"], CFG["tokens_per_gpu"], CFG["hidden"], CFG["n_out"]
     e_local = E // world
@@ -295,7 +300,7 @@ def main():
         dist.destroy_process_group()
 
 
-def extra_workloads(torch, dg, synth, dev, peaks):
+def extra_workloads(torch, dg, synth, dev, peaks, only=None):
     """Single-GPU numbers of the other benchmark configurations (CUDA events, >= 3 warm-ups,
     inputs larger than L2 or rotated)."""
     from deepgemm import Dtype, Operand, Output
@@ -334,6 +339,9 @@ def extra_workloads(torch, dg, synth, dev, peaks):
     g = torch.Generator(device=dev).manual_seed(0)
     res = {}
 
+    def want(name):
+        return only is None or name.startswith(only)
+
     def dense(kind, m, n, k):
         if kind == "fp8":
             da, sa = dg.quant_mx(torch.randn((m, k), device=dev, generator=g), m, k, Dtype.Fp8, 128)
@@ -360,41 +368,50 @@ def extra_workloads(torch, dg, synth, dev, peaks):
 
     for m in (128, 4096):
         for n, k in ((24576, 1536), (7168, 16384), (4096, 7168)):
-            res[f"fp8_gemm_nt_M{m}_N{n}_K{k}"] = dense("fp8", m, n, k)
-    res["fp4_gemm_nt_M8192_N8192_K8192"] = dense("fp4", 8192, 8192, 8192)
-    res["fp4_gemm_nt_M4096_N7168_K7168"] = dense("fp4", 4096, 7168, 7168)
+            if want(f"fp8_gemm_nt_M{m}_N{n}_K{k}"):
+                res[f"fp8_gemm_nt_M{m}_N{n}_K{k}"] = dense("fp8", m, n, k)
+    if want("fp4_gemm_nt_M8192_N8192_K8192"):
+        res["fp4_gemm_nt_M8192_N8192_K8192"] = dense("fp4", 8192, 8192, 8192)
+    if want("fp4_gemm_nt_M4096_N7168_K7168"):
+        res["fp4_gemm_nt_M4096_N7168_K7168"] = dense("fp4", 4096, 7168, 7168)
 
     # masked decode: 32 experts, expected_m 128, masked_m uniform in [0, 256]
-    G, max_m, n, k = 32, 256, 4096, 7168
-    w = synth.random_expert_weights(G, n, k, seed=5, device=dev)
-    da, sa = dg.quant_mx(torch.randn((G * max_m, k), device=dev, generator=g), G * max_m, k, Dtype.Fp8, 128)
-    a = Operand.k_major(Dtype.Fp8, max_m, k, k, sa, da)
-    masked = torch.randint(0, 257, (G,), device=dev, generator=g, dtype=torch.int32)
-    out = Output(Dtype.Bf16, max_m, n, n, torch.empty((G * max_m, n), dtype=torch.bfloat16, device=dev))
-    ms = timeit(lambda: dg.m_grouped_fp8_gemm_nt_masked(a, w, out, masked, G, 128))
-    sm = int(masked.sum().item())
-    byts = sm * k + G * n * k + sm * n * 2
-    res["m_grouped_fp8_gemm_nt_masked_G32"] = {"ms": ms, "sum_masked_m": sm, "tflops": 2.0 * sm * n * k / ms / 1e9,
-                                               "hbm_gbs": byts / ms / 1e6, "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
+    if want("m_grouped_fp8_gemm_nt_masked_G32"):
+        G, max_m, n, k = 32, 256, 4096, 7168
+        w = synth.random_expert_weights(G, n, k, seed=5, device=dev)
+        da, sa = dg.quant_mx(torch.randn((G * max_m, k), device=dev, generator=g), G * max_m, k, Dtype.Fp8, 128)
+        a = Operand.k_major(Dtype.Fp8, max_m, k, k, sa, da)
+        masked = torch.randint(0, 257, (G,), device=dev, generator=g, dtype=torch.int32)
+        out = Output(Dtype.Bf16, max_m, n, n, torch.empty((G * max_m, n), dtype=torch.bfloat16, device=dev))
+        ms = timeit(lambda: dg.m_grouped_fp8_gemm_nt_masked(a, w, out, masked, G, 128))
+        sm = int(masked.sum().item())
+        byts = sm * k + G * n * k + sm * n * 2
+        res["m_grouped_fp8_gemm_nt_masked_G32"] = {"ms": ms, "sum_masked_m": sm, "tflops": 2.0 * sm * n * k / ms / 1e9,
+                                                   "hbm_gbs": byts / ms / 1e6,
+                                                   "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
 
     # mqa_logits, fp32 contract
-    T, S, H, D = 4096, 32768, 64, 128
-    q = torch.randn((T, H, D), device=dev, generator=g).to(torch.float8_e4m3fn).view(torch.uint8)
-    kvf = torch.randn((S, D), device=dev, generator=g)
-    scale = kvf.abs().amax(dim=1) / 448.0
-    kv = (kvf / scale[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
-    wq = torch.randn((T, H), device=dev, generator=g)
-    ks = torch.zeros(T, dtype=torch.int32, device=dev)
-    ke = (S - T + torch.arange(T, device=dev) + 1).to(torch.int32)
-    logits = torch.empty((T, S), dtype=torch.float32, device=dev)
-    ms = timeit(lambda: dg.mqa_logits_f32(q, kv, scale, wq, ks, ke, T, S, H, D, logits, S), iters=5)
-    pairs = int(ke.sum().item())
-    res["mqa_logits_T4096_S32768_H64_D128"] = {"ms": ms, "tflops": 2.0 * H * D * pairs / ms / 1e9,
-                                               "frac_of_measured_tensor_peak": 2.0 * H * D * pairs / ms / 1e9 / (2 * peaks["bf16_tflops"])}
+    if want("mqa_logits_T4096_S32768_H64_D128"):
+        T, S, H, D = 4096, 32768, 64, 128
+        q = torch.randn((T, H, D), device=dev, generator=g).to(torch.float8_e4m3fn).view(torch.uint8)
+        kvf = torch.randn((S, D), device=dev, generator=g)
+        scale = kvf.abs().amax(dim=1) / 448.0
+        kv = (kvf / scale[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+        wq = torch.randn((T, H), device=dev, generator=g)
+        ks = torch.zeros(T, dtype=torch.int32, device=dev)
+        ke = (S - T + torch.arange(T, device=dev) + 1).to(torch.int32)
+        logits = torch.empty((T, S), dtype=torch.float32, device=dev)
+        ms = timeit(lambda: dg.mqa_logits_f32(q, kv, scale, wq, ks, ke, T, S, H, D, logits, S), iters=5)
+        pairs = int(ke.sum().item())
+        tf = 2.0 * H * D * pairs / ms / 1e9
+        res["mqa_logits_T4096_S32768_H64_D128"] = {"ms": ms, "tflops": tf,
+                                                   "frac_of_measured_tensor_peak": tf / (2 * peaks["bf16_tflops"])}
 
     # quant_mx bandwidth
     for (m, k, dt, gran, name) in ((16384, 7168, Dtype.Fp8, 128, "fp8_g128"), (16384, 7168, Dtype.Fp8, 32, "fp8_g32"),
                                    (16384, 7168, Dtype.Fp4, 32, "fp4_g32"), (4096, 16384, Dtype.Fp8, 128, "fp8_g128")):
+        if not want(f"quant_mx_{name}_{m}x{k}"):
+            continue
         x = torch.randn((m, k), device=dev, generator=g)
         ms = timeit(lambda: dg.quant_mx(x, m, k, dt, gran))
         byts = 4 * m * k + (m * k if dt == Dtype.Fp8 else m * k // 2) + 4 * (-(-(k // gran) // 4)) * m

@@ -70,7 +70,6 @@ struct GemmParams {
     uint32_t b_group_rows;      // rows of B per group (grouped GEMMs); >= n when only a column range is computed
     uint32_t b_row_offset;      // first B row inside every group
     uint32_t pf_chunk;          // k-blocks per L2 prefetch of B (0 = off)
-    uint32_t dbg;               // development switches (timing experiments only; results become wrong)
     unsigned long long* trace;  // debug: per-k-block clock64 stamps of CTA 0's first tile (or null)
 };
 
@@ -88,7 +87,7 @@ struct Tile {
 // A tile is (128 * CL) x BLOCK_N; CTA `rank` of a pair owns rows [rank*128, rank*128 + 128) of it.
 // Tile ids walk bands of `band` m-tiles, m fastest inside a band, so that the tiles in flight
 // share a few A row-blocks and B column-blocks in L2.
-template <int GTYPE, int CL>
+template <int GTYPE, int CL, bool SPLIT = false>
 struct Scheduler {
     uint32_t next_id, stride, rank;
     uint32_t g = 0, g_first_tile = 0;  // masked: current group and its first tile id
@@ -131,7 +130,7 @@ struct Scheduler {
             return true;
         } else if (GTYPE != kMasked) {
             uint32_t tile = id;
-            if (GTYPE == kNormal && p.k_splits > 1) {
+            if (SPLIT) {
                 // work item = (tile, K range); ranges of one tile are neighbours in the order
                 if (id >= p.num_m_blocks * p.num_n_blocks * p.k_splits) return false;
                 tile = id / p.k_splits;
@@ -195,7 +194,10 @@ static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 // CL = 1: one CTA per tile.  CL = 2: a CTA pair per 256-row tile (tcgen05 cta_group::2): each CTA
 // loads its own 128 rows of A and its own half of the B tile, the leader CTA issues MMAs that read
 // both CTAs' shared memory and write both CTAs' TMEM, each CTA drains its own accumulator.
-template <int KIND, int GTYPE, int CL>
+// SPLIT (dense, single CTA only): a work item is a K range of a tile and the epilogue stores f32
+// partial tiles.  It is a separate instantiation because a k-loop that starts at a run-time
+// block measurably slows the common case (the k-block index feeds every role's bookkeeping).
+template <int KIND, int GTYPE, int CL, bool SPLIT>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -299,14 +301,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
     if (warp == 0) {
         // ===================================================== TMA producer (warp-converged, one lane issues)
-        Scheduler<GTYPE, CL> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        Scheduler<GTYPE, CL, SPLIT> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
         const uint32_t b_rows_per_cta = p.block_n / CL;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
-            for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
+            const uint32_t kb_first = SPLIT ? t.kb0 : 0u, kb_count = SPLIT ? t.kb1 - t.kb0 : p.num_k_blocks;
+            for (uint32_t ki = 0; ki < kb_count; ++ki) {
+                const uint32_t kb = kb_first + ki;
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
                 if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[kb] = clock64();
                 const uint32_t sa = stage_addr(stage);
@@ -354,7 +358,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else if (warp == 1 && leader) {
         // ===================================================== MMA issuer (warp-converged, one lane issues)
-        Scheduler<GTYPE, CL> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        Scheduler<GTYPE, CL, SPLIT> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         Tile t;
         uint32_t stage = 0, phase = 0, tile_count = 0;
         uint32_t sf_bits = 0;  // per-stage parity of sf_ready (it completes only on SF k-blocks)
@@ -368,7 +372,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem + as * kAccStageCols;
-            for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
+            const uint32_t kb_first = SPLIT ? t.kb0 : 0u, kb_count = SPLIT ? t.kb1 - t.kb0 : p.num_k_blocks;
+            for (uint32_t ki = 0; ki < kb_count; ++ki) {
+                const uint32_t kb = kb_first + ki;
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->full[stage]), phase, wc, kWaitFull))) break;
                 if (kHasSf && (kb % p.sfa_period == 0 || kb % p.sfb_period == 0)) {
                     if (!(ok = DG_WARP_WAIT(smem_u32(&bars->sf_ready[stage]), (sf_bits >> stage) & 1u, wc, kWaitSfReady))) break;
@@ -378,7 +384,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[512 + kb] = clock64();
                 const uint32_t sa = stage_addr(stage);
                 if (elect_one()) {
-                    if (kHasSf && !(p.dbg & 1u)) {
+                    if (kHasSf) {
                         if (kb % p.sfa_period == 0) {
                             for (uint32_t j = 0; j < p.sf_sub; ++j)
                                 tc_cp_32x128b_warpx4<CL>(tmem + kSfaCol + j * 4u, make_sf_desc(sa + p.off_sfa + j * 512u));
@@ -394,10 +400,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     const uint64_t b_desc = make_kmajor_sw128_desc(sa + p.off_b);
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {
-                        if ((p.dbg & 4u) && k) break;
                         // 32 bytes of K per MMA (32 FP8, 64 FP4, 16 BF16): +2 in the >>4 address field.
                         const uint64_t ad = a_desc + 2u * k, bd = b_desc + 2u * k;
-                        const uint32_t acc = (kb != t.kb0 || k != 0u) ? 1u : 0u;
+                        const uint32_t acc = (ki | k) != 0u ? 1u : 0u;
                         if (KIND == kBf16) {
                             tc_mma_bf16<CL>(d_tmem, ad, bd, idesc, acc);
                         } else if (KIND == kFp8) {
@@ -416,7 +421,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     // free the stage in both CTAs / publish the accumulator to both epilogues
                     tc_commit<CL>(smem_u32(&bars->empty[stage]));
                     if (CL == 2) tc_commit<CL>(mapa(smem_u32(&bars->empty[stage]), 1));
-                    if (kb + 1 == t.kb1) {
+                    if (ki + 1 == kb_count) {
                         tc_commit<CL>(smem_u32(&bars->tmem_full[as]));
                         if (CL == 2) tc_commit<CL>(mapa(smem_u32(&bars->tmem_full[as]), 1));
                     }
@@ -428,13 +433,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else if (warp == 2 && kHasSf) {
         // ===================================================== SF transposer
-        Scheduler<GTYPE, CL> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        Scheduler<GTYPE, CL, SPLIT> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         Tile t;
         uint32_t stage = 0, sf_bits = 0;
         bool ok = true;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
-            for (uint32_t kb = t.kb0; kb < t.kb1; ++kb) {
+            const uint32_t kb_first = SPLIT ? t.kb0 : 0u, kb_count = SPLIT ? t.kb1 - t.kb0 : p.num_k_blocks;
+            for (uint32_t ki = 0; ki < kb_count; ++ki) {
+                const uint32_t kb = kb_first + ki;
                 const bool has_a = kb % p.sfa_period == 0, has_b = kb % p.sfb_period == 0;
                 if (has_a || has_b) {
                     const uint32_t parity = (sf_bits >> stage) & 1u;
@@ -448,7 +455,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     // Up to 6 chunks of 128 words: word of row 32*i + lane -> position lane*4 + i.
                     // All loads are issued before the first store.
                     uint4 v[6];
-                    if (!(p.dbg & 2u)) {
 #pragma unroll
                     for (uint32_t c = 0; c < 6; ++c) {
                         if (c < na + nb) {
@@ -464,8 +470,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             *reinterpret_cast<uint4*>(q + lane * 4u) = v[c];
                         }
                     }
-                    }
-                    if (!(p.dbg & 8u)) fence_proxy_async_smem();
+                    fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
                         if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
@@ -478,7 +483,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else if (warp >= 4) {
         // ===================================================== epilogue
-        Scheduler<GTYPE, CL> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        Scheduler<GTYPE, CL, SPLIT> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         Tile t;
         const uint32_t q = warp - 4u;  // TMEM lane quarter == warp index % 4
         uint32_t tile_count = 0;
@@ -516,7 +521,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 const uint32_t col0 = t.n0 + c * 32u;
                 if (!row_ok || col0 >= p.n) continue;
-                if (GTYPE == kNormal && p.k_splits > 1) {
+                if (SPLIT) {
                     // partial sum of this K range; reduced in range order by split_reduce_kernel
                     float* dst = p.split_ws + ((size_t)t.split * p.m + row) * p.n + col0;
                     if (p.n % 4 == 0 && col0 + 32u <= p.n) {
@@ -745,7 +750,6 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     plan->grid = clusters * cl;
     p.status = dev->status;
     p.trace = g_trace;
-    p.dbg = env_u32("DG_DEBUG_SKIP", 0);
     p.pf_chunk = env_u32("DG_PREFETCH", 0);
     if (p.pf_chunk > 16) p.pf_chunk = 16;
     if (env_u32("DG_PRINT_CONFIGS", 0))
@@ -754,10 +758,10 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     return DG_OK;
 }
 
-template <int KIND, int GTYPE, int CL>
+template <int KIND, int GTYPE, int CL, bool SPLIT = false>
 static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                       const CUtensorMap& tsb, const CUtensorMap& tbpf, cudaStream_t s) {
-    auto* fn = gemm_kernel<KIND, GTYPE, CL>;
+    auto* fn = gemm_kernel<KIND, GTYPE, CL, SPLIT>;
     static thread_local uint32_t configured[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -904,19 +908,49 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (p.k_splits > 1) {
-        // stream-ordered scratch for the partial tiles; freed after the reduction below
-        DG_CUDA_CHECK(cudaMallocAsync(&p.split_ws, sizeof(float) * (size_t)p.k_splits * m * n, s));
+        // Scratch for the partial tiles: one buffer per (thread, device, stream), grown on demand with
+        // stream-ordered allocation and kept for the next call (work on one stream is ordered, so
+        // consecutive calls may share it; allocating per call costs more host time than the GEMM).
+        struct SplitWs { cudaStream_t stream; int device; float* ptr; size_t bytes; };
+        static thread_local SplitWs cache[8] = {};
+        static thread_local int cache_next = 0;
+        const size_t need = sizeof(float) * (size_t)p.k_splits * m * n;
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(s, &capturing);
+        float* graph_ws = nullptr;
+        SplitWs* slot = nullptr;
+        if (capturing != cudaStreamCaptureStatusNone) {
+            // inside a graph capture the buffer must belong to the graph: allocate and free per call
+            DG_CUDA_CHECK(cudaMallocAsync(&graph_ws, need, s));
+            p.split_ws = graph_ws;
+        } else {
+        for (auto& c : cache)
+            if (c.ptr && c.stream == s && c.device == dev->device) { slot = &c; break; }
+        if (!slot) {
+            slot = &cache[cache_next];
+            cache_next = (cache_next + 1) % 8;
+            if (slot->ptr) { cudaFreeAsync(slot->ptr, slot->stream); *slot = SplitWs{}; }
+        }
+        if (slot->bytes < need) {
+            if (slot->ptr) cudaFreeAsync(slot->ptr, s);
+            *slot = SplitWs{};
+            float* fresh = nullptr;
+            DG_CUDA_CHECK(cudaMallocAsync(&fresh, need, s));
+            *slot = SplitWs{s, dev->device, fresh, need};
+        }
+        p.split_ws = slot->ptr;
+        }
         int32_t lst = DG_OK;
-        if (kind == kFp8) lst = launch<kFp8, kNormal, 1>(plan, ta, tb, tsa, tsb, tbpf, s);
-        else if (kind == kFp4) lst = launch<kFp4, kNormal, 1>(plan, ta, tb, tsa, tsb, tbpf, s);
-        else lst = launch<kBf16, kNormal, 1>(plan, ta, tb, tsa, tsb, tbpf, s);
+        if (kind == kFp8) lst = launch<kFp8, kNormal, 1, true>(plan, ta, tb, tsa, tsb, tbpf, s);
+        else if (kind == kFp4) lst = launch<kFp4, kNormal, 1, true>(plan, ta, tb, tsa, tsb, tbpf, s);
+        else lst = launch<kBf16, kNormal, 1, true>(plan, ta, tb, tsa, tsb, tbpf, s);
         if (lst == DG_OK) {
             const size_t total = (size_t)m * n;
             split_reduce_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, s>>>(p.split_ws, p.k_splits, m, n, out->data, out->stride,
                                                                                  p.out_f32, p.accumulate);
             note_launch();
         }
-        cudaFreeAsync(p.split_ws, s);
+        if (graph_ws) cudaFreeAsync(graph_ws, s);
         if (lst != DG_OK) return lst;
         DG_CUDA_CHECK(cudaGetLastError());
         return DG_OK;

@@ -22,6 +22,8 @@
 #include "host.h"
 #include "ptx.cuh"
 
+#include <cstdlib>
+
 namespace dg {
 
 constexpr uint32_t kMqaBlockKv = 128;

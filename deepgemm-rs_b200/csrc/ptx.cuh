@@ -14,6 +14,9 @@
 namespace dg {
 
 constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
+#ifndef DG_PARK_NS
+#define DG_PARK_NS 20000u
+#endif
 
 // Status word layout: low byte = which wait gave up, bits 8.. = blockIdx.x.
 enum WaitSite : uint32_t {
@@ -89,10 +92,22 @@ struct WaitCtx {
     volatile uint32_t* abort;    // shared; non-zero = some role gave up
 };
 
+// try_wait that lets the hardware park the thread for up to `ns` nanoseconds (it still wakes as
+// soon as the phase completes), so that a waiting role does not take issue slots from working warps.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t site) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_parked(bar, parity, DG_PARK_NS)) {
         if ((++spins & 63u) == 0) {
             if (*w.abort) return false;
             if (globaltimer_ns() - t0 > kWaitTimeoutNs) {
