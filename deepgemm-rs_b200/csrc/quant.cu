@@ -29,10 +29,14 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
     uint32_t r = (uint32_t)lo | ((uint32_t)hi << 16);
-    if (a != a) r = (r & 0xffffff00u) | ((__float_as_uint(a) >> 31) << 7);
-    if (b != b) r = (r & 0xffff00ffu) | ((__float_as_uint(b) >> 31) << 15);
-    if (c != c) r = (r & 0xff00ffffu) | ((__float_as_uint(c) >> 31) << 23);
-    if (d != d) r = (r & 0x00ffffffu) | ((__float_as_uint(d) >> 31) << 31);
+    // The saturating conversion never produces 0x7f / 0xff for a number (the largest finite code is
+    // 0x7e), so a byte with all seven low bits set marks a NaN input: a rare, single test.
+    if (((r & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) {
+        if (a != a) r = (r & 0xffffff00u) | ((__float_as_uint(a) >> 31) << 7);
+        if (b != b) r = (r & 0xffff00ffu) | ((__float_as_uint(b) >> 31) << 15);
+        if (c != c) r = (r & 0xff00ffffu) | ((__float_as_uint(c) >> 31) << 23);
+        if (d != d) r = (r & 0x00ffffffu) | ((__float_as_uint(d) >> 31) << 31);
+    }
     return r;
 }
 // Two scaled floats -> one byte of two E2M1 nibbles (first element in the low nibble).
@@ -114,11 +118,12 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
                     if (ok) *reinterpret_cast<uint32_t*>(data + (size_t)row * k + col) = b;
                 }
                 if (G == 32) {
-                    // group leaders are lanes 0, 8, 16, 24
-                    const uint32_t e0 = __shfl_sync(0xffffffffu, e, 0), e1 = __shfl_sync(0xffffffffu, e, 8);
-                    const uint32_t e2 = __shfl_sync(0xffffffffu, e, 16), e3 = __shfl_sync(0xffffffffu, e, 24);
-                    word = e0 | (groups_here > 1 ? e1 << 8 : 0u) | (groups_here > 2 ? e2 << 16 : 0u) |
-                           (groups_here > 3 ? e3 << 24 : 0u);
+                    // every lane of group g holds the group's exponent: place it in byte g and OR the
+                    // four 8-lane groups together (two butterfly steps)
+                    uint32_t part = grp < groups_here ? e << (8u * grp) : 0u;
+                    part |= __shfl_xor_sync(0xffffffffu, part, 8);
+                    part |= __shfl_xor_sync(0xffffffffu, part, 16);
+                    word = part;
                 } else {
                     if (j < groups_here) word |= e << (8u * j);
                 }

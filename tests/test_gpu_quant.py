@@ -30,7 +30,8 @@ def _special(m, k, seed):
     rng = np.random.default_rng(seed + 1)
     idx = rng.choice(flat.size, size=min(flat.size // 4, 4000), replace=False)
     specials = np.array([0.0, -0.0, 1e-38, -1e-38, 1e-30, 448.0, -448.0, 464.0, 6.0, -6.0, 3.5, 2.5, 0.25, 1.75,
-                         5.0, 7.0, 1e30, -1e30, 2.0 ** -9, 3 * 2.0 ** -10, 0.0625, 500.0], dtype=np.float32)
+                         5.0, 7.0, 1e30, -1e30, 2.0 ** -9, 3 * 2.0 ** -10, 0.0625, 500.0, np.nan, -np.nan],
+                        dtype=np.float32)
     flat[idx] = specials[rng.integers(0, specials.size, idx.size)]
     if m > 2:
         x[1, :] = 0.0                         # an all-zero row: amax floor
