@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libdeepgemm_b200.so")
-SOURCES = ["host.cu", "quant.cu", "gemm.cu", "mqa_logits.cu", "moe.cu"]
+SOURCES = ["host.cu", "quant.cu", "gemm.cu", "mqa_logits.cu", "moe.cu", "peer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

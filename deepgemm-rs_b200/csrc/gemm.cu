@@ -63,6 +63,7 @@ struct GemmParams {
     void* d;
     const int32_t* layout; // m_indices (contiguous) or masked_m (masked)
     const int32_t* d_row_map;  // optional: D row of every A row (negative = drop the row); NULL = identity
+    const uint64_t* d_row_ptr; // optional (contiguous, bf16): address of every A row's D row, this or a peer GPU's (0 = drop)
     uint32_t* status;
     uint32_t k_splits;          // dense GEMM with few tiles: K is cut into this many ranges (1 = off)
     uint32_t kb_per_split;      // k-blocks per range (a multiple of 4)
@@ -498,7 +499,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             tc_fence_after();
             uint32_t row = t.a_row + q * 32u + lane;
             bool row_ok = row < t.row_end;
-            if (p.d_row_map && row_ok) {
+            // rows of D addressed one by one (they may live in a peer GPU's memory)
+            const bool by_ptr = GTYPE == kContiguous && !SPLIT && p.d_row_ptr != nullptr;
+            uint64_t row_addr = 0;
+            if (by_ptr) {
+                if (row_ok) row_addr = __ldg(reinterpret_cast<const unsigned long long*>(p.d_row_ptr) + row);
+                row_ok = row_ok && row_addr != 0;
+            } else if (p.d_row_map && row_ok) {
                 const int32_t mapped = __ldg(p.d_row_map + row);
                 row_ok = mapped >= 0;
                 row = (uint32_t)mapped;
@@ -555,8 +562,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             if (col0 + i < p.n) dst[i] = __uint_as_float(r[i]) + (p.accumulate ? dst[i] : 0.f);
                     }
                 } else {
-                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.d) + (size_t)row * p.ldd + col0;
-                    if (vec_ok && col0 + 32u <= p.n) {
+                    __nv_bfloat16* dst = by_ptr ? reinterpret_cast<__nv_bfloat16*>(row_addr) + col0
+                                                : reinterpret_cast<__nv_bfloat16*>(p.d) + (size_t)row * p.ldd + col0;
+                    if ((vec_ok || by_ptr) && col0 + 32u <= p.n) {
 #pragma unroll
                         for (uint32_t i = 0; i < 4; ++i) {
                             uint32_t w[4];
@@ -808,17 +816,20 @@ static int32_t validate_operand(const dg_operand_t* op, const char* name) {
 
 static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int gtype, const int32_t* layout,
                         uint32_t layout_len, uint32_t num_groups, uint32_t expected_m, int32_t accumulate, void* stream,
-                        const int32_t* d_row_map = nullptr, uint32_t n_begin = 0, uint32_t n_count = 0) {
+                        const int32_t* d_row_map = nullptr, uint32_t n_begin = 0, uint32_t n_count = 0,
+                        const uint64_t* d_row_ptr = nullptr) {
     int32_t st;
     if ((st = validate_operand(a, "A")) != DG_OK) return st;
     if ((st = validate_operand(b, "B")) != DG_OK) return st;
-    if (!out || !out->data) return fail(DG_ERR_INVALID_ARG, "null output");
+    if (!out || (!out->data && !d_row_ptr)) return fail(DG_ERR_INVALID_ARG, "null output");
+    if (d_row_ptr && (out->dtype != DG_BF16 || out->cols % 8 != 0))
+        return fail(DG_ERR_INVALID_ARG, "row-pointer output must be BF16 with a multiple of 8 columns");
     if (a->k != b->k) return fail(DG_ERR_INVALID_ARG, "A/B K mismatch");
     if (n_count == 0) { n_begin = 0; n_count = b ? b->rows : 0; }
     if (n_begin + n_count > b->rows || n_begin % 4 != 0)
         return fail(DG_ERR_INVALID_ARG, "column range [%u, %u) must lie inside N = %u and start on a multiple of 4", n_begin,
                     n_begin + n_count, b->rows);
-    if (out->cols != n_count || (!d_row_map && out->rows != a->rows)) return fail(DG_ERR_INVALID_ARG, "output shape mismatch");
+    if (out->cols != n_count || (!d_row_map && !d_row_ptr && out->rows != a->rows)) return fail(DG_ERR_INVALID_ARG, "output shape mismatch");
     if (out->dtype != DG_BF16 && out->dtype != DG_F32) return fail(DG_ERR_INVALID_ARG, "output must be BF16 or FP32");
     if (out->stride < out->cols) return fail(DG_ERR_INVALID_ARG, "output stride (%u) smaller than its columns (%u)", out->stride, out->cols);
     if (a->dtype != b->dtype)
@@ -876,6 +887,7 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     p.d = out->data;
     p.layout = layout;
     p.d_row_map = d_row_map;
+    p.d_row_ptr = d_row_ptr;
     p.b_group_rows = n_full;
     p.b_row_offset = n_begin;
 
@@ -1006,6 +1018,17 @@ int32_t dg_m_grouped_gemm_nt_contiguous_scatter(const dg_operand_t* a, const dg_
     if (a->major != DG_MAJOR_K) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous requires K-major A");
     return dg::run_gemm(a, b, out, dg::kContiguous, m_indices, m_indices_len, num_groups, a->rows, 0, stream, d_row_map,
                         n_begin, n_count);
+}
+int32_t dg_m_grouped_gemm_nt_contiguous_rowptr(const dg_operand_t* a, const dg_operand_t* b, const int32_t* m_indices,
+                                               uint32_t m_indices_len, uint32_t num_groups, const uint64_t* d_row_ptr,
+                                               uint32_t n_begin, uint32_t n_count, void* stream) {
+    if (!d_row_ptr) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous rowptr requires the row address table");
+    if (!a || !b) return dg::fail(DG_ERR_INVALID_ARG, "null operand");
+    if (a->major != DG_MAJOR_K) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous requires K-major A");
+    if (n_count == 0) { n_begin = 0; n_count = b->rows; }
+    dg_output_t out = {DG_BF16, 0, n_count, n_count, nullptr};
+    return dg::run_gemm(a, b, &out, dg::kContiguous, m_indices, m_indices_len, num_groups, a->rows, 0, stream, nullptr,
+                        n_begin, n_count, d_row_ptr);
 }
 int32_t dg_m_grouped_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, const int32_t* masked_m,
                                     uint32_t num_groups, uint32_t expected_m, void* stream) {

@@ -19,11 +19,13 @@ import os
 from dataclasses import dataclass
 from typing import Optional
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
 from . import _lib
-from .api import _check, _stream_ptr, m_grouped_gemm_nt_contiguous, m_grouped_gemm_nt_contiguous_scatter
+from .api import (_check, _stream_ptr, m_grouped_gemm_nt_contiguous, m_grouped_gemm_nt_contiguous_rowptr,
+                  m_grouped_gemm_nt_contiguous_scatter)
 from .types import Dtype, Operand, Output, SfGran, SfTensor
 
 BLOCK = 128  # rows per m_indices entry (heuristics::mk_alignment_for_contiguous_layout)
@@ -192,6 +194,37 @@ def combine(src, pos, weights, out=None):
     return out
 
 
+def peer_step_tables(tot, me):
+    """Host-side index arithmetic of one expert-parallel step over peer memory, for rank `me`.
+
+    tot[src, chunk, dst] = rows that rank src sends to the experts of rank dst in token slice chunk
+    (known to every rank after one all-gather).  Returns
+      seg[chunk, world + 1]   first received position of every source rank in `me`'s receive area
+                              (rows arrive ordered by source rank, then local expert);
+      row0[chunk, src]        row of src's return buffer where the results computed by `me` begin
+                              (a return buffer holds the slices in order, inside a slice the
+                              destination ranks in order: the order of src's sorted copies);
+      chunk_base[src, chunk]  first row of every slice in src's return buffer;
+      copies[chunk]           list of (dst, first row in my sorted copies, first row in dst's
+                              receive area of that slice, rows), destinations rotated so that the
+                              ranks do not all push to the same peer at once."""
+    tot = np.asarray(tot, dtype=np.int64)
+    world, chunks, _ = tot.shape
+    seg = np.zeros((chunks, world + 1), dtype=np.int32)
+    seg[:, 1:] = np.cumsum(tot[:, :, me].T, axis=1)
+    chunk_rows = tot.sum(2)
+    chunk_base = np.cumsum(chunk_rows, axis=1) - chunk_rows
+    row0 = (chunk_base + tot[:, :, :me].sum(2)).T.astype(np.int32)
+    copies = []
+    for c in range(chunks):
+        lst = []
+        for step in range(world):
+            dst = (me + 1 + step) % world
+            lst.append((dst, int(tot[me, c, :dst].sum()), int(tot[:me, c, dst].sum()), int(tot[me, c, dst])))
+        copies.append(lst)
+    return seg, row0, chunk_base, copies
+
+
 class ExpertParallelMoE:
     """Grouped-GEMM MoE projection with experts sharded over the ranks of `group`.
 
@@ -200,12 +233,24 @@ class ExpertParallelMoE:
     packed SF; returns bf16 [T, n_out] = sum_j topk_w[t, j] * (x[t] . W[topk_idx[t, j]]^T).
     """
 
-    def __init__(self, weights: Operand, num_experts: int, group=None, chunks: int = 1, return_parts: int = 1):
-        # chunks > 1: token slices pipelined through dispatch / GEMM / return; return_parts > 1: the
-        # GEMM of a slice runs in column ranges whose return transfers overlap the next range.  Both
-        # overlap NCCL kernels with a GEMM that wants every SM; measured on 2 GPUs they lost more
-        # than they hid, so the default is the plain sequence.
+    def __init__(self, weights: Operand, num_experts: int, group=None, chunks: int = 1, return_parts: int = 1,
+                 transport: str = "peer"):
+        # transport "peer" (several GPUs): token rows reach the expert owners by copy engine into
+        # peer-mapped buffers, the grouped GEMM stores its result rows straight into the token owner's
+        # memory, and flag barriers replace collectives, so nothing on the data path needs an SM
+        # besides the GEMM itself; `chunks` token slices pipeline dispatch under the previous GEMM.
+        # transport "nccl": all-to-alls over NCCL.  There, chunks > 1 pipelines token slices and
+        # return_parts > 1 runs the GEMM of a slice in column ranges whose return transfers overlap
+        # the next range; both overlap NCCL kernels with a GEMM that wants every SM and, measured on
+        # 2 GPUs, lost more than they hid, so the NCCL default is the plain sequence.
         self.chunks = chunks
+        self.transport = os.environ.get("DG_EP_TRANSPORT", transport)
+        if self.transport not in ("push", "peer", "nccl"):
+            raise ValueError("transport must be 'push', 'peer' or 'nccl'")
+        self._win = None
+        self._win_shape = None
+        self._streams = None
+        self._pinned = None
         self.return_parts = int(os.environ.get("DG_EP_RETURN_PARTS", return_parts))
         self.w = weights
         self.num_experts = num_experts
@@ -229,6 +274,10 @@ class ExpertParallelMoE:
                                          self.e_local)
             self.last_m_indices = p.block_expert
             return combine(d, p.slot_of_row.view(tokens, topk), topk_w)
+        if self.transport == "push":
+            return self._forward_push(x, x_sf, topk_idx, topk_w)
+        if self.transport == "peer":
+            return self._forward_peer(x, x_sf, topk_idx, topk_w)
         # Several GPUs: the tokens are cut into `chunks` slices that flow through
         # dispatch -> GEMM -> return as a pipeline, so that NCCL traffic of one slice overlaps the
         # grouped GEMM of another.  All count exchanges happen first (one all-to-all, one host sync).
@@ -314,3 +363,202 @@ class ExpertParallelMoE:
                 finish(c - 1, states[c - 1])
         finish(chunks - 1, states[chunks - 1])
         return out
+
+    # ---- peer-memory transport -------------------------------------------------------------
+    def _ensure_window(self, recv_rows_needed, ret_rows_needed, chunks, row_bytes, wire_bytes, n_out):
+        """(Re)allocates the peer window when a step needs more room than it has.  Every rank sees the
+        same global counts, so all of them take this branch in the same step."""
+        shape = self._win_shape
+        if shape and shape["chunks"] == chunks and shape["cap"] >= recv_rows_needed and shape["ret_rows"] >= ret_rows_needed \
+                and shape["row_bytes"] == row_bytes and shape["wire_bytes"] == wire_bytes and shape["n_out"] == n_out:
+            return
+        from .peer import PeerWindow
+        if self._win is not None:
+            self._win.close()
+        cap = (int(recv_rows_needed * 1.25) + 1023) // 1024 * 1024
+        ret_rows = (int(ret_rows_needed) + 1023) // 1024 * 1024
+        a256 = lambda v: (v + 255) // 256 * 256
+        off_rows = 0
+        off_wire = off_rows + a256(chunks * cap * row_bytes)
+        off_ret = off_wire + a256(chunks * cap * wire_bytes)
+        total = off_ret + a256(ret_rows * n_out * 2)
+        self._win = PeerWindow(total, self.group)
+        self._win_shape = dict(chunks=chunks, cap=cap, ret_rows=ret_rows, row_bytes=row_bytes, wire_bytes=wire_bytes, n_out=n_out,
+                               off_rows=off_rows, off_wire=off_wire, off_ret=off_ret)
+        dev = self._win.local.device
+        self._ret_bases = torch.tensor([self._win.payload_ptr(r, off_ret) for r in range(self.world)], dtype=torch.int64, device=dev)
+        if self._streams is None:
+            self._streams = (torch.cuda.Stream(), torch.cuda.Stream())
+
+    def close(self):
+        """Collective: releases the peer window."""
+        if self._win is not None:
+            self._win.close()
+            self._win, self._win_shape = None, None
+
+    def _forward_peer(self, x, x_sf, topk_idx, topk_w):
+        """Every rank must pass the same number of tokens (the slices and barrier counts follow from it)."""
+        L = _lib.load()
+        me, world = dist.get_rank(self.group), self.world
+        tokens, topk = topk_idx.shape
+        k, n_out = x.shape[1], self.w.rows
+        k_elems = k if self.w.dtype != Dtype.Fp4 else k * 2
+        dev = x.device
+        rows_per_expert = tokens * topk * world // self.num_experts
+        chunks = max(1, min(self.chunks, rows_per_expert // 1024, tokens // 64 or 1))
+        if os.environ.get("DG_EP_CHUNKS"):
+            chunks = max(1, int(os.environ["DG_EP_CHUNKS"]))
+        bounds = [tokens * c // chunks for c in range(chunks + 1)]
+        sps = [device_plan(topk_idx[bounds[c]:bounds[c + 1]], self.num_experts, 1, div=topk,
+                           capacity=(bounds[c + 1] - bounds[c]) * topk) for c in range(chunks)]
+        send_counts = torch.stack([sp.counts for sp in sps]).view(chunks, world, self.e_local).contiguous()
+        full = torch.empty((world, chunks, world, self.e_local), dtype=torch.int32, device=dev)      # [src, chunk, dst, expert]
+        dist.all_gather_into_tensor(full, send_counts, group=self.group)
+        tot = full.sum(-1).cpu().numpy().astype("int64")                                              # the one host sync of the step
+        row_bytes, wire_bytes = k * x.element_size(), x_sf.rows * 4
+        self._ensure_window(int(tot.sum(0).max()), int(tot.sum((1, 2)).max()), chunks, row_bytes, wire_bytes, n_out)
+        win, sh = self._win, self._win_shape
+        comm, ret_stream = self._streams
+        main = torch.cuda.current_stream()
+        cap = sh["cap"]
+        seg, row0, chunk_base, copies = peer_step_tables(tot, me)                                     # uploaded once per step
+        # (the pinned staging array is reused: the host synchronisation above has waited for the previous step's upload)
+        flat = np.concatenate([seg.reshape(-1), row0.reshape(-1)])
+        if self._pinned is None or self._pinned.numel() < flat.size:
+            self._pinned = torch.empty(max(flat.size, 1024), dtype=torch.int32).pin_memory()
+        self._pinned[:flat.size].copy_(torch.from_numpy(flat))
+        tables = self._pinned[:flat.size].to(dev, non_blocking=True)
+        seg_dev = tables[:chunks * (world + 1)].view(chunks, world + 1)
+        row0_dev = tables[chunks * (world + 1):].view(chunks, world)
+        out = torch.empty((tokens, n_out), dtype=torch.bfloat16, device=dev)
+        experts = torch.arange(self.e_local, device=dev, dtype=torch.int32).repeat(world)
+        recv_rows_all = win.payload(sh["off_rows"], chunks * cap * row_bytes).view(chunks, cap, row_bytes)
+        recv_wire_all = win.payload(sh["off_wire"], chunks * cap * wire_bytes).view(torch.int32).view(chunks, cap, x_sf.rows)
+        ret_all = win.payload(sh["off_ret"], sh["ret_rows"] * n_out * 2).view(torch.bfloat16).view(sh["ret_rows"], n_out)
+        self.last_m_indices = []
+
+        def dispatch(c):
+            xs = x[bounds[c]:bounds[c + 1]]
+            rows = gather_rows(xs, sps[c].slot_src)
+            wire = torch.empty((rows.shape[0], x_sf.rows), dtype=torch.int32, device=dev)
+            _gather_sf(x_sf.buf[:, bounds[c]:], x_sf.cols, 1, sps[c].slot_src, wire, 1, x_sf.rows, x_sf.rows)
+            ready = torch.cuda.Event()
+            ready.record(main)
+            arrived = torch.cuda.Event()
+            with torch.cuda.stream(comm):
+                comm.wait_event(ready)
+                for dst, src_off, dst_off, n in copies[c]:
+                    dst_off += c * cap
+                    win.copy_to(dst, sh["off_rows"] + dst_off * row_bytes, rows.data_ptr() + src_off * row_bytes, n * row_bytes)
+                    win.copy_to(dst, sh["off_wire"] + dst_off * wire_bytes, wire.data_ptr() + src_off * wire_bytes, n * wire_bytes)
+                win.barrier(0)
+                arrived.record(comm)
+            return dict(keep=(rows, wire), arrived=arrived)
+
+        def compute_and_return(c, st):
+            main.wait_event(st["arrived"])
+            r = int(tot[:, c, me].sum())
+            recv_expert = torch.repeat_interleave(experts, full[:, c, me, :].reshape(-1), output_size=r)
+            rp = device_plan(recv_expert, self.e_local, BLOCK, div=1, capacity=contiguous_capacity(r, self.e_local))
+            a = gather_rows(recv_rows_all[c, :max(r, 1)].view(x.dtype), rp.slot_src)
+            a_sf = sf_from_wire(recv_wire_all[c, :max(r, 1)], rp.slot_src, x_sf.gran)
+            ptrs = torch.empty(rp.capacity, dtype=torch.int64, device=dev)
+            _check(L.dg_moe_return_ptrs(rp.slot_src.data_ptr(), rp.capacity, seg_dev[c].data_ptr(), self._ret_bases.data_ptr(),
+                                        row0_dev[c].data_ptr(), world, n_out * 2, ptrs.data_ptr(), _stream_ptr(None)))
+            a_op = Operand.k_major(self.w.dtype, rp.capacity, k_elems, k_elems, a_sf, a)
+            self.last_m_indices.append(rp.block_expert)
+            m_grouped_gemm_nt_contiguous_rowptr(a_op, self.w, rp.block_expert, self.e_local, ptrs)
+            done = torch.cuda.Event()
+            done.record(main)
+            returned = torch.cuda.Event()
+            with torch.cuda.stream(ret_stream):
+                ret_stream.wait_event(done)
+                win.barrier(1)
+                returned.record(ret_stream)
+            st["returned"] = returned
+            st["keep"] += (a, a_sf, ptrs, rp)
+
+        def finish(c, st):
+            main.wait_event(st["returned"])
+            tw = topk_w[bounds[c]:bounds[c + 1]] if topk_w is not None else None
+            r0 = int(chunk_base[me, c])
+            combine(ret_all[r0:r0 + (bounds[c + 1] - bounds[c]) * topk], sps[c].slot_of_row.view(-1, topk), tw,
+                    out=out[bounds[c]:bounds[c + 1]])
+
+        states = [None] * chunks
+        states[0] = dispatch(0)
+        for c in range(chunks):
+            if c + 1 < chunks:
+                states[c + 1] = dispatch(c + 1)
+            compute_and_return(c, states[c])
+            if c >= 1:
+                finish(c - 1, states[c - 1])
+        finish(chunks - 1, states[chunks - 1])
+        self._keep = states   # buffers the side streams read stay referenced until the next step replaces them
+        return out
+
+    # ---- push transport: no host synchronisation, no staging copies --------------------------
+    def _ensure_push_window(self, tokens, topk, row_bytes, sf_rows, n_out):
+        key = ("push", tokens, topk, row_bytes, sf_rows, n_out)
+        if self._win_shape and self._win_shape.get("key") == key:
+            return
+        from .peer import PeerWindow
+        if self._win is not None:
+            self._win.close()
+        world = self.world
+        # room for the worst case (every copy of every rank routed to this rank) plus padding: no
+        # routing can overflow it, so no step has to look at the counts on the host
+        cap = (world * tokens * topk + self.e_local * (BLOCK - 1) + BLOCK - 1) // BLOCK * BLOCK
+        a256 = lambda v: (v + 255) // 256 * 256
+        off_a = 0
+        off_sf = off_a + a256(cap * row_bytes)
+        off_ticket = off_sf + a256(sf_rows * cap * 4)
+        off_ret = off_ticket + a256(cap * 8)
+        total = off_ret + a256(tokens * topk * n_out * 2)
+        self._win = win = PeerWindow(total, self.group)
+        dev = win.local.device
+        table = lambda off: torch.tensor([win.payload_ptr(r, off) for r in range(world)], dtype=torch.int64, device=dev)
+        self._win_shape = dict(key=key, cap=cap, a_bases=table(off_a), sf_bases=table(off_sf), ticket_bases=table(off_ticket),
+                               ret_bases=table(off_ret),
+                               a=win.payload(off_a, cap * row_bytes).view(cap, row_bytes),
+                               sf=win.payload(off_sf, sf_rows * cap * 4).view(torch.int32).view(sf_rows, cap),
+                               tickets=win.payload(off_ticket, cap * 8).view(torch.int64),
+                               ret=win.payload(off_ret, tokens * topk * n_out * 2).view(torch.bfloat16).view(tokens * topk, n_out),
+                               ptrs=torch.empty(cap, dtype=torch.int64, device=dev),
+                               dest_base=torch.empty(self.num_experts, dtype=torch.int32, device=dev),
+                               block_expert=torch.empty(cap // BLOCK, dtype=torch.int32, device=dev),
+                               counts=torch.empty((world, self.num_experts), dtype=torch.int32, device=dev))
+
+    def _forward_push(self, x, x_sf, topk_idx, topk_w):
+        """Every rank must pass the same number of tokens.  The whole step is queued on the current
+        stream without the host ever waiting for the device."""
+        L = _lib.load()
+        me, world = dist.get_rank(self.group), self.world
+        tokens, topk = topk_idx.shape
+        k, n_out = x.shape[1], self.w.rows
+        k_elems = k if self.w.dtype != Dtype.Fp4 else k * 2
+        row_bytes = k * x.element_size()
+        n = tokens * topk
+        self._ensure_push_window(tokens, topk, row_bytes, x_sf.rows, n_out)
+        win, sh = self._win, self._win_shape
+        cap = sh["cap"]
+        stream = _stream_ptr(None)
+        # my copies sorted by global expert (= by owner rank): counts, first position per expert,
+        # token of every position, position of every copy
+        p = device_plan(topk_idx, self.num_experts, 1, div=topk, capacity=n)
+        dist.all_gather_into_tensor(sh["counts"], p.counts, group=self.group)
+        _check(L.dg_ep_route(sh["counts"].data_ptr(), world, me, self.num_experts, BLOCK, cap, sh["dest_base"].data_ptr(),
+                             sh["block_expert"].data_ptr(), stream))
+        _check(L.dg_ep_push(x.data_ptr(), x.stride(0) * x.element_size(), row_bytes, x_sf.buf.data_ptr(), x_sf.rows, x_sf.cols,
+                            p.slot_src.data_ptr(), p.offsets.data_ptr(), sh["dest_base"].data_ptr(), self.num_experts, world, me, n,
+                            cap, sh["a_bases"].data_ptr(), sh["sf_bases"].data_ptr(), sh["ticket_bases"].data_ptr(), 0, stream))
+        win.barrier(0)          # every rank's rows, scale factors and tickets have landed here
+        _check(L.dg_ep_return_ptrs(sh["tickets"].data_ptr(), cap, sh["ret_bases"].data_ptr(), world, n_out * 2,
+                                   sh["ptrs"].data_ptr(), stream))
+        a_op = Operand.k_major(self.w.dtype, cap, k_elems, k_elems, SfTensor(x_sf.rows, cap, x_sf.gran, sh["sf"]),
+                               sh["a"].view(x.dtype))
+        self.last_m_indices = sh["block_expert"]
+        m_grouped_gemm_nt_contiguous_rowptr(a_op, self.w, sh["block_expert"], self.e_local, sh["ptrs"])
+        win.barrier(1)          # every rank's GEMM has stored its result rows, mine included, into the owners' buffers
+        self._keep = p
+        return combine(sh["ret"], p.slot_of_row.view(tokens, topk), topk_w)

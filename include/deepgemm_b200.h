@@ -232,6 +232,72 @@ DG_API int32_t dg_moe_combine(const void* src_bf16, uint64_t src_pitch, const in
                               void* out_bf16, uint64_t out_pitch, uint32_t tokens, uint32_t topk, uint32_t cols,
                               void* stream);
 
+/* ---- expert parallelism over peer memory (extensions; the reference runs on one GPU and has no
+ * counterpart for any entry of this block) ---------------------------------------------------
+ * One process per GPU inside one NVLink/NVSwitch domain.  A rank allocates buffers that the other
+ * ranks map through a 64-byte handle; token rows travel to the expert owners by copy engine
+ * (dg_peer_copy, no SM involved), the grouped GEMM stores its result rows straight into the token
+ * owner's buffer (dg_m_grouped_gemm_nt_contiguous_rowptr), and dg_peer_barrier tells every rank that
+ * the others' writes have landed. */
+/* Device memory (cleared) whose handle other processes can open; free with dg_peer_free. */
+DG_API int32_t dg_peer_alloc(uint64_t bytes, void** ptr);
+DG_API int32_t dg_peer_free(void* ptr);
+/* handle64: 64 bytes to hand to the other ranks (any host channel). */
+DG_API int32_t dg_peer_export(const void* ptr, void* handle64);
+/* Maps another process's buffer into this one (not valid for a handle this process exported). */
+DG_API int32_t dg_peer_open(const void* handle64, void** ptr);
+DG_API int32_t dg_peer_close(void* ptr);
+/* Asynchronous copy between any two device addresses visible here, local or mapped. */
+DG_API int32_t dg_peer_copy(void* dst, const void* src, uint64_t bytes, void* stream);
+/* Barrier between the `world` ranks on `stream`: peer_flags (device array of `world` addresses) points
+ * at every rank's flag array (`world` 64-bit words, cleared at allocation, one array per barrier
+ * channel), local_flags is this rank's own.  `seq` must grow by one per call on a channel, alike on
+ * all ranks.  Work queued on `stream` before the call is visible to every rank once its own barrier
+ * call has completed.  The wait gives up after 10 s (dg_poll_device_status reports it). */
+DG_API int32_t dg_peer_barrier(const uint64_t* peer_flags, uint64_t* local_flags, uint32_t me, uint32_t world,
+                               uint64_t seq, void* stream);
+/* Row address table for the return path of an expert-parallel step: ptrs[s] (device, uint64) = where
+ * slot s of the padded expert layout must store its result row, 0 for padding.  slot_src[s] = position
+ * of the slot's row in the received order (source rank 0's rows first); seg_start[world+1] = first
+ * position of every source; dst_base[r] = rank r's return buffer as mapped here; dst_row0[r] = row of
+ * that buffer where this rank's results begin; row_bytes = pitch of the return buffers. */
+DG_API int32_t dg_moe_return_ptrs(const int32_t* slot_src, uint32_t slots, const int32_t* seg_start,
+                                  const uint64_t* dst_base, const int32_t* dst_row0, uint32_t world,
+                                  uint64_t row_bytes, uint64_t* ptrs, void* stream);
+/* Dispatch by direct stores, without any host synchronisation.  counts[src * num_experts + g] (device)
+ * = copies that rank src routes to global expert g, alike on every rank (one all-gather).  Experts of
+ * one owner rank follow each other in its layout, each padded to `align` rows; inside an expert the
+ * source ranks follow each other.  dg_ep_route writes dest_base[g] = first slot of this rank's copies
+ * of expert g in the owner's layout (-1 and a recorded status if the owner's `cap` rows would
+ * overflow) and block_expert[cap / align] = `m_indices` of this rank's own layout. */
+DG_API int32_t dg_ep_route(const int32_t* counts, uint32_t world, uint32_t me, uint32_t num_experts, uint32_t align,
+                           uint32_t cap, int32_t* dest_base, int32_t* block_expert, void* stream);
+/* Stores every copy of this rank into its owner's memory: for copy p of the copies sorted by global
+ * expert (slot_src[p] = token row, my_offsets[num_experts + 1] = first p of every expert, both from
+ * dg_moe_plan with align 1), the token's row of x goes to row `slot` of the owner's A buffer
+ * (a_bases[owner], rows of row_bytes), its scale-factor words to column `slot` of the owner's packed
+ * SF tensor [sf_rows, cap] (sf_bases[owner]) and a return ticket (this rank, p) to ticket_bases[owner][slot]
+ * (64-bit words, zero = empty).  The three address tables are device arrays of `world` addresses, this
+ * GPU's own or mapped peers'.  max_blocks > 0 bounds the grid (to share the GPU with a running GEMM). */
+DG_API int32_t dg_ep_push(const void* x, uint64_t x_pitch_bytes, uint32_t row_bytes, const uint32_t* x_sf, uint32_t sf_rows,
+                          uint64_t sf_cols, const int32_t* slot_src, const int32_t* my_offsets, const int32_t* dest_base,
+                          uint32_t num_experts, uint32_t world, uint32_t me, uint32_t n_copies, uint64_t cap,
+                          const uint64_t* a_bases, const uint64_t* sf_bases, const uint64_t* ticket_bases,
+                          uint32_t max_blocks, void* stream);
+/* Turns the tickets of this rank's layout into the row address table of
+ * dg_m_grouped_gemm_nt_contiguous_rowptr (ptrs[s] = ret_bases[ticket rank] + position * row_bytes,
+ * 0 for slots without a ticket) and clears the tickets for the next step. */
+DG_API int32_t dg_ep_return_ptrs(uint64_t* tickets, uint32_t slots, const uint64_t* ret_bases, uint32_t world,
+                                 uint64_t row_bytes, uint64_t* ptrs, void* stream);
+/* m_grouped_gemm_nt_contiguous whose BF16 result rows are stored at d_row_ptr[r] + column * 2 for
+ * every row r of A (device table of a.rows addresses, 16-byte aligned, in this GPU's memory or a
+ * mapped peer's; 0 = drop the row).  Columns [n_begin, n_begin + n_count) of every expert are computed
+ * (n_count = 0: all); column n_begin lands at the row address itself. */
+DG_API int32_t dg_m_grouped_gemm_nt_contiguous_rowptr(const dg_operand_t* a, const dg_operand_t* b,
+                                                      const int32_t* m_indices, uint32_t m_indices_len,
+                                                      uint32_t num_groups, const uint64_t* d_row_ptr,
+                                                      uint32_t n_begin, uint32_t n_count, void* stream);
+
 /* ---- tuning / introspection -------------------------------------------------------------
  * Describes the tile configuration the library would use for a dense / grouped GEMM
  * (counterpart of heuristics::get_best_config, deepgemm/src/heuristics.rs:559-608, and of

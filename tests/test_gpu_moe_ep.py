@@ -1,6 +1,10 @@
-"""Expert-parallel MoE step on 2 GPUs (NCCL) against the single-GPU step with all experts
-resident: identical routing and tokens must give bit-identical outputs, because every copy is
-multiplied by the same weights and combined in the same order.  Skipped with fewer than 2 GPUs."""
+"""Expert-parallel MoE step on 2 GPUs against the single-GPU step with all experts resident:
+identical routing and tokens must give bit-identical outputs, because every copy is multiplied by
+the same weights and combined in the same order.  All transports run over repeated steps (the
+buffers are reused): "push" (rows stored into the expert owner's layout by a kernel, result rows
+stored into the token owner's buffer by the GEMM epilogue, flag barriers, no host synchronisation),
+"peer" (copy-engine dispatch with one and two token slices, same return path) and NCCL all-to-alls.
+Skipped with fewer than 2 GPUs."""
 import os
 import socket
 
@@ -42,10 +46,21 @@ def _worker(rank, world, port, out):
                                 SfTensor(full.sf.rows, e_local * N, SfGran.G128, full.sf.buf[:, rows].contiguous()),
                                 full.data[rows].contiguous())
         x8, x_sf, idx, w = _inputs(rank, dev)
-        got = moe.ExpertParallelMoE(local, E, dist.group.WORLD).forward(x8, x_sf, idx, w)
         want = moe.ExpertParallelMoE(full, E, None).forward(x8, x_sf, idx, w)
-        poll_device_status()
-        out[rank] = "ok" if torch.equal(got, want) else f"mismatch: max diff {(got.float() - want.float()).abs().max().item()}"
+        x8b, x_sfb, idxb, wb = _inputs(rank + 10, dev)
+        wantb = moe.ExpertParallelMoE(full, E, None).forward(x8b, x_sfb, idxb, wb)
+        verdicts = []
+        for transport, chunks in (("push", 1), ("peer", 1), ("peer", 2), ("nccl", 1)):
+            os.environ["DG_EP_CHUNKS"] = str(chunks)
+            layer = moe.ExpertParallelMoE(local, E, dist.group.WORLD, transport=transport)
+            for step in range(3):
+                xa, sa, ia, wa, ref = (x8, x_sf, idx, w, want) if step != 1 else (x8b, x_sfb, idxb, wb, wantb)
+                got = layer.forward(xa, sa, ia, wa)
+                poll_device_status()
+                if not torch.equal(got, ref):
+                    verdicts.append(f"{transport} chunks={chunks} step {step}: max diff {(got.float() - ref.float()).abs().max().item()}")
+            layer.close()
+        out[rank] = "ok" if not verdicts else "; ".join(verdicts)
     except Exception as ex:
         out[rank] = repr(ex)
     finally:

@@ -128,3 +128,67 @@ def test_plan_two_ranks_over_gloo():
         p.join(100)
         assert p.exitcode == 0
     assert dict(results) == {0: "ok", 1: "ok"}
+
+
+@pytest.mark.parametrize("world,chunks", [(2, 1), (3, 2), (4, 3)])
+def test_peer_step_tables_route_every_copy_home(world, chunks):
+    """Plays one expert-parallel step over peer memory on the host: the copy list moves row ids
+    into the owners' receive areas, the padded layout and the row-address arithmetic of
+    dg_moe_return_ptrs (restated here) send every result row back, and every rank must find copy
+    (token, j) at the position its combine step reads."""
+    from deepgemm.moe import peer_step_tables
+    rng = np.random.default_rng(world * 10 + chunks)
+    e_local, topk, tokens = 2, 2, 37
+    experts = world * e_local
+    idx = np.stack([np.stack([rng.permutation(experts)[:topk] for _ in range(tokens)]) for _ in range(world)])  # [rank, T, k]
+    bounds = [tokens * c // chunks for c in range(chunks + 1)]
+    full = np.zeros((world, chunks, world, e_local), dtype=np.int64)
+    sorted_ids, pos_of_copy = {}, {}
+    for r in range(world):
+        for c in range(chunks):
+            flat = idx[r, bounds[c]:bounds[c + 1]].reshape(-1)
+            order = np.argsort(flat, kind="stable")
+            sorted_ids[r, c] = [(r, bounds[c] + int(o) // topk, int(o) % topk) for o in order]
+            pos = np.empty_like(order)
+            pos[order] = np.arange(order.size)
+            pos_of_copy[r, c] = pos.reshape(-1, topk)
+            full[r, c] = np.bincount(flat, minlength=experts).reshape(world, e_local)
+    tot = full.sum(-1)
+    tables = [peer_step_tables(tot, me) for me in range(world)]
+    cap = int(tot.sum(0).max())
+    recv = {(d, c): [None] * cap for d in range(world) for c in range(chunks)}
+    for me in range(world):
+        for c in range(chunks):
+            seen = set()
+            for dst, src_off, dst_off, n in tables[me][3][c]:
+                seen.add(dst)
+                for i in range(n):
+                    assert recv[dst, c][dst_off + i] is None
+                    recv[dst, c][dst_off + i] = sorted_ids[me, c][src_off + i]
+            assert seen == set(range(world))
+    ret = {r: [None] * int(tot[r].sum()) for r in range(world)}
+    for d in range(world):
+        seg, row0, chunk_base, _ = tables[d]
+        for c in range(chunks):
+            r_rows = int(tot[:, c, d].sum())
+            assert seg[c, world] == r_rows and all(v is not None for v in recv[d, c][:r_rows])
+            recv_expert = np.repeat(np.tile(np.arange(e_local), world), full[:, c, d, :].reshape(-1))
+            for i in range(r_rows):
+                src, t, j = recv[d, c][i]
+                assert idx[src, t, j] == d * e_local + recv_expert[i]
+            lay = build_contiguous_layout(torch.from_numpy(recv_expert), e_local, contiguous_capacity(r_rows, e_local))
+            for s, i in enumerate(lay.src_row.tolist()):
+                if i < 0:
+                    continue
+                r = 0
+                while r + 1 < world and i >= seg[c, r + 1]:
+                    r += 1
+                row = int(row0[c, r]) + i - int(seg[c, r])
+                assert ret[r][row] is None
+                ret[r][row] = recv[d, c][i]
+    for r in range(world):
+        chunk_base = tables[r][2]
+        for c in range(chunks):
+            for t in range(bounds[c], bounds[c + 1]):
+                for j in range(topk):
+                    assert ret[r][int(chunk_base[r, c]) + int(pos_of_copy[r, c][t - bounds[c], j])] == (r, t, j)
