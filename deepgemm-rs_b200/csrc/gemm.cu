@@ -64,6 +64,7 @@ struct GemmParams {
     const int32_t* layout; // m_indices (contiguous) or masked_m (masked)
     const int32_t* d_row_map;  // optional: D row of every A row (negative = drop the row); NULL = identity
     const uint64_t* d_row_ptr; // optional (contiguous, bf16): address of every A row's D row, this or a peer GPU's (0 = drop)
+    const int32_t* m_blocks_dev;  // optional (contiguous, single CTA): device-side count of leading 128-row blocks to visit
     uint32_t* status;
     uint32_t k_splits;          // dense GEMM with few tiles: K is cut into this many ranges (1 = off)
     uint32_t kb_per_split;      // k-blocks per range (a multiple of 4)
@@ -131,6 +132,9 @@ struct Scheduler {
             return true;
         } else if (GTYPE != kMasked) {
             uint32_t tile = id;
+            // a layout sized for the worst case is mostly unused blocks: the device-side count ends the walk early
+            const uint32_t m_blocks = (GTYPE == kContiguous && CL == 1 && p.m_blocks_dev)
+                                          ? min(p.num_m_blocks, (uint32_t)__ldg(p.m_blocks_dev)) : p.num_m_blocks;
             if (SPLIT) {
                 // work item = (tile, K range); ranges of one tile are neighbours in the order
                 if (id >= p.num_m_blocks * p.num_n_blocks * p.k_splits) return false;
@@ -138,13 +142,13 @@ struct Scheduler {
                 t.split = id - tile * p.k_splits;
                 t.kb0 = t.split * p.kb_per_split;
                 t.kb1 = min(p.num_k_blocks, t.kb0 + p.kb_per_split);
-            } else if (id >= p.num_m_blocks * p.num_n_blocks) {
+            } else if (id >= m_blocks * p.num_n_blocks) {
                 return false;
             }
             const uint32_t per_band = p.band * p.num_n_blocks;
             const uint32_t b = tile / per_band, rem = tile - b * per_band;
             const uint32_t mb0 = b * p.band;
-            const uint32_t rows = min(p.band, p.num_m_blocks - mb0);
+            const uint32_t rows = min(p.band, m_blocks - mb0);
             const uint32_t nb = rem / rows, mb = mb0 + (rem - nb * rows);
             t.a_row = mb * kTileM + rank * kBlockM;
             t.row_end = p.m;
@@ -817,7 +821,7 @@ static int32_t validate_operand(const dg_operand_t* op, const char* name) {
 static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int gtype, const int32_t* layout,
                         uint32_t layout_len, uint32_t num_groups, uint32_t expected_m, int32_t accumulate, void* stream,
                         const int32_t* d_row_map = nullptr, uint32_t n_begin = 0, uint32_t n_count = 0,
-                        const uint64_t* d_row_ptr = nullptr) {
+                        const uint64_t* d_row_ptr = nullptr, const int32_t* m_blocks_dev = nullptr) {
     int32_t st;
     if ((st = validate_operand(a, "A")) != DG_OK) return st;
     if ((st = validate_operand(b, "B")) != DG_OK) return st;
@@ -888,6 +892,7 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     p.layout = layout;
     p.d_row_map = d_row_map;
     p.d_row_ptr = d_row_ptr;
+    p.m_blocks_dev = m_blocks_dev;
     p.b_group_rows = n_full;
     p.b_row_offset = n_begin;
 
@@ -1021,14 +1026,14 @@ int32_t dg_m_grouped_gemm_nt_contiguous_scatter(const dg_operand_t* a, const dg_
 }
 int32_t dg_m_grouped_gemm_nt_contiguous_rowptr(const dg_operand_t* a, const dg_operand_t* b, const int32_t* m_indices,
                                                uint32_t m_indices_len, uint32_t num_groups, const uint64_t* d_row_ptr,
-                                               uint32_t n_begin, uint32_t n_count, void* stream) {
+                                               const int32_t* m_blocks_used, uint32_t n_begin, uint32_t n_count, void* stream) {
     if (!d_row_ptr) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous rowptr requires the row address table");
     if (!a || !b) return dg::fail(DG_ERR_INVALID_ARG, "null operand");
     if (a->major != DG_MAJOR_K) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous requires K-major A");
     if (n_count == 0) { n_begin = 0; n_count = b->rows; }
     dg_output_t out = {DG_BF16, 0, n_count, n_count, nullptr};
     return dg::run_gemm(a, b, &out, dg::kContiguous, m_indices, m_indices_len, num_groups, a->rows, 0, stream, nullptr,
-                        n_begin, n_count, d_row_ptr);
+                        n_begin, n_count, d_row_ptr, m_blocks_used);
 }
 int32_t dg_m_grouped_gemm_nt_masked(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, const int32_t* masked_m,
                                     uint32_t num_groups, uint32_t expected_m, void* stream) {

@@ -79,10 +79,14 @@ __global__ void __launch_bounds__(256) return_ptrs_kernel(const int32_t* __restr
 
 // One block.  dest_base[g] = first slot, in the owner's layout, of this rank's copies for expert g
 // (-1 if the owner's layout would overflow `cap` rows; the status word records it).
-// block_expert[b] = local expert of the b-th `align`-row block of this rank's own layout, -1 = unused.
+// The local experts are cut into `slices` ranges of per_slice experts that are dispatched and
+// computed one after the other: block_expert[s][b] = local expert of the b-th `align`-row block of
+// this rank's own layout if it belongs to slice s, else -1; blocks_used[s] = blocks up to the end
+// of slice s.
 __global__ void __launch_bounds__(1024) ep_route_kernel(const int32_t* __restrict__ counts, uint32_t world, uint32_t me,
                                                        uint32_t num_experts, uint32_t e_local, uint32_t align, uint32_t cap,
-                                                       int32_t* __restrict__ dest_base, int32_t* __restrict__ block_expert,
+                                                       uint32_t slices, uint32_t per_slice, int32_t* __restrict__ dest_base,
+                                                       int32_t* __restrict__ block_expert, int32_t* __restrict__ blocks_used,
                                                        uint32_t* status) {
     __shared__ int32_t s_padded[1024];
     __shared__ int32_t s_base[1024];
@@ -108,26 +112,33 @@ __global__ void __launch_bounds__(1024) ep_route_kernel(const int32_t* __restric
         if (!fits) atomicCAS(status, 0u, (uint32_t)kWaitPeer | 0x8000u | (g << 16));
     }
     __syncthreads();
-    for (uint32_t b = threadIdx.x; b < cap / align; b += blockDim.x) {
+    const uint32_t n_blocks = cap / align;
+    for (uint32_t b = threadIdx.x; b < n_blocks; b += blockDim.x) {
         const int32_t row = (int32_t)(b * align);
         int32_t found = -1;
         for (uint32_t e = 0; e < e_local; ++e) {
             const uint32_t gg = me * e_local + e;
             if (row >= s_base[gg] && row < s_base[gg] + s_padded[gg]) { found = (int32_t)e; break; }
         }
-        block_expert[b] = found;
+        for (uint32_t sl = 0; sl < slices; ++sl)
+            block_expert[(size_t)sl * n_blocks + b] = (found >= 0 && (uint32_t)found / per_slice == sl) ? found : -1;
+    }
+    if (threadIdx.x < slices) {
+        const uint32_t last = min(e_local, (threadIdx.x + 1u) * per_slice) - 1u, gg = me * e_local + last;
+        blocks_used[threadIdx.x] = (int32_t)min((uint32_t)(s_base[gg] + s_padded[gg]) / align, n_blocks);
     }
 }
 
-// One warp per copy p of this rank's copies sorted by global expert: stores the token's row, its
+// One warp per copy p of this rank's copies sorted by global expert (only copies whose local expert
+// index at the owner lies in [e_lo, e_hi) are handled): stores the token's row, its
 // scale-factor words (straight into the owner's packed SF tensor [sf_rows, cap]) and the return
 // ticket (source rank + 1, position p) at the copy's slot in the owner's memory, local or peer.
 __global__ void __launch_bounds__(256) ep_push_kernel(const uint4* __restrict__ x, uint64_t x_pitch_vec, uint32_t vec_per_row,
                                                      const uint32_t* __restrict__ x_sf, uint32_t sf_rows, uint64_t sf_cols,
                                                      const int32_t* __restrict__ slot_src, const int32_t* __restrict__ my_offsets,
                                                      const int32_t* __restrict__ dest_base, uint32_t num_experts,
-                                                     uint32_t e_local, uint32_t n, uint32_t me, uint64_t cap,
-                                                     const unsigned long long* __restrict__ a_bases,
+                                                     uint32_t e_local, uint32_t e_lo, uint32_t e_hi, uint32_t n, uint32_t me,
+                                                     uint64_t cap, const unsigned long long* __restrict__ a_bases,
                                                      const unsigned long long* __restrict__ sf_bases,
                                                      const unsigned long long* __restrict__ ticket_bases) {
     const uint32_t lane = threadIdx.x & 31u;
@@ -141,12 +152,17 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const uint4* __restrict__ 
             if ((uint32_t)__ldg(my_offsets + mid) <= p) lo = mid; else hi = mid;
         }
         const int32_t base = __ldg(dest_base + lo);
-        if (base < 0) continue;
-        const uint32_t owner = lo / e_local;
+        const uint32_t owner = lo / e_local, e = lo - owner * e_local;
+        if (base < 0 || e < e_lo || e >= e_hi) continue;
         const uint64_t slot = (uint64_t)(uint32_t)base + (p - (uint32_t)__ldg(my_offsets + lo));
         uint4* dst = reinterpret_cast<uint4*>(a_bases[owner]) + slot * vec_per_row;
         const uint4* src = x + (uint64_t)token * x_pitch_vec;
-        for (uint32_t v = lane; v < vec_per_row; v += 32u) dst[v] = __ldg(src + v);
+        uint32_t v = lane;
+        for (; v + 96u < vec_per_row; v += 128u) {     // four loads in flight per lane before the stores
+            const uint4 r0 = __ldg(src + v), r1 = __ldg(src + v + 32u), r2 = __ldg(src + v + 64u), r3 = __ldg(src + v + 96u);
+            dst[v] = r0; dst[v + 32u] = r1; dst[v + 64u] = r2; dst[v + 96u] = r3;
+        }
+        for (; v < vec_per_row; v += 32u) dst[v] = __ldg(src + v);
         uint32_t* sf_dst = reinterpret_cast<uint32_t*>(sf_bases[owner]);
         for (uint32_t r = lane; r < sf_rows; r += 32u) sf_dst[r * cap + slot] = __ldg(x_sf + r * sf_cols + (uint32_t)token);
         if (lane == 0)
@@ -156,11 +172,15 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const uint4* __restrict__ 
 
 // ptrs[s] = where slot s's result row goes: row `position` of the ticket's source rank's return
 // buffer; 0 for slots nobody wrote this step.  Tickets are cleared for the next step.
+// With block_expert given, only slots of blocks with a non-negative entry are touched (the slice
+// whose rows have arrived; other slices' tickets may still be in flight).
 __global__ void __launch_bounds__(256) ep_return_ptrs_kernel(unsigned long long* __restrict__ tickets, uint32_t slots,
                                                             const unsigned long long* __restrict__ ret_bases, uint32_t world,
-                                                            uint64_t row_bytes, unsigned long long* __restrict__ ptrs) {
+                                                            uint64_t row_bytes, const int32_t* __restrict__ block_expert,
+                                                            uint32_t align, unsigned long long* __restrict__ ptrs) {
     const uint32_t s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= slots) return;
+    if (block_expert && __ldg(block_expert + s / align) < 0) return;
     const unsigned long long w = tickets[s];
     const uint32_t src = (uint32_t)(w >> 32);
     ptrs[s] = (src == 0 || src > world) ? 0ull : ret_bases[src - 1u] + (w & 0xffffffffull) * row_bytes;
@@ -258,16 +278,19 @@ int32_t dg_moe_return_ptrs(const int32_t* slot_src, uint32_t slots, const int32_
 }
 
 int32_t dg_ep_route(const int32_t* counts, uint32_t world, uint32_t me, uint32_t num_experts, uint32_t align, uint32_t cap,
-                    int32_t* dest_base, int32_t* block_expert, void* stream) {
-    if (!counts || !dest_base || !block_expert) return dg::fail(DG_ERR_INVALID_ARG, "ep_route: null buffer");
+                    uint32_t slices, int32_t* dest_base, int32_t* block_expert, int32_t* blocks_used, void* stream) {
+    if (!counts || !dest_base || !block_expert || !blocks_used) return dg::fail(DG_ERR_INVALID_ARG, "ep_route: null buffer");
     if (world == 0 || me >= world || num_experts == 0 || num_experts > 1024 || num_experts % world != 0)
         return dg::fail(DG_ERR_INVALID_ARG, "ep_route: %u experts over %u ranks (at most 1024 experts, divisible by the ranks)", num_experts, world);
     if (align == 0 || cap % align != 0) return dg::fail(DG_ERR_INVALID_ARG, "ep_route: capacity must be a multiple of the alignment");
     const dg::DeviceInfo* dev;
     int32_t st = dg::current_device(&dev);
     if (st != DG_OK) return st;
-    dg::ep_route_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(counts, world, me, num_experts, num_experts / world,
-                                                                           align, cap, dest_base, block_expert, dev->status);
+    const uint32_t e_local = num_experts / world;
+    if (slices == 0 || slices > e_local) return dg::fail(DG_ERR_INVALID_ARG, "ep_route: %u slices for %u local experts", slices, e_local);
+    dg::ep_route_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(counts, world, me, num_experts, e_local, align, cap,
+                                                                           slices, dg::ceil_div(e_local, slices), dest_base,
+                                                                           block_expert, blocks_used, dev->status);
     dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;
@@ -275,8 +298,9 @@ int32_t dg_ep_route(const int32_t* counts, uint32_t world, uint32_t me, uint32_t
 
 int32_t dg_ep_push(const void* x, uint64_t x_pitch_bytes, uint32_t row_bytes, const uint32_t* x_sf, uint32_t sf_rows,
                    uint64_t sf_cols, const int32_t* slot_src, const int32_t* my_offsets, const int32_t* dest_base,
-                   uint32_t num_experts, uint32_t world, uint32_t me, uint32_t n_copies, uint64_t cap, const uint64_t* a_bases,
-                   const uint64_t* sf_bases, const uint64_t* ticket_bases, uint32_t max_blocks, void* stream) {
+                   uint32_t num_experts, uint32_t world, uint32_t me, uint32_t e_lo, uint32_t e_hi, uint32_t n_copies, uint64_t cap,
+                   const uint64_t* a_bases, const uint64_t* sf_bases, const uint64_t* ticket_bases, uint32_t max_blocks,
+                   void* stream) {
     if (!x || !x_sf || !slot_src || !my_offsets || !dest_base || !a_bases || !sf_bases || !ticket_bases)
         return dg::fail(DG_ERR_INVALID_ARG, "ep_push: null buffer");
     if (row_bytes % 16 || x_pitch_bytes % 16 || (reinterpret_cast<uintptr_t>(x) & 15u))
@@ -290,7 +314,7 @@ int32_t dg_ep_push(const void* x, uint64_t x_pitch_bytes, uint32_t row_bytes, co
     if (max_blocks && blocks > max_blocks) blocks = max_blocks;
     dg::ep_push_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(x), x_pitch_bytes / 16, row_bytes / 16, x_sf, sf_rows, sf_cols, slot_src, my_offsets, dest_base,
-        num_experts, num_experts / world, n_copies, me, cap, reinterpret_cast<const unsigned long long*>(a_bases),
+        num_experts, num_experts / world, e_lo, e_hi, n_copies, me, cap, reinterpret_cast<const unsigned long long*>(a_bases),
         reinterpret_cast<const unsigned long long*>(sf_bases), reinterpret_cast<const unsigned long long*>(ticket_bases));
     dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
@@ -298,16 +322,17 @@ int32_t dg_ep_push(const void* x, uint64_t x_pitch_bytes, uint32_t row_bytes, co
 }
 
 int32_t dg_ep_return_ptrs(uint64_t* tickets, uint32_t slots, const uint64_t* ret_bases, uint32_t world, uint64_t row_bytes,
-                          uint64_t* ptrs, void* stream) {
+                          const int32_t* block_expert, uint32_t align, uint64_t* ptrs, void* stream) {
     if (!tickets || !ret_bases || !ptrs) return dg::fail(DG_ERR_INVALID_ARG, "ep_return_ptrs: null buffer");
     if (row_bytes % 16 != 0) return dg::fail(DG_ERR_INVALID_ARG, "ep_return_ptrs: rows must be multiples of 16 bytes");
+    if (block_expert && align == 0) return dg::fail(DG_ERR_INVALID_ARG, "ep_return_ptrs: zero alignment");
     if (slots == 0) return DG_OK;
     const dg::DeviceInfo* dev;
     int32_t st = dg::current_device(&dev);
     if (st != DG_OK) return st;
     dg::ep_return_ptrs_kernel<<<dg::ceil_div(slots, 256u), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<unsigned long long*>(tickets), slots, reinterpret_cast<const unsigned long long*>(ret_bases), world,
-        row_bytes, reinterpret_cast<unsigned long long*>(ptrs));
+        row_bytes, block_expert, align, reinterpret_cast<unsigned long long*>(ptrs));
     dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;

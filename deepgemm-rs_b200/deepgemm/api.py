@@ -117,13 +117,16 @@ def m_grouped_gemm_nt_contiguous_scatter(a, b, out, m_indices, num_groups, d_row
                                                                n_begin, n_count, _stream_ptr(stream)))
 
 
-def m_grouped_gemm_nt_contiguous_rowptr(a, b, m_indices, num_groups, d_row_ptr, n_begin=0, n_count=0, stream=None):
+def m_grouped_gemm_nt_contiguous_rowptr(a, b, m_indices, num_groups, d_row_ptr, n_begin=0, n_count=0, stream=None,
+                                        m_blocks_used=None):
     """Extension: BF16 result row r is stored at the address d_row_ptr[r] (int64 device tensor of
-    a.rows addresses in this GPU's memory or a mapped peer's; 0 = dropped)."""
+    a.rows addresses in this GPU's memory or a mapped peer's; 0 = dropped).  m_blocks_used: optional
+    int32 device scalar, only that many leading entries of m_indices are visited."""
     ac, bc = _op_c(a), _op_c(b)
     _check(_lib.load().dg_m_grouped_gemm_nt_contiguous_rowptr(C.byref(ac), C.byref(bc), m_indices.data_ptr(), m_indices.numel(),
-                                                              num_groups, d_row_ptr.data_ptr(), n_begin, n_count,
-                                                              _stream_ptr(stream)))
+                                                              num_groups, d_row_ptr.data_ptr(),
+                                                              None if m_blocks_used is None else m_blocks_used.data_ptr(),
+                                                              n_begin, n_count, _stream_ptr(stream)))
 
 
 def m_grouped_gemm_nt_masked(a, b, out, masked_m, num_groups, expected_m, stream=None):

@@ -234,19 +234,26 @@ class ExpertParallelMoE:
     """
 
     def __init__(self, weights: Operand, num_experts: int, group=None, chunks: int = 1, return_parts: int = 1,
-                 transport: str = "peer"):
-        # transport "peer" (several GPUs): token rows reach the expert owners by copy engine into
-        # peer-mapped buffers, the grouped GEMM stores its result rows straight into the token owner's
-        # memory, and flag barriers replace collectives, so nothing on the data path needs an SM
-        # besides the GEMM itself; `chunks` token slices pipeline dispatch under the previous GEMM.
-        # transport "nccl": all-to-alls over NCCL.  There, chunks > 1 pipelines token slices and
-        # return_parts > 1 runs the GEMM of a slice in column ranges whose return transfers overlap
-        # the next range; both overlap NCCL kernels with a GEMM that wants every SM and, measured on
-        # 2 GPUs, lost more than they hid, so the NCCL default is the plain sequence.
+                 transport: str = "push", single_rank_transport: bool = False):
+        # Transports between several GPUs (one NVSwitch domain):
+        # "push": a kernel stores every token copy (row, scale factors, return ticket) straight into
+        #   its slot of the expert owner's padded layout, the grouped GEMM stores its result rows
+        #   straight into the token owner's buffer, flag barriers replace collectives, and every
+        #   position follows on the device from one all-gather of the per-expert counts: a step
+        #   never waits on the host.  `chunks` > 1 cuts the local experts into slices whose rows
+        #   are pushed while the previous slice's GEMM runs.
+        # "peer": dispatch by copy engine into peer-mapped buffers (the host reads the counts to size
+        #   the copies), `chunks` token slices pipelined; same return path as "push".
+        # "nccl": all-to-alls over NCCL.  There, chunks > 1 pipelines token slices and
+        #   return_parts > 1 runs the GEMM of a slice in column ranges whose return transfers overlap
+        #   the next range; both overlap NCCL kernels with a GEMM that wants every SM and, measured
+        #   on 2 GPUs, lost more than they hid.
         self.chunks = chunks
         self.transport = os.environ.get("DG_EP_TRANSPORT", transport)
         if self.transport not in ("push", "peer", "nccl"):
             raise ValueError("transport must be 'push', 'peer' or 'nccl'")
+        # one rank normally takes the local path below; True runs the chosen transport against itself
+        self.single_rank_transport = single_rank_transport
         self._win = None
         self._win_shape = None
         self._streams = None
@@ -263,7 +270,7 @@ class ExpertParallelMoE:
         tokens, topk = topk_idx.shape
         k, n_out = x.shape[1], self.w.rows
         k_elems = k if self.w.dtype != Dtype.Fp4 else k * 2
-        if self.world == 1:
+        if self.world == 1 and not (self.single_rank_transport and self.transport == "push"):
             # one device-side plan straight into the padded layout; no host synchronisation
             p = device_plan(topk_idx, self.num_experts, BLOCK, div=topk)
             a = gather_rows(x, p.slot_src)
@@ -498,8 +505,8 @@ class ExpertParallelMoE:
         return out
 
     # ---- push transport: no host synchronisation, no staging copies --------------------------
-    def _ensure_push_window(self, tokens, topk, row_bytes, sf_rows, n_out):
-        key = ("push", tokens, topk, row_bytes, sf_rows, n_out)
+    def _ensure_push_window(self, tokens, topk, row_bytes, sf_rows, n_out, slices):
+        key = ("push", tokens, topk, row_bytes, sf_rows, n_out, slices)
         if self._win_shape and self._win_shape.get("key") == key:
             return
         from .peer import PeerWindow
@@ -518,6 +525,7 @@ class ExpertParallelMoE:
         self._win = win = PeerWindow(total, self.group)
         dev = win.local.device
         table = lambda off: torch.tensor([win.payload_ptr(r, off) for r in range(world)], dtype=torch.int64, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
         self._win_shape = dict(key=key, cap=cap, a_bases=table(off_a), sf_bases=table(off_sf), ticket_bases=table(off_ticket),
                                ret_bases=table(off_ret),
                                a=win.payload(off_a, cap * row_bytes).view(cap, row_bytes),
@@ -525,40 +533,75 @@ class ExpertParallelMoE:
                                tickets=win.payload(off_ticket, cap * 8).view(torch.int64),
                                ret=win.payload(off_ret, tokens * topk * n_out * 2).view(torch.bfloat16).view(tokens * topk, n_out),
                                ptrs=torch.empty(cap, dtype=torch.int64, device=dev),
-                               dest_base=torch.empty(self.num_experts, dtype=torch.int32, device=dev),
-                               block_expert=torch.empty(cap // BLOCK, dtype=torch.int32, device=dev),
-                               counts=torch.empty((world, self.num_experts), dtype=torch.int32, device=dev))
+                               dest_base=torch.empty(self.num_experts, **i32),
+                               block_expert=torch.empty((slices, cap // BLOCK), **i32),
+                               blocks_used=torch.empty(slices, **i32),
+                               counts=torch.empty((world, self.num_experts), **i32))
+        if self._streams is None:
+            self._streams = (torch.cuda.Stream(), torch.cuda.Stream())
 
     def _forward_push(self, x, x_sf, topk_idx, topk_w):
-        """Every rank must pass the same number of tokens.  The whole step is queued on the current
-        stream without the host ever waiting for the device."""
+        """Every rank must pass the same number of tokens.  The whole step is queued without the host
+        ever waiting for the device.  With `chunks` > 1 the local experts are cut into that many
+        slices: the rows of slice s + 1 are pushed (by a kernel limited to a few blocks per SM, on a
+        second stream) while the GEMM of slice s runs."""
         L = _lib.load()
-        me, world = dist.get_rank(self.group), self.world
+        world = self.world
+        me = dist.get_rank(self.group) if world > 1 else 0
         tokens, topk = topk_idx.shape
         k, n_out = x.shape[1], self.w.rows
         k_elems = k if self.w.dtype != Dtype.Fp4 else k * 2
         row_bytes = k * x.element_size()
         n = tokens * topk
-        self._ensure_push_window(tokens, topk, row_bytes, x_sf.rows, n_out)
+        slices = max(1, min(int(os.environ.get("DG_EP_CHUNKS", self.chunks)), self.e_local))
+        per_slice = (self.e_local + slices - 1) // slices
+        slices = (self.e_local + per_slice - 1) // per_slice
+        self._ensure_push_window(tokens, topk, row_bytes, x_sf.rows, n_out, slices)
         win, sh = self._win, self._win_shape
         cap = sh["cap"]
-        stream = _stream_ptr(None)
+        main = torch.cuda.current_stream()
+        comm = self._streams[0]
         # my copies sorted by global expert (= by owner rank): counts, first position per expert,
         # token of every position, position of every copy
         p = device_plan(topk_idx, self.num_experts, 1, div=topk, capacity=n)
-        dist.all_gather_into_tensor(sh["counts"], p.counts, group=self.group)
-        _check(L.dg_ep_route(sh["counts"].data_ptr(), world, me, self.num_experts, BLOCK, cap, sh["dest_base"].data_ptr(),
-                             sh["block_expert"].data_ptr(), stream))
-        _check(L.dg_ep_push(x.data_ptr(), x.stride(0) * x.element_size(), row_bytes, x_sf.buf.data_ptr(), x_sf.rows, x_sf.cols,
-                            p.slot_src.data_ptr(), p.offsets.data_ptr(), sh["dest_base"].data_ptr(), self.num_experts, world, me, n,
-                            cap, sh["a_bases"].data_ptr(), sh["sf_bases"].data_ptr(), sh["ticket_bases"].data_ptr(), 0, stream))
-        win.barrier(0)          # every rank's rows, scale factors and tickets have landed here
-        _check(L.dg_ep_return_ptrs(sh["tickets"].data_ptr(), cap, sh["ret_bases"].data_ptr(), world, n_out * 2,
-                                   sh["ptrs"].data_ptr(), stream))
+        if world > 1:
+            dist.all_gather_into_tensor(sh["counts"], p.counts, group=self.group)
+            counts = sh["counts"]
+        else:
+            counts = p.counts
+        _check(L.dg_ep_route(counts.data_ptr(), world, me, self.num_experts, BLOCK, cap, slices, sh["dest_base"].data_ptr(),
+                             sh["block_expert"].data_ptr(), sh["blocks_used"].data_ptr(), main.cuda_stream))
+
+        def push(s, stream, max_blocks):
+            _check(L.dg_ep_push(x.data_ptr(), x.stride(0) * x.element_size(), row_bytes, x_sf.buf.data_ptr(), x_sf.rows, x_sf.cols,
+                                p.slot_src.data_ptr(), p.offsets.data_ptr(), sh["dest_base"].data_ptr(), self.num_experts, world,
+                                me, s * per_slice, min(self.e_local, (s + 1) * per_slice), n, cap, sh["a_bases"].data_ptr(),
+                                sh["sf_bases"].data_ptr(), sh["ticket_bases"].data_ptr(), max_blocks, stream.cuda_stream))
+            win.barrier(0, stream.cuda_stream)      # every rank's rows, scale factors and tickets of the slice have landed here
+
+        arrived = []
+        if slices > 1:
+            routed = torch.cuda.Event()
+            routed.record(main)
+            comm.wait_event(routed)
+            side_blocks = int(os.environ.get("DG_EP_PUSH_BLOCKS", 296))
+            for s in range(slices):
+                push(s, comm, 0 if s == 0 else side_blocks)
+                ev = torch.cuda.Event()
+                ev.record(comm)
+                arrived.append(ev)
         a_op = Operand.k_major(self.w.dtype, cap, k_elems, k_elems, SfTensor(x_sf.rows, cap, x_sf.gran, sh["sf"]),
                                sh["a"].view(x.dtype))
         self.last_m_indices = sh["block_expert"]
-        m_grouped_gemm_nt_contiguous_rowptr(a_op, self.w, sh["block_expert"], self.e_local, sh["ptrs"])
-        win.barrier(1)          # every rank's GEMM has stored its result rows, mine included, into the owners' buffers
+        for s in range(slices):
+            if slices > 1:
+                main.wait_event(arrived[s])
+            else:
+                push(0, main, 0)
+            blocks = sh["block_expert"][s]
+            _check(L.dg_ep_return_ptrs(sh["tickets"].data_ptr(), cap, sh["ret_bases"].data_ptr(), world, n_out * 2,
+                                       blocks.data_ptr(), BLOCK, sh["ptrs"].data_ptr(), main.cuda_stream))
+            m_grouped_gemm_nt_contiguous_rowptr(a_op, self.w, blocks, self.e_local, sh["ptrs"], m_blocks_used=sh["blocks_used"][s:])
+        win.barrier(1, main.cuda_stream)   # every rank's GEMMs have stored their result rows, mine included, into the owners' buffers
         self._keep = p
         return combine(sh["ret"], p.slot_of_row.view(tokens, topk), topk_w)

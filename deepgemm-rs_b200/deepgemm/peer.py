@@ -30,8 +30,9 @@ class PeerWindow:
     def __init__(self, payload_bytes, group=None):
         L = _lib.load()
         self.group = group
-        self.world = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        self.single = not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1
+        self.world = 1 if self.single else dist.get_world_size(group)
+        self.rank = 0 if self.single else dist.get_rank(group)
         if self.world > MAX_RANKS:
             raise ValueError(f"at most {MAX_RANKS} ranks")
         self.nbytes = FLAG_BYTES + (int(payload_bytes) + 255) // 256 * 256
@@ -40,8 +41,10 @@ class PeerWindow:
         self.ptr = p.value
         handle = C.create_string_buffer(64)
         _check(L.dg_peer_export(self.ptr, handle))
-        handles = [None] * self.world
-        dist.all_gather_object(handles, handle.raw, group=group)
+        handles = [handle.raw]
+        if not self.single:
+            handles = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
         self.ptrs = []
         for r, h in enumerate(handles):
             if r == self.rank:
@@ -56,7 +59,8 @@ class PeerWindow:
         self._flag_tables = [torch.tensor([q + ch * 8 * MAX_RANKS for q in self.ptrs], dtype=torch.int64, device=dev)
                              for ch in range(CHANNELS)]
         self._seq = [0] * CHANNELS
-        dist.barrier(group=group)   # every rank has mapped every buffer before anyone writes
+        if not self.single:
+            dist.barrier(group=group)   # every rank has mapped every buffer before anyone writes
 
     def payload(self, offset, nbytes):
         """uint8 view of this rank's payload bytes [offset, offset + nbytes)."""
@@ -65,17 +69,17 @@ class PeerWindow:
     def payload_ptr(self, rank, offset=0):
         return self.ptrs[rank] + FLAG_BYTES + offset
 
-    def copy_to(self, rank, offset, src_ptr, nbytes, stream=None):
-        """Copy-engine push of nbytes from a local address into rank's payload at `offset`."""
+    def copy_to(self, rank, offset, src_ptr, nbytes):
+        """Copy-engine push of nbytes from a local address into rank's payload at `offset`, on the current stream."""
         if nbytes:
-            _check(_lib.load().dg_peer_copy(self.payload_ptr(rank, offset), src_ptr, nbytes, _stream_ptr(stream)))
+            _check(_lib.load().dg_peer_copy(self.payload_ptr(rank, offset), src_ptr, nbytes, _stream_ptr(None)))
 
     def barrier(self, channel, stream=None):
-        """Queues a barrier between all ranks on `stream` (the current stream by default).  Calls on
-        one channel must come in the same order on every rank and stay on one stream."""
+        """Queues a barrier between all ranks on `stream` (a raw stream handle; the current stream by
+        default).  Calls on one channel must come in the same order on every rank and stay on one stream."""
         self._seq[channel] += 1
         _check(_lib.load().dg_peer_barrier(self._flag_tables[channel].data_ptr(), self.ptr + channel * 8 * MAX_RANKS, self.rank,
-                                           self.world, self._seq[channel], _stream_ptr(stream)))
+                                           self.world, self._seq[channel], _stream_ptr(None) if stream is None else stream))
 
     def close(self):
         """Collective: unmaps the peers' buffers, then frees this rank's."""
@@ -83,11 +87,12 @@ class PeerWindow:
             return
         L = _lib.load()
         torch.cuda.synchronize()
-        dist.barrier(group=self.group)
-        for r, q in enumerate(self.ptrs):
-            if r != self.rank:
-                _check(L.dg_peer_close(q))
-        dist.barrier(group=self.group)
+        if not self.single:
+            dist.barrier(group=self.group)
+            for r, q in enumerate(self.ptrs):
+                if r != self.rank:
+                    _check(L.dg_peer_close(q))
+            dist.barrier(group=self.group)
         self.local = None
         _check(L.dg_peer_free(self.ptr))
         self.ptr = None

@@ -269,34 +269,44 @@ DG_API int32_t dg_moe_return_ptrs(const int32_t* slot_src, uint32_t slots, const
  * one owner rank follow each other in its layout, each padded to `align` rows; inside an expert the
  * source ranks follow each other.  dg_ep_route writes dest_base[g] = first slot of this rank's copies
  * of expert g in the owner's layout (-1 and a recorded status if the owner's `cap` rows would
- * overflow) and block_expert[cap / align] = `m_indices` of this rank's own layout. */
+ * overflow).  The local experts are cut into `slices` ranges of ceil(e_local / slices) experts that
+ * can be dispatched and computed one after the other: block_expert[s * (cap / align) + b] = `m_indices`
+ * entry of block b of this rank's own layout for slice s (-1 for blocks of other slices),
+ * blocks_used[s] = number of leading blocks that hold slices 0..s. */
 DG_API int32_t dg_ep_route(const int32_t* counts, uint32_t world, uint32_t me, uint32_t num_experts, uint32_t align,
-                           uint32_t cap, int32_t* dest_base, int32_t* block_expert, void* stream);
-/* Stores every copy of this rank into its owner's memory: for copy p of the copies sorted by global
- * expert (slot_src[p] = token row, my_offsets[num_experts + 1] = first p of every expert, both from
- * dg_moe_plan with align 1), the token's row of x goes to row `slot` of the owner's A buffer
- * (a_bases[owner], rows of row_bytes), its scale-factor words to column `slot` of the owner's packed
- * SF tensor [sf_rows, cap] (sf_bases[owner]) and a return ticket (this rank, p) to ticket_bases[owner][slot]
- * (64-bit words, zero = empty).  The three address tables are device arrays of `world` addresses, this
- * GPU's own or mapped peers'.  max_blocks > 0 bounds the grid (to share the GPU with a running GEMM). */
+                           uint32_t cap, uint32_t slices, int32_t* dest_base, int32_t* block_expert,
+                           int32_t* blocks_used, void* stream);
+/* Stores the copies of this rank whose local expert index at the owner lies in [e_lo, e_hi) into the
+ * owner's memory: for copy p of the copies sorted by global expert (slot_src[p] = token row,
+ * my_offsets[num_experts + 1] = first p of every expert, both from dg_moe_plan with align 1), the
+ * token's row of x goes to row `slot` of the owner's A buffer (a_bases[owner], rows of row_bytes), its
+ * scale-factor words to column `slot` of the owner's packed SF tensor [sf_rows, cap] (sf_bases[owner])
+ * and a return ticket (this rank, p) to ticket_bases[owner][slot] (64-bit words, zero = empty).  The
+ * three address tables are device arrays of `world` addresses, this GPU's own or mapped peers'.
+ * max_blocks > 0 bounds the grid (to share the GPU with a running GEMM). */
 DG_API int32_t dg_ep_push(const void* x, uint64_t x_pitch_bytes, uint32_t row_bytes, const uint32_t* x_sf, uint32_t sf_rows,
                           uint64_t sf_cols, const int32_t* slot_src, const int32_t* my_offsets, const int32_t* dest_base,
-                          uint32_t num_experts, uint32_t world, uint32_t me, uint32_t n_copies, uint64_t cap,
-                          const uint64_t* a_bases, const uint64_t* sf_bases, const uint64_t* ticket_bases,
-                          uint32_t max_blocks, void* stream);
+                          uint32_t num_experts, uint32_t world, uint32_t me, uint32_t e_lo, uint32_t e_hi,
+                          uint32_t n_copies, uint64_t cap, const uint64_t* a_bases, const uint64_t* sf_bases,
+                          const uint64_t* ticket_bases, uint32_t max_blocks, void* stream);
 /* Turns the tickets of this rank's layout into the row address table of
  * dg_m_grouped_gemm_nt_contiguous_rowptr (ptrs[s] = ret_bases[ticket rank] + position * row_bytes,
- * 0 for slots without a ticket) and clears the tickets for the next step. */
+ * 0 for slots without a ticket) and clears the tickets for the next step.  With block_expert given
+ * (entries per `align` slots), only slots of blocks with a non-negative entry are touched. */
 DG_API int32_t dg_ep_return_ptrs(uint64_t* tickets, uint32_t slots, const uint64_t* ret_bases, uint32_t world,
-                                 uint64_t row_bytes, uint64_t* ptrs, void* stream);
+                                 uint64_t row_bytes, const int32_t* block_expert, uint32_t align, uint64_t* ptrs,
+                                 void* stream);
 /* m_grouped_gemm_nt_contiguous whose BF16 result rows are stored at d_row_ptr[r] + column * 2 for
  * every row r of A (device table of a.rows addresses, 16-byte aligned, in this GPU's memory or a
  * mapped peer's; 0 = drop the row).  Columns [n_begin, n_begin + n_count) of every expert are computed
- * (n_count = 0: all); column n_begin lands at the row address itself. */
+ * (n_count = 0: all); column n_begin lands at the row address itself.  m_blocks_used (device int32,
+ * may be NULL): only the first *m_blocks_used entries of m_indices are visited, so a layout sized for
+ * the worst case costs nothing for its unused tail. */
 DG_API int32_t dg_m_grouped_gemm_nt_contiguous_rowptr(const dg_operand_t* a, const dg_operand_t* b,
                                                       const int32_t* m_indices, uint32_t m_indices_len,
                                                       uint32_t num_groups, const uint64_t* d_row_ptr,
-                                                      uint32_t n_begin, uint32_t n_count, void* stream);
+                                                      const int32_t* m_blocks_used, uint32_t n_begin,
+                                                      uint32_t n_count, void* stream);
 
 /* ---- tuning / introspection -------------------------------------------------------------
  * Describes the tile configuration the library would use for a dense / grouped GEMM

@@ -50,7 +50,7 @@ def _worker(rank, world, port, out):
         x8b, x_sfb, idxb, wb = _inputs(rank + 10, dev)
         wantb = moe.ExpertParallelMoE(full, E, None).forward(x8b, x_sfb, idxb, wb)
         verdicts = []
-        for transport, chunks in (("push", 1), ("peer", 1), ("peer", 2), ("nccl", 1)):
+        for transport, chunks in (("push", 1), ("push", 2), ("peer", 1), ("peer", 2), ("nccl", 1)):
             os.environ["DG_EP_CHUNKS"] = str(chunks)
             layer = moe.ExpertParallelMoE(local, E, dist.group.WORLD, transport=transport)
             for step in range(3):

@@ -89,3 +89,32 @@ def test_peer_barrier_single_rank_and_copy():
         assert L.dg_peer_barrier(table.data_ptr(), p.value, 1, 1, 4, None) != 0     # rank outside the world
     finally:
         assert L.dg_peer_free(p.value) == 0
+
+
+@pytest.mark.parametrize("slices", [1, 3])
+def test_push_transport_against_itself_equals_local_step(slices):
+    """The push transport run by one rank against its own window (route -> push -> tickets ->
+    row-pointer GEMM -> combine, worst-case capacity, device-side block bound) must reproduce the
+    local step bit for bit, also when the buffers are reused by a second and third step."""
+    import os
+    from deepgemm import Dtype, moe, quant_mx, synth
+    E, TOPK, T, K, N = 6, 2, 300, 512, 256
+    dev_ = torch.device("cuda")
+    w = synth.random_expert_weights(E, N, K, seed=5, device=dev_)
+    local = moe.ExpertParallelMoE(w, E, None)
+    layer = moe.ExpertParallelMoE(w, E, None, chunks=slices, transport="push", single_rank_transport=True)
+    os.environ.pop("DG_EP_CHUNKS", None)
+    try:
+        for step in range(3):
+            g = torch.Generator(device=dev_).manual_seed(80 + step % 2)
+            x = torch.randn((T, K), device=dev_, generator=g)
+            x8, x_sf = quant_mx(x, T, K, Dtype.Fp8, 128)
+            idx, tw = synth.random_topk_routing(T, E, TOPK, seed=90 + step % 2, device=dev_)
+            if step == 2:
+                idx = torch.where(idx == 4, torch.full_like(idx, 3), idx)   # an expert without rows, duplicates allowed
+            want = local.forward(x8, x_sf, idx, tw)
+            got = layer.forward(x8, x_sf, idx, tw)
+            poll_device_status()
+            assert torch.equal(got, want), f"step {step}"
+    finally:
+        layer.close()
