@@ -516,6 +516,106 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             }
             const uint32_t taddr = tmem + ((q * 32u) << 16) + as * kAccStageCols;
             const uint32_t chunks = p.block_n / 32u;
+            if (!SPLIT && !p.out_f32 && !p.accumulate && (vec_ok || by_ptr) && p.n % 8u == 0) {
+                // BF16 rows leave the SM in runs of 128 contiguous bytes.  A lane holds 32 columns of
+                // its own row after the TMEM load; the lanes of a group of 8 exchange 16-byte pieces
+                // of two neighbouring column chunks (an 8x8 transpose by shuffles) so that one store
+                // instruction writes 128 bytes of one row per group: full lines for the memory
+                // system and full-size packets when the row lives in a peer GPU's memory.
+                const unsigned long long my_row = !row_ok ? 0ull
+                    : by_ptr ? row_addr : reinterpret_cast<unsigned long long>(p.d) + (unsigned long long)row * p.ldd * 2ull;
+                uint32_t c = 0;
+                while (c < chunks) {
+                    const uint32_t col0 = t.n0 + c * 32u;
+                    const bool two = (col0 % 64u) == 0 && c + 1u < chunks;   // pairs start on 128-byte boundaries of the row
+                    uint32_t r0[32], r1[32];
+                    __syncwarp();
+                    tmem_ld_x32(taddr + c * 32u, r0);
+                    if (two) tmem_ld_x32(taddr + (c + 1u) * 32u, r1);
+                    tmem_ld_wait();
+                    c += two ? 2u : 1u;
+                    if (c >= chunks) {
+                        // accumulator drained into registers: hand the TMEM stage back to the MMA issuer
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+                            else mbar_arrive_cluster(mapa(smem_u32(&bars->tmem_empty[as]), 0));
+                        }
+                    }
+                    if (col0 >= p.n) continue;
+                    uint4 a[8];
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        a[i] = make_uint4(pack_bf16x2(__uint_as_float(r0[8 * i]), __uint_as_float(r0[8 * i + 1])),
+                                          pack_bf16x2(__uint_as_float(r0[8 * i + 2]), __uint_as_float(r0[8 * i + 3])),
+                                          pack_bf16x2(__uint_as_float(r0[8 * i + 4]), __uint_as_float(r0[8 * i + 5])),
+                                          pack_bf16x2(__uint_as_float(r0[8 * i + 6]), __uint_as_float(r0[8 * i + 7])));
+                        a[4 + i] = make_uint4(pack_bf16x2(__uint_as_float(r1[8 * i]), __uint_as_float(r1[8 * i + 1])),
+                                              pack_bf16x2(__uint_as_float(r1[8 * i + 2]), __uint_as_float(r1[8 * i + 3])),
+                                              pack_bf16x2(__uint_as_float(r1[8 * i + 4]), __uint_as_float(r1[8 * i + 5])),
+                                              pack_bf16x2(__uint_as_float(r1[8 * i + 6]), __uint_as_float(r1[8 * i + 7])));
+                    }
+                    if (two && col0 + 64u <= p.n) {
+#pragma unroll
+                        for (uint32_t sft = 4; sft >= 1; sft >>= 1) {
+                            const bool up = (lane & sft) != 0;
+#pragma unroll
+                            for (uint32_t k = 0; k < 8; ++k) {
+                                if ((k & sft) != 0) continue;
+                                const uint4 send = up ? a[k] : a[k | sft];
+                                uint4 recv;
+                                recv.x = __shfl_xor_sync(0xffffffffu, send.x, sft);
+                                recv.y = __shfl_xor_sync(0xffffffffu, send.y, sft);
+                                recv.z = __shfl_xor_sync(0xffffffffu, send.z, sft);
+                                recv.w = __shfl_xor_sync(0xffffffffu, send.w, sft);
+                                if (up) a[k] = recv; else a[k | sft] = recv;
+                            }
+                        }
+                        // a[i] = piece (lane % 8) of the row held by lane (lane & 24) + i
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) {
+                            const unsigned long long dst = __shfl_sync(0xffffffffu, my_row, (lane & 24u) + i);
+                            if (dst) *reinterpret_cast<uint4*>(dst + col0 * 2ull + (lane & 7u) * 16ull) = a[i];
+                        }
+                    } else {
+                        // a single chunk (64-byte runs by a 4x4 transpose inside groups of 4 lanes), or
+                        // the ragged end of the row, stored piece by piece by the lane that owns the row
+#pragma unroll
+                        for (uint32_t h = 0; h < 2; ++h) {
+                            const uint32_t cc = col0 + 32u * h;
+                            if ((h == 1 && !two) || cc >= p.n) break;
+                            if (cc + 32u <= p.n) {
+#pragma unroll
+                                for (uint32_t sft = 2; sft >= 1; sft >>= 1) {
+                                    const bool up = (lane & sft) != 0;
+#pragma unroll
+                                    for (uint32_t k = 0; k < 4; ++k) {
+                                        if ((k & sft) != 0) continue;
+                                        const uint4 send = up ? a[4 * h + k] : a[4 * h + (k | sft)];
+                                        uint4 recv;
+                                        recv.x = __shfl_xor_sync(0xffffffffu, send.x, sft);
+                                        recv.y = __shfl_xor_sync(0xffffffffu, send.y, sft);
+                                        recv.z = __shfl_xor_sync(0xffffffffu, send.z, sft);
+                                        recv.w = __shfl_xor_sync(0xffffffffu, send.w, sft);
+                                        if (up) a[4 * h + k] = recv; else a[4 * h + (k | sft)] = recv;
+                                    }
+                                }
+#pragma unroll
+                                for (uint32_t i = 0; i < 4; ++i) {
+                                    const unsigned long long dst = __shfl_sync(0xffffffffu, my_row, (lane & 28u) + i);
+                                    if (dst) *reinterpret_cast<uint4*>(dst + cc * 2ull + (lane & 3u) * 16ull) = a[4 * h + i];
+                                }
+                            } else if (my_row) {
+#pragma unroll
+                                for (uint32_t i = 0; i < 4; ++i)
+                                    if (cc + 8u * i + 8u <= p.n) *reinterpret_cast<uint4*>(my_row + (cc + 8u * i) * 2ull) = a[4 * h + i];
+                            }
+                        }
+                    }
+                }
+                continue;
+            }
             for (uint32_t c = 0; c < chunks; ++c) {
                 uint32_t r[32];
                 __syncwarp();

@@ -75,7 +75,8 @@ __global__ void __launch_bounds__(256) return_ptrs_kernel(const int32_t* __restr
 // Every rank knows counts[src][g] = copies that rank src routes to global expert g (one all-gather).
 // From that table alone each rank derives, without talking to anyone, where in the owner's padded
 // expert layout its own copies of expert g begin: experts of one owner follow each other, each padded
-// to `align` rows, and inside an expert the source ranks follow each other in rank order.
+// to `align` rows, and inside an expert of owner d the source ranks follow each other in the order
+// d+1, d+2, ..., d.
 
 // One block.  dest_base[g] = first slot, in the owner's layout, of this rank's copies for expert g
 // (-1 if the owner's layout would overflow `cap` rows; the status word records it).
@@ -93,10 +94,13 @@ __global__ void __launch_bounds__(1024) ep_route_kernel(const int32_t* __restric
     const uint32_t g = threadIdx.x;
     int32_t before = 0;
     if (g < num_experts) {
+        // Inside an expert of owner d the sources follow each other in the order d+1, d+2, ..., d:
+        // ranks that walk their layouts in step then store their result rows to different peers.
+        const uint32_t owner = g / e_local, my_pos = (me + world - owner - 1u) % world;
         int32_t total = 0;
         for (uint32_t src = 0; src < world; ++src) {
             const int32_t v = __ldg(counts + (size_t)src * num_experts + g);
-            if (src < me) before += v;
+            if ((src + world - owner - 1u) % world < my_pos) before += v;
             total += v;
         }
         s_padded[g] = (int32_t)((((uint32_t)total + align - 1u) / align) * align);
@@ -129,40 +133,49 @@ __global__ void __launch_bounds__(1024) ep_route_kernel(const int32_t* __restric
     }
 }
 
-// One warp per copy p of this rank's copies sorted by global expert (only copies whose local expert
-// index at the owner lies in [e_lo, e_hi) are handled): stores the token's row, its
-// scale-factor words (straight into the owner's packed SF tensor [sf_rows, cap]) and the return
-// ticket (source rank + 1, position p) at the copy's slot in the owner's memory, local or peer.
+// One warp per copy of this rank's copies (sorted by global expert, so the copies for one owner
+// rank are one run; only local experts [e_lo, e_hi) of every owner are handled): stores the token's
+// row, its scale-factor words (straight into the owner's packed SF tensor [sf_rows, cap]) and the
+// return ticket (source rank + 1, position p) at the copy's slot in the owner's memory, local or
+// peer.  Consecutive warps serve different owners, starting with this rank's successor, so that at
+// any moment the ranks spread their stores over all peers instead of converging on one.
 __global__ void __launch_bounds__(256) ep_push_kernel(const uint4* __restrict__ x, uint64_t x_pitch_vec, uint32_t vec_per_row,
                                                      const uint32_t* __restrict__ x_sf, uint32_t sf_rows, uint64_t sf_cols,
                                                      const int32_t* __restrict__ slot_src, const int32_t* __restrict__ my_offsets,
                                                      const int32_t* __restrict__ dest_base, uint32_t num_experts,
-                                                     uint32_t e_local, uint32_t e_lo, uint32_t e_hi, uint32_t n, uint32_t me,
+                                                     uint32_t e_local, uint32_t e_lo, uint32_t e_hi, uint32_t world, uint32_t me,
                                                      uint64_t cap, const unsigned long long* __restrict__ a_bases,
                                                      const unsigned long long* __restrict__ sf_bases,
                                                      const unsigned long long* __restrict__ ticket_bases) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t warps = gridDim.x * (blockDim.x >> 5);
-    for (uint32_t p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); p < n; p += warps) {
+    uint32_t longest = 0;
+    for (uint32_t d = 0; d < world; ++d)
+        longest = max(longest, (uint32_t)(__ldg(my_offsets + d * e_local + e_hi) - __ldg(my_offsets + d * e_local + e_lo)));
+    const uint32_t total = longest * world;
+    for (uint32_t v = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); v < total; v += warps) {
+        const uint32_t owner = (me + 1u + v % world) % world, i = v / world;
+        const uint32_t first = (uint32_t)__ldg(my_offsets + owner * e_local + e_lo);
+        const uint32_t p = first + i;
+        if (p >= (uint32_t)__ldg(my_offsets + owner * e_local + e_hi)) continue;
         const int32_t token = __ldg(slot_src + p);
         if (token < 0) continue;
-        uint32_t lo = 0, hi = num_experts;          // largest g with my_offsets[g] <= p
+        uint32_t lo = owner * e_local + e_lo, hi = owner * e_local + e_hi;   // largest g in the range with my_offsets[g] <= p
         while (hi - lo > 1u) {
             const uint32_t mid = (lo + hi) >> 1;
             if ((uint32_t)__ldg(my_offsets + mid) <= p) lo = mid; else hi = mid;
         }
         const int32_t base = __ldg(dest_base + lo);
-        const uint32_t owner = lo / e_local, e = lo - owner * e_local;
-        if (base < 0 || e < e_lo || e >= e_hi) continue;
+        if (base < 0) continue;
         const uint64_t slot = (uint64_t)(uint32_t)base + (p - (uint32_t)__ldg(my_offsets + lo));
         uint4* dst = reinterpret_cast<uint4*>(a_bases[owner]) + slot * vec_per_row;
         const uint4* src = x + (uint64_t)token * x_pitch_vec;
-        uint32_t v = lane;
-        for (; v + 96u < vec_per_row; v += 128u) {     // four loads in flight per lane before the stores
-            const uint4 r0 = __ldg(src + v), r1 = __ldg(src + v + 32u), r2 = __ldg(src + v + 64u), r3 = __ldg(src + v + 96u);
-            dst[v] = r0; dst[v + 32u] = r1; dst[v + 64u] = r2; dst[v + 96u] = r3;
+        uint32_t c = lane;
+        for (; c + 96u < vec_per_row; c += 128u) {     // four loads in flight per lane before the stores
+            const uint4 r0 = __ldg(src + c), r1 = __ldg(src + c + 32u), r2 = __ldg(src + c + 64u), r3 = __ldg(src + c + 96u);
+            dst[c] = r0; dst[c + 32u] = r1; dst[c + 64u] = r2; dst[c + 96u] = r3;
         }
-        for (; v < vec_per_row; v += 32u) dst[v] = __ldg(src + v);
+        for (; c < vec_per_row; c += 32u) dst[c] = __ldg(src + c);
         uint32_t* sf_dst = reinterpret_cast<uint32_t*>(sf_bases[owner]);
         for (uint32_t r = lane; r < sf_rows; r += 32u) sf_dst[r * cap + slot] = __ldg(x_sf + r * sf_cols + (uint32_t)token);
         if (lane == 0)
@@ -306,6 +319,7 @@ int32_t dg_ep_push(const void* x, uint64_t x_pitch_bytes, uint32_t row_bytes, co
     if (row_bytes % 16 || x_pitch_bytes % 16 || (reinterpret_cast<uintptr_t>(x) & 15u))
         return dg::fail(DG_ERR_INVALID_ARG, "ep_push: rows must be 16-byte aligned multiples of 16 bytes");
     if (world == 0 || me >= world || num_experts % world != 0) return dg::fail(DG_ERR_INVALID_ARG, "ep_push: bad rank layout");
+    if (e_lo >= e_hi || e_hi > num_experts / world) return dg::fail(DG_ERR_INVALID_ARG, "ep_push: expert range [%u, %u) outside the %u local experts", e_lo, e_hi, num_experts / world);
     if (n_copies == 0) return DG_OK;
     const dg::DeviceInfo* dev;
     int32_t st = dg::current_device(&dev);
@@ -314,7 +328,7 @@ int32_t dg_ep_push(const void* x, uint64_t x_pitch_bytes, uint32_t row_bytes, co
     if (max_blocks && blocks > max_blocks) blocks = max_blocks;
     dg::ep_push_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(x), x_pitch_bytes / 16, row_bytes / 16, x_sf, sf_rows, sf_cols, slot_src, my_offsets, dest_base,
-        num_experts, num_experts / world, e_lo, e_hi, n_copies, me, cap, reinterpret_cast<const unsigned long long*>(a_bases),
+        num_experts, num_experts / world, e_lo, e_hi, world, me, cap, reinterpret_cast<const unsigned long long*>(a_bases),
         reinterpret_cast<const unsigned long long*>(sf_bases), reinterpret_cast<const unsigned long long*>(ticket_bases));
     dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());

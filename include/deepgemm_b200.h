@@ -266,10 +266,10 @@ DG_API int32_t dg_moe_return_ptrs(const int32_t* slot_src, uint32_t slots, const
                                   uint64_t row_bytes, uint64_t* ptrs, void* stream);
 /* Dispatch by direct stores, without any host synchronisation.  counts[src * num_experts + g] (device)
  * = copies that rank src routes to global expert g, alike on every rank (one all-gather).  Experts of
- * one owner rank follow each other in its layout, each padded to `align` rows; inside an expert the
- * source ranks follow each other.  dg_ep_route writes dest_base[g] = first slot of this rank's copies
- * of expert g in the owner's layout (-1 and a recorded status if the owner's `cap` rows would
- * overflow).  The local experts are cut into `slices` ranges of ceil(e_local / slices) experts that
+ * one owner rank follow each other in its layout, each padded to `align` rows; inside an expert of
+ * owner d the source ranks follow each other in the order d+1, d+2, ..., d.  dg_ep_route writes
+ * dest_base[g] = first slot of this rank's copies of expert g in the owner's layout (-1 and a recorded
+ * status if the owner's `cap` rows would overflow).  The local experts are cut into `slices` ranges of ceil(e_local / slices) experts that
  * can be dispatched and computed one after the other: block_expert[s * (cap / align) + b] = `m_indices`
  * entry of block b of this rank's own layout for slice s (-1 for blocks of other slices),
  * blocks_used[s] = number of leading blocks that hold slices 0..s. */
