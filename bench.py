@@ -267,7 +267,9 @@ def main():
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
-        "data": "synthetic", "config": workload_config(world),
+        "data": "synthetic", "config": dict(workload_config(world), **({"transport": layer.transport,
+                                                                         "expert_slices": len(layer._slice_bounds()) - 1}
+                                                                        if world > 1 else {})),
         "e2e": {"value": e2e_value, "unit": "TFLOPS", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": x_host.numel() * 4 + idx_host.numel() * 4 + w_host.numel() * 4,
                 "d2h_bytes_per_step": out_host.numel() * 2,

@@ -22,6 +22,8 @@
 // BLOCK_N, the stage count and the scale granularities are run-time parameters: the TMA boxes
 // come from the tensor maps and the MMA shape from a run-time instruction descriptor.
 #include "host.h"
+
+#include <mutex>
 #include "ptx.cuh"
 
 #include <cstdio>
@@ -65,6 +67,7 @@ struct GemmParams {
     const int32_t* d_row_map;  // optional: D row of every A row (negative = drop the row); NULL = identity
     const uint64_t* d_row_ptr; // optional (contiguous, bf16): address of every A row's D row, this or a peer GPU's (0 = drop)
     const int32_t* m_blocks_dev;  // optional (contiguous, single CTA): device-side count of leading 128-row blocks to visit
+    uint32_t* tile_counter;       // dynamic schedule: [0] next tile id, [1] CTAs that have finished; both zero at launch
     uint32_t* status;
     uint32_t k_splits;          // dense GEMM with few tiles: K is cut into this many ranges (1 = off)
     uint32_t kb_per_split;      // k-blocks per range (a multiple of 4)
@@ -89,9 +92,24 @@ struct Tile {
 // A tile is (128 * CL) x BLOCK_N; CTA `rank` of a pair owns rows [rank*128, rank*128 + 128) of it.
 // Tile ids walk bands of `band` m-tiles, m fastest inside a band, so that the tiles in flight
 // share a few A row-blocks and B column-blocks in L2.
-template <int GTYPE, int CL, bool SPLIT = false>
+// DYN (contiguous layout, single CTA): tile ids are not strided but claimed one by one from a global
+// counter by the CTA's scheduler warp and handed to the roles through a small ring in shared memory,
+// so that a CTA that is slowed down (an SM shared with another kernel, a slow tile) simply takes
+// fewer tiles instead of holding up the whole grid.
+constexpr uint32_t kSchedRing = 4;
+enum : uint32_t { kWaitSched = 8 };
+struct SchedRing {
+    uint64_t full[kSchedRing];     // scheduler warp -> roles: tile id published
+    uint64_t empty[kSchedRing];    // roles -> scheduler warp: every role has read the id
+    uint32_t tile[kSchedRing];
+};
+
+template <int GTYPE, int CL, bool SPLIT = false, bool DYN = false>
 struct Scheduler {
     uint32_t next_id, stride, rank;
+    SchedRing* ring = nullptr;         // DYN
+    const WaitCtx* wc = nullptr;
+    uint32_t slot = 0, ring_phase = 0;
     uint32_t g = 0, g_first_tile = 0;  // masked: current group and its first tile id
     const uint16_t* mtiles = nullptr;  // contiguous on CTA pairs: first block of every m-tile, bit 15 = both blocks share the expert
     const uint16_t* run_first = nullptr;  // first m-tile of every run of equal experts, [n_runs + 1]
@@ -100,11 +118,20 @@ struct Scheduler {
     __device__ Scheduler(uint32_t rank_, const uint16_t* mt, uint32_t n, const uint16_t* rf, uint32_t nr)
         : next_id(blockIdx.x / CL), stride(gridDim.x / CL), rank(rank_), mtiles(mt), run_first(rf), n_mtiles(n), n_runs(nr) {}
     __device__ bool first_tile_pending() const { return next_id == blockIdx.x / CL + stride; }
+    __device__ void attach(SchedRing* r, const WaitCtx* w) { ring = r; wc = w; }
 
+    // Called by all lanes of a converged warp; the result is warp-uniform.
     __device__ bool next(const GemmParams& p, Tile& t) {
         constexpr uint32_t kTileM = kBlockM * CL;
-        const uint32_t id = next_id;
+        uint32_t id = next_id;
         next_id += stride;
+        if (DYN) {
+            if (!DG_WARP_WAIT(smem_u32(&ring->full[slot]), ring_phase, *wc, kWaitSched)) return false;
+            id = *reinterpret_cast<volatile uint32_t*>(&ring->tile[slot]);
+            __syncwarp();
+            if ((threadIdx.x & 31u) == 0) mbar_arrive(smem_u32(&ring->empty[slot]));
+            if (++slot == kSchedRing) { slot = 0; ring_phase ^= 1u; }
+        }
         t.skip = false;
         t.kb0 = 0; t.kb1 = p.num_k_blocks; t.split = 0;
         if (GTYPE == kContiguous && CL == 2) {
@@ -193,6 +220,7 @@ struct __align__(8) Barriers {
     uint32_t tmem_base;
     uint32_t abort;
     uint32_t n_mtiles, n_runs;
+    SchedRing sched;                // dynamic schedule only
 };
 static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 
@@ -202,7 +230,7 @@ static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 // SPLIT (dense, single CTA only): a work item is a K range of a tile and the epilogue stores f32
 // partial tiles.  It is a separate instantiation because a k-loop that starts at a run-time
 // block measurably slows the common case (the k-block index feeds every role's bookkeeping).
-template <int KIND, int GTYPE, int CL, bool SPLIT>
+template <int KIND, int GTYPE, int CL, bool SPLIT, bool DYN>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
@@ -235,6 +263,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         for (uint32_t s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&bars->tmem_full[s]), 1);
             mbar_init(smem_u32(&bars->tmem_empty[s]), 4 * CL);
+        }
+        if (DYN) {
+            // readers of a tile id: producer, MMA issuer, (SF transposer,) four epilogue warps
+            for (uint32_t s = 0; s < kSchedRing; ++s) {
+                mbar_init(smem_u32(&bars->sched.full[s]), 1);
+                mbar_init(smem_u32(&bars->sched.empty[s]), kHasSf ? 7 : 6);
+            }
         }
         fence_barrier_init();
         tma_prefetch_desc(&tm_a);
@@ -306,7 +341,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 
     if (warp == 0) {
         // ===================================================== TMA producer (warp-converged, one lane issues)
-        Scheduler<GTYPE, CL, SPLIT> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        Scheduler<GTYPE, CL, SPLIT, DYN> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        sched.attach(&bars->sched, &wc);
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
@@ -363,7 +399,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else if (warp == 1 && leader) {
         // ===================================================== MMA issuer (warp-converged, one lane issues)
-        Scheduler<GTYPE, CL, SPLIT> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        Scheduler<GTYPE, CL, SPLIT, DYN> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        sched.attach(&bars->sched, &wc);
         Tile t;
         uint32_t stage = 0, phase = 0, tile_count = 0;
         uint32_t sf_bits = 0;  // per-stage parity of sf_ready (it completes only on SF k-blocks)
@@ -438,7 +475,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
     } else if (warp == 2 && kHasSf) {
         // ===================================================== SF transposer
-        Scheduler<GTYPE, CL, SPLIT> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        Scheduler<GTYPE, CL, SPLIT, DYN> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        sched.attach(&bars->sched, &wc);
         Tile t;
         uint32_t stage = 0, sf_bits = 0;
         bool ok = true;
@@ -486,9 +524,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 if (++stage == p.num_stages) stage = 0;
             }
         }
+    } else if (DYN && warp == 3) {
+        // ===================================================== tile scheduler (dynamic schedule)
+        const uint32_t m_blocks = p.m_blocks_dev ? min(p.num_m_blocks, (uint32_t)__ldg(p.m_blocks_dev)) : p.num_m_blocks;
+        const uint32_t total = m_blocks * p.num_n_blocks;
+        uint32_t slot = 0, phase = 0;
+        for (;;) {
+            if (!DG_WARP_WAIT(smem_u32(&bars->sched.empty[slot]), phase ^ 1u, wc, kWaitSched)) break;
+            uint32_t id = 0;
+            if (lane == 0) {
+                id = atomicAdd(p.tile_counter, 1u);
+                *reinterpret_cast<volatile uint32_t*>(&bars->sched.tile[slot]) = id;
+                mbar_arrive(smem_u32(&bars->sched.full[slot]));   // release: the id is visible to the waiters
+            }
+            id = __shfl_sync(0xffffffffu, id, 0);
+            if (id >= total) break;                               // the roles read this id and stop as well
+            if (++slot == kSchedRing) { slot = 0; phase ^= 1u; }
+        }
     } else if (warp >= 4) {
         // ===================================================== epilogue
-        Scheduler<GTYPE, CL, SPLIT> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        Scheduler<GTYPE, CL, SPLIT, DYN> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        sched.attach(&bars->sched, &wc);
         Tile t;
         const uint32_t q = warp - 4u;  // TMEM lane quarter == warp index % 4
         uint32_t tile_count = 0;
@@ -712,6 +768,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         tc_fence_after();
         tmem_dealloc<CL>(tmem, kTmemCols);
     }
+    if (DYN && threadIdx.x == 0) {
+        // the last CTA to leave puts the counters back to zero for the next launch that uses them
+        __threadfence();
+        if (atomicAdd(p.tile_counter + 1, 1u) == gridDim.x - 1u) {
+            p.tile_counter[0] = 0;
+            p.tile_counter[1] = 0;
+            __threadfence();
+        }
+    }
 }
 
 // D[r][c] (+)= sum over K ranges, added in range order (fixed, so results repeat bit for bit),
@@ -741,7 +806,28 @@ struct Plan {
     uint32_t grid;
     uint32_t num_tiles;
     uint32_t cluster;   // CTAs per tile: 1, or 2 (CTA pair)
+    bool dynamic;       // tiles claimed from a global counter instead of strided (contiguous layout, single CTA)
 };
+
+// A pair of zeroed counters for one launch of the dynamic schedule.  Launches take the pairs of a
+// per-device pool in turn; a kernel leaves its pair zeroed, so a pair is reusable as soon as the
+// launch that used it has finished, and 256 pairs outlast any realistic number of GEMMs in flight.
+static int32_t tile_counters(const DeviceInfo* dev, cudaStream_t s, uint32_t** out) {
+    constexpr uint32_t kPairs = 256;
+    static std::mutex mu;
+    static uint32_t* pools[64] = {nullptr};
+    static uint32_t next[64] = {0};
+    std::lock_guard<std::mutex> lock(mu);
+    const int d = dev->device & 63;
+    if (!pools[d]) {
+        uint32_t* pool = nullptr;
+        DG_CUDA_CHECK(cudaMalloc(&pool, kPairs * 2 * sizeof(uint32_t)));
+        DG_CUDA_CHECK(cudaMemsetAsync(pool, 0, kPairs * 2 * sizeof(uint32_t), s));
+        pools[d] = pool;
+    }
+    *out = pools[d] + 2u * (next[d]++ % kPairs);
+    return DG_OK;
+}
 
 static unsigned long long* g_trace = nullptr;  // set by dg_debug_set_trace (development aid)
 
@@ -862,6 +948,8 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     plan->grid = clusters * cl;
     p.status = dev->status;
     p.trace = g_trace;
+    plan->dynamic = gtype == kContiguous && cl == 1 && p.k_splits == 1 && env_u32("DG_DYNAMIC", 1) != 0;
+    p.tile_counter = nullptr;
     p.pf_chunk = env_u32("DG_PREFETCH", 0);
     if (p.pf_chunk > 16) p.pf_chunk = 16;
     if (env_u32("DG_PRINT_CONFIGS", 0))
@@ -870,10 +958,10 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     return DG_OK;
 }
 
-template <int KIND, int GTYPE, int CL, bool SPLIT = false>
+template <int KIND, int GTYPE, int CL, bool SPLIT = false, bool DYN = false>
 static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                       const CUtensorMap& tsb, const CUtensorMap& tbpf, cudaStream_t s) {
-    auto* fn = gemm_kernel<KIND, GTYPE, CL, SPLIT>;
+    auto* fn = gemm_kernel<KIND, GTYPE, CL, SPLIT, DYN>;
     static thread_local uint32_t configured[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1071,6 +1159,12 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
         if (lst != DG_OK) return lst;
         DG_CUDA_CHECK(cudaGetLastError());
         return DG_OK;
+    }
+    if (plan.dynamic) {
+        if ((st = tile_counters(dev, s, &p.tile_counter)) != DG_OK) return st;
+        if (kind == kFp8) return launch<kFp8, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, tbpf, s);
+        if (kind == kFp4) return launch<kFp4, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, tbpf, s);
+        return launch<kBf16, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, tbpf, s);
     }
 #define DG_DISPATCH(K, G)                                                                  \
     if (kind == K && gtype == G) {                                                         \

@@ -80,13 +80,15 @@ __global__ void __launch_bounds__(256) return_ptrs_kernel(const int32_t* __restr
 
 // One block.  dest_base[g] = first slot, in the owner's layout, of this rank's copies for expert g
 // (-1 if the owner's layout would overflow `cap` rows; the status word records it).
-// The local experts are cut into `slices` ranges of per_slice experts that are dispatched and
+// The local experts are cut into `slices` ranges [first[s], first[s + 1]) that are dispatched and
 // computed one after the other: block_expert[s][b] = local expert of the b-th `align`-row block of
 // this rank's own layout if it belongs to slice s, else -1; blocks_used[s] = blocks up to the end
 // of slice s.
+constexpr uint32_t kMaxSlices = 16;
+struct SliceBounds { uint32_t first[kMaxSlices + 1]; };
 __global__ void __launch_bounds__(1024) ep_route_kernel(const int32_t* __restrict__ counts, uint32_t world, uint32_t me,
                                                        uint32_t num_experts, uint32_t e_local, uint32_t align, uint32_t cap,
-                                                       uint32_t slices, uint32_t per_slice, int32_t* __restrict__ dest_base,
+                                                       uint32_t slices, const SliceBounds bounds, int32_t* __restrict__ dest_base,
                                                        int32_t* __restrict__ block_expert, int32_t* __restrict__ blocks_used,
                                                        uint32_t* status) {
     __shared__ int32_t s_padded[1024];
@@ -125,10 +127,11 @@ __global__ void __launch_bounds__(1024) ep_route_kernel(const int32_t* __restric
             if (row >= s_base[gg] && row < s_base[gg] + s_padded[gg]) { found = (int32_t)e; break; }
         }
         for (uint32_t sl = 0; sl < slices; ++sl)
-            block_expert[(size_t)sl * n_blocks + b] = (found >= 0 && (uint32_t)found / per_slice == sl) ? found : -1;
+            block_expert[(size_t)sl * n_blocks + b] =
+                (found >= 0 && (uint32_t)found >= bounds.first[sl] && (uint32_t)found < bounds.first[sl + 1]) ? found : -1;
     }
     if (threadIdx.x < slices) {
-        const uint32_t last = min(e_local, (threadIdx.x + 1u) * per_slice) - 1u, gg = me * e_local + last;
+        const uint32_t last = bounds.first[threadIdx.x + 1u] - 1u, gg = me * e_local + last;
         blocks_used[threadIdx.x] = (int32_t)min((uint32_t)(s_base[gg] + s_padded[gg]) / align, n_blocks);
     }
 }
@@ -291,7 +294,8 @@ int32_t dg_moe_return_ptrs(const int32_t* slot_src, uint32_t slots, const int32_
 }
 
 int32_t dg_ep_route(const int32_t* counts, uint32_t world, uint32_t me, uint32_t num_experts, uint32_t align, uint32_t cap,
-                    uint32_t slices, int32_t* dest_base, int32_t* block_expert, int32_t* blocks_used, void* stream) {
+                    uint32_t slices, const uint32_t* slice_first, int32_t* dest_base, int32_t* block_expert, int32_t* blocks_used,
+                    void* stream) {
     if (!counts || !dest_base || !block_expert || !blocks_used) return dg::fail(DG_ERR_INVALID_ARG, "ep_route: null buffer");
     if (world == 0 || me >= world || num_experts == 0 || num_experts > 1024 || num_experts % world != 0)
         return dg::fail(DG_ERR_INVALID_ARG, "ep_route: %u experts over %u ranks (at most 1024 experts, divisible by the ranks)", num_experts, world);
@@ -300,10 +304,20 @@ int32_t dg_ep_route(const int32_t* counts, uint32_t world, uint32_t me, uint32_t
     int32_t st = dg::current_device(&dev);
     if (st != DG_OK) return st;
     const uint32_t e_local = num_experts / world;
-    if (slices == 0 || slices > e_local) return dg::fail(DG_ERR_INVALID_ARG, "ep_route: %u slices for %u local experts", slices, e_local);
+    if (slices == 0 || slices > e_local || slices > dg::kMaxSlices)
+        return dg::fail(DG_ERR_INVALID_ARG, "ep_route: %u slices for %u local experts (at most %u)", slices, e_local, dg::kMaxSlices);
+    dg::SliceBounds bounds = {};
+    for (uint32_t i = 0; i <= slices; ++i) {
+        // slice_first (host, slices + 1 entries, ascending from 0 to e_local); NULL = equal slices
+        bounds.first[i] = slice_first ? slice_first[i] : (uint32_t)((uint64_t)e_local * i / slices);
+        if (bounds.first[i] > e_local || (i > 0 && bounds.first[i] <= bounds.first[i - 1]))
+            return dg::fail(DG_ERR_INVALID_ARG, "ep_route: slice bounds must ascend from 0 to %u", e_local);
+    }
+    if (bounds.first[0] != 0 || bounds.first[slices] != e_local)
+        return dg::fail(DG_ERR_INVALID_ARG, "ep_route: slice bounds must start at 0 and end at %u", e_local);
     dg::ep_route_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(counts, world, me, num_experts, e_local, align, cap,
-                                                                           slices, dg::ceil_div(e_local, slices), dest_base,
-                                                                           block_expert, blocks_used, dev->status);
+                                                                           slices, bounds, dest_base, block_expert, blocks_used,
+                                                                           dev->status);
     dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;

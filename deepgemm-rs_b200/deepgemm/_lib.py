@@ -98,7 +98,7 @@ def load(build_if_missing=True):
     L.dg_peer_copy.argtypes = [vp, vp, u64, vp]
     L.dg_peer_barrier.argtypes = [vp, vp, u32, u32, u64, vp]
     L.dg_moe_return_ptrs.argtypes = [vp, u32, vp, vp, vp, u32, u64, vp, vp]
-    L.dg_ep_route.argtypes = [vp, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp]
+    L.dg_ep_route.argtypes = [vp, u32, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp]
     L.dg_ep_push.argtypes = [vp, u64, u32, vp, u32, u64, vp, vp, vp, u32, u32, u32, u32, u32, u32, u64, vp, vp, vp, u32, vp]
     L.dg_ep_return_ptrs.argtypes = [vp, u32, vp, u32, u64, vp, u32, vp, vp]
     L.dg_m_grouped_gemm_nt_contiguous_rowptr.argtypes = [opp, opp, vp, u32, u32, vp, vp, u32, u32, vp]

@@ -233,8 +233,8 @@ class ExpertParallelMoE:
     packed SF; returns bf16 [T, n_out] = sum_j topk_w[t, j] * (x[t] . W[topk_idx[t, j]]^T).
     """
 
-    def __init__(self, weights: Operand, num_experts: int, group=None, chunks: int = 1, return_parts: int = 1,
-                 transport: str = "push", single_rank_transport: bool = False):
+    def __init__(self, weights: Operand, num_experts: int, group=None, chunks: Optional[int] = None, return_parts: int = 1,
+                 transport: str = "push", single_rank_transport: bool = False, slice_weights=None):
         # Transports between several GPUs (one NVSwitch domain):
         # "push": a kernel stores every token copy (row, scale factors, return ticket) straight into
         #   its slot of the expert owner's padded layout, the grouped GEMM stores its result rows
@@ -248,12 +248,12 @@ class ExpertParallelMoE:
         #   return_parts > 1 runs the GEMM of a slice in column ranges whose return transfers overlap
         #   the next range; both overlap NCCL kernels with a GEMM that wants every SM and, measured
         #   on 2 GPUs, lost more than they hid.
-        self.chunks = chunks
         self.transport = os.environ.get("DG_EP_TRANSPORT", transport)
         if self.transport not in ("push", "peer", "nccl"):
             raise ValueError("transport must be 'push', 'peer' or 'nccl'")
         # one rank normally takes the local path below; True runs the chosen transport against itself
         self.single_rank_transport = single_rank_transport
+        self.slice_weights = slice_weights     # push transport: proportions of the expert slices, e.g. (1, 3)
         self._win = None
         self._win_shape = None
         self._streams = None
@@ -264,6 +264,9 @@ class ExpertParallelMoE:
         self.group = group
         self.world = dist.get_world_size(group) if group is not None else 1
         self.e_local = num_experts // self.world
+        # default: four expert slices for the push transport between GPUs (measured best on 2 and 8
+        # GPUs), the plain sequence everywhere else
+        self.chunks = chunks if chunks is not None else (4 if self.transport == "push" and self.world > 1 else 1)
         self.last_m_indices: Optional[torch.Tensor] = None
 
     def forward(self, x, x_sf, topk_idx, topk_w=None):
@@ -540,6 +543,23 @@ class ExpertParallelMoE:
         if self._streams is None:
             self._streams = (torch.cuda.Stream(), torch.cuda.Stream())
 
+    def _slice_bounds(self):
+        """First local expert of every slice, plus e_local.  `chunks` (or DG_EP_CHUNKS) = n gives n
+        equal slices; DG_EP_SLICES = "1,3" gives slices in those proportions (a small first slice
+        starts the GEMM early while the bulk of the rows is still travelling)."""
+        spec = os.environ.get("DG_EP_SLICES", self.slice_weights)
+        if spec:
+            w = [float(v) for v in (spec.split(",") if isinstance(spec, str) else spec)]
+        else:
+            w = [1.0] * max(1, min(int(os.environ.get("DG_EP_CHUNKS", self.chunks)), self.e_local, 16))
+        cuts, acc = [0], 0.0
+        for v in w:
+            acc += v
+            cuts.append(min(self.e_local, max(cuts[-1] + 1, round(self.e_local * acc / sum(w)))))
+        cuts[-1] = self.e_local
+        cuts = sorted(set(cuts))
+        return cuts if len(cuts) >= 2 else [0, self.e_local]
+
     def _forward_push(self, x, x_sf, topk_idx, topk_w):
         """Every rank must pass the same number of tokens.  The whole step is queued without the host
         ever waiting for the device.  With `chunks` > 1 the local experts are cut into that many
@@ -553,9 +573,8 @@ class ExpertParallelMoE:
         k_elems = k if self.w.dtype != Dtype.Fp4 else k * 2
         row_bytes = k * x.element_size()
         n = tokens * topk
-        slices = max(1, min(int(os.environ.get("DG_EP_CHUNKS", self.chunks)), self.e_local))
-        per_slice = (self.e_local + slices - 1) // slices
-        slices = (self.e_local + per_slice - 1) // per_slice
+        bounds = self._slice_bounds()
+        slices = len(bounds) - 1
         self._ensure_push_window(tokens, topk, row_bytes, x_sf.rows, n_out, slices)
         win, sh = self._win, self._win_shape
         cap = sh["cap"]
@@ -569,13 +588,14 @@ class ExpertParallelMoE:
             counts = sh["counts"]
         else:
             counts = p.counts
-        _check(L.dg_ep_route(counts.data_ptr(), world, me, self.num_experts, BLOCK, cap, slices, sh["dest_base"].data_ptr(),
-                             sh["block_expert"].data_ptr(), sh["blocks_used"].data_ptr(), main.cuda_stream))
+        _check(L.dg_ep_route(counts.data_ptr(), world, me, self.num_experts, BLOCK, cap, slices, (C.c_uint32 * len(bounds))(*bounds),
+                             sh["dest_base"].data_ptr(), sh["block_expert"].data_ptr(), sh["blocks_used"].data_ptr(),
+                             main.cuda_stream))
 
         def push(s, stream, max_blocks):
             _check(L.dg_ep_push(x.data_ptr(), x.stride(0) * x.element_size(), row_bytes, x_sf.buf.data_ptr(), x_sf.rows, x_sf.cols,
                                 p.slot_src.data_ptr(), p.offsets.data_ptr(), sh["dest_base"].data_ptr(), self.num_experts, world,
-                                me, s * per_slice, min(self.e_local, (s + 1) * per_slice), n, cap, sh["a_bases"].data_ptr(),
+                                me, bounds[s], bounds[s + 1], n, cap, sh["a_bases"].data_ptr(),
                                 sh["sf_bases"].data_ptr(), sh["ticket_bases"].data_ptr(), max_blocks, stream.cuda_stream))
             win.barrier(0, stream.cuda_stream)      # every rank's rows, scale factors and tickets of the slice have landed here
 
@@ -584,7 +604,7 @@ class ExpertParallelMoE:
             routed = torch.cuda.Event()
             routed.record(main)
             comm.wait_event(routed)
-            side_blocks = int(os.environ.get("DG_EP_PUSH_BLOCKS", 296))
+            side_blocks = int(os.environ.get("DG_EP_PUSH_BLOCKS", 64))
             for s in range(slices):
                 push(s, comm, 0 if s == 0 else side_blocks)
                 ev = torch.cuda.Event()

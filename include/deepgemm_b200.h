@@ -269,13 +269,15 @@ DG_API int32_t dg_moe_return_ptrs(const int32_t* slot_src, uint32_t slots, const
  * one owner rank follow each other in its layout, each padded to `align` rows; inside an expert of
  * owner d the source ranks follow each other in the order d+1, d+2, ..., d.  dg_ep_route writes
  * dest_base[g] = first slot of this rank's copies of expert g in the owner's layout (-1 and a recorded
- * status if the owner's `cap` rows would overflow).  The local experts are cut into `slices` ranges of ceil(e_local / slices) experts that
- * can be dispatched and computed one after the other: block_expert[s * (cap / align) + b] = `m_indices`
- * entry of block b of this rank's own layout for slice s (-1 for blocks of other slices),
- * blocks_used[s] = number of leading blocks that hold slices 0..s. */
+ * status if the owner's `cap` rows would overflow).  The local experts are cut into `slices` ranges
+ * [slice_first[s], slice_first[s + 1]) (host array of slices + 1 entries from 0 to e_local; NULL =
+ * equal ranges; at most 16) that can be dispatched and computed one after the other:
+ * block_expert[s * (cap / align) + b] = `m_indices` entry of block b of this rank's own layout for
+ * slice s (-1 for blocks of other slices), blocks_used[s] = number of leading blocks that hold
+ * slices 0..s. */
 DG_API int32_t dg_ep_route(const int32_t* counts, uint32_t world, uint32_t me, uint32_t num_experts, uint32_t align,
-                           uint32_t cap, uint32_t slices, int32_t* dest_base, int32_t* block_expert,
-                           int32_t* blocks_used, void* stream);
+                           uint32_t cap, uint32_t slices, const uint32_t* slice_first, int32_t* dest_base,
+                           int32_t* block_expert, int32_t* blocks_used, void* stream);
 /* Stores the copies of this rank whose local expert index at the owner lies in [e_lo, e_hi) into the
  * owner's memory: for copy p of the copies sorted by global expert (slot_src[p] = token row,
  * my_offsets[num_experts + 1] = first p of every expert, both from dg_moe_plan with align 1), the
