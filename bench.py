@@ -188,7 +188,6 @@ def main():
     idx_host = topk_idx.cpu().pin_memory()
     w_host = topk_w.cpu().pin_memory()
     x8, x_sf = synth.quantised_tokens(x_dev)
-    out_host = torch.empty((T, N), dtype=torch.bfloat16).pin_memory()
 
     gemm_events = []
     gemm_names = ("m_grouped_gemm_nt_contiguous", "m_grouped_gemm_nt_contiguous_scatter", "m_grouped_gemm_nt_contiguous_rowptr")
@@ -206,14 +205,42 @@ def main():
     def step_resident():
         return layer.forward(x8, x_sf, topk_idx, topk_w)
 
-    def step_e2e():
-        xd = x_host.to(dev, non_blocking=True)
-        idx = idx_host.to(dev, non_blocking=True)
-        w = w_host.to(dev, non_blocking=True)
-        c, sf = synth.quantised_tokens(xd)
-        out = layer.forward(c, sf, idx, w)
-        out_host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    # End to end: every step copies its inputs from pinned host memory and its result back.  The
+    # three legs run on three streams over two sets of buffers, so the upload of step i overlaps
+    # the compute of step i-1 and the download of step i-2, the way a caller streaming batches
+    # through the layer would do it; every step still moves all of its bytes inside the timed region.
+    e2e_streams = [torch.cuda.Stream() for _ in range(3)]
+    e2e_bufs = [dict(x=torch.empty((T, K), dtype=torch.float32, device=dev), idx=torch.empty_like(topk_idx),
+                     w=torch.empty_like(topk_w), out_host=torch.empty((T, N), dtype=torch.bfloat16).pin_memory(),
+                     consumed=None, downloaded=None) for _ in range(2)]
+
+    def run_e2e(steps):
+        s_in, s_cmp, s_out = e2e_streams
+        cur = torch.cuda.current_stream()
+        for st in e2e_streams:
+            st.wait_stream(cur)
+        for i in range(steps):
+            b = e2e_bufs[i % 2]
+            with torch.cuda.stream(s_in):
+                if b["consumed"] is not None:
+                    s_in.wait_event(b["consumed"])          # the step that last read this set has quantised its tokens
+                b["x"].copy_(x_host, non_blocking=True)
+                b["idx"].copy_(idx_host, non_blocking=True)
+                b["w"].copy_(w_host, non_blocking=True)
+                uploaded = torch.cuda.Event()
+                uploaded.record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(uploaded)
+                c, sf = synth.quantised_tokens(b["x"])
+                out = layer.forward(c, sf, b["idx"], b["w"])
+                b["consumed"] = torch.cuda.Event()
+                b["consumed"].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(b["consumed"])
+                out.record_stream(s_out)
+                b["out_host"].copy_(out, non_blocking=True)
+        for st in e2e_streams:
+            cur.wait_stream(st)
 
     def barrier():
         torch.cuda.synchronize()
@@ -258,7 +285,18 @@ def main():
     gemm_ms = sum(a.elapsed_time(b) for a, b in ev) / args.steps    # all slices of one step
     for n in gemm_names:
         setattr(moe, n, orig_gemms[n])
-    ms_e2e, _ = timed(step_e2e, max(2, min(args.steps, 5)), 1)
+    e2e_steps = max(4, min(args.steps, 8))
+    run_e2e(2)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run_e2e(e2e_steps)
+    e1.record()
+    barrier()
+    ms_t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
+    ms_e2e = ms_t.item() / e2e_steps
 
     value = flops_per_step / (ms_step * 1e-3) / 1e12
     e2e_value = flops_per_step / (ms_e2e * 1e-3) / 1e12
@@ -272,8 +310,10 @@ def main():
                                                                         if world > 1 else {})),
         "e2e": {"value": e2e_value, "unit": "TFLOPS", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": x_host.numel() * 4 + idx_host.numel() * 4 + w_host.numel() * 4,
-                "d2h_bytes_per_step": out_host.numel() * 2,
-                "path": "pinned host f32 tokens -> quant_mx -> expert-parallel grouped GEMM -> combine -> pinned host bf16"},
+                "d2h_bytes_per_step": T * N * 2,
+                "steps": e2e_steps,
+                "path": "pinned host f32 tokens -> quant_mx -> expert-parallel grouped GEMM -> combine -> pinned host bf16; "
+                        "upload, compute and download of consecutive steps overlap on three streams"},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "gemm_kernel<fp8, contiguous>", "achieved": gemm_tflops, "peak": fp8_peak,

@@ -23,8 +23,9 @@ __device__ __forceinline__ uint32_t ue8m0_exp(float amax) {
 }
 
 // Four scaled floats -> four E4M3 bytes (element 0 in the low byte), RNE, saturating.
-// NaN encodes as a signed zero code, like the golden model's grid search (golden.rs:142-189).
-__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+// NaN encodes as a signed zero code, like the golden model's grid search (golden.rs:142-189); its
+// sign is the input's (`src`): the multiplication by the scale returns the canonical positive NaN.
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d, const float4& src) {
     uint16_t lo, hi;
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a), "f"(b));
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(c), "f"(d));
@@ -32,20 +33,20 @@ __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float 
     // The saturating conversion never produces 0x7f / 0xff for a number (the largest finite code is
     // 0x7e), so a byte with all seven low bits set marks a NaN input: a rare, single test.
     if (((r & 0x7f7f7f7fu) + 0x01010101u) & 0x80808080u) {
-        if (a != a) r = (r & 0xffffff00u) | ((__float_as_uint(a) >> 31) << 7);
-        if (b != b) r = (r & 0xffff00ffu) | ((__float_as_uint(b) >> 31) << 15);
-        if (c != c) r = (r & 0xff00ffffu) | ((__float_as_uint(c) >> 31) << 23);
-        if (d != d) r = (r & 0x00ffffffu) | ((__float_as_uint(d) >> 31) << 31);
+        if (a != a) r = (r & 0xffffff00u) | ((__float_as_uint(src.x) >> 31) << 7);
+        if (b != b) r = (r & 0xffff00ffu) | ((__float_as_uint(src.y) >> 31) << 15);
+        if (c != c) r = (r & 0xff00ffffu) | ((__float_as_uint(src.z) >> 31) << 23);
+        if (d != d) r = (r & 0x00ffffffu) | ((__float_as_uint(src.w) >> 31) << 31);
     }
     return r;
 }
 // Two scaled floats -> one byte of two E2M1 nibbles (first element in the low nibble).
-__device__ __forceinline__ uint32_t cvt_e2m1x2(float a, float b) {
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float a, float b, float src_a, float src_b) {
     uint16_t r;
     asm("{ .reg .b8 t;\n cvt.rn.satfinite.e2m1x2.f32 t, %2, %1;\n mov.b16 %0, {t, 0}; }" : "=h"(r) : "f"(a), "f"(b));
     uint32_t v = r;
-    if (a != a) v = (v & 0xf0u) | ((__float_as_uint(a) >> 31) << 3);
-    if (b != b) v = (v & 0x0fu) | ((__float_as_uint(b) >> 31) << 7);
+    if (a != a) v = (v & 0xf0u) | ((__float_as_uint(src_a) >> 31) << 3);
+    if (b != b) v = (v & 0x0fu) | ((__float_as_uint(src_b) >> 31) << 7);
     return v;
 }
 
@@ -111,10 +112,10 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
                 const float4 q = make_float4(v[i][j].x * inv, v[i][j].y * inv, v[i][j].z * inv, v[i][j].w * inv);
                 const size_t col = col0 + j * 128u + lane * 4u;
                 if (FP4) {
-                    const uint32_t b = cvt_e2m1x2(q.x, q.y) | (cvt_e2m1x2(q.z, q.w) << 8);
+                    const uint32_t b = cvt_e2m1x2(q.x, q.y, v[i][j].x, v[i][j].y) | (cvt_e2m1x2(q.z, q.w, v[i][j].z, v[i][j].w) << 8);
                     if (ok) *reinterpret_cast<uint16_t*>(data + ((size_t)row * k + col) / 2) = (uint16_t)b;
                 } else {
-                    const uint32_t b = cvt_e4m3x4(q.x, q.y, q.z, q.w);
+                    const uint32_t b = cvt_e4m3x4(q.x, q.y, q.z, q.w, v[i][j]);
                     if (ok) *reinterpret_cast<uint32_t*>(data + (size_t)row * k + col) = b;
                 }
                 if (G == 32) {
