@@ -284,10 +284,18 @@ class ExpertParallelMoE:
                                          self.e_local)
             self.last_m_indices = p.block_expert
             return combine(d, p.slot_of_row.view(tokens, topk), topk_w)
-        if self.transport == "push":
-            return self._forward_push(x, x_sf, topk_idx, topk_w)
-        if self.transport == "peer":
-            return self._forward_peer(x, x_sf, topk_idx, topk_w)
+        if self.transport in ("push", "peer"):
+            from .peer import PeerMappingError
+            try:
+                if self.transport == "push":
+                    return self._forward_push(x, x_sf, topk_idx, topk_w)
+                return self._forward_peer(x, x_sf, topk_idx, topk_w)
+            except PeerMappingError as ex:
+                # raised on all ranks alike, before anything of the step was queued: the GPUs cannot
+                # map each other's memory here, so the step goes over NCCL from now on
+                import sys
+                print(f"[deepgemm] {ex}; expert parallelism falls back to NCCL all-to-alls", file=sys.stderr)
+                self.transport, self.chunks, self._win, self._win_shape = "nccl", 1, None, None
         # Several GPUs: the tokens are cut into `chunks` slices that flow through
         # dispatch -> GEMM -> return as a pipeline, so that NCCL traffic of one slice overlaps the
         # grouped GEMM of another.  All count exchanges happen first (one all-to-all, one host sync).

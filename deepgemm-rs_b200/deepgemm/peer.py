@@ -19,6 +19,10 @@ MAX_RANKS = 64
 CHANNELS = FLAG_BYTES // (8 * MAX_RANKS)
 
 
+class PeerMappingError(RuntimeError):
+    """Raised on every rank alike when some rank could not map another rank's buffer."""
+
+
 class _RawDeviceMemory:
     """Lets torch view device memory that this library allocated."""
 
@@ -46,13 +50,29 @@ class PeerWindow:
             handles = [None] * self.world
             dist.all_gather_object(handles, handle.raw, group=group)
         self.ptrs = []
+        problem = None
         for r, h in enumerate(handles):
             if r == self.rank:
                 self.ptrs.append(self.ptr)
-            else:
-                q = C.c_void_p()
+                continue
+            q = C.c_void_p()
+            try:
                 _check(L.dg_peer_open(C.create_string_buffer(h, 64), C.byref(q)))
-                self.ptrs.append(q.value)
+            except Exception as ex:      # keep going: every rank must reach the agreement below
+                problem = problem or ex
+            self.ptrs.append(q.value)
+        if not self.single:
+            # all ranks map all buffers, or none keeps a window (the caller may then choose another transport)
+            verdicts = [None] * self.world
+            dist.all_gather_object(verdicts, None if problem is None else repr(problem), group=group)
+            if any(v is not None for v in verdicts):
+                for r, q in enumerate(self.ptrs):
+                    if r != self.rank and q:
+                        L.dg_peer_close(q)
+                dist.barrier(group=group)
+                L.dg_peer_free(self.ptr)
+                self.ptr = None
+                raise PeerMappingError("mapping the peers' buffers failed: " + "; ".join(f"rank {r}: {v}" for r, v in enumerate(verdicts) if v))
         dev = torch.device("cuda", torch.cuda.current_device())
         self.local = torch.as_tensor(_RawDeviceMemory(self.ptr, self.nbytes), device=dev)
         # per channel: device table of every rank's flag array, and the next sequence number
