@@ -19,8 +19,14 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restric
     if (s < 0) {
         for (uint32_t v = lane; v < vec_per_row; v += 32u) d[v] = make_uint4(0, 0, 0, 0);
     } else {
+        // source rows are read once per top-k copy: keep them cached, stream the copies out
         const uint4* p = src + (size_t)s * src_pitch_vec;
-        for (uint32_t v = lane; v < vec_per_row; v += 32u) d[v] = __ldcs(p + v);
+        uint32_t v = lane;
+        for (; v + 96u < vec_per_row; v += 128u) {     // four loads in flight per lane before the stores
+            const uint4 r0 = __ldg(p + v), r1 = __ldg(p + v + 32u), r2 = __ldg(p + v + 64u), r3 = __ldg(p + v + 96u);
+            __stcs(d + v, r0); __stcs(d + v + 32u, r1); __stcs(d + v + 64u, r2); __stcs(d + v + 96u, r3);
+        }
+        for (; v < vec_per_row; v += 32u) __stcs(d + v, __ldg(p + v));
     }
 }
 
