@@ -823,6 +823,11 @@ static int32_t tile_counters(const DeviceInfo* dev, cudaStream_t s, uint32_t** o
         uint32_t* pool = nullptr;
         DG_CUDA_CHECK(cudaMalloc(&pool, kPairs * 2 * sizeof(uint32_t)));
         DG_CUDA_CHECK(cudaMemsetAsync(pool, 0, kPairs * 2 * sizeof(uint32_t), s));
+        // other streams may use other pairs right away: wait for the clearing, unless `s` is being
+        // captured (then the clearing is ordered before this launch, the only user so far)
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        DG_CUDA_CHECK(cudaStreamIsCapturing(s, &cap));
+        if (cap == cudaStreamCaptureStatusNone) DG_CUDA_CHECK(cudaStreamSynchronize(s));
         pools[d] = pool;
     }
     *out = pools[d] + 2u * (next[d]++ % kPairs);

@@ -158,6 +158,13 @@ int32_t dg_poll_device_status(void* stream) {
     if (word != 0) {
         DG_CUDA_CHECK(cudaMemsetAsync(d->status, 0, 4, s));
         DG_CUDA_CHECK(cudaStreamSynchronize(s));
+        // site 7 comes from the peer-memory kernels: bit 15 set = a layout overflow found by
+        // dg_ep_route (expert in bits 16..), else the barrier gave up waiting for the rank in bits 8..
+        if ((word & 0xffu) == 7u && (word & 0x8000u))
+            return dg::fail(DG_ERR_RUNTIME, "expert-parallel dispatch: the rows routed to the owner of expert %u exceed its layout capacity; they were dropped",
+                            word >> 16);
+        if ((word & 0xffu) == 7u)
+            return dg::fail(DG_ERR_DEVICE_TIMEOUT, "a barrier between ranks gave up waiting for rank %u", word >> 8);
         return dg::fail(DG_ERR_DEVICE_TIMEOUT, "a device-side wait gave up: site %u in block %u", word & 0xffu, word >> 8);
     }
     return DG_OK;

@@ -14,6 +14,7 @@
 #include "host.h"
 #include "ptx.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace dg {
@@ -26,7 +27,7 @@ constexpr unsigned long long kPeerWaitNs = 10000000000ull;  // 10 s: ranks may b
 // kernel starts; the system-scope fence orders it before the flag for observers on other GPUs.
 __global__ void __launch_bounds__(64) peer_barrier_kernel(unsigned long long* const* __restrict__ peer_flags,
                                                          volatile unsigned long long* local_flags, uint32_t me, uint32_t world,
-                                                         unsigned long long seq, uint32_t* status) {
+                                                         unsigned long long seq, unsigned long long wait_ns, uint32_t* status) {
     const uint32_t r = threadIdx.x;
     if (r >= world) return;
     __threadfence_system();
@@ -39,7 +40,7 @@ __global__ void __launch_bounds__(64) peer_barrier_kernel(unsigned long long* co
         asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(local_flags + r) : "memory");
         if (v >= seq) break;
         if ((++spins & 63u) == 0) {
-            if (globaltimer_ns() - t0 > kPeerWaitNs) {
+            if (globaltimer_ns() - t0 > wait_ns) {
                 atomicCAS(status, 0u, (uint32_t)kWaitPeer | (r << 8));
                 break;
             }
@@ -269,9 +270,15 @@ int32_t dg_peer_barrier(const uint64_t* peer_flags, uint64_t* local_flags, uint3
     const dg::DeviceInfo* dev;
     int32_t st = dg::current_device(&dev);
     if (st != DG_OK) return st;
+    // DG_PEER_WAIT_MS shortens (or extends) the bound of the wait, e.g. for failure-detection tests
+    unsigned long long wait_ns = dg::kPeerWaitNs;
+    if (const char* v = getenv("DG_PEER_WAIT_MS")) {
+        const unsigned long long ms = strtoull(v, nullptr, 10);
+        if (ms > 0) wait_ns = ms * 1000000ull;
+    }
     dg::peer_barrier_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<unsigned long long* const*>(peer_flags), reinterpret_cast<volatile unsigned long long*>(local_flags), me,
-        world, seq, dev->status);
+        world, seq, wait_ns, dev->status);
     dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;

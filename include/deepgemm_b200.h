@@ -253,7 +253,8 @@ DG_API int32_t dg_peer_copy(void* dst, const void* src, uint64_t bytes, void* st
  * at every rank's flag array (`world` 64-bit words, cleared at allocation, one array per barrier
  * channel), local_flags is this rank's own.  `seq` must grow by one per call on a channel, alike on
  * all ranks.  Work queued on `stream` before the call is visible to every rank once its own barrier
- * call has completed.  The wait gives up after 10 s (dg_poll_device_status reports it). */
+ * call has completed.  The wait gives up after 10 s (DG_PEER_WAIT_MS in the environment changes the
+ * bound); dg_poll_device_status then reports DG_ERR_DEVICE_TIMEOUT and names the missing rank. */
 DG_API int32_t dg_peer_barrier(const uint64_t* peer_flags, uint64_t* local_flags, uint32_t me, uint32_t world,
                                uint64_t seq, void* stream);
 /* Row address table for the return path of an expert-parallel step: ptrs[s] (device, uint64) = where

@@ -118,3 +118,39 @@ def test_push_transport_against_itself_equals_local_step(slices):
             assert torch.equal(got, want), f"step {step}"
     finally:
         layer.close()
+
+
+def test_barrier_gives_up_on_a_missing_rank_and_reports_it(monkeypatch):
+    """Failure detection without a fault: rank 1 of a two-rank barrier never writes its flag; the
+    wait runs out (shortened to 0.3 s), the kernel returns, the status word names the rank and the
+    context stays usable."""
+    from deepgemm import DeviceTimeout
+    L = _lib.load()
+    monkeypatch.setenv("DG_PEER_WAIT_MS", "300")
+    mine, other = C.c_void_p(), C.c_void_p()
+    assert L.dg_peer_alloc(4096, C.byref(mine)) == 0 and L.dg_peer_alloc(4096, C.byref(other)) == 0
+    try:
+        table = torch.tensor([mine.value, other.value], dtype=torch.int64, device="cuda")
+        assert L.dg_peer_barrier(table.data_ptr(), mine.value, 0, 2, 1, None) == 0
+        with pytest.raises(DeviceTimeout, match="rank 1"):
+            poll_device_status()
+        poll_device_status()                                   # the word was cleared; the GPU still answers
+        assert int(torch.arange(4, device="cuda").sum().item()) == 6
+    finally:
+        assert L.dg_peer_free(mine.value) == 0 and L.dg_peer_free(other.value) == 0
+
+
+def test_route_reports_a_layout_overflow():
+    """More rows than the owner's layout holds: dg_ep_route marks the expert's copies as dropped
+    (dest_base -1) and the status word says so."""
+    from deepgemm import DgError
+    L = _lib.load()
+    counts = torch.tensor([[100, 300, 50, 20]], dtype=torch.int32, device="cuda")     # one rank, four experts
+    dest = torch.empty(4, dtype=torch.int32, device="cuda")
+    blocks = torch.empty(4, dtype=torch.int32, device="cuda")
+    used = torch.empty(1, dtype=torch.int32, device="cuda")
+    assert L.dg_ep_route(counts.data_ptr(), 1, 0, 4, 128, 512, 1, None, dest.data_ptr(), blocks.data_ptr(), used.data_ptr(), None) == 0
+    with pytest.raises(DgError, match="exceed"):
+        poll_device_status()
+    assert dest.cpu().tolist() == [0, 128, -1, -1]             # 128 + 384 rows fit into 512, the rest does not
+    assert blocks.cpu().tolist() == [0, 1, 1, 1] and used.item() == 4
