@@ -285,7 +285,7 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     v = SCALED ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.weights)[idx])
                                : reinterpret_cast<const float*>(p.weights)[idx];
                 }
-                w[et] = v;
+                w[et] = 0.5f * v;      // see the epilogue loop: relu(x) * w = (x + |x|) * (w / 2)
             }
             // The two buffers alternate, and no warp can run more than one query block ahead of
             // the slowest one (it waits here), so a buffer is never rewritten while still read.
@@ -303,32 +303,38 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 float scale = 1.f;
                 if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
                 const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride + col_base;
-                uint64_t acc0 = 0, acc1 = 0;                     // two f32x2 accumulators of the current query
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;    // four partial sums of the current query
 
                 // One 32-column chunk: weighted ReLU into the accumulators; on a query's last
-                // chunk, scale and store its logit.
+                // chunk, scale and store its logit.  relu(x) * w is computed as (x + |x|) * (w / 2):
+                // the addition takes |x| as a source modifier and runs on the FMA pipe at full rate,
+                // where a max would go through the half-rate ALU pipe that bounds this loop; both
+                // scalings are by powers of two, so the result is the same bit for bit.  The weights
+                // in shared memory are already halved.
                 auto consume = [&](const uint32_t (&v)[32], uint32_t c) {
                     const float4* w4 = reinterpret_cast<const float4*>(w + col_base + c * 32u);
 #pragma unroll
                     for (uint32_t i = 0; i < 8; ++i) {
                         const float4 ww = w4[i];
-                        const float x0 = fmaxf(__uint_as_float(v[4 * i]), 0.f), x1 = fmaxf(__uint_as_float(v[4 * i + 1]), 0.f);
-                        const float x2 = fmaxf(__uint_as_float(v[4 * i + 2]), 0.f), x3 = fmaxf(__uint_as_float(v[4 * i + 3]), 0.f);
-                        acc0 = fma_f32x2(pack_f32x2(x0, x1), pack_f32x2(ww.x, ww.y), acc0);
-                        acc1 = fma_f32x2(pack_f32x2(x2, x3), pack_f32x2(ww.z, ww.w), acc1);
+                        const float x0 = __uint_as_float(v[4 * i]), x1 = __uint_as_float(v[4 * i + 1]);
+                        const float x2 = __uint_as_float(v[4 * i + 2]), x3 = __uint_as_float(v[4 * i + 3]);
+                        a0 = fmaf(x0 + fabsf(x0), ww.x, a0);
+                        a1 = fmaf(x1 + fabsf(x1), ww.y, a1);
+                        a2 = fmaf(x2 + fabsf(x2), ww.z, a2);
+                        a3 = fmaf(x3 + fabsf(x3), ww.w, a3);
                     }
                     if ((c + 1) % chunks_per_q == 0) {
                         const uint32_t q = qb * p.block_q + wg * q_per_wg + c / chunks_per_q;
                         if (q < p.num_tokens) {
                             const uint32_t s = __ldg(p.ks + q), e = min(__ldg(p.ke + q), p.num_kv);
                             if (j >= s && j < e) {
-                                const float val = (sum_f32x2(acc0) + sum_f32x2(acc1)) * scale;
+                                const float val = ((a0 + a1) + (a2 + a3)) * scale;
                                 const size_t o = (size_t)q * p.logits_stride + (j - s);
                                 if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
                                 else reinterpret_cast<float*>(p.logits)[o] = val;
                             }
                         }
-                        acc0 = 0; acc1 = 0;
+                        a0 = a1 = a2 = a3 = 0.f;
                     }
                 };
                 auto release = [&]() {
