@@ -105,6 +105,13 @@ __device__ __forceinline__ float sum_f32x2(uint64_t v) {
     return lo + hi;
 }
 
+#ifdef DG_MQA_TRACE
+__device__ unsigned long long g_mqa_trace[8 * 256];
+#define MQA_STAMP(row, idx) do { if (blockIdx.x == 0 && lane == 0 && (idx) < 256u) g_mqa_trace[(row) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define MQA_STAMP(row, idx) do { } while (0)
+#endif
+
 template <bool SCALED>
 __global__ void __launch_bounds__(kMqaMaxThreads, 1)
 mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
@@ -116,6 +123,8 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     uint8_t* base_ptr = smem_raw + (base - raw_u32);
     MqaBarriers* bars = reinterpret_cast<MqaBarriers*>(base_ptr);
     float* w_smem = reinterpret_cast<float*>(base_ptr + p.off_w);   // [2][n]
+    uint32_t* win_smem = reinterpret_cast<uint32_t*>(base_ptr + 512);  // [2][2][16]: ks / ke of the queries of a block
+    static_assert(sizeof(MqaBarriers) <= 512, "barrier block overlaps the window table");
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const WaitCtx wc{p.status, &bars->abort};
 
@@ -207,7 +216,9 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 ++acount;
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull))) break;
                 if (SCALED && !(ok = DG_WARP_WAIT(smem_u32(&bars->kv_ready[stage]), phase, wc, kWaitSfReady))) break;
+                MQA_STAMP(0, acount - 1u);
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
+                MQA_STAMP(1, acount - 1u);
                 tc_fence_after();
                 const uint32_t kaddr = base + p.off_kv + stage * p.kv_stage_bytes;
                 const uint64_t kv_desc = make_smem_desc(kaddr, p.sbo, 0, p.layout);
@@ -266,9 +277,10 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t wg = et >> 7;                  // which share of the query block
         const uint32_t quarter = warp & 3u;           // TMEM lane quarter of this warp
         const uint32_t q_per_wg = p.block_q / p.ep_groups;
-        const uint32_t chunks_per_q = p.num_heads / 32u;
-        const uint32_t nchunks = q_per_wg * chunks_per_q;      // 32-column TMEM loads per kv block
-        const uint32_t col_base = wg * q_per_wg * p.num_heads;
+        const uint32_t units_per_q = p.num_heads / 16u;
+        const uint32_t nunits = q_per_wg * units_per_q;        // 16-column TMEM loads per kv block
+        const uint32_t q_first = wg * q_per_wg;
+        const uint32_t col_base = q_first * p.num_heads;
         uint32_t qcount = 0, acount = 0;
         bool ok = true;
         for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
@@ -287,6 +299,14 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 }
                 w[et] = 0.5f * v;      // see the epilogue loop: relu(x) * w = (x + |x|) * (w / 2)
             }
+            // the kv windows of the block's queries travel with the weights: the reduction loop reads
+            // them from shared memory instead of waiting on two global loads per query and kv block
+            uint32_t* win = win_smem + wb * 32u;
+            if (et < p.block_q) {
+                const uint32_t q = qb * p.block_q + et;
+                win[et] = q < p.num_tokens ? __ldg(p.ks + q) : 0u;
+                win[16u + et] = q < p.num_tokens ? min(__ldg(p.ke + q), p.num_kv) : 0u;
+            }
             // The two buffers alternate, and no warp can run more than one query block ahead of
             // the slowest one (it waits here), so a buffer is never rewritten while still read.
             __syncwarp();
@@ -296,45 +316,54 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
                 const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
                 ++acount;
+                if (warp == 4 || warp == 12) MQA_STAMP(2, acount - 1u);
                 ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull));
                 if (!ok) break;
+                if (warp == 4 || warp == 12) MQA_STAMP(3, acount - 1u);
                 tc_fence_after();
                 const uint32_t j = kb * kMqaBlockKv + quarter * 32u + lane;
                 float scale = 1.f;
                 if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
                 const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride + col_base;
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;    // four partial sums of the current query
+                uint32_t unit_in_q = 0, q_done = 0;              // position inside this warp's share of the query block
 
-                // One 32-column chunk: weighted ReLU into the accumulators; on a query's last
-                // chunk, scale and store its logit.  relu(x) * w is computed as (x + |x|) * (w / 2):
-                // the addition takes |x| as a source modifier and runs on the FMA pipe at full rate,
-                // where a max would go through the half-rate ALU pipe that bounds this loop; both
-                // scalings are by powers of two, so the result is the same bit for bit.  The weights
-                // in shared memory are already halved.
-                auto consume = [&](const uint32_t (&v)[32], uint32_t c) {
-                    const float4* w4 = reinterpret_cast<const float4*>(w + col_base + c * 32u);
+                // The reduction runs in units of 16 columns.  relu(x) * w is computed as
+                // (x + |x|) * (w / 2): the addition takes |x| as a source modifier and runs on the FMA
+                // pipe at full rate, where a max would go through the half-rate ALU pipe; both
+                // scalings are by powers of two, so the result is the same bit for bit (the weights in
+                // shared memory are already halved).  The TMEM load and the four weight vectors of
+                // unit u + 1 are requested before the arithmetic of unit u starts, so that neither the
+                // tensor-memory latency nor the shared-memory latency sits between dependent
+                // instructions; 16-column units keep both register sets inside the 102 registers a
+                // 640-thread block leaves per thread.
+                auto load_w = [&](float4 (&dst)[4], uint32_t u) {
+                    const float4* w4 = reinterpret_cast<const float4*>(w + col_base + u * 16u);
 #pragma unroll
-                    for (uint32_t i = 0; i < 8; ++i) {
-                        const float4 ww = w4[i];
+                    for (uint32_t i = 0; i < 4; ++i) dst[i] = w4[i];
+                };
+                auto consume = [&](const uint32_t (&v)[16], const float4 (&ww)[4]) {
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
                         const float x0 = __uint_as_float(v[4 * i]), x1 = __uint_as_float(v[4 * i + 1]);
                         const float x2 = __uint_as_float(v[4 * i + 2]), x3 = __uint_as_float(v[4 * i + 3]);
-                        a0 = fmaf(x0 + fabsf(x0), ww.x, a0);
-                        a1 = fmaf(x1 + fabsf(x1), ww.y, a1);
-                        a2 = fmaf(x2 + fabsf(x2), ww.z, a2);
-                        a3 = fmaf(x3 + fabsf(x3), ww.w, a3);
+                        a0 = fmaf(x0 + fabsf(x0), ww[i].x, a0);
+                        a1 = fmaf(x1 + fabsf(x1), ww[i].y, a1);
+                        a2 = fmaf(x2 + fabsf(x2), ww[i].z, a2);
+                        a3 = fmaf(x3 + fabsf(x3), ww[i].w, a3);
                     }
-                    if ((c + 1) % chunks_per_q == 0) {
-                        const uint32_t q = qb * p.block_q + wg * q_per_wg + c / chunks_per_q;
-                        if (q < p.num_tokens) {
-                            const uint32_t s = __ldg(p.ks + q), e = min(__ldg(p.ke + q), p.num_kv);
-                            if (j >= s && j < e) {
-                                const float val = ((a0 + a1) + (a2 + a3)) * scale;
-                                const size_t o = (size_t)q * p.logits_stride + (j - s);
-                                if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
-                                else reinterpret_cast<float*>(p.logits)[o] = val;
-                            }
+                    if (++unit_in_q == units_per_q) {
+                        const uint32_t qi = q_first + q_done;        // index inside the query block
+                        const uint32_t s = win[qi], e = win[16u + qi];   // e = 0 for queries past the end
+                        if (j >= s && j < e) {
+                            const float val = ((a0 + a1) + (a2 + a3)) * scale;
+                            const size_t o = (size_t)(qb * p.block_q + qi) * p.logits_stride + (j - s);
+                            if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
+                            else reinterpret_cast<float*>(p.logits)[o] = val;
                         }
                         a0 = a1 = a2 = a3 = 0.f;
+                        unit_in_q = 0;
+                        ++q_done;
                     }
                 };
                 auto release = [&]() {
@@ -343,21 +372,24 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
                 };
-                // Two register buffers: the load of chunk c+1 is in flight while chunk c is consumed.
-                uint32_t va[32], vb[32];
+                uint32_t va[16], vb[16];
+                float4 wa[4], wb4[4];
                 __syncwarp();
-                tmem_ld_x32(taddr, va);
+                tmem_ld_x16(taddr, va);
+                load_w(wa, 0);
                 tmem_ld_wait();
-                for (uint32_t c = 0; c < nchunks; c += 2) {
-                    if (c + 1 < nchunks) tmem_ld_x32(taddr + (c + 1) * 32u, vb); else release();
-                    consume(va, c);
-                    if (c + 1 < nchunks) {
+                if (warp == 4 || warp == 12) MQA_STAMP(4, acount - 1u);
+                for (uint32_t u = 0; u < nunits; u += 2) {
+                    if (u + 1 < nunits) { tmem_ld_x16(taddr + (u + 1) * 16u, vb); load_w(wb4, u + 1); } else release();
+                    consume(va, wa);
+                    if (u + 1 < nunits) {
                         tmem_ld_wait();
-                        if (c + 2 < nchunks) tmem_ld_x32(taddr + (c + 2) * 32u, va); else release();
-                        consume(vb, c + 1);
-                        if (c + 2 < nchunks) tmem_ld_wait();
+                        if (u + 2 < nunits) { tmem_ld_x16(taddr + (u + 2) * 16u, va); load_w(wa, u + 2); } else release();
+                        consume(vb, wb4);
+                        if (u + 2 < nunits) tmem_ld_wait();
                     }
                 }
+                if (warp == 4 || warp == 12) MQA_STAMP(5, acount - 1u);
             }
         }
     }
@@ -370,6 +402,13 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
 }
 
+#ifdef DG_MQA_TRACE
+}  // namespace dg
+extern "C" __attribute__((visibility("default"))) int dg_debug_mqa_trace(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, dg::g_mqa_trace, sizeof(dg::g_mqa_trace));
+}
+namespace dg {
+#endif
 // ============================================================================ host side
 static int32_t check_mqa_common(uint32_t num_tokens, uint32_t num_kv, uint32_t num_heads, uint32_t head_dim,
                                 uint32_t logits_stride, const void* ks, const void* ke, const void* w, const void* logits) {
