@@ -68,6 +68,7 @@ struct GemmParams {
     const uint64_t* d_row_ptr; // optional (contiguous, bf16): address of every A row's D row, this or a peer GPU's (0 = drop)
     const int32_t* m_blocks_dev;  // optional (contiguous, single CTA): device-side count of leading 128-row blocks to visit
     uint32_t* tile_counter;       // dynamic schedule: [0] next tile id, [1] CTAs that have finished; both zero at launch
+    uint32_t sched_runs;          // dynamic schedule: bands restart at every run of equal m_indices entries (0 = plain bands)
     uint32_t* status;
     uint32_t k_splits;          // dense GEMM with few tiles: K is cut into this many ranges (1 = off)
     uint32_t kb_per_split;      // k-blocks per range (a multiple of 4)
@@ -98,10 +99,11 @@ struct Tile {
 // fewer tiles instead of holding up the whole grid.
 constexpr uint32_t kSchedRing = 4;
 enum : uint32_t { kWaitSched = 8 };
+constexpr uint32_t kSchedMaxRuns = 255;   // runs of equal m_indices entries the scheduler warp keeps (u16 first blocks)
 struct SchedRing {
-    uint64_t full[kSchedRing];     // scheduler warp -> roles: tile id published
-    uint64_t empty[kSchedRing];    // roles -> scheduler warp: every role has read the id
-    uint32_t tile[kSchedRing];
+    uint64_t full[kSchedRing];     // scheduler warp -> roles: tile published
+    uint64_t empty[kSchedRing];    // roles -> scheduler warp: every role has read the tile
+    uint64_t tile[kSchedRing];     // (m block << 32) | n block; m block 0xffffffff = no more tiles
 };
 
 template <int GTYPE, int CL, bool SPLIT = false, bool DYN = false>
@@ -126,11 +128,22 @@ struct Scheduler {
         uint32_t id = next_id;
         next_id += stride;
         if (DYN) {
+            // the scheduler warp has already turned the claimed id into a tile (contiguous layout, one CTA)
             if (!DG_WARP_WAIT(smem_u32(&ring->full[slot]), ring_phase, *wc, kWaitSched)) return false;
-            id = *reinterpret_cast<volatile uint32_t*>(&ring->tile[slot]);
+            const uint64_t entry = *reinterpret_cast<volatile uint64_t*>(&ring->tile[slot]);
             __syncwarp();
             if ((threadIdx.x & 31u) == 0) mbar_arrive(smem_u32(&ring->empty[slot]));
             if (++slot == kSchedRing) { slot = 0; ring_phase ^= 1u; }
+            const uint32_t mb = (uint32_t)(entry >> 32), nb = (uint32_t)entry;
+            if (mb == 0xffffffffu) return false;
+            t.kb0 = 0; t.kb1 = p.num_k_blocks; t.split = 0;
+            t.a_row = mb * kBlockM;
+            t.row_end = p.m;
+            t.n0 = nb * p.block_n;
+            const int32_t e = __ldg(p.layout + mb);
+            t.skip = e < 0 || (uint32_t)e >= p.num_groups;
+            t.b_row = (t.skip ? 0u : (uint32_t)e * p.b_group_rows + p.b_row_offset) + t.n0;
+            return true;
         }
         t.skip = false;
         t.kb0 = 0; t.kb1 = p.num_k_blocks; t.split = 0;
@@ -527,18 +540,68 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     } else if (DYN && warp == 3) {
         // ===================================================== tile scheduler (dynamic schedule)
         const uint32_t m_blocks = p.m_blocks_dev ? min(p.num_m_blocks, (uint32_t)__ldg(p.m_blocks_dev)) : p.num_m_blocks;
-        const uint32_t total = m_blocks * p.num_n_blocks;
+        const uint32_t nn = p.num_n_blocks;
+        const uint32_t total = m_blocks * nn;
+        // Runs of equal m_indices entries (an expert's blocks; also runs of unused blocks, whose tiles
+        // the roles skip).  Bands of `band` row blocks, m fastest, never straddle a run: the tiles in
+        // flight then share the weight tiles of one or two experts, and an expert's weights are read
+        // from DRAM once instead of once per band they fall into.  More than kSchedMaxRuns runs (or
+        // more blocks than a u16 holds): plain bands over the whole layout.
+        uint16_t* run_block0 = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(bars) + kSmemBarrierBytes);
+        uint32_t n_runs = 0;
+        if (p.sched_runs && m_blocks <= 0xffffu) {
+            int32_t carry = -0x7fffffff;
+            bool fits = true;
+            for (uint32_t base = 0; base < m_blocks && fits; base += 32u) {
+                const uint32_t b = base + lane;
+                int32_t e = -0x7ffffffe;
+                if (b < m_blocks) {
+                    e = __ldg(p.layout + b);
+                    if (e < 0 || (uint32_t)e >= p.num_groups) e = -1;
+                }
+                int32_t e_prev = __shfl_up_sync(0xffffffffu, e, 1);
+                if (lane == 0) e_prev = carry;
+                const bool begins = b < m_blocks && e != e_prev;
+                const uint32_t mask = __ballot_sync(0xffffffffu, begins);
+                const uint32_t pos = n_runs + __popc(mask & ((1u << lane) - 1u));
+                fits = n_runs + __popc(mask) <= kSchedMaxRuns;
+                if (begins && fits) run_block0[pos] = (uint16_t)b;
+                n_runs += __popc(mask);
+                carry = __shfl_sync(0xffffffffu, e, 31);
+            }
+            if (!fits) n_runs = 0;
+            else if (lane == 0) run_block0[n_runs] = (uint16_t)m_blocks;
+            __syncwarp();
+        }
         uint32_t slot = 0, phase = 0;
         for (;;) {
             if (!DG_WARP_WAIT(smem_u32(&bars->sched.empty[slot]), phase ^ 1u, wc, kWaitSched)) break;
             uint32_t id = 0;
-            if (lane == 0) {
-                id = atomicAdd(p.tile_counter, 1u);
-                *reinterpret_cast<volatile uint32_t*>(&bars->sched.tile[slot]) = id;
-                mbar_arrive(smem_u32(&bars->sched.full[slot]));   // release: the id is visible to the waiters
-            }
+            if (lane == 0) id = atomicAdd(p.tile_counter, 1u);
             id = __shfl_sync(0xffffffffu, id, 0);
-            if (id >= total) break;                               // the roles read this id and stop as well
+            uint32_t mb = 0xffffffffu, nb = 0;
+            if (id < total) {
+                uint32_t b0 = 0, b1 = m_blocks;                   // the run (or the whole layout) the tile lies in
+                if (n_runs) {
+                    uint32_t lo = 0, hi = n_runs;                 // last run with run_block0[run] * nn <= id
+                    while (hi - lo > 1u) {
+                        const uint32_t mid = (lo + hi) >> 1;
+                        if ((uint32_t)run_block0[mid] * nn <= id) lo = mid; else hi = mid;
+                    }
+                    b0 = run_block0[lo];
+                    b1 = run_block0[lo + 1];
+                }
+                const uint32_t rem = id - b0 * nn, per_band = p.band * nn;
+                const uint32_t bi = rem / per_band, rem2 = rem - bi * per_band;
+                const uint32_t mb0 = b0 + bi * p.band, rows = min(p.band, b1 - mb0);
+                nb = rem2 / rows;
+                mb = mb0 + (rem2 - nb * rows);
+            }
+            if (lane == 0) {
+                *reinterpret_cast<volatile uint64_t*>(&bars->sched.tile[slot]) = ((uint64_t)mb << 32) | nb;
+                mbar_arrive(smem_u32(&bars->sched.full[slot]));   // release: the tile is visible to the waiters
+            }
+            if (id >= total) break;                               // the roles read the end marker and stop as well
             if (++slot == kSchedRing) { slot = 0; phase ^= 1u; }
         }
     } else if (warp >= 4) {
@@ -955,6 +1018,7 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     p.trace = g_trace;
     plan->dynamic = gtype == kContiguous && cl == 1 && p.k_splits == 1 && env_u32("DG_DYNAMIC", 1) != 0;
     p.tile_counter = nullptr;
+    p.sched_runs = env_u32("DG_SCHED_RUNS", 1);
     p.pf_chunk = env_u32("DG_PREFETCH", 0);
     if (p.pf_chunk > 16) p.pf_chunk = 16;
     if (env_u32("DG_PRINT_CONFIGS", 0))
