@@ -154,3 +154,61 @@ def test_route_reports_a_layout_overflow():
         poll_device_status()
     assert dest.cpu().tolist() == [0, 128, -1, -1]             # 128 + 384 rows fit into 512, the rest does not
     assert blocks.cpu().tolist() == [0, 1, 1, 1] and used.item() == 4
+
+
+@pytest.mark.parametrize("world,slices", [(2, 1), (3, 2), (4, 2), (8, 1)])
+def test_push_dispatch_with_emulated_ranks_equals_local_steps(world, slices):
+    """The whole push transport for `world` ranks played on one GPU: every rank has its own buffers
+    (plain device tensors standing in for the peer windows), the kernels of the ranks run one after
+    the other (none waits for another), and every rank's combined output must equal its single-rank
+    step with all experts resident, bit for bit.  Covers the slot arithmetic of dg_ep_route for any
+    rank count (rotated source order, padded expert bases, slices), dg_ep_push, the tickets and the
+    row-pointer GEMM."""
+    from deepgemm import Dtype, Operand, SfGran, SfTensor, moe, quant_mx, synth
+    L = _lib.load()
+    e_local, topk, T, K, N = 2, 2, 50, 512, 128
+    E = world * e_local
+    d0 = torch.device("cuda")
+    full = synth.random_expert_weights(E, N, K, seed=21, device=d0)
+    local_layer = moe.ExpertParallelMoE(full, E, None)
+    ranks = []
+    for r in range(world):
+        g = torch.Generator(device=d0).manual_seed(100 + r)
+        x8, x_sf = quant_mx(torch.randn((T, K), device=d0, generator=g), T, K, Dtype.Fp8, 128)
+        idx, tw = synth.random_topk_routing(T, E, topk, seed=200 + r, device=d0)
+        ranks.append(dict(x=x8, sf=x_sf, idx=idx, tw=tw, want=local_layer.forward(x8, x_sf, idx, tw),
+                          plan=moe.device_plan(idx, E, 1, div=topk, capacity=T * topk)))
+    n = T * topk
+    cap = (world * n + e_local * 127 + 127) // 128 * 128
+    sf_rows = ranks[0]["sf"].rows
+    i32, i64 = dict(dtype=torch.int32, device=d0), dict(dtype=torch.int64, device=d0)
+    for rk in ranks:
+        rk.update(a=torch.zeros((cap, K), dtype=torch.uint8, device=d0), asf=torch.zeros((sf_rows, cap), **i32),
+                  tickets=torch.zeros(cap, **i64), ret=torch.full((n, N), 7.0, dtype=torch.bfloat16, device=d0),
+                  dest=torch.empty(E, **i32), blocks=torch.empty((slices, cap // 128), **i32), used=torch.empty(slices, **i32),
+                  ptrs=torch.zeros(cap, **i64))
+    table = lambda key: torch.tensor([rk[key].data_ptr() for rk in ranks], **i64)
+    a_bases, sf_bases, ticket_bases, ret_bases = table("a"), table("asf"), table("tickets"), table("ret")
+    counts = torch.stack([rk["plan"].counts for rk in ranks]).contiguous()
+    for me, rk in enumerate(ranks):
+        assert L.dg_ep_route(counts.data_ptr(), world, me, E, 128, cap, slices, None, rk["dest"].data_ptr(), rk["blocks"].data_ptr(),
+                             rk["used"].data_ptr(), None) == 0
+    bounds = [e_local * s // slices for s in range(slices + 1)]
+    for s in range(slices):
+        for me, rk in enumerate(ranks):
+            assert L.dg_ep_push(rk["x"].data_ptr(), K, K, rk["sf"].buf.data_ptr(), sf_rows, rk["sf"].cols, rk["plan"].slot_src.data_ptr(),
+                                rk["plan"].offsets.data_ptr(), rk["dest"].data_ptr(), E, world, me, bounds[s], bounds[s + 1], n, cap,
+                                a_bases.data_ptr(), sf_bases.data_ptr(), ticket_bases.data_ptr(), 0 if s == 0 else 8, None) == 0
+        for d, rk in enumerate(ranks):
+            assert L.dg_ep_return_ptrs(rk["tickets"].data_ptr(), cap, ret_bases.data_ptr(), world, N * 2, rk["blocks"][s].data_ptr(), 128,
+                                       rk["ptrs"].data_ptr(), None) == 0
+            rows = slice(d * e_local * N, (d + 1) * e_local * N)
+            w_local = Operand.k_major(Dtype.Fp8, N, K, K, SfTensor(full.sf.rows, e_local * N, SfGran.G128, full.sf.buf[:, rows].contiguous()),
+                                      full.data[rows].contiguous())
+            a_op = Operand.k_major(Dtype.Fp8, cap, K, K, SfTensor(sf_rows, cap, SfGran.G128, rk["asf"]), rk["a"])
+            m_grouped_gemm_nt_contiguous_rowptr(a_op, w_local, rk["blocks"][s], e_local, rk["ptrs"], m_blocks_used=rk["used"][s:])
+    poll_device_status()
+    for r, rk in enumerate(ranks):
+        assert int(rk["tickets"].abs().sum().item()) == 0, "tickets must be cleared for the next step"
+        got = moe.combine(rk["ret"], rk["plan"].slot_of_row.view(T, topk), rk["tw"])
+        assert torch.equal(got, rk["want"]), f"rank {r} of {world}"
