@@ -252,7 +252,7 @@ class ExpertParallelMoE:
         if self.transport not in ("push", "peer", "nccl"):
             raise ValueError("transport must be 'push', 'peer' or 'nccl'")
         # one rank normally takes the local path below; True runs the chosen transport against itself
-        self.single_rank_transport = single_rank_transport
+        self.single_rank_transport = single_rank_transport or os.environ.get("DG_EP_SINGLE_RANK", "0") == "1"
         self.slice_weights = slice_weights     # push transport: proportions of the expert slices, e.g. (1, 3)
         self._win = None
         self._win_shape = None
