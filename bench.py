@@ -435,6 +435,23 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
                                                    "hbm_gbs": byts / ms / 1e6,
                                                    "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
 
+    # whole MoE feed-forward layer (gate/up GEMM -> SwiGLU + FP8 re-quantisation -> down GEMM -> combine),
+    # 256 experts, top-8, 16384 tokens, hidden 7168, intermediate 2048: the layer around the headline GEMM
+    if want("moe_ffn_layer_T16384_E256_top8_H7168_I2048"):
+        from deepgemm import moe
+        E, topk, T, H, I = 256, 8, 16384, 7168, 2048
+        w13 = synth.random_expert_weights(E, 2 * I, H, seed=11, device=dev)
+        w2 = synth.random_expert_weights(E, H, I, seed=12, device=dev)
+        x8, x_sf = synth.quantised_tokens(torch.randn((T, H), device=dev, generator=g))
+        idx, tw = synth.random_topk_routing(T, E, topk, seed=13, device=dev)
+        layer = moe.GroupedMoEFfn(w13, w2, E)
+        ms = timeit(lambda: layer.forward(x8, x_sf, idx, tw), iters=5, warm=2)
+        flops = 2.0 * T * topk * (2 * I * H + H * I)
+        res["moe_ffn_layer_T16384_E256_top8_H7168_I2048"] = {"ms": ms, "tflops": flops / ms / 1e9,
+                                                             "frac_of_measured_tensor_peak": flops / ms / 1e9 / (2 * peaks["bf16_tflops_sustained"])}
+        del layer, w13, w2
+        torch.cuda.empty_cache()
+
     # mqa_logits, fp32 contract
     if want("mqa_logits_T4096_S32768_H64_D128"):
         T, S, H, D = 4096, 32768, 64, 128

@@ -59,10 +59,15 @@ __device__ __forceinline__ float amax4(const float4& v) {
 // produces whole SF words: lane r keeps the word of row r and the warp stores 128 contiguous
 // bytes of the SF row.  G = 32: one float4 per lane covers the span (8 lanes per group);
 // G = 128: four float4 per lane, load j is group j.
-template <uint32_t G, bool FP4>
+// SWIGLU: the values to quantise are not read as f32 but formed on the fly from the BF16 output
+// [m, 2k] of an MoE gate/up projection (row pitch src_pitch elements): silu(gate) * up with gate =
+// columns [0, k), up = columns [k, 2k), f32 arithmetic on the bf16 values (the golden model's
+// convention, deepgemm/src/golden.rs:569-577, without clamp).
+template <uint32_t G, bool FP4, bool SWIGLU = false>
 __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__ x, uint32_t m, uint32_t k,
                                                       uint8_t* __restrict__ data, uint32_t* __restrict__ sf,
-                                                      uint32_t sf_cols, uint32_t num_spans, uint32_t num_row_blocks) {
+                                                      uint32_t sf_cols, uint32_t num_spans, uint32_t num_row_blocks,
+                                                      uint64_t src_pitch = 0) {
     constexpr uint32_t kLoads = G / 32;                   // float4 loads per lane per row
     constexpr uint32_t kRowsPerIter = G == 32 ? 8 : 2;    // rows in flight per warp
     const uint32_t lane = threadIdx.x & 31u;
@@ -86,8 +91,23 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
             for (uint32_t j = 0; j < kLoads; ++j) {
                 const uint32_t grp = G == 32 ? (lane >> 3) : j;
                 const bool ok = row < m && grp < groups_here;
-                v[i][j] = ok ? __ldcs(reinterpret_cast<const float4*>(x + (size_t)row * k + col0 + j * 128u + lane * 4u))
-                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (SWIGLU) {
+                    v[i][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (ok) {
+                        const uint16_t* src = reinterpret_cast<const uint16_t*>(x) + (size_t)row * src_pitch + col0 + j * 128u + lane * 4u;
+                        const uint2 gb = __ldcs(reinterpret_cast<const uint2*>(src));
+                        const uint2 ub = __ldcs(reinterpret_cast<const uint2*>(src + k));
+                        const float g[4] = {__uint_as_float(gb.x << 16), __uint_as_float(gb.x & 0xffff0000u),
+                                            __uint_as_float(gb.y << 16), __uint_as_float(gb.y & 0xffff0000u)};
+                        const float u[4] = {__uint_as_float(ub.x << 16), __uint_as_float(ub.x & 0xffff0000u),
+                                            __uint_as_float(ub.y << 16), __uint_as_float(ub.y & 0xffff0000u)};
+                        v[i][j] = make_float4(g[0] / (1.f + expf(-g[0])) * u[0], g[1] / (1.f + expf(-g[1])) * u[1],
+                                              g[2] / (1.f + expf(-g[2])) * u[2], g[3] / (1.f + expf(-g[3])) * u[3]);
+                    }
+                } else {
+                    v[i][j] = ok ? __ldcs(reinterpret_cast<const float4*>(x + (size_t)row * k + col0 + j * 128u + lane * 4u))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
             }
         }
 #pragma unroll
@@ -246,6 +266,33 @@ static int32_t launch_quant(const float* x, uint32_t m, uint32_t k, int32_t dtyp
 }  // namespace dg
 
 extern "C" {
+
+int32_t dg_swiglu_quant(const void* gate_up_bf16, uint64_t pitch, uint32_t m, uint32_t inter, uint32_t gran, void* data_out,
+                        uint32_t* sf_out, void* stream) {
+    if (!gate_up_bf16 || !data_out || !sf_out) return dg::fail(DG_ERR_INVALID_ARG, "swiglu_quant: null buffer");
+    if (gran != 32 && gran != 128) return dg::fail(DG_ERR_INVALID_ARG, "swiglu_quant: SF granularity must be 32 or 128");
+    if (m == 0 || inter == 0 || inter % gran != 0 || inter % 4 != 0)
+        return dg::fail(DG_ERR_INVALID_ARG, "swiglu_quant: the intermediate width (%u) must be a positive multiple of the granularity", inter);
+    if (pitch < 2ull * inter || pitch % 4 != 0 || (reinterpret_cast<uintptr_t>(gate_up_bf16) & 7u))
+        return dg::fail(DG_ERR_INVALID_ARG, "swiglu_quant: the row pitch must cover 2 x %u columns and keep rows 8-byte aligned", inter);
+    const dg::DeviceInfo* dev;
+    int32_t st = dg::current_device(&dev);
+    if (st != DG_OK) return st;
+    const uint32_t sf_cols = dg::align_up(m, 4);
+    const uint32_t num_spans = dg::ceil_div(inter / gran, 4);
+    const uint32_t num_row_blocks = dg::ceil_div(sf_cols, 32);
+    const uint32_t blocks = (uint32_t)(((uint64_t)num_spans * num_row_blocks + 7) / 8);
+    const float* src = static_cast<const float*>(gate_up_bf16);
+    uint8_t* d = static_cast<uint8_t*>(data_out);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (gran == 32)
+        dg::quant_mx_kernel<32, false, true><<<blocks, 256, 0, s>>>(src, m, inter, d, sf_out, sf_cols, num_spans, num_row_blocks, pitch);
+    else
+        dg::quant_mx_kernel<128, false, true><<<blocks, 256, 0, s>>>(src, m, inter, d, sf_out, sf_cols, num_spans, num_row_blocks, pitch);
+    dg::note_launch();
+    DG_CUDA_CHECK(cudaGetLastError());
+    return DG_OK;
+}
 
 int32_t dg_quant_mx(const float* x, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran, void* data_out,
                     uint32_t* sf_out, void* stream) {

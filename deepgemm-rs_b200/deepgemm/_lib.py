@@ -57,7 +57,7 @@ def load(build_if_missing=True):
         spec.loader.exec_module(mod)
         mod.build()
     L = C.CDLL(LIB_PATH)
-    vp, u32, i32 = C.c_void_p, C.c_uint32, C.c_int32
+    vp, u32, i32, u64 = C.c_void_p, C.c_uint32, C.c_int32, C.c_uint64
     opp, outp = C.POINTER(OperandC), C.POINTER(OutputC)
     L.dg_last_error.restype = C.c_char_p
     L.dg_version.restype = C.c_char_p
@@ -78,6 +78,7 @@ def load(build_if_missing=True):
     L.dg_quant_mx.argtypes = [vp, u32, u32, i32, u32, vp, vp, vp]
     L.dg_quant_mx_host.argtypes = [vp, u32, u32, i32, u32, vp, vp, vp]
     L.dg_quant_mx_host_static.argtypes = [vp, u32, u32, i32, u32, vp, vp, vp]
+    L.dg_swiglu_quant.argtypes = [vp, u64, u32, u32, u32, vp, vp, vp]
     L.dg_dequant_mx.argtypes = [vp, C.POINTER(SfTensorC), u32, u32, i32, vp, vp]
     L.dg_transform_sf.argtypes = [vp, u32, u32, vp, vp]
     L.dg_transform_sf_host.argtypes = [vp, u32, u32, vp, vp]
@@ -85,7 +86,6 @@ def load(build_if_missing=True):
         L.dg_mqa_logits_f32.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, vp, u32, vp]
     if hasattr(L, "dg_mqa_logits"):
         L.dg_mqa_logits.argtypes = [opp, opp, vp, vp, vp, u32, u32, u32, u32, vp, u32, vp]
-    u64 = C.c_uint64
     L.dg_gather_rows.argtypes = [vp, u64, vp, vp, u64, u32, u32, vp]
     L.dg_gather_sf.argtypes = [vp, u64, u64, vp, vp, u64, u64, u32, u32, vp]
     L.dg_moe_plan.argtypes = [vp, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, vp]

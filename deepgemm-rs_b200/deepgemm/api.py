@@ -179,6 +179,19 @@ def quant_mx(x, m, k, dtype, gran, stream=None):
     return data, SfTensor(rows, cols, gran, sf)
 
 
+def swiglu_quant(gate_up, m, inter, gran, stream=None):
+    """gate_up: bf16 device tensor [m, >= 2 * inter] (gate half, up half), the output of an MoE gate/up
+    projection.  Returns (E4M3 codes u8 [m, inter] of silu(gate) * up, their packed SfTensor): the A
+    operand of the down projection (the step deepgemm/src/api_serving.rs:371-375 leaves to the caller)."""
+    gran = SfGran(int(gran))
+    rows, cols = sf_shape(m, inter, gran)
+    data = torch.empty((m, inter), dtype=torch.uint8, device=gate_up.device)
+    sf = torch.empty((rows, cols), dtype=torch.int32, device=gate_up.device)
+    _check(_lib.load().dg_swiglu_quant(gate_up.data_ptr(), gate_up.stride(0), m, inter, int(gran), data.data_ptr(), sf.data_ptr(),
+                                       _stream_ptr(stream)))
+    return data, SfTensor(rows, cols, gran, sf)
+
+
 def dequant_mx(data, sf, m, k, dtype, stream=None):
     out = torch.empty((m, k), dtype=torch.float32, device=data.device)
     sc = _sf_c(sf)

@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 from . import _lib
 from .api import (_check, _stream_ptr, m_grouped_gemm_nt_contiguous, m_grouped_gemm_nt_contiguous_rowptr,
-                  m_grouped_gemm_nt_contiguous_scatter)
+                  m_grouped_gemm_nt_contiguous_scatter, swiglu_quant)
 from .types import Dtype, Operand, Output, SfGran, SfTensor
 
 BLOCK = 128  # rows per m_indices entry (heuristics::mk_alignment_for_contiguous_layout)
@@ -192,6 +192,40 @@ def combine(src, pos, weights, out=None):
                                       weights.data_ptr() if weights is not None else None, out.data_ptr(), out.stride(0),
                                       tokens, topk, src.shape[1], _stream_ptr(None)))
     return out
+
+
+class GroupedMoEFfn:
+    """A whole MoE feed-forward layer on one GPU: gate/up grouped GEMM -> SwiGLU + FP8 re-quantisation ->
+    down grouped GEMM -> top-k combine.  The reference's Serving::moe_grouped_layer
+    (deepgemm/src/api_serving.rs:293-377) stops after the first GEMM and leaves the rest to its caller.
+
+    w13: Operand of the stacked gate/up weights [E * 2 * inter, hidden] (per expert: `inter` gate rows,
+    then `inter` up rows), rows = 2 * inter.  w2: Operand of the stacked down weights
+    [E * hidden, inter], rows = hidden.  forward(x, x_sf, topk_idx, topk_w) -> bf16 [T, hidden]."""
+
+    def __init__(self, w13: Operand, w2: Operand, num_experts: int, gran: int = 128):
+        if w13.rows % 2 or w2.k != w13.rows // 2:
+            raise ValueError("w13 must hold 2 * inter rows per expert and w2 must contract over inter")
+        self.w13, self.w2, self.num_experts, self.gran = w13, w2, num_experts, gran
+        self.inter = w13.rows // 2
+
+    def forward(self, x, x_sf, topk_idx, topk_w=None):
+        tokens, topk = topk_idx.shape
+        hidden, out_dim = x.shape[1], self.w2.rows
+        p = device_plan(topk_idx, self.num_experts, BLOCK, div=topk)
+        a = gather_rows(x, p.slot_src)
+        a_sf = sf_permute(x_sf, p.slot_src)
+        gate_up = torch.empty((p.capacity, 2 * self.inter), dtype=torch.bfloat16, device=x.device)
+        m_grouped_gemm_nt_contiguous(Operand.k_major(self.w13.dtype, p.capacity, hidden, hidden, a_sf, a), self.w13,
+                                     Output(Dtype.Bf16, p.capacity, 2 * self.inter, 2 * self.inter, gate_up), p.block_expert,
+                                     self.num_experts)
+        # rows of unused blocks hold whatever the allocation held: they are quantised like the others
+        # and never read, because the second GEMM skips their blocks and the combine step their slots
+        h, h_sf = swiglu_quant(gate_up, p.capacity, self.inter, self.gran)
+        d = torch.empty((p.capacity, out_dim), dtype=torch.bfloat16, device=x.device)
+        m_grouped_gemm_nt_contiguous(Operand.k_major(Dtype.Fp8, p.capacity, self.inter, self.inter, h_sf, h), self.w2,
+                                     Output(Dtype.Bf16, p.capacity, out_dim, out_dim, d), p.block_expert, self.num_experts)
+        return combine(d, p.slot_of_row.view(tokens, topk), topk_w)
 
 
 def peer_step_tables(tot, me):

@@ -232,6 +232,15 @@ DG_API int32_t dg_moe_combine(const void* src_bf16, uint64_t src_pitch, const in
                               void* out_bf16, uint64_t out_pitch, uint32_t tokens, uint32_t topk, uint32_t cols,
                               void* stream);
 
+/* SwiGLU + re-quantisation between the two grouped GEMMs of an MoE layer, the step the reference's
+ * Serving::moe_grouped_layer leaves to its caller (deepgemm/src/api_serving.rs:371-375): gate_up is the
+ * BF16 output [m, 2 * inter] of the gate/up projection (pitch in elements; gate = columns [0, inter), up =
+ * columns [inter, 2 * inter)); writes E4M3 codes [m, inter] of silu(gate) * up and their packed UE8M0 scale
+ * factors [ceil(inter / (4 * gran)), align4(m)], ready to be the A operand of the down projection.
+ * Arithmetic as in the golden model's fused path (golden.rs:569-577): f32 on the bf16 values, no clamp. */
+DG_API int32_t dg_swiglu_quant(const void* gate_up_bf16, uint64_t pitch, uint32_t m, uint32_t inter, uint32_t gran,
+                               void* data_out, uint32_t* sf_out, void* stream);
+
 /* ---- expert parallelism over peer memory (extensions; the reference runs on one GPU and has no
  * counterpart for any entry of this block) ---------------------------------------------------
  * One process per GPU inside one NVLink/NVSwitch domain.  A rank allocates buffers that the other

@@ -377,3 +377,22 @@ void dgo_quant_fp8_block128_host(const float* x, uint32_t n, uint32_t k, uint8_t
         }
     }
 }
+
+/* SwiGLU between the two grouped GEMMs of an MoE layer, on the BF16 output [m, 2 * inter] of the
+ * gate/up projection (row pitch ld elements): gate = columns [0, inter), up = columns
+ * [inter, 2 * inter) ("the two halves", deepgemm/src/api_serving.rs:371-373).  As in the golden model of
+ * the fused path (golden.rs:569-577) both factors are the bf16-rounded GEMM outputs and the product
+ * silu(g) * u, silu(g) = g / (1 + exp(-g)), is formed in f32; there is no clamp and the routing weight is
+ * applied later, when the copies of a token are combined.  out: f32 [m, inter], the input of the
+ * re-quantisation (dgo_quant_mx_host). */
+void dgo_swiglu_f32(const uint16_t* inter_bf16, uint32_t m, uint32_t inter, uint32_t ld, float* out) {
+#pragma omp parallel for schedule(static)
+    for (uint32_t r = 0; r < m; ++r) {
+        const uint16_t* row = inter_bf16 + (size_t)r * ld;
+        for (uint32_t c = 0; c < inter; ++c) {
+            float g = u2f((uint32_t)row[c] << 16), u = u2f((uint32_t)row[inter + c] << 16);
+            float sig = g / (1.0f + expf(-g));
+            out[(size_t)r * inter + c] = sig * u;
+        }
+    }
+}

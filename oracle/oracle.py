@@ -60,6 +60,7 @@ def lib():
         L.dgo_gemm_ref_naive.argtypes = opnd + opnd + [u32, u32, u32, f32p]
         L.dgo_gemm_f32_ref.argtypes = [f32p, f32p, u32, u32, u32, f32p]
         L.dgo_mqa_logits_ref.argtypes = [f32p, f32p, f32p, u32, u32, u32, u32p, u32p, u32p, u32, f32p]
+        L.dgo_swiglu_f32.argtypes = [C.POINTER(C.c_uint16), u32, u32, u32, f32p]
         L.dgo_calc_diff.restype = C.c_double
         L.dgo_calc_diff.argtypes = [f32p, f32p, C.c_size_t]
         _lib = L
@@ -183,6 +184,15 @@ def mqa_logits_ref(q, kv, weights, k_start, k_end, tokens=None):
     out = np.zeros((nt, S), dtype=np.float32)
     lib().dgo_mqa_logits_ref(_p(q, C.c_float), _p(kv, C.c_float), _p(weights, C.c_float), H, D, S,
                              _p(ks, C.c_uint32), _p(ke, C.c_uint32), _p(t, C.c_uint32), nt, _p(out, C.c_float))
+    return out
+
+
+def swiglu_f32(inter_bf16_bits, inter):
+    """bf16 bits [m, 2 * inter] (gate half, up half) -> f32 [m, inter] = silu(gate) * up."""
+    a = _c(inter_bf16_bits, np.uint16)
+    m = a.shape[0]
+    out = np.zeros((m, inter), dtype=np.float32)
+    lib().dgo_swiglu_f32(_p(a, C.c_uint16), m, inter, a.shape[1], _p(out, C.c_float))
     return out
 
 
