@@ -307,9 +307,6 @@ int32_t dg_ep_route(const int32_t* counts, uint32_t world, uint32_t me, uint32_t
     if (world == 0 || me >= world || num_experts == 0 || num_experts > 1024 || num_experts % world != 0)
         return dg::fail(DG_ERR_INVALID_ARG, "ep_route: %u experts over %u ranks (at most 1024 experts, divisible by the ranks)", num_experts, world);
     if (align == 0 || cap % align != 0) return dg::fail(DG_ERR_INVALID_ARG, "ep_route: capacity must be a multiple of the alignment");
-    const dg::DeviceInfo* dev;
-    int32_t st = dg::current_device(&dev);
-    if (st != DG_OK) return st;
     const uint32_t e_local = num_experts / world;
     if (slices == 0 || slices > e_local || slices > dg::kMaxSlices)
         return dg::fail(DG_ERR_INVALID_ARG, "ep_route: %u slices for %u local experts (at most %u)", slices, e_local, dg::kMaxSlices);
@@ -322,6 +319,9 @@ int32_t dg_ep_route(const int32_t* counts, uint32_t world, uint32_t me, uint32_t
     }
     if (bounds.first[0] != 0 || bounds.first[slices] != e_local)
         return dg::fail(DG_ERR_INVALID_ARG, "ep_route: slice bounds must start at 0 and end at %u", e_local);
+    const dg::DeviceInfo* dev;
+    int32_t st = dg::current_device(&dev);
+    if (st != DG_OK) return st;
     dg::ep_route_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(counts, world, me, num_experts, e_local, align, cap,
                                                                            slices, bounds, dest_base, block_expert, blocks_used,
                                                                            dev->status);

@@ -100,3 +100,20 @@ def test_no_cpu_fallback(L):
     assert "SM100" in _err(L)
     assert L.dg_quant_mx(0x1000, 16, 256, 0, 32, 0x2000, 0x3000, None) == 4
     assert L.dg_transform_sf(0x1000, 4, 4, 0x2000, None) == 4
+
+
+def test_peer_and_ffn_entry_checks(L):
+    """The entries beyond the reference's API validate before they touch a device."""
+    assert L.dg_swiglu_quant(0x1000, 512, 8, 192, 128, 0x2000, 0x3000, None) == 3      # width % granularity
+    assert L.dg_swiglu_quant(0x1000, 512, 8, 512, 128, 0x2000, 0x3000, None) == 3      # pitch < 2 * inter
+    assert L.dg_swiglu_quant(0x1000, 512, 8, 256, 64, 0x2000, 0x3000, None) == 3       # granularity
+    assert L.dg_peer_barrier(0x1000, 0x2000, 2, 2, 1, None) == 3                       # rank outside the world
+    assert L.dg_peer_barrier(0x1000, 0x2000, 0, 65, 1, None) == 3                      # more than 64 ranks
+    assert L.dg_ep_route(0x1000, 3, 0, 8, 128, 1024, 1, None, 0x2000, 0x3000, 0x4000, None) == 3   # experts % ranks
+    assert L.dg_ep_route(0x1000, 2, 0, 8, 128, 1000, 1, None, 0x2000, 0x3000, 0x4000, None) == 3   # capacity % alignment
+    bounds = (C.c_uint32 * 3)(0, 3, 3)
+    assert L.dg_ep_route(0x1000, 2, 0, 8, 128, 1024, 2, bounds, 0x2000, 0x3000, 0x4000, None) == 3          # bounds must ascend to e_local
+    assert L.dg_moe_return_ptrs(0x1000, 4, 0x2000, 0x3000, 0x4000, 2, 100, 0x5000, None) == 3     # row bytes % 16
+    assert L.dg_peer_copy(None, 0x1000, 16, None) == 3
+    assert L.dg_peer_copy(0x1000, 0x2000, 0, None) == 0                                # empty copy is a no-op
+    assert L.dg_m_grouped_gemm_nt_contiguous_rowptr(None, None, 0x1000, 1, 1, 0x2000, None, 0, 0, None) == 3
