@@ -478,6 +478,15 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
         ms = timeit(lambda: dg.quant_mx(x, m, k, dt, gran))
         byts = 4 * m * k + (m * k if dt == Dtype.Fp8 else m * k // 2) + 4 * (-(-(k // gran) // 4)) * m
         res[f"quant_mx_{name}_{m}x{k}"] = {"ms": ms, "gbs": byts / ms / 1e6, "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
+    # SwiGLU + FP8 re-quantisation between the two GEMMs of the FFN layer (HBM-bound): 139264 rows
+    # (131072 copies + padding) x 2 * 2048 bf16 in, 2048 codes + scale factors out
+    if want("swiglu_quant_139264x2048"):
+        m, inter = 139264, 2048
+        gu = torch.randn((m, 2 * inter), device=dev, generator=g).to(torch.bfloat16)
+        ms = timeit(lambda: dg.swiglu_quant(gu, m, inter, 128))
+        byts = m * inter * 5 + m * (inter // 128)
+        res["swiglu_quant_139264x2048"] = {"ms": ms, "gbs": byts / ms / 1e6, "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
+        del gu
     dg.poll_device_status()
     return res
 

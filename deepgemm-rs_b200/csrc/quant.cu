@@ -60,8 +60,11 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
                                             __uint_as_float(gb.y << 16), __uint_as_float(gb.y & 0xffff0000u)};
                         const float u[4] = {__uint_as_float(ub.x << 16), __uint_as_float(ub.x & 0xffff0000u),
                                             __uint_as_float(ub.y << 16), __uint_as_float(ub.y & 0xffff0000u)};
-                        v[i][j] = make_float4(g[0] / (1.f + expf(-g[0])) * u[0], g[1] / (1.f + expf(-g[1])) * u[1],
-                                              g[2] / (1.f + expf(-g[2])) * u[2], g[3] / (1.f + expf(-g[3])) * u[3]);
+                        // fast exponential and division (a few ulp): the kernel would otherwise be bound by
+                        // their instruction count, not by memory; an element lands on the neighbouring E4M3
+                        // code only when it sits within ~1e-6 of a rounding boundary
+                        v[i][j] = make_float4(__fdividef(g[0], 1.f + __expf(-g[0])) * u[0], __fdividef(g[1], 1.f + __expf(-g[1])) * u[1],
+                                              __fdividef(g[2], 1.f + __expf(-g[2])) * u[2], __fdividef(g[3], 1.f + __expf(-g[3])) * u[3]);
                     }
                 } else {
                     v[i][j] = ok ? __ldcs(reinterpret_cast<const float4*>(x + (size_t)row * k + col0 + j * 128u + lane * 4u))
