@@ -42,7 +42,7 @@ constexpr uint32_t kMaxPairedBlocks = 4096;   // contiguous layout on CTA pairs:
 constexpr uint32_t kPairedListBytes = 17 * 1024;  // tile list + run list (u16 each), 1024-aligned
 
 enum Kind : int { kFp8 = 0, kFp4 = 1, kBf16 = 2 };
-enum GType : int { kNormal = 0, kContiguous = 1, kMasked = 2 };
+enum GType : int { kNormal = 0, kContiguous = 1, kMasked = 2, kBatched = 3 };
 
 struct GemmParams {
     uint32_t m;            // rows of A/D (normal, contiguous); rows per group (masked)
@@ -73,10 +73,19 @@ struct GemmParams {
     uint32_t k_splits;          // dense GEMM with few tiles: K is cut into this many ranges (1 = off)
     uint32_t kb_per_split;      // k-blocks per range (a multiple of 4)
     float* split_ws;            // f32 partial tiles [k_splits][m][n] when k_splits > 1
+    uint32_t* split_cnt;        // arrival counters [tiles][4] of the K ranges, zero between launches
+    float alpha;                // factor on the product before the output cast (1 = none)
+    uint32_t idesc;             // tcgen05 instruction descriptor
     uint32_t b_group_rows;      // rows of B per group (grouped GEMMs); >= n when only a column range is computed
     uint32_t b_row_offset;      // first B row inside every group
-    uint32_t pf_chunk;          // k-blocks per L2 prefetch of B (0 = off)
-    unsigned long long* trace;  // debug: per-k-block clock64 stamps of CTA 0's first tile (or null)
+    uint32_t sf_rows_a, sf_rows_b;  // batched: packed SF rows per batch
+    // MN-major operand views ([K, MN] buffers; the MNM instantiation only)
+    uint32_t a_mn, b_mn;        // 1 = the operand is MN-major
+    uint32_t a_boxes, b_boxes;  // TMA boxes (one 128-byte swizzle atom wide, BLOCK_K rows deep) per stage
+    uint32_t box_elems;         // MN elements per box (128 for FP8, 64 for BF16)
+    uint32_t box_bytes;         // bytes per box = distance between neighbouring atoms along MN (LBO)
+    uint32_t mn_kstep;          // descriptor advance (16-byte units) per MMA along K for an MN-major operand
+    uint32_t k_elems;           // K per batch in elements (first K row of batch b = b * k_elems)
 };
 
 struct Tile {
@@ -86,6 +95,9 @@ struct Tile {
     uint32_t b_row;     // first row in (stacked) B / SFB-column coordinates
     uint32_t kb0, kb1;  // k-block range of this work item
     uint32_t split;     // index of the K range (0 without split-K)
+    uint32_t tile;      // split-K: index of the output tile
+    uint32_t mn_a;      // batched: first row of the tile inside its batch (SFA column, MN coordinate of an MN-major A)
+    uint32_t batch;     // batched: index of the batch
     bool skip;
 };
 
@@ -98,8 +110,10 @@ struct Tile {
 // so that a CTA that is slowed down (an SM shared with another kernel, a slow tile) simply takes
 // fewer tiles instead of holding up the whole grid.
 constexpr uint32_t kSchedRing = 4;
+constexpr uint32_t kSplitHeaderBytes = 16384;   // split-K: 4 arrival counters per output tile in front of the partial tiles
 enum : uint32_t { kWaitSched = 8 };
-constexpr uint32_t kSchedMaxRuns = 255;   // runs of equal m_indices entries the scheduler warp keeps (u16 first blocks)
+constexpr uint32_t kSchedRunBytes = 4096; // dynamic schedule: room for the run list behind the barrier block
+constexpr uint32_t kSchedMaxRuns = kSchedRunBytes / 2 - 1;   // runs of equal m_indices entries the scheduler warp keeps (u16 first blocks + end)
 struct SchedRing {
     uint64_t full[kSchedRing];     // scheduler warp -> roles: tile published
     uint64_t empty[kSchedRing];    // roles -> scheduler warp: every role has read the tile
@@ -170,7 +184,7 @@ struct Scheduler {
             t.n0 = nb * p.block_n;
             t.b_row = (uint32_t)__ldg(p.layout + blk) * p.b_group_rows + p.b_row_offset + t.n0;
             return true;
-        } else if (GTYPE != kMasked) {
+        } else if (GTYPE != kMasked && GTYPE != kBatched) {
             uint32_t tile = id;
             // a layout sized for the worst case is mostly unused blocks: the device-side count ends the walk early
             const uint32_t m_blocks = (GTYPE == kContiguous && CL == 1 && p.m_blocks_dev)
@@ -179,6 +193,7 @@ struct Scheduler {
                 // work item = (tile, K range); ranges of one tile are neighbours in the order
                 if (id >= p.num_m_blocks * p.num_n_blocks * p.k_splits) return false;
                 tile = id / p.k_splits;
+                t.tile = tile;
                 t.split = id - tile * p.k_splits;
                 t.kb0 = t.split * p.kb_per_split;
                 t.kb1 = min(p.num_k_blocks, t.kb0 + p.kb_per_split);
@@ -199,6 +214,21 @@ struct Scheduler {
                 t.skip = e < 0 || (uint32_t)e >= p.num_groups;
                 t.b_row = (t.skip ? 0u : (uint32_t)e * p.b_group_rows + p.b_row_offset) + t.n0;
             }
+            return true;
+        } else if (GTYPE == kBatched) {
+            // every batch is a dense [m, n] problem of its own: A, B and D stacked along the rows, the
+            // packed scale factors stacked along their K rows (transform_sf_batched's arena)
+            const uint32_t mbs = (p.m + kTileM - 1) / kTileM;
+            const uint32_t per_batch = mbs * p.num_n_blocks;
+            if (id >= per_batch * p.num_groups) return false;
+            const uint32_t b = id / per_batch, rem = id - b * per_batch;
+            const uint32_t nb = rem / mbs, mb = rem - nb * mbs;
+            t.batch = b;
+            t.mn_a = mb * kTileM + rank * kBlockM;
+            t.a_row = b * p.m + t.mn_a;
+            t.row_end = b * p.m + p.m;
+            t.n0 = nb * p.block_n;
+            t.b_row = b * p.b_group_rows + p.b_row_offset + t.n0;
             return true;
         } else {
             while (g < p.num_groups) {
@@ -243,11 +273,10 @@ static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 // SPLIT (dense, single CTA only): a work item is a K range of a tile and the epilogue stores f32
 // partial tiles.  It is a separate instantiation because a k-loop that starts at a run-time
 // block measurably slows the common case (the k-block index feeds every role's bookkeeping).
-template <int KIND, int GTYPE, int CL, bool SPLIT, bool DYN>
+template <int KIND, int GTYPE, int CL, bool SPLIT, bool DYN, bool MNM = false>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-            const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
-            const __grid_constant__ CUtensorMap tm_bpf, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
     constexpr bool kHasSf = KIND != kBf16;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // Dynamic shared memory: [barriers (512 B, padded to 1024)] [stage 0] [stage 1] ...
@@ -258,7 +287,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     // [tile list, 16 KB] only for the contiguous layout on CTA pairs
     uint16_t* mtiles = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(bars) + 1024);
     uint16_t* run_first = mtiles + kMaxPairedBlocks;    // [kMaxPairedBlocks + 1], padded to 17 KB
-    const uint32_t stages_base = smem_base + 1024u + (kPairedContig ? kPairedListBytes : 0u);
+    // [run list, 4 KB] only for the dynamic schedule
+    const uint32_t stages_base = smem_base + 1024u + (kPairedContig ? kPairedListBytes : 0u) + (DYN ? kSchedRunBytes : 0u);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t rank = CL == 2 ? cluster_ctarank() : 0u;
@@ -296,6 +326,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         tmem_alloc<CL>(smem_u32(&bars->tmem_base), kTmemCols);
         tmem_relinquish<CL>();
     }
+    // Everything above touches no global data; from here on the kernel before this one in the
+    // stream must have finished (its outputs are this kernel's operands, layout and row tables).
+    griddep_wait();
+    griddep_launch_dependents();
     if (kPairedContig && warp == 3) {
         // Tile list of the contiguous layout: walk m_indices 32 blocks at a time.  Inside a run of
         // equal experts every second block starts a tile; it is a pair when the next block has
@@ -350,7 +384,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     const uint32_t n_runs = kPairedContig ? *reinterpret_cast<volatile uint32_t*>(&bars->n_runs) : 0u;
 
     auto stage_addr = [&](uint32_t s) { return stages_base + s * p.stage_bytes; };
-    const bool tracing = p.trace != nullptr && blockIdx.x == 0;
 
     if (warp == 0) {
         // ===================================================== TMA producer (warp-converged, one lane issues)
@@ -366,33 +399,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             for (uint32_t ki = 0; ki < kb_count; ++ki) {
                 const uint32_t kb = kb_first + ki;
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
-                if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[kb] = clock64();
                 const uint32_t sa = stage_addr(stage);
                 const bool ld_sfa = kHasSf && (kb % p.sfa_period == 0);
                 const bool ld_sfb = kHasSf && (kb % p.sfb_period == 0);
                 // Inner coordinate kx in elements: 128 bytes per k-block (128 FP8, 256 FP4 = 128 B, 64 BF16).
                 const int32_t kx = (int32_t)(kb * (KIND == kBf16 ? 64u : 128u));
                 if (elect_one()) {
-                    // Weights stream from HBM in 128-byte row pieces, one piece per k-block; asking
-                    // L2 for `pf_chunk` k-blocks of every row at once (two chunks ahead) turns that
-                    // into long contiguous DRAM reads.
-                    if (p.pf_chunk && kb % p.pf_chunk == 0) {
-                        const int32_t brow = (int32_t)(t.b_row + rank * b_rows_per_cta);
-                        if (kb == 0) {
-                            tma_prefetch_2d(&tm_bpf, 0, brow);
-                            if (p.pf_chunk < p.num_k_blocks) tma_prefetch_2d(&tm_bpf, (int32_t)(p.pf_chunk * 16u), brow);
-                        }
-                        if (kb + 2 * p.pf_chunk < p.num_k_blocks) tma_prefetch_2d(&tm_bpf, (int32_t)((kb + 2 * p.pf_chunk) * 16u), brow);
-                    }
                     // Scale factors go first and complete on this CTA's own barrier, so that their
                     // transposition overlaps the (much larger) A/B transfer.
                     if (ld_sfa || ld_sfb) {
                         const uint32_t sbar = smem_u32(&bars->sf_full[stage]);
                         mbar_arrive_expect_tx(sbar, (ld_sfa ? p.tx_sfa : 0u) + (ld_sfb ? p.tx_sfb : 0u));
-                        if (ld_sfa) tma_load_2d(&tm_sfa, sbar, sa + p.off_sfa, (int32_t)t.a_row, (int32_t)((kb / p.sfa_period) * p.sf_sub));
-                        if (ld_sfb) tma_load_2d(&tm_sfb, sbar, sa + p.off_sfb, (int32_t)t.b_row, (int32_t)((kb / p.sfb_period) * p.sf_sub));
+                        // batched: the SF rows of batch b start at b * (packed rows per batch), columns count inside the batch
+                        const uint32_t sfa_x = GTYPE == kBatched ? t.mn_a : t.a_row, sfb_x = GTYPE == kBatched ? t.n0 : t.b_row;
+                        const uint32_t sfa_y = (GTYPE == kBatched ? t.batch * p.sf_rows_a : 0u) + (kb / p.sfa_period) * p.sf_sub;
+                        const uint32_t sfb_y = (GTYPE == kBatched ? t.batch * p.sf_rows_b : 0u) + (kb / p.sfb_period) * p.sf_sub;
+                        if (ld_sfa) tma_load_2d(&tm_sfa, sbar, sa + p.off_sfa, (int32_t)sfa_x, (int32_t)sfa_y);
+                        if (ld_sfb) tma_load_2d(&tm_sfb, sbar, sa + p.off_sfb, (int32_t)sfb_x, (int32_t)sfb_y);
                     }
-                    if (CL == 1) {
+                    if (MNM) {
+                        // An MN-major operand is a [K, MN] buffer: a box is one swizzle atom (128 bytes of MN)
+                        // wide and BLOCK_K rows deep, neighbouring atoms along MN lie box_bytes apart.
+                        const uint32_t bar = smem_u32(&bars->full[stage]);
+                        mbar_arrive_expect_tx(bar, p.tx_ab);
+                        const int32_t ky = (int32_t)((GTYPE == kBatched ? t.batch * p.k_elems : 0u) + (uint32_t)kx);
+                        if (p.a_mn) {
+                            const uint32_t mn0 = GTYPE == kBatched ? t.mn_a : t.a_row;
+                            for (uint32_t i = 0; i < p.a_boxes; ++i)
+                                tma_load_2d(&tm_a, bar, sa + i * p.box_bytes, (int32_t)(mn0 + i * p.box_elems), ky);
+                        } else {
+                            tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
+                        }
+                        if (p.b_mn) {
+                            const uint32_t mn0 = GTYPE == kBatched ? t.n0 + p.b_row_offset : t.b_row;
+                            for (uint32_t i = 0; i < p.b_boxes; ++i)
+                                tma_load_2d(&tm_b, bar, sa + p.off_b + i * p.box_bytes, (int32_t)(mn0 + i * p.box_elems), ky);
+                        } else {
+                            tma_load_2d(&tm_b, bar, sa + p.off_b, kx, (int32_t)t.b_row);
+                        }
+                    } else if (CL == 1) {
                         const uint32_t bar = smem_u32(&bars->full[stage]);
                         mbar_arrive_expect_tx(bar, p.tx_ab);
                         tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
@@ -406,7 +451,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                 }
                 __syncwarp();
-                if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[256 + kb] = clock64();
                 if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -417,8 +461,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         Tile t;
         uint32_t stage = 0, phase = 0, tile_count = 0;
         uint32_t sf_bits = 0;  // per-stage parity of sf_ready (it completes only on SF k-blocks)
-        const uint32_t idesc = KIND == kBf16 ? make_idesc_bf16(kBlockM * CL, p.block_n)
-                                             : make_idesc_bs(KIND == kFp4 ? 1u : 0u, kBlockM * CL, p.block_n);
+        const uint32_t idesc = p.idesc;   // operand formats, tile shape and majors, built by the host
         bool ok = true;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
@@ -436,7 +479,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     sf_bits ^= 1u << stage;
                 }
                 tc_fence_after();
-                if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[512 + kb] = clock64();
                 const uint32_t sa = stage_addr(stage);
                 if (elect_one()) {
                     if (kHasSf) {
@@ -451,12 +493,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                                                              make_sf_desc(sa + p.off_sfb + (j * p.sfb_chunks + c) * 512u));
                         }
                     }
-                    const uint64_t a_desc = make_kmajor_sw128_desc(sa);
-                    const uint64_t b_desc = make_kmajor_sw128_desc(sa + p.off_b);
+                    // K-major tile: 8-row groups 1024 B apart.  MN-major tile: 8 K rows of an atom are 1024 B
+                    // apart (SBO), atoms along MN box_bytes apart (LBO).
+                    const uint64_t a_desc = (MNM && p.a_mn) ? make_smem_desc(sa, 1024, p.box_bytes, kLayoutSw128) : make_kmajor_sw128_desc(sa);
+                    const uint64_t b_desc = (MNM && p.b_mn) ? make_smem_desc(sa + p.off_b, 1024, p.box_bytes, kLayoutSw128)
+                                                            : make_kmajor_sw128_desc(sa + p.off_b);
+                    const uint32_t a_step = (MNM && p.a_mn) ? p.mn_kstep : 2u, b_step = (MNM && p.b_mn) ? p.mn_kstep : 2u;
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k) {
-                        // 32 bytes of K per MMA (32 FP8, 64 FP4, 16 BF16): +2 in the >>4 address field.
-                        const uint64_t ad = a_desc + 2u * k, bd = b_desc + 2u * k;
+                        // 32 bytes of K per MMA (32 FP8, 64 FP4, 16 BF16): +2 in the >>4 address field of a
+                        // K-major tile, that many whole K rows of 128 bytes in an MN-major one.
+                        const uint64_t ad = a_desc + a_step * k, bd = b_desc + b_step * k;
                         const uint32_t acc = (ki | k) != 0u ? 1u : 0u;
                         if (KIND == kBf16) {
                             tc_mma_bf16<CL>(d_tmem, ad, bd, idesc, acc);
@@ -482,7 +529,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                 }
                 __syncwarp();
-                if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[768 + kb] = clock64();
                 if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -504,7 +550,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     sf_bits ^= 1u << stage;
                     ok = DG_WARP_WAIT(smem_u32(&bars->sf_full[stage]), parity, wc, kWaitFull);
                     if (!ok) break;
-                    if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[1024 + kb] = clock64();
                     uint32_t* sfa = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfa - smem_u32(smem_raw)));
                     uint32_t* sfb = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfb - smem_u32(smem_raw)));
                     const uint32_t na = has_a ? p.sf_sub : 0u, nb = has_b ? p.sf_sub * p.sfb_chunks : 0u;
@@ -532,7 +577,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
                         else mbar_arrive_cluster(mapa(smem_u32(&bars->sf_ready[stage]), 0));
                     }
-                    if (tracing && kb < 256 && sched.first_tile_pending() && lane == 0) p.trace[1280 + kb] = clock64();
                 }
                 if (++stage == p.num_stages) stage = 0;
             }
@@ -547,7 +591,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         // flight then share the weight tiles of one or two experts, and an expert's weights are read
         // from DRAM once instead of once per band they fall into.  More than kSchedMaxRuns runs (or
         // more blocks than a u16 holds): plain bands over the whole layout.
-        uint16_t* run_block0 = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(bars) + kSmemBarrierBytes);
+        uint16_t* run_block0 = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(bars) + 1024);
         uint32_t n_runs = 0;
         if (p.sched_runs && m_blocks <= 0xffffu) {
             int32_t carry = -0x7fffffff;
@@ -666,14 +710,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     uint4 a[8];
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
-                        a[i] = make_uint4(pack_bf16x2(__uint_as_float(r0[8 * i]), __uint_as_float(r0[8 * i + 1])),
-                                          pack_bf16x2(__uint_as_float(r0[8 * i + 2]), __uint_as_float(r0[8 * i + 3])),
-                                          pack_bf16x2(__uint_as_float(r0[8 * i + 4]), __uint_as_float(r0[8 * i + 5])),
-                                          pack_bf16x2(__uint_as_float(r0[8 * i + 6]), __uint_as_float(r0[8 * i + 7])));
-                        a[4 + i] = make_uint4(pack_bf16x2(__uint_as_float(r1[8 * i]), __uint_as_float(r1[8 * i + 1])),
-                                              pack_bf16x2(__uint_as_float(r1[8 * i + 2]), __uint_as_float(r1[8 * i + 3])),
-                                              pack_bf16x2(__uint_as_float(r1[8 * i + 4]), __uint_as_float(r1[8 * i + 5])),
-                                              pack_bf16x2(__uint_as_float(r1[8 * i + 6]), __uint_as_float(r1[8 * i + 7])));
+                        const float al = p.alpha;
+                        a[i] = make_uint4(pack_bf16x2(__uint_as_float(r0[8 * i]) * al, __uint_as_float(r0[8 * i + 1]) * al),
+                                          pack_bf16x2(__uint_as_float(r0[8 * i + 2]) * al, __uint_as_float(r0[8 * i + 3]) * al),
+                                          pack_bf16x2(__uint_as_float(r0[8 * i + 4]) * al, __uint_as_float(r0[8 * i + 5]) * al),
+                                          pack_bf16x2(__uint_as_float(r0[8 * i + 6]) * al, __uint_as_float(r0[8 * i + 7]) * al));
+                        a[4 + i] = make_uint4(pack_bf16x2(__uint_as_float(r1[8 * i]) * al, __uint_as_float(r1[8 * i + 1]) * al),
+                                              pack_bf16x2(__uint_as_float(r1[8 * i + 2]) * al, __uint_as_float(r1[8 * i + 3]) * al),
+                                              pack_bf16x2(__uint_as_float(r1[8 * i + 4]) * al, __uint_as_float(r1[8 * i + 5]) * al),
+                                              pack_bf16x2(__uint_as_float(r1[8 * i + 6]) * al, __uint_as_float(r1[8 * i + 7]) * al));
                     }
                     if (two && col0 + 64u <= p.n) {
 #pragma unroll
@@ -735,44 +780,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 continue;
             }
-            for (uint32_t c = 0; c < chunks; ++c) {
-                uint32_t r[32];
-                __syncwarp();
-                tmem_ld_x32(taddr + c * 32u, r);
-                tmem_ld_wait();
-                if (c + 1 == chunks) {
-                    // accumulator drained into registers: hand the TMEM stage back to the MMA issuer
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
-                        else mbar_arrive_cluster(mapa(smem_u32(&bars->tmem_empty[as]), 0));
-                    }
-                }
-                const uint32_t col0 = t.n0 + c * 32u;
-                if (!row_ok || col0 >= p.n) continue;
-                if (SPLIT) {
-                    // partial sum of this K range; reduced in range order by split_reduce_kernel
-                    float* dst = p.split_ws + ((size_t)t.split * p.m + row) * p.n + col0;
-                    if (p.n % 4 == 0 && col0 + 32u <= p.n) {
-#pragma unroll
-                        for (uint32_t i = 0; i < 8; ++i)
-                            *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                                                                  __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-                    } else {
-#pragma unroll
-                        for (uint32_t i = 0; i < 32; ++i)
-                            if (col0 + i < p.n) dst[i] = __uint_as_float(r[i]);
-                    }
-                    continue;
-                }
+            // One row's 32 columns starting at col0, as f32 bit patterns, to the output: scaled by
+            // alpha, rounded to the output type, optionally added to what D holds.
+            auto store_chunk = [&](const uint32_t (&r)[32], uint32_t col0) {
                 if (p.out_f32) {
                     float* dst = reinterpret_cast<float*>(p.d) + (size_t)row * p.ldd + col0;
                     if (vec_ok && col0 + 32u <= p.n) {
 #pragma unroll
                         for (uint32_t i = 0; i < 8; ++i) {
-                            float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                                   __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                            float4 v = make_float4(__uint_as_float(r[4 * i]) * p.alpha, __uint_as_float(r[4 * i + 1]) * p.alpha,
+                                                   __uint_as_float(r[4 * i + 2]) * p.alpha, __uint_as_float(r[4 * i + 3]) * p.alpha);
                             if (p.accumulate) {
                                 const float4 o = *reinterpret_cast<const float4*>(dst + 4 * i);
                                 v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -782,7 +799,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else {
 #pragma unroll
                         for (uint32_t i = 0; i < 32; ++i)
-                            if (col0 + i < p.n) dst[i] = __uint_as_float(r[i]) + (p.accumulate ? dst[i] : 0.f);
+                            if (col0 + i < p.n) dst[i] = __uint_as_float(r[i]) * p.alpha + (p.accumulate ? dst[i] : 0.f);
                     }
                 } else {
                     __nv_bfloat16* dst = by_ptr ? reinterpret_cast<__nv_bfloat16*>(row_addr) + col0
@@ -793,7 +810,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             uint32_t w[4];
 #pragma unroll
                             for (uint32_t j = 0; j < 4; ++j)
-                                w[j] = pack_bf16x2(__uint_as_float(r[8 * i + 2 * j]), __uint_as_float(r[8 * i + 2 * j + 1]));
+                                w[j] = pack_bf16x2(__uint_as_float(r[8 * i + 2 * j]) * p.alpha, __uint_as_float(r[8 * i + 2 * j + 1]) * p.alpha);
                             if (p.accumulate) {
                                 // D += bf16(acc), the add itself rounded to bf16 (the reference
                                 // accumulates with a bf16 reduce-add, gemm_sm100.cu:309-315)
@@ -812,11 +829,86 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 #pragma unroll
                         for (uint32_t i = 0; i < 32; ++i) {
                             if (col0 + i < p.n) {
-                                __nv_bfloat16 v = __float2bfloat16_rn(__uint_as_float(r[i]));
+                                __nv_bfloat16 v = __float2bfloat16_rn(__uint_as_float(r[i]) * p.alpha);
                                 if (p.accumulate) v = __float2bfloat16_rn(__bfloat162float(dst[i]) + __bfloat162float(v));
                                 dst[i] = v;
                             }
                         }
+                    }
+                }
+            };
+            for (uint32_t c = 0; c < chunks; ++c) {
+                uint32_t r[32];
+                __syncwarp();
+                tmem_ld_x32(taddr + c * 32u, r);
+                tmem_ld_wait();
+                if (c + 1 == chunks) {
+                    // accumulator drained into registers: hand the TMEM stage back to the MMA issuer
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+                        else mbar_arrive_cluster(mapa(smem_u32(&bars->tmem_empty[as]), 0));
+                    }
+                }
+                const uint32_t col0 = t.n0 + c * 32u;
+                if (!row_ok || col0 >= p.n) continue;
+                if (SPLIT) {
+                    // partial sum of this K range
+                    float* dst = p.split_ws + ((size_t)t.split * p.m + row) * p.n + col0;
+                    if (p.n % 4 == 0 && col0 + 32u <= p.n) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i)
+                            *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                                                                  __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+                    } else {
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i)
+                            if (col0 + i < p.n) dst[i] = __uint_as_float(r[i]);
+                    }
+                    continue;
+                }
+                store_chunk(r, col0);
+            }
+            if (SPLIT) {
+                // The K ranges of a tile finish in any order.  Each warp counts the arrivals for its 32
+                // rows; the warp that arrives last adds the partial tiles in range order (always the
+                // same order, so results repeat bit for bit), rounds once and writes D.  The counter
+                // goes back to zero for the next launch.
+                __threadfence();
+                __syncwarp();
+                uint32_t* cnt = p.split_cnt + t.tile * 4u + q;
+                uint32_t arrived = 0;
+                if (lane == 0) arrived = atomicAdd(cnt, 1u);
+                arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                if (arrived + 1u == p.k_splits) {
+                    __threadfence();
+                    if (lane == 0) *cnt = 0u;
+                    for (uint32_t c = 0; c < chunks; ++c) {
+                        const uint32_t col0 = t.n0 + c * 32u;
+                        if (!row_ok || col0 >= p.n) continue;
+                        uint32_t r[32];
+                        float acc[32];
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) acc[i] = 0.f;
+                        const bool vec = p.n % 4 == 0 && col0 + 32u <= p.n;
+                        for (uint32_t sp = 0; sp < p.k_splits; ++sp) {
+                            const float* src = p.split_ws + ((size_t)sp * p.m + row) * p.n + col0;
+                            if (vec) {
+#pragma unroll
+                                for (uint32_t i = 0; i < 8; ++i) {
+                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src) + i);
+                                    acc[4 * i] += v.x; acc[4 * i + 1] += v.y; acc[4 * i + 2] += v.z; acc[4 * i + 3] += v.w;
+                                }
+                            } else {
+#pragma unroll
+                                for (uint32_t i = 0; i < 32; ++i)
+                                    if (col0 + i < p.n) acc[i] += __ldcg(src + i);
+                            }
+                        }
+#pragma unroll
+                        for (uint32_t i = 0; i < 32; ++i) r[i] = __float_as_uint(acc[i]);
+                        store_chunk(r, col0);
                     }
                 }
             }
@@ -842,26 +934,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
 }
 
-// D[r][c] (+)= sum over K ranges, added in range order (fixed, so results repeat bit for bit),
-// then rounded once to the output type.
-__global__ void __launch_bounds__(256) split_reduce_kernel(const float* __restrict__ ws, uint32_t splits, uint32_t m, uint32_t n,
-                                                          void* __restrict__ d, uint64_t ldd, uint32_t out_f32, uint32_t accumulate) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)m * n) return;
-    const uint32_t r = (uint32_t)(idx / n), c = (uint32_t)(idx % n);
-    float acc = 0.f;
-    for (uint32_t s = 0; s < splits; ++s) acc += ws[((size_t)s * m + r) * n + c];
-    if (out_f32) {
-        float* o = reinterpret_cast<float*>(d) + (size_t)r * ldd + c;
-        *o = accumulate ? *o + acc : acc;
-    } else {
-        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(d) + (size_t)r * ldd + c;
-        __nv_bfloat16 v = __float2bfloat16_rn(acc);
-        if (accumulate) v = __float2bfloat16_rn(__bfloat162float(*o) + __bfloat162float(v));
-        *o = v;
-    }
-}
-
 // ============================================================================ host side
 struct Plan {
     GemmParams p;
@@ -872,32 +944,18 @@ struct Plan {
     bool dynamic;       // tiles claimed from a global counter instead of strided (contiguous layout, single CTA)
 };
 
-// A pair of zeroed counters for one launch of the dynamic schedule.  Launches take the pairs of a
-// per-device pool in turn; a kernel leaves its pair zeroed, so a pair is reusable as soon as the
-// launch that used it has finished, and 256 pairs outlast any realistic number of GEMMs in flight.
-static int32_t tile_counters(const DeviceInfo* dev, cudaStream_t s, uint32_t** out) {
-    constexpr uint32_t kPairs = 256;
+// A pair of zeroed counters for one launch of the dynamic schedule.  Launches take the pairs of the
+// device's pool (allocated and cleared with the device entry, outside any stream) in turn; a kernel
+// leaves its pair zeroed, so a pair is reusable as soon as the launch that used it has finished, and
+// 256 pairs outlast any realistic number of GEMMs in flight.  A launch recorded into a CUDA graph
+// would keep its pair for the life of the graph and collide with later eager launches, so captured
+// launches use the static schedule instead (see run_gemm).
+static uint32_t* tile_counters(const DeviceInfo* dev) {
     static std::mutex mu;
-    static uint32_t* pools[64] = {nullptr};
     static uint32_t next[64] = {0};
     std::lock_guard<std::mutex> lock(mu);
-    const int d = dev->device & 63;
-    if (!pools[d]) {
-        uint32_t* pool = nullptr;
-        DG_CUDA_CHECK(cudaMalloc(&pool, kPairs * 2 * sizeof(uint32_t)));
-        DG_CUDA_CHECK(cudaMemsetAsync(pool, 0, kPairs * 2 * sizeof(uint32_t), s));
-        // other streams may use other pairs right away: wait for the clearing, unless `s` is being
-        // captured (then the clearing is ordered before this launch, the only user so far)
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        DG_CUDA_CHECK(cudaStreamIsCapturing(s, &cap));
-        if (cap == cudaStreamCaptureStatusNone) DG_CUDA_CHECK(cudaStreamSynchronize(s));
-        pools[d] = pool;
-    }
-    *out = pools[d] + 2u * (next[d]++ % kPairs);
-    return DG_OK;
+    return dev->tile_pool + 2u * (next[dev->device & 63]++ % kTilePoolPairs);
 }
-
-static unsigned long long* g_trace = nullptr;  // set by dg_debug_set_trace (development aid)
 
 static uint32_t env_u32(const char* name, uint32_t dflt) {
     const char* v = getenv(name);
@@ -908,13 +966,13 @@ static uint32_t env_u32(const char* name, uint32_t dflt) {
 // BF16, which needs no SF columns in TMEM), chosen to minimise waves x per-tile cost, where a
 // tile's cost is its MMA time (~BLOCK_N) plus a share of its operand traffic and a fixed part.
 // DG_BLOCK_N / DG_NUM_STAGES / DG_CLUSTER override (the reference's DG_* overrides: heuristics.rs:41-58).
-static uint32_t pick_block_n(int kind, uint32_t m_tiles_total, uint32_t n, uint32_t units) {
+static uint32_t pick_block_n(int kind, uint32_t m_tiles_total, uint32_t n, uint32_t units, uint32_t step = 32) {
     const uint32_t max_bn = kind == kBf16 ? 256u : 224u;
     const uint32_t forced = env_u32("DG_BLOCK_N", 0);
-    if (forced >= 32 && forced <= max_bn && forced % 32 == 0) return forced;
-    uint32_t best = 32;
+    if (forced >= step && forced <= max_bn && forced % step == 0) return forced;
+    uint32_t best = step;
     double best_cost = 1e30;
-    for (uint32_t bn = 32; bn <= max_bn; bn += 32) {
+    for (uint32_t bn = step; bn <= max_bn; bn += step) {
         const uint64_t tiles = (uint64_t)m_tiles_total * ceil_div(n, bn);
         const uint64_t waves = (tiles + units - 1) / units;
         const double per_tile = (double)bn + 0.25 * (128.0 + bn) + 24.0;
@@ -925,7 +983,8 @@ static uint32_t pick_block_n(int kind, uint32_t m_tiles_total, uint32_t n, uint3
 }
 
 static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k, uint32_t num_groups,
-                         uint32_t expected_m, uint32_t gran_a, uint32_t gran_b, const DeviceInfo* dev, Plan* plan) {
+                         uint32_t expected_m, uint32_t gran_a, uint32_t gran_b, const DeviceInfo* dev, Plan* plan,
+                         bool allow_dynamic = true, bool a_mn = false, bool b_mn = false) {
     GemmParams& p = plan->p;
     p = GemmParams{};
     const uint32_t sms = (uint32_t)dev->sm_count;
@@ -943,13 +1002,16 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     const uint32_t forced_cl = env_u32("DG_CLUSTER", 0);
     if (forced_cl == 1 || forced_cl == 2) cl = forced_cl;
     if (gtype == kContiguous && m / kBlockM > kMaxPairedBlocks) cl = 1;   // the in-kernel tile list is bounded
+    if (a_mn || b_mn) cl = 1;   // MN-major tiles are loaded atom by atom by one CTA
     plan->cluster = cl;
     const uint32_t tile_m = kBlockM * cl;
     const uint32_t units = sms / cl;
     uint32_t m_tiles_total;
     if (gtype == kMasked) m_tiles_total = num_groups * ceil_div(rows_per_group, tile_m);
+    else if (gtype == kBatched) m_tiles_total = num_groups * ceil_div(m, tile_m);
     else m_tiles_total = ceil_div(m, tile_m);
-    p.block_n = pick_block_n(kind, m_tiles_total, n, units);
+    // an MN-major B is loaded in whole swizzle atoms of 128 bytes along N: 128 columns of FP8, 64 of BF16
+    p.block_n = pick_block_n(kind, m_tiles_total, n, units, b_mn ? (kind == kBf16 ? 64u : 128u) : 32u);
     p.num_m_blocks = ceil_div(m, tile_m);
     p.num_n_blocks = ceil_div(n, p.block_n);
     // Split-K for weight-streaming shapes (a single row block, long K): with one tile per SM at
@@ -957,13 +1019,14 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     // otherwise idle SMs; partial tiles are summed in range order by a second kernel.
     p.k_splits = 1;
     p.kb_per_split = p.num_k_blocks;
-    if (gtype == kNormal && cl == 1 && m <= kBlockM && p.num_k_blocks >= 16 && env_u32("DG_SPLIT_K", 1)) {
+    if (gtype == kNormal && cl == 1 && !a_mn && !b_mn && m <= kBlockM && p.num_k_blocks >= 16 && env_u32("DG_SPLIT_K", 1)) {
         const uint32_t forced_bn = env_u32("DG_BLOCK_N", 0);
         uint32_t best_bn = p.block_n, best_splits = 1;
         double best_cost = 1e30;
         for (uint32_t bn = 64; bn <= 224; bn += 32) {
             if (forced_bn && bn != forced_bn) continue;
             const uint32_t tiles = ceil_div(n, bn);
+            if (tiles * 16u > kSplitHeaderBytes) continue;   // 4 counters of 4 bytes per tile
             for (uint32_t sp = 1; sp <= 16; ++sp) {
                 const uint32_t per = align_up(ceil_div(p.num_k_blocks, sp), 4);
                 if (ceil_div(p.num_k_blocks, per) != sp) continue;
@@ -974,7 +1037,7 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
             }
         }
         const uint32_t forced_sp = env_u32("DG_SPLIT_K", 1);
-        if (forced_sp > 1) best_splits = forced_sp;
+        if (forced_sp > 1 && ceil_div(n, best_bn) * 16u <= kSplitHeaderBytes) best_splits = forced_sp;
         p.block_n = best_bn;
         p.num_n_blocks = ceil_div(n, p.block_n);
         p.kb_per_split = align_up(ceil_div(p.num_k_blocks, best_splits), 4);
@@ -987,7 +1050,16 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     p.sfb_chunks = ceil_div(p.block_n, 128u);
     p.sfa_period = gran_a == 128 ? 4u : 1u;
     p.sfb_period = gran_b == 128 ? 4u : 1u;
-    const uint32_t a_bytes = kBlockM * 128u, b_bytes = p.block_n / cl * 128u;   // per CTA
+    // per CTA; a K-major tile holds its rows x 128 bytes of K, an MN-major one whole atoms of 128 bytes x BLOCK_K rows
+    const uint32_t block_k_rows = kind == kBf16 ? 64u : 128u;
+    p.a_mn = a_mn; p.b_mn = b_mn;
+    p.box_elems = kind == kBf16 ? 64u : 128u;
+    p.box_bytes = 128u * block_k_rows;
+    p.a_boxes = kBlockM / p.box_elems;
+    p.b_boxes = ceil_div(p.block_n, p.box_elems);
+    p.mn_kstep = (kind == kBf16 ? 16u : 32u) * 128u / 16u;
+    p.k_elems = k;
+    const uint32_t a_bytes = kBlockM * 128u, b_bytes = b_mn ? p.b_boxes * p.box_bytes : p.block_n / cl * 128u;
     const uint32_t sfa_bytes = has_sf ? p.sf_sub * 512u : 0u;
     const uint32_t sfb_bytes = has_sf ? p.sf_sub * p.sfb_chunks * 512u : 0u;
     p.off_b = a_bytes;
@@ -998,8 +1070,10 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     p.tx_sfa = sfa_bytes;
     p.tx_sfb = sfb_bytes;
     const uint32_t budget = (uint32_t)dev->smem_optin;
+    plan->dynamic = allow_dynamic && gtype == kContiguous && cl == 1 && p.k_splits == 1 && env_u32("DG_DYNAMIC", 1) != 0;
     const uint32_t fixed = 1024u /*alignment slack*/ + 1024u /*barriers*/ +
-                           ((gtype == kContiguous && cl == 2) ? kPairedListBytes : 0u) /*tile and run lists*/;
+                           ((gtype == kContiguous && cl == 2) ? kPairedListBytes : 0u) /*tile and run lists*/ +
+                           (plan->dynamic ? kSchedRunBytes : 0u) /*run list of the scheduler warp*/;
     uint32_t stages = (budget - fixed) / p.stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     const uint32_t forced = env_u32("DG_NUM_STAGES", 0);
@@ -1007,7 +1081,7 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     if (stages < 2) return fail(DG_ERR_RUNTIME, "shared memory budget %u B too small for a %u-wide tile", budget, p.block_n);
     p.num_stages = stages;
     plan->smem_bytes = fixed + stages * p.stage_bytes;
-    plan->num_tiles = gtype == kMasked ? m_tiles_total * p.num_n_blocks : p.num_m_blocks * p.num_n_blocks * p.k_splits;
+    plan->num_tiles = (gtype == kMasked || gtype == kBatched) ? m_tiles_total * p.num_n_blocks : p.num_m_blocks * p.num_n_blocks * p.k_splits;
     uint32_t clusters = units;
     uint32_t worst = gtype == kMasked ? num_groups * ceil_div(m, tile_m) * p.num_n_blocks : plan->num_tiles;
     if (gtype == kContiguous && cl == 2) worst = (m / kBlockM) * p.num_n_blocks;   // every block may be a tile of its own
@@ -1015,22 +1089,23 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     if (clusters == 0) clusters = 1;
     plan->grid = clusters * cl;
     p.status = dev->status;
-    p.trace = g_trace;
-    plan->dynamic = gtype == kContiguous && cl == 1 && p.k_splits == 1 && env_u32("DG_DYNAMIC", 1) != 0;
     p.tile_counter = nullptr;
     p.sched_runs = env_u32("DG_SCHED_RUNS", 1);
-    p.pf_chunk = env_u32("DG_PREFETCH", 0);
-    if (p.pf_chunk > 16) p.pf_chunk = 16;
     if (env_u32("DG_PRINT_CONFIGS", 0))
         fprintf(stderr, "[deepgemm_b200] kind=%d gtype=%d m=%u n=%u k=%u groups=%u -> tile %ux%ux%u cluster=%u stages=%u smem=%u grid=%u tiles=%u\n",
                 kind, gtype, m, n, k, num_groups, tile_m, p.block_n, block_k, cl, stages, plan->smem_bytes, plan->grid, plan->num_tiles);
     return DG_OK;
 }
 
-template <int KIND, int GTYPE, int CL, bool SPLIT = false, bool DYN = false>
+static bool pdl_enabled() {
+    static const bool on = env_u32("DG_PDL", 1) != 0;
+    return on;
+}
+
+template <int KIND, int GTYPE, int CL, bool SPLIT = false, bool DYN = false, bool MNM = false>
 static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
-                      const CUtensorMap& tsb, const CUtensorMap& tbpf, cudaStream_t s) {
-    auto* fn = gemm_kernel<KIND, GTYPE, CL, SPLIT, DYN>;
+                      const CUtensorMap& tsb, cudaStream_t s) {
+    auto* fn = gemm_kernel<KIND, GTYPE, CL, SPLIT, DYN, MNM>;
     static thread_local uint32_t configured[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1043,14 +1118,17 @@ static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = plan.smem_bytes;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CL;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    // programmatic dependent launch: the set-up of this kernel overlaps the tail of the one before it
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, ta, tb, tsa, tsb, tbpf, plan.p));
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, ta, tb, tsa, tsb, plan.p));
     note_launch();
     return DG_OK;
 }
@@ -1071,14 +1149,18 @@ static int32_t validate_operand(const dg_operand_t* op, const char* name) {
         default: return fail(DG_ERR_INVALID_ARG, "%s: operand dtype must be FP8, FP4 or BF16", name);
     }
     if (k == 0 || op->rows == 0) return fail(DG_ERR_INVALID_ARG, "%s: empty operand (%u x %u)", name, op->rows, k);
-    if (op->outer_stride < k) return fail(DG_ERR_INVALID_ARG, "%s: outer_stride (%u) smaller than K (%u)", name, op->outer_stride, k);
+    if (op->major != DG_MAJOR_K && op->major != DG_MAJOR_MN) return fail(DG_ERR_INVALID_ARG, "%s: major must be K or MN", name);
+    if (op->major == DG_MAJOR_K && op->outer_stride < k)
+        return fail(DG_ERR_INVALID_ARG, "%s: outer_stride (%u) smaller than K (%u)", name, op->outer_stride, k);
+    if (op->major == DG_MAJOR_MN && op->outer_stride < op->rows)
+        return fail(DG_ERR_INVALID_ARG, "%s: MN-major outer_stride (%u) smaller than its rows (%u)", name, op->outer_stride, op->rows);
     return DG_OK;
 }
 
 static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int gtype, const int32_t* layout,
                         uint32_t layout_len, uint32_t num_groups, uint32_t expected_m, int32_t accumulate, void* stream,
                         const int32_t* d_row_map = nullptr, uint32_t n_begin = 0, uint32_t n_count = 0,
-                        const uint64_t* d_row_ptr = nullptr, const int32_t* m_blocks_dev = nullptr) {
+                        const uint64_t* d_row_ptr = nullptr, const int32_t* m_blocks_dev = nullptr, float alpha = 1.f) {
     int32_t st;
     if ((st = validate_operand(a, "A")) != DG_OK) return st;
     if ((st = validate_operand(b, "B")) != DG_OK) return st;
@@ -1093,21 +1175,24 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     if (out->cols != n_count || (!d_row_map && !d_row_ptr && out->rows != a->rows)) return fail(DG_ERR_INVALID_ARG, "output shape mismatch");
     if (out->dtype != DG_BF16 && out->dtype != DG_F32) return fail(DG_ERR_INVALID_ARG, "output must be BF16 or FP32");
     if (out->stride < out->cols) return fail(DG_ERR_INVALID_ARG, "output stride (%u) smaller than its columns (%u)", out->stride, out->cols);
-    if (a->dtype != b->dtype)
-        return fail(DG_ERR_UNSUPPORTED, "mixed operand dtypes (%s x %s) are not built", dtype_name(a->dtype), dtype_name(b->dtype));
-    if (a->major != DG_MAJOR_K || b->major != DG_MAJOR_K) {
-        if (a->dtype == DG_FP4) return fail(DG_ERR_INVALID_ARG, "MXF4 MMA requires K-major operands");
-        return fail(DG_ERR_UNSUPPORTED, "MN-major operand views are not built; pass K-major A and B");
-    }
-    const int kind = a->dtype == DG_FP8 ? kFp8 : (a->dtype == DG_FP4 ? kFp4 : kBf16);
+    const bool a_mn = a->major == DG_MAJOR_MN, b_mn = b->major == DG_MAJOR_MN;
+    // FP8 x FP4 (either way round) runs as kind::mxf8f6f4 with the FP4 operand unpacked to one code per
+    // byte on its way into shared memory (deepgemm/src/api.rs:264-265); everything else needs equal dtypes.
+    const bool mixed = (a->dtype == DG_FP8 && b->dtype == DG_FP4) || (a->dtype == DG_FP4 && b->dtype == DG_FP8);
+    if (a->dtype != b->dtype && !mixed)
+        return fail(DG_ERR_INVALID_ARG, "operand dtypes %s x %s cannot be multiplied", dtype_name(a->dtype), dtype_name(b->dtype));
+    if ((a_mn && a->dtype == DG_FP4) || (b_mn && b->dtype == DG_FP4)) return fail(DG_ERR_INVALID_ARG, "FP4 operands must be K-major");
+    if ((a_mn || b_mn) && gtype != kNormal && gtype != kBatched)
+        return fail(DG_ERR_INVALID_ARG, "m-grouped GEMMs require K-major operands");
+    const int kind = mixed ? kFp8 : a->dtype == DG_FP8 ? kFp8 : (a->dtype == DG_FP4 ? kFp4 : kBf16);
     const bool has_sf = kind != kBf16;
     if (has_sf && (!a->sf.data || !b->sf.data)) return fail(DG_ERR_INVALID_ARG, "FP8/FP4 operands require scale factors");
-    const uint32_t groups_a = gtype == kMasked ? num_groups : 1u;
+    const uint32_t groups_a = (gtype == kMasked || gtype == kBatched) ? num_groups : 1u;
     const uint32_t groups_b = gtype == kNormal ? 1u : num_groups;
     if (gtype != kNormal) {
         if (num_groups == 0) return fail(DG_ERR_INVALID_ARG, "num_groups must be positive");
-        if (!layout) return fail(DG_ERR_INVALID_ARG, "grouped GEMM requires a layout buffer");
-        if (accumulate) return fail(DG_ERR_INVALID_ARG, "grouped GEMM does not accumulate");
+        if (!layout && gtype != kBatched) return fail(DG_ERR_INVALID_ARG, "grouped GEMM requires a layout buffer");
+        if (accumulate && gtype != kBatched) return fail(DG_ERR_INVALID_ARG, "grouped GEMM does not accumulate");
     }
     if (gtype == kContiguous) {
         if (a->rows % 128 != 0)
@@ -1124,14 +1209,18 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
         if ((gran_a != 32 && gran_a != 128) || (gran_b != 32 && gran_b != 128))
             return fail(DG_ERR_INVALID_ARG, "SF granularity must be 32 or 128");
         if (kind == kFp4 && (gran_a != 32 || gran_b != 32)) return fail(DG_ERR_INVALID_ARG, "FP4 requires SF granularity 32");
-        if (a->sf.rows < ceil_div(k, gran_a * 4) || a->sf.cols < align_up(groups_a * m, 4))
-            return fail(DG_ERR_INVALID_ARG, "A scale-factor tensor is %u x %u, need at least %u x %u", a->sf.rows, a->sf.cols,
-                        ceil_div(k, gran_a * 4), align_up(groups_a * m, 4));
-        if (b->sf.rows < ceil_div(k, gran_b * 4) || b->sf.cols < align_up(groups_b * n_full, 4))
-            return fail(DG_ERR_INVALID_ARG, "B scale-factor tensor is %u x %u, need at least %u x %u", b->sf.rows, b->sf.cols,
-                        ceil_div(k, gran_b * 4), align_up(groups_b * n_full, 4));
+        if (mixed && (a->dtype == DG_FP4 ? gran_a : gran_b) != 32) return fail(DG_ERR_INVALID_ARG, "FP4 requires SF granularity 32");
+        // grouped layouts stack the groups along the SF columns; batches stack along the packed K rows
+        const uint32_t sfr_a = (gtype == kBatched ? num_groups : 1u) * ceil_div(k, gran_a * 4);
+        const uint32_t sfr_b = (gtype == kBatched ? num_groups : 1u) * ceil_div(k, gran_b * 4);
+        const uint32_t sfc_a = align_up((gtype == kBatched ? 1u : groups_a) * m, 4);
+        const uint32_t sfc_b = align_up((gtype == kBatched ? 1u : groups_b) * n_full, 4);
+        if (a->sf.rows < sfr_a || a->sf.cols < sfc_a)
+            return fail(DG_ERR_INVALID_ARG, "A scale-factor tensor is %u x %u, need at least %u x %u", a->sf.rows, a->sf.cols, sfr_a, sfc_a);
+        if (b->sf.rows < sfr_b || b->sf.cols < sfc_b)
+            return fail(DG_ERR_INVALID_ARG, "B scale-factor tensor is %u x %u, need at least %u x %u", b->sf.rows, b->sf.cols, sfr_b, sfc_b);
         // TMA starts SF boxes at column group*rows + tile offset: keep that 16-byte aligned.
-        if (gtype != kNormal && n_full % 4 != 0) return fail(DG_ERR_INVALID_ARG, "grouped GEMM requires N (%u) %% 4 == 0", n_full);
+        if (gtype != kNormal && gtype != kBatched && n_full % 4 != 0) return fail(DG_ERR_INVALID_ARG, "grouped GEMM requires N (%u) %% 4 == 0", n_full);
         if (gtype == kMasked && m % 4 != 0) return fail(DG_ERR_INVALID_ARG, "masked GEMM requires per-group M (%u) %% 4 == 0", m);
     }
 
@@ -1139,8 +1228,12 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     // device gate follows (deepgemm/src/api.rs:168-173).
     const DeviceInfo* dev;
     if ((st = current_device(&dev)) != DG_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    DG_CUDA_CHECK(cudaStreamIsCapturing(s, &capturing));
     Plan plan;
-    if ((st = make_plan(kind, gtype, m, n, k, num_groups, expected_m, gran_a, gran_b, dev, &plan)) != DG_OK) return st;
+    if ((st = make_plan(kind, gtype, m, n, k, num_groups, expected_m, gran_a, gran_b, dev, &plan,
+                        capturing == cudaStreamCaptureStatusNone, a_mn, b_mn)) != DG_OK) return st;
     GemmParams& p = plan.p;
     p.out_f32 = out->dtype == DG_F32;
     p.accumulate = accumulate ? 1u : 0u;
@@ -1152,19 +1245,34 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     p.m_blocks_dev = m_blocks_dev;
     p.b_group_rows = n_full;
     p.b_row_offset = n_begin;
+    p.alpha = alpha;
+    p.sf_rows_a = has_sf ? ceil_div(k, gran_a * 4) : 0u;
+    p.sf_rows_b = has_sf ? ceil_div(k, gran_b * 4) : 0u;
+    // instruction descriptor: operand formats (mxf8f6f4: E4M3 = 0, E2M1 = 5; mxf4: E2M1 = 1), tile shape, majors
+    if (kind == kBf16) p.idesc = make_idesc_bf16(kBlockM * plan.cluster, p.block_n);
+    else if (kind == kFp4) p.idesc = make_idesc_bs(1u, 1u, kBlockM * plan.cluster, p.block_n);
+    else p.idesc = make_idesc_bs(a->dtype == DG_FP4 ? 5u : 0u, b->dtype == DG_FP4 ? 5u : 0u, kBlockM * plan.cluster, p.block_n);
+    p.idesc |= ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16);   // bits 15 / 16: A / B is MN-major
 
     CUtensorMap ta, tb, tsa, tsb;
     const uint32_t ebytes = kind == kBf16 ? 2u : 1u;
-    // FP4 rows are k/2 bytes and are moved as bytes (two codes per byte stay packed in shared memory).
-    const uint64_t inner = kind == kFp4 ? k / 2 : k;
-    const uint64_t pitch_a = kind == kFp4 ? a->outer_stride / 2 : (uint64_t)a->outer_stride * ebytes;
-    const uint64_t pitch_b = kind == kFp4 ? b->outer_stride / 2 : (uint64_t)b->outer_stride * ebytes;
-    const CUtensorMapDataType dt = kind == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-    const uint32_t box_inner = kind == kBf16 ? 64u : 128u;
-    if ((st = make_tmap_2d(&ta, dt, ebytes, a->data, inner, (uint64_t)groups_a * m, pitch_a, box_inner, kBlockM,
-                           CU_TENSOR_MAP_SWIZZLE_128B, "A")) != DG_OK) return st;
-    if ((st = make_tmap_2d(&tb, dt, ebytes, b->data, inner, (uint64_t)groups_b * n_full, pitch_b, box_inner, p.block_n / plan.cluster,
-                           CU_TENSOR_MAP_SWIZZLE_128B, "B")) != DG_OK) return st;
+    const uint32_t box_k = kind == kBf16 ? 64u : 128u;      // K elements (FP4 x FP4: bytes) per k-block
+    auto operand_map = [&](CUtensorMap* tm, const dg_operand_t* op, bool mn, uint32_t groups, uint32_t box_rows, const char* what) -> int32_t {
+        if (mn)   // [groups * K, MN] buffer: boxes of one swizzle atom along MN x BLOCK_K rows
+            return make_tmap_2d(tm, kind == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, ebytes, op->data,
+                                op->rows, (uint64_t)groups * k, (uint64_t)op->outer_stride * ebytes, p.box_elems, box_k,
+                                CU_TENSOR_MAP_SWIZZLE_128B, what);
+        if (kind == kFp4)   // FP4 x FP4: rows of k/2 bytes moved as bytes (two codes per byte stay packed in shared memory)
+            return make_tmap_2d(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, op->data, k / 2, (uint64_t)groups * op->rows, op->outer_stride / 2,
+                                128u, box_rows, CU_TENSOR_MAP_SWIZZLE_128B, what);
+        if (op->dtype == DG_FP4)   // FP4 against FP8: 16 codes are unpacked into 16 bytes of shared memory by the copy itself
+            return make_tmap_2d(tm, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 1, op->data, k, (uint64_t)groups * op->rows, op->outer_stride / 2,
+                                128u, box_rows, CU_TENSOR_MAP_SWIZZLE_128B, what);
+        return make_tmap_2d(tm, kind == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, ebytes, op->data, k,
+                            (uint64_t)groups * op->rows, (uint64_t)op->outer_stride * ebytes, box_k, box_rows, CU_TENSOR_MAP_SWIZZLE_128B, what);
+    };
+    if ((st = operand_map(&ta, a, a_mn, groups_a, kBlockM, "A")) != DG_OK) return st;
+    if ((st = operand_map(&tb, b, b_mn, groups_b, p.block_n / plan.cluster, "B")) != DG_OK) return st;
     if (has_sf) {
         if ((st = make_tmap_2d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a->sf.data, a->sf.cols, a->sf.rows,
                                (uint64_t)a->sf.cols * 4, 128u, p.sf_sub, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA")) != DG_OK) return st;
@@ -1173,76 +1281,71 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     } else {
         tsa = ta; tsb = tb;
     }
-    // Prefetch view of B: 8-byte elements, `pf_chunk` k-blocks (128 B each) x the CTA's rows per box.
-    CUtensorMap tbpf = tb;
-    if (p.pf_chunk) {
-        const uint64_t row_bytes = kind == kBf16 ? (uint64_t)k * 2 : inner;
-        if ((st = make_tmap_2d(&tbpf, CU_TENSOR_MAP_DATA_TYPE_INT64, 8, b->data, row_bytes / 8, (uint64_t)groups_b * n_full, pitch_b,
-                               p.pf_chunk * 16u, p.block_n / plan.cluster, CU_TENSOR_MAP_SWIZZLE_NONE, "B prefetch")) != DG_OK) return st;
-    }
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (p.k_splits > 1) {
-        // Scratch for the partial tiles: one buffer per (thread, device, stream), grown on demand with
-        // stream-ordered allocation and kept for the next call (work on one stream is ordered, so
-        // consecutive calls may share it; allocating per call costs more host time than the GEMM).
-        struct SplitWs { cudaStream_t stream; int device; float* ptr; size_t bytes; };
+        // Scratch for the partial tiles, behind a header of arrival counters (zero between launches:
+        // cleared when the buffer is allocated, put back to zero by the kernel).  One buffer per
+        // (thread, device, stream), grown on demand with stream-ordered allocation and kept for the
+        // next call (work on one stream is ordered, so consecutive calls may share it; allocating per
+        // call costs more host time than the GEMM).
+        struct SplitWs { cudaStream_t stream; int device; uint8_t* ptr; size_t bytes; };
         static thread_local SplitWs cache[8] = {};
         static thread_local int cache_next = 0;
-        const size_t need = sizeof(float) * (size_t)p.k_splits * m * n;
-        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
-        cudaStreamIsCapturing(s, &capturing);
-        float* graph_ws = nullptr;
-        SplitWs* slot = nullptr;
+        const size_t need = kSplitHeaderBytes + sizeof(float) * (size_t)p.k_splits * m * n;
+        uint8_t* graph_ws = nullptr;
+        uint8_t* ws = nullptr;
         if (capturing != cudaStreamCaptureStatusNone) {
-            // inside a graph capture the buffer must belong to the graph: allocate and free per call
+            // inside a graph capture the buffer must belong to the graph: allocate, clear and free per call
             DG_CUDA_CHECK(cudaMallocAsync(&graph_ws, need, s));
-            p.split_ws = graph_ws;
+            DG_CUDA_CHECK(cudaMemsetAsync(graph_ws, 0, kSplitHeaderBytes, s));
+            ws = graph_ws;
         } else {
-        for (auto& c : cache)
-            if (c.ptr && c.stream == s && c.device == dev->device) { slot = &c; break; }
-        if (!slot) {
-            slot = &cache[cache_next];
-            cache_next = (cache_next + 1) % 8;
-            if (slot->ptr) { cudaFreeAsync(slot->ptr, slot->stream); *slot = SplitWs{}; }
+            SplitWs* slot = nullptr;
+            for (auto& c : cache)
+                if (c.ptr && c.stream == s && c.device == dev->device) { slot = &c; break; }
+            if (!slot) {
+                slot = &cache[cache_next];
+                cache_next = (cache_next + 1) % 8;
+                if (slot->ptr) { cudaFreeAsync(slot->ptr, slot->stream); *slot = SplitWs{}; }
+            }
+            if (slot->bytes < need) {
+                if (slot->ptr) cudaFreeAsync(slot->ptr, s);
+                *slot = SplitWs{};
+                uint8_t* fresh = nullptr;
+                DG_CUDA_CHECK(cudaMallocAsync(&fresh, need, s));
+                DG_CUDA_CHECK(cudaMemsetAsync(fresh, 0, kSplitHeaderBytes, s));
+                *slot = SplitWs{s, dev->device, fresh, need};
+            }
+            ws = slot->ptr;
         }
-        if (slot->bytes < need) {
-            if (slot->ptr) cudaFreeAsync(slot->ptr, s);
-            *slot = SplitWs{};
-            float* fresh = nullptr;
-            DG_CUDA_CHECK(cudaMallocAsync(&fresh, need, s));
-            *slot = SplitWs{s, dev->device, fresh, need};
-        }
-        p.split_ws = slot->ptr;
-        }
+        p.split_cnt = reinterpret_cast<uint32_t*>(ws);
+        p.split_ws = reinterpret_cast<float*>(ws + kSplitHeaderBytes);
         int32_t lst = DG_OK;
-        if (kind == kFp8) lst = launch<kFp8, kNormal, 1, true>(plan, ta, tb, tsa, tsb, tbpf, s);
-        else if (kind == kFp4) lst = launch<kFp4, kNormal, 1, true>(plan, ta, tb, tsa, tsb, tbpf, s);
-        else lst = launch<kBf16, kNormal, 1, true>(plan, ta, tb, tsa, tsb, tbpf, s);
-        if (lst == DG_OK) {
-            const size_t total = (size_t)m * n;
-            split_reduce_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, s>>>(p.split_ws, p.k_splits, m, n, out->data, out->stride,
-                                                                                 p.out_f32, p.accumulate);
-            note_launch();
-        }
+        if (kind == kFp8) lst = launch<kFp8, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
+        else if (kind == kFp4) lst = launch<kFp4, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
+        else lst = launch<kBf16, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
         if (graph_ws) cudaFreeAsync(graph_ws, s);
-        if (lst != DG_OK) return lst;
-        DG_CUDA_CHECK(cudaGetLastError());
-        return DG_OK;
+        return lst;
     }
     if (plan.dynamic) {
-        if ((st = tile_counters(dev, s, &p.tile_counter)) != DG_OK) return st;
-        if (kind == kFp8) return launch<kFp8, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, tbpf, s);
-        if (kind == kFp4) return launch<kFp4, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, tbpf, s);
-        return launch<kBf16, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, tbpf, s);
+        p.tile_counter = tile_counters(dev);
+        if (kind == kFp8) return launch<kFp8, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, s);
+        if (kind == kFp4) return launch<kFp4, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, s);
+        return launch<kBf16, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, s);
     }
-#define DG_DISPATCH(K, G)                                                                  \
-    if (kind == K && gtype == G) {                                                         \
-        if (plan.cluster == 2) return launch<K, G, 2>(plan, ta, tb, tsa, tsb, tbpf, s);    \
-        return launch<K, G, 1>(plan, ta, tb, tsa, tsb, tbpf, s);                           \
+    if (a_mn || b_mn) {
+        if (kind == kFp8 && gtype == kNormal) return launch<kFp8, kNormal, 1, false, false, true>(plan, ta, tb, tsa, tsb, s);
+        if (kind == kFp8 && gtype == kBatched) return launch<kFp8, kBatched, 1, false, false, true>(plan, ta, tb, tsa, tsb, s);
+        if (kind == kBf16 && gtype == kNormal) return launch<kBf16, kNormal, 1, false, false, true>(plan, ta, tb, tsa, tsb, s);
+        if (kind == kBf16 && gtype == kBatched) return launch<kBf16, kBatched, 1, false, false, true>(plan, ta, tb, tsa, tsb, s);
     }
-    DG_DISPATCH(kFp8, kNormal) DG_DISPATCH(kFp8, kContiguous) DG_DISPATCH(kFp8, kMasked)
-    DG_DISPATCH(kFp4, kNormal) DG_DISPATCH(kFp4, kContiguous) DG_DISPATCH(kFp4, kMasked)
-    DG_DISPATCH(kBf16, kNormal) DG_DISPATCH(kBf16, kContiguous) DG_DISPATCH(kBf16, kMasked)
+#define DG_DISPATCH(K, G)                                                            \
+    if (kind == K && gtype == G) {                                                   \
+        if (plan.cluster == 2) return launch<K, G, 2>(plan, ta, tb, tsa, tsb, s);    \
+        return launch<K, G, 1>(plan, ta, tb, tsa, tsb, s);                           \
+    }
+    DG_DISPATCH(kFp8, kNormal) DG_DISPATCH(kFp8, kContiguous) DG_DISPATCH(kFp8, kMasked) DG_DISPATCH(kFp8, kBatched)
+    DG_DISPATCH(kFp4, kNormal) DG_DISPATCH(kFp4, kContiguous) DG_DISPATCH(kFp4, kMasked) DG_DISPATCH(kFp4, kBatched)
+    DG_DISPATCH(kBf16, kNormal) DG_DISPATCH(kBf16, kContiguous) DG_DISPATCH(kBf16, kMasked) DG_DISPATCH(kBf16, kBatched)
 #undef DG_DISPATCH
     return fail(DG_ERR_RUNTIME, "no kernel for kind %d / type %d", kind, gtype);
 }
@@ -1253,6 +1356,44 @@ extern "C" {
 
 int32_t dg_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream) {
     return dg::run_gemm(a, b, out, dg::kNormal, nullptr, 0, 1, a ? a->rows : 0, accumulate, stream);
+}
+// api::gemm_nt_alpha (deepgemm/src/api.rs:663-673): D = alpha * (A . B^T) (+ D); alpha multiplies the f32
+// accumulator before the output cast, the accumulated D is not scaled.
+int32_t dg_gemm_nt_alpha(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, float alpha, void* stream) {
+    return dg::run_gemm(a, b, out, dg::kNormal, nullptr, 0, 1, a ? a->rows : 0, accumulate, stream, nullptr, 0, 0, nullptr, nullptr, alpha);
+}
+// api::gemm_nn / gemm_tn / gemm_tt (deepgemm/src/api.rs:717-759): the BLAS layouts are the NT GEMM over
+// operands described as MN-major views; the entries only check that the view has the orientation the
+// layout needs, so that a mis-described operand fails here instead of computing wrong numbers.
+static int32_t want_major(const dg_operand_t* op, int32_t major, const char* fn, const char* name) {
+    if (!op) return dg::fail(DG_ERR_INVALID_ARG, "%s: null operand", fn);
+    if (op->major != major)
+        return dg::fail(DG_ERR_INVALID_ARG, "%s: %s must be described as %s", fn, name,
+                        major == DG_MAJOR_MN ? "an MN-major view ([K, MN] buffer, outer_stride = pitch of the K slices)" : "a K-major operand");
+    return DG_OK;
+}
+int32_t dg_gemm_nn(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream) {
+    int32_t st = want_major(b, DG_MAJOR_MN, "gemm_nn", "B");
+    return st != DG_OK ? st : dg_gemm_nt(a, b, out, accumulate, stream);
+}
+int32_t dg_gemm_tn(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream) {
+    int32_t st = want_major(a, DG_MAJOR_MN, "gemm_tn", "A");
+    return st != DG_OK ? st : dg_gemm_nt(a, b, out, accumulate, stream);
+}
+int32_t dg_gemm_tt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream) {
+    int32_t st = want_major(a, DG_MAJOR_MN, "gemm_tt", "A");
+    if (st == DG_OK) st = want_major(b, DG_MAJOR_MN, "gemm_tt", "B");
+    return st != DG_OK ? st : dg_gemm_nt(a, b, out, accumulate, stream);
+}
+// api::fp8_bmm (deepgemm/src/api.rs:966-993): `batch` independent GEMMs, A [batch * M, K], B [batch * N, K]
+// and D [batch * M, N] stacked along the rows, scale factors in transform_sf_batched's arena.
+int32_t dg_bmm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, uint32_t batch, int32_t accumulate, void* stream) {
+    return dg::run_gemm(a, b, out, dg::kBatched, nullptr, 0, batch, a ? a->rows : 0, accumulate, stream);
+}
+static int32_t typed(const dg_operand_t* a, const dg_operand_t* b, int32_t want, const char* fn);
+int32_t dg_fp8_bmm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, uint32_t batch, int32_t accumulate, void* stream) {
+    int32_t st = typed(a, b, DG_FP8, "fp8_bmm");
+    return st != DG_OK ? st : dg_bmm(a, b, out, batch, accumulate, stream);
 }
 static int32_t typed(const dg_operand_t* a, const dg_operand_t* b, int32_t want, const char* fn) {
     if (!a || !b) return dg::fail(DG_ERR_INVALID_ARG, "%s: null operand", fn);
@@ -1320,11 +1461,6 @@ DG_TYPED_GROUPED(fp8, DG_FP8)
 DG_TYPED_GROUPED(fp4, DG_FP4)
 DG_TYPED_GROUPED(bf16, DG_BF16)
 #undef DG_TYPED_GROUPED
-
-// Development aid, not part of the public header: a device buffer of 2048 u64 that receives
-// clock64 stamps of CTA 0's first tile (producer: stage free / loads issued; MMA issuer:
-// stage full / MMAs issued), or NULL to switch tracing off.
-__attribute__((visibility("default"))) void dg_debug_set_trace(void* buf) { dg::g_trace = static_cast<unsigned long long*>(buf); }
 
 int32_t dg_get_gemm_config(int32_t dtype, int32_t kind, uint32_t m, uint32_t n, uint32_t k, uint32_t num_groups,
                            dg_gemm_config_t* cfg) {

@@ -44,8 +44,12 @@ int32_t current_device(const DeviceInfo** out) {
         d.cc_major = p.major;
         d.cc_minor = p.minor;
         d.smem_optin = (int)p.sharedMemPerBlockOptin;
-        DG_CUDA_CHECK(cudaMalloc(&d.status, 256));
-        DG_CUDA_CHECK(cudaMemset(d.status, 0, 256));
+        // status word (first 256 bytes) and the tile-counter pool behind it, cleared before any stream uses them
+        const size_t bytes = 256 + kTilePoolPairs * 2 * sizeof(uint32_t);
+        DG_CUDA_CHECK(cudaMalloc(&d.status, bytes));
+        DG_CUDA_CHECK(cudaMemset(d.status, 0, bytes));
+        DG_CUDA_CHECK(cudaDeviceSynchronize());
+        d.tile_pool = d.status + 64;
         d.device = dev;
     }
     *out = &d;

@@ -25,7 +25,9 @@ struct DeviceInfo {
     int cc_major = 0, cc_minor = 0;
     int smem_optin = 0;
     uint32_t* status = nullptr;  // one zero-initialised word in global memory
+    uint32_t* tile_pool = nullptr;  // kTilePoolPairs zeroed counter pairs for dynamically scheduled GEMMs
 };
+constexpr uint32_t kTilePoolPairs = 256;
 
 // Information about the current device (cached per device).  Returns a status; on success
 // `*out` points at the cached entry.  Fails with DG_ERR_UNSUPPORTED when there is no CUDA

@@ -192,7 +192,7 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     } else if (warp == 1) {
         // ===================================================== MMA issuer (warp-converged, one lane issues)
         uint32_t stage = 0, phase = 0, qcount = 0, acount = 0;
-        const uint32_t idesc = SCALED ? make_idesc_bs(0u, kMqaBlockKv, p.n) : make_idesc_f8(kMqaBlockKv, p.n);
+        const uint32_t idesc = SCALED ? make_idesc_bs(0u, 0u, kMqaBlockKv, p.n) : make_idesc_f8(kMqaBlockKv, p.n);
         bool ok = true;
         for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
             const QRange r = q_block_range(p, qb);

@@ -45,6 +45,64 @@ __device__ __forceinline__ uint32_t cvt_e2m1x2(float a, float b, float src_a, fl
     return v;
 }
 
+// 32 well-mixed bits from a 64-bit element index and a seed (the finaliser of MurmurHash3 over the folded
+// index); the stochastic quantiser's only source of randomness.
+__host__ __device__ __forceinline__ uint32_t hash_u32(uint64_t idx, uint32_t seed) {
+    uint32_t x = (uint32_t)idx * 0x9E3779B9u + (uint32_t)(idx >> 32) * 0x7F4A7C15u + seed;
+    x ^= x >> 16; x *= 0x85EBCA6Bu;
+    x ^= x >> 13; x *= 0xC2B2AE35u;
+    x ^= x >> 16;
+    return x;
+}
+// Stochastic rounding of a scaled value (|v| <= 448) onto the E4M3 grid: returns the chosen grid value
+// (exactly representable, so the RNE conversion that follows encodes it unchanged).  lo = the grid
+// value at or below |v|, one grid step = 2^-9 below 2^-6 (subnormals) and 2^(exponent - 3) above; the
+// value goes up when the top 24 bits of `rnd`, read as a fraction, lie below (|v| - lo) / step.
+// Every operation is exact in f32.  NaN passes through (it encodes as a signed zero afterwards).
+__host__ __device__ __forceinline__ float stochastic_e4m3_value(float v, uint32_t rnd) {
+    union { float f; uint32_t u; } in, t;
+    in.f = v;
+    const uint32_t sign = in.u & 0x80000000u, mag_bits = in.u & 0x7fffffffu;
+    if (mag_bits > 0x7f800000u) return v;                 // NaN
+    t.u = mag_bits;
+    const float a = t.f;
+    if (a >= 448.f) { t.u = sign | 0x43e00000u; return t.f; }   // the scale keeps |v| <= 448; clamp anyway
+    uint32_t e = mag_bits >> 23;                          // biased exponent
+    if (e < 121u) e = 121u;                               // below 2^-6 the grid step stays 2^-9
+    t.u = (e - 3u) << 23;  const float step = t.f;
+    t.u = (257u - e) << 23; const float inv_step = t.f;
+    const float units = a * inv_step;                     // exact: a power-of-two scaling
+    const float fl = (float)(uint32_t)units;              // floor, units < 16
+    const float frac = units - fl;
+    const float u = (float)(rnd >> 8) * (1.0f / 16777216.0f);
+    const float r = (u < frac ? fl + 1.0f : fl) * step;
+    t.f = r;
+    t.u |= sign;
+    return t.f;
+}
+
+// silu(g) * u in f32 with an exponential that is defined operation by operation, so that the CPU
+// checker can state the same function and the re-quantised codes agree bit for bit:
+//   exp(x), x = -g clamped to [-87, 87]:  n = rint(x * log2 e), f = x - n * ln 2 (two-step Cody-Waite),
+//   degree-6 Taylor polynomial of exp(f) in Horner form with fused multiply-adds, times 2^n;
+//   silu(g) = g / (1 + exp(-g)) with the IEEE division.
+// About 1 ulp from the exact exponential; 20 FMA-pipe instructions instead of two special-function
+// ones, which cost as many issue slots (the special-function unit has an eighth of the lanes).
+__device__ __forceinline__ float swiglu_value(float g, float u) {
+    const float x = fminf(fmaxf(-g, -87.0f), 87.0f);
+    const float n = rintf(x * 1.44269502162933349609375f);
+    float f = fmaf(n, -0.693145751953125f, x);
+    f = fmaf(n, -1.428606765330187045037746429443359375e-06f, f);
+    float p = fmaf(f, 1.0f / 720.0f, 1.0f / 120.0f);
+    p = fmaf(p, f, 1.0f / 24.0f);
+    p = fmaf(p, f, 1.0f / 6.0f);
+    p = fmaf(p, f, 0.5f);
+    p = fmaf(p, f, 1.0f);
+    p = fmaf(p, f, 1.0f);
+    const float e = p * __uint_as_float((uint32_t)((int)n + 127) << 23);
+    return __fdiv_rn(g, 1.0f + e) * u;
+}
+
 __device__ __forceinline__ float amax4(const float4& v) {
     return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
 }

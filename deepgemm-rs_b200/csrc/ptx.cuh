@@ -44,6 +44,17 @@ __device__ __forceinline__ bool elect_one() {
 // Bounded wait by every lane of a converged warp; the result is warp-uniform.
 #define DG_WARP_WAIT(bar, parity, wc, site) __all_sync(0xffffffffu, ::dg::mbar_wait((bar), (parity), (wc), (site)))
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running; griddep_wait() blocks until that kernel has
+// completed and its writes are visible, so everything before the call (barrier set-up, TMEM
+// allocation, descriptor prefetch) overlaps the predecessor's tail.  griddep_launch_dependents()
+// lets the successor start as soon as every CTA of this grid has got this far.  Both are no-ops
+// for a normally launched kernel.  (The reference launches with the same attribute,
+// deepgemm/src/sys.rs:287-294, and waits at deepgemm/kernels/gemm_sm100.cu:566.)
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- clusters (CTA pairs)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -213,9 +224,10 @@ __device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
 __host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t m, uint32_t n) {
     return (1u << 4) /*D=f32*/ | (1u << 7) /*A=bf16*/ | (1u << 10) /*B=bf16*/ | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
-// Block-scaled kinds (mxf8f6f4: fmt 0 = E4M3; mxf4: fmt 1 = E2M1), UE8M0 scales, K-major.
-__host__ __device__ constexpr uint32_t make_idesc_bs(uint32_t fmt, uint32_t m, uint32_t n) {
-    return (fmt << 7) | (fmt << 10) | ((n >> 3) << 17) | (1u << 23) /*UE8M0*/ | ((m >> 4) << 24);
+// Block-scaled kinds (mxf8f6f4: format 0 = E4M3, 5 = E2M1 in byte containers; mxf4: 1 = E2M1),
+// UE8M0 scales, K-major.
+__host__ __device__ constexpr uint32_t make_idesc_bs(uint32_t fmt_a, uint32_t fmt_b, uint32_t m, uint32_t n) {
+    return (fmt_a << 7) | (fmt_b << 10) | ((n >> 3) << 17) | (1u << 23) /*UE8M0*/ | ((m >> 4) << 24);
 }
 __device__ __forceinline__ uint32_t idesc_with_sf_ids(uint32_t idesc, uint32_t a_sf_id, uint32_t b_sf_id) {
     return idesc | (b_sf_id << 4) | (a_sf_id << 29);

@@ -7,6 +7,8 @@
 // (deepgemm/src/api.rs:1031-1135, 1480-1601).
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "host.h"
 #include "mx_codec.cuh"
 
@@ -22,11 +24,16 @@ namespace dg {
 // [m, 2k] of an MoE gate/up projection (row pitch src_pitch elements): silu(gate) * up with gate =
 // columns [0, k), up = columns [k, 2k), f32 arithmetic on the bf16 values (the golden model's
 // convention, deepgemm/src/golden.rs:569-577, without clamp).
-template <uint32_t G, bool FP4, bool SWIGLU = false>
+// STOCH (FP8, G = 32; api::quantize_output_fp8 with `stochastic`): instead of rounding to nearest, a
+// scaled value between two neighbouring E4M3 values lo < hi becomes hi with probability
+// (v - lo) / (hi - lo), so that the expectation is v.  The 24 random bits of element (row, col) come from
+// a counter-based hash of its index and `seed`; all the arithmetic is exact in f32, so the result is
+// a pure function of (x, seed) and is checked bit for bit against the same definition on the CPU.
+template <uint32_t G, bool FP4, bool SWIGLU = false, bool STOCH = false>
 __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__ x, uint32_t m, uint32_t k,
                                                       uint8_t* __restrict__ data, uint32_t* __restrict__ sf,
                                                       uint32_t sf_cols, uint32_t num_spans, uint32_t num_row_blocks,
-                                                      uint64_t src_pitch = 0) {
+                                                      uint64_t src_pitch = 0, uint32_t seed = 0) {
     constexpr uint32_t kLoads = G / 32;                   // float4 loads per lane per row
     constexpr uint32_t kRowsPerIter = G == 32 ? 8 : 2;    // rows in flight per warp
     const uint32_t lane = threadIdx.x & 31u;
@@ -60,14 +67,10 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
                                             __uint_as_float(gb.y << 16), __uint_as_float(gb.y & 0xffff0000u)};
                         const float u[4] = {__uint_as_float(ub.x << 16), __uint_as_float(ub.x & 0xffff0000u),
                                             __uint_as_float(ub.y << 16), __uint_as_float(ub.y & 0xffff0000u)};
-                        // fast exponential and division (a few ulp): the kernel would otherwise be bound by
-                        // their instruction count, not by memory; an element lands on the neighbouring E4M3
-                        // code only when it sits within ~1e-6 of a rounding boundary
-                        v[i][j] = make_float4(__fdividef(g[0], 1.f + __expf(-g[0])) * u[0], __fdividef(g[1], 1.f + __expf(-g[1])) * u[1],
-                                              __fdividef(g[2], 1.f + __expf(-g[2])) * u[2], __fdividef(g[3], 1.f + __expf(-g[3])) * u[3]);
+                        v[i][j] = make_float4(swiglu_value(g[0], u[0]), swiglu_value(g[1], u[1]), swiglu_value(g[2], u[2]), swiglu_value(g[3], u[3]));
                     }
                 } else {
-                    v[i][j] = ok ? __ldcs(reinterpret_cast<const float4*>(x + (size_t)row * k + col0 + j * 128u + lane * 4u))
+                    v[i][j] = ok ? __ldcs(reinterpret_cast<const float4*>(x + (size_t)row * (src_pitch ? src_pitch : k) + col0 + j * 128u + lane * 4u))
                                  : make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             }
@@ -91,8 +94,15 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
                 const float inv = __uint_as_float((254u - e) << 23);
                 const uint32_t grp = G == 32 ? (lane >> 3) : j;
                 const bool ok = row < m && grp < groups_here;
-                const float4 q = make_float4(v[i][j].x * inv, v[i][j].y * inv, v[i][j].z * inv, v[i][j].w * inv);
+                float4 q = make_float4(v[i][j].x * inv, v[i][j].y * inv, v[i][j].z * inv, v[i][j].w * inv);
                 const size_t col = col0 + j * 128u + lane * 4u;
+                if (STOCH) {
+                    const uint64_t idx = (uint64_t)row * k + col;
+                    q.x = stochastic_e4m3_value(q.x, hash_u32(idx, seed));
+                    q.y = stochastic_e4m3_value(q.y, hash_u32(idx + 1, seed));
+                    q.z = stochastic_e4m3_value(q.z, hash_u32(idx + 2, seed));
+                    q.w = stochastic_e4m3_value(q.w, hash_u32(idx + 3, seed));
+                }
                 if (FP4) {
                     const uint32_t b = cvt_e2m1x2(q.x, q.y, v[i][j].x, v[i][j].y) | (cvt_e2m1x2(q.z, q.w, v[i][j].z, v[i][j].w) << 8);
                     if (ok) *reinterpret_cast<uint16_t*>(data + ((size_t)row * k + col) / 2) = (uint16_t)b;
@@ -170,6 +180,9 @@ __global__ void __launch_bounds__(256) dequant_mx_kernel(const uint8_t* __restri
 __global__ void __launch_bounds__(256) transform_sf_kernel(const float* __restrict__ sf, uint32_t mn, uint32_t sf_k,
                                                           uint32_t* __restrict__ out, uint32_t out_cols) {
     __shared__ uint32_t tile[64][65];
+    // blockIdx.z = batch (transform_sf_batched): inputs [batch, mn, sf_k], outputs stacked along the word rows
+    sf += (size_t)blockIdx.z * mn * sf_k;
+    out += (size_t)blockIdx.z * ((sf_k + 3u) / 4u) * out_cols;
     const uint32_t m0 = blockIdx.x * 64u, k0 = blockIdx.y * 64u;
     for (uint32_t i = threadIdx.x; i < 64u * 64u; i += 256u) {
         const uint32_t r = i >> 6, c = i & 63u;
@@ -192,7 +205,7 @@ __global__ void __launch_bounds__(256) transform_sf_kernel(const float* __restri
 
 // ------------------------------------------------------------------------- host side
 static int32_t check_quant_args(const void* x, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran,
-                                const void* data_out, const void* sf_out) {
+                                const void* data_out, const void* sf_out, bool x_on_host = false) {
     if (!x || !data_out || !sf_out) return fail(DG_ERR_INVALID_ARG, "quant_mx: null buffer");
     if (m == 0 || k == 0) return fail(DG_ERR_INVALID_ARG, "quant_mx: empty shape %u x %u", m, k);
     if (dtype != DG_FP8 && dtype != DG_FP4) return fail(DG_ERR_INVALID_ARG, "quant_mx: dtype must be FP8 or FP4");
@@ -201,8 +214,9 @@ static int32_t check_quant_args(const void* x, uint32_t m, uint32_t k, int32_t d
     if (dtype == DG_FP4 && (gran != 32 || k % 32 != 0))
         return fail(DG_ERR_INVALID_ARG, "quant_mx: FP4 requires granularity 32 and K (%u) %% 32 == 0", k);
     if (k % gran != 0) return fail(DG_ERR_INVALID_ARG, "quant_mx: K (%u) must be a multiple of the SF granularity %u", k, gran);
-    if ((reinterpret_cast<uintptr_t>(x) & 15u) || (reinterpret_cast<uintptr_t>(data_out) & 3u))
-        return fail(DG_ERR_INVALID_ARG, "quant_mx: x must be 16-byte aligned and the code buffer 4-byte aligned");
+    // the kernel reads x in 16-byte vectors; a host tensor is only the source of a copy into an aligned staging area
+    if (!x_on_host && (reinterpret_cast<uintptr_t>(x) & 15u)) return fail(DG_ERR_INVALID_ARG, "quant_mx: x must be 16-byte aligned");
+    if (reinterpret_cast<uintptr_t>(data_out) & 3u) return fail(DG_ERR_INVALID_ARG, "quant_mx: the code buffer must be 4-byte aligned");
     return DG_OK;
 }
 
@@ -267,7 +281,7 @@ int32_t dg_quant_mx(const float* x, uint32_t m, uint32_t k, int32_t dtype, uint3
 
 int32_t dg_quant_mx_host(const float* x_host, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran, void* data_out,
                          uint32_t* sf_out, void* stream) {
-    int32_t st = dg::check_quant_args(x_host, m, k, dtype, gran, data_out, sf_out);
+    int32_t st = dg::check_quant_args(x_host, m, k, dtype, gran, data_out, sf_out, true);
     if (st != DG_OK) return st;
     const dg::DeviceInfo* dev;
     if ((st = dg::current_device(&dev)) != DG_OK) return st;
@@ -289,11 +303,13 @@ constexpr size_t kStaticStagingBytes = 16u << 20;   // 16 MiB = 4 Mi f32 element
 static __device__ __align__(256) unsigned char g_quant_staging[kStaticStagingBytes];
 // g_quant_staging names a host-side handle in host code, not a device address: the address the
 // kernel and the copy engine need comes from cudaGetSymbolAddress, once per device.
-static float* g_quant_staging_addr[64] = {nullptr};
+// (Several host threads may make the first call on a device at once: they all look up the same address,
+// and the atomic slot keeps the publication well defined.)
+static std::atomic<float*> g_quant_staging_addr[64];
 
 int32_t dg_quant_mx_host_static(const float* x_host, uint32_t m, uint32_t k, int32_t dtype, uint32_t gran,
                                 void* data_out, uint32_t* sf_out, void* stream) {
-    int32_t st = dg::check_quant_args(x_host, m, k, dtype, gran, data_out, sf_out);
+    int32_t st = dg::check_quant_args(x_host, m, k, dtype, gran, data_out, sf_out, true);
     if (st != DG_OK) return st;
     const size_t bytes = (size_t)m * k * sizeof(float);
     if (bytes > kStaticStagingBytes)
@@ -306,7 +322,7 @@ int32_t dg_quant_mx_host_static(const float* x_host, uint32_t m, uint32_t k, int
         cudaGetLastError();
         return dg::fail(DG_ERR_UNSUPPORTED, "no usable CUDA device; the kernels require SM100 (Blackwell)");
     }
-    if (!g_quant_staging_addr[dev]) {
+    if (!g_quant_staging_addr[dev].load(std::memory_order_acquire)) {
         // one-time set-up on this device (it is the current one)
         int major = 0;
         DG_CUDA_CHECK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
@@ -315,9 +331,9 @@ int32_t dg_quant_mx_host_static(const float* x_host, uint32_t m, uint32_t k, int
         cudaError_t e = cudaGetSymbolAddress(&p, g_quant_staging);
         if (e != cudaSuccess || !p)
             return dg::fail(DG_ERR_DRIVER, "cudaGetSymbolAddress(static staging area) failed: %s", cudaGetErrorString(e));
-        g_quant_staging_addr[dev] = static_cast<float*>(p);
+        g_quant_staging_addr[dev].store(static_cast<float*>(p), std::memory_order_release);
     }
-    float* staging = g_quant_staging_addr[dev];
+    float* staging = g_quant_staging_addr[dev].load(std::memory_order_acquire);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     DG_CUDA_CHECK(cudaMemcpyAsync(staging, x_host, bytes, cudaMemcpyHostToDevice, s));
     return dg::launch_quant(staging, m, k, dtype, gran, data_out, sf_out, s);
@@ -349,9 +365,9 @@ int32_t dg_dequant_mx(const void* data, const dg_sf_tensor_t* sf, uint32_t m, ui
     return DG_OK;
 }
 
-static int32_t transform_sf_impl(const float* sf, uint32_t mn, uint32_t sf_k, uint32_t* out, cudaStream_t s) {
+static int32_t transform_sf_impl(const float* sf, uint32_t mn, uint32_t sf_k, uint32_t* out, cudaStream_t s, uint32_t batch = 1) {
     const uint32_t cols = dg::align_up(mn, 4);
-    dim3 grid(dg::ceil_div(cols, 64), dg::ceil_div(sf_k, 64));
+    dim3 grid(dg::ceil_div(cols, 64), dg::ceil_div(sf_k, 64), batch);
     dg::transform_sf_kernel<<<grid, 256, 0, s>>>(sf, mn, sf_k, out, cols);
     dg::note_launch();
     DG_CUDA_CHECK(cudaGetLastError());
@@ -365,6 +381,41 @@ int32_t dg_transform_sf(const float* sf, uint32_t mn, uint32_t sf_k, uint32_t* o
     int32_t st = dg::current_device(&dev);
     if (st != DG_OK) return st;
     return transform_sf_impl(sf, mn, sf_k, out, static_cast<cudaStream_t>(stream));
+}
+
+int32_t dg_transform_sf_batched(const float* sf, uint32_t batch, uint32_t mn, uint32_t sf_k, uint32_t* out, void* stream) {
+    if (!sf || !out) return dg::fail(DG_ERR_INVALID_ARG, "transform_sf_batched: null buffer");
+    if (batch == 0) return dg::fail(DG_ERR_INVALID_ARG, "batch must be nonzero");
+    if (batch > 65535) return dg::fail(DG_ERR_INVALID_ARG, "transform_sf_batched: at most 65535 batches");
+    if (mn == 0 || sf_k == 0) return dg::fail(DG_ERR_INVALID_ARG, "batched SF must hold batch * mn * sf_k values");
+    const dg::DeviceInfo* dev;
+    int32_t st = dg::current_device(&dev);
+    if (st != DG_OK) return st;
+    return transform_sf_impl(sf, mn, sf_k, out, static_cast<cudaStream_t>(stream), batch);
+}
+
+int32_t dg_quantize_output_fp8(const float* src, uint32_t m, uint32_t n, uint32_t in_stride, int32_t stochastic, uint32_t seed,
+                               void* data_out, uint32_t* sf_out, void* stream) {
+    if (!src || !data_out || !sf_out) return dg::fail(DG_ERR_INVALID_ARG, "quantize_output_fp8: null buffer");
+    if (m == 0 || n == 0 || n % 32 != 0) return dg::fail(DG_ERR_INVALID_ARG, "quantize_output_fp8 needs n %% 32 == 0 (n = %u, m = %u)", n, m);
+    if (in_stride < n || in_stride % 4 != 0 || (reinterpret_cast<uintptr_t>(src) & 15u) || (reinterpret_cast<uintptr_t>(data_out) & 3u))
+        return dg::fail(DG_ERR_INVALID_ARG, "quantize_output_fp8: in_stride (%u) must cover n, rows must stay 16-byte aligned", in_stride);
+    const dg::DeviceInfo* dev;
+    int32_t st = dg::current_device(&dev);
+    if (st != DG_OK) return st;
+    const uint32_t sf_cols = dg::align_up(m, 4);
+    const uint32_t num_spans = dg::ceil_div(n / 32, 4);
+    const uint32_t num_row_blocks = dg::ceil_div(sf_cols, 32);
+    const uint32_t blocks = (uint32_t)(((uint64_t)num_spans * num_row_blocks + 7) / 8);
+    uint8_t* d = static_cast<uint8_t*>(data_out);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (stochastic)
+        dg::quant_mx_kernel<32, false, false, true><<<blocks, 256, 0, s>>>(src, m, n, d, sf_out, sf_cols, num_spans, num_row_blocks, in_stride, seed);
+    else
+        dg::quant_mx_kernel<32, false><<<blocks, 256, 0, s>>>(src, m, n, d, sf_out, sf_cols, num_spans, num_row_blocks, in_stride);
+    dg::note_launch();
+    DG_CUDA_CHECK(cudaGetLastError());
+    return DG_OK;
 }
 
 int32_t dg_transform_sf_host(const float* sf_host, uint32_t mn, uint32_t sf_k, uint32_t* out, void* stream) {

@@ -68,6 +68,13 @@ def load(build_if_missing=True):
     L.dg_sf_shape.restype = None
     for n in ("dg_gemm_nt", "dg_fp8_gemm_nt", "dg_fp4_gemm_nt", "dg_bf16_gemm_nt"):
         getattr(L, n).argtypes = [opp, opp, outp, i32, vp]
+    L.dg_gemm_nt_alpha.argtypes = [opp, opp, outp, i32, C.c_float, vp]
+    for n in ("dg_gemm_nn", "dg_gemm_tn", "dg_gemm_tt"):
+        getattr(L, n).argtypes = [opp, opp, outp, i32, vp]
+    for n in ("dg_bmm", "dg_fp8_bmm"):
+        getattr(L, n).argtypes = [opp, opp, outp, u32, i32, vp]
+    L.dg_transform_sf_batched.argtypes = [vp, u32, u32, u32, vp, vp]
+    L.dg_quantize_output_fp8.argtypes = [vp, u32, u32, u32, i32, u32, vp, vp, vp]
     for n in ("dg_m_grouped_gemm_nt_contiguous", "dg_m_grouped_fp8_gemm_nt_contiguous",
               "dg_m_grouped_fp4_gemm_nt_contiguous", "dg_m_grouped_bf16_gemm_nt_contiguous"):
         getattr(L, n).argtypes = [opp, opp, outp, vp, u32, u32, vp]

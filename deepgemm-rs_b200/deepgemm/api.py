@@ -92,6 +92,41 @@ def bf16_gemm_nt(a, b, out, accumulate=False, stream=None):
     _gemm(_lib.load().dg_bf16_gemm_nt, a, b, out, accumulate, stream)
 
 
+def gemm_nt_alpha(a, b, out, accumulate=False, alpha=None, stream=None):
+    """D = alpha * (A . B^T) (+ D) (api.rs:663-673); alpha None = 1."""
+    ac, bc, oc = _op_c(a), _op_c(b), _out_c(out)
+    _check(_lib.load().dg_gemm_nt_alpha(C.byref(ac), C.byref(bc), C.byref(oc), 1 if accumulate else 0,
+                                        C.c_float(1.0 if alpha is None else alpha), _stream_ptr(stream)))
+
+
+def gemm_nn(a, b, out, accumulate=False, stream=None):
+    """A K-major [M, K], B an MN-major view of a [K, N] buffer (api.rs:720-732)."""
+    _gemm(_lib.load().dg_gemm_nn, a, b, out, accumulate, stream)
+
+
+def gemm_tn(a, b, out, accumulate=False, stream=None):
+    """A an MN-major view of a [K, M] buffer, B K-major [N, K] (api.rs:734-746)."""
+    _gemm(_lib.load().dg_gemm_tn, a, b, out, accumulate, stream)
+
+
+def gemm_tt(a, b, out, accumulate=False, stream=None):
+    """A and B MN-major views (api.rs:748-759)."""
+    _gemm(_lib.load().dg_gemm_tt, a, b, out, accumulate, stream)
+
+
+def fp8_bmm(a, b, out, batch, accumulate=False, stream=None):
+    """Batched GEMM (api.rs:966-993): a / b / out describe one batch, the tensors hold `batch` of them stacked
+    along the rows, the scale factors are transform_sf_batched arenas."""
+    ac, bc, oc = _op_c(a), _op_c(b), _out_c(out)
+    _check(_lib.load().dg_fp8_bmm(C.byref(ac), C.byref(bc), C.byref(oc), batch, 1 if accumulate else 0, _stream_ptr(stream)))
+
+
+def bmm(a, b, out, batch, accumulate=False, stream=None):
+    """fp8_bmm for any operand dtype."""
+    ac, bc, oc = _op_c(a), _op_c(b), _out_c(out)
+    _check(_lib.load().dg_bmm(C.byref(ac), C.byref(bc), C.byref(oc), batch, 1 if accumulate else 0, _stream_ptr(stream)))
+
+
 # ---- grouped GEMM (api.rs:859-963) -----------------------------------------------------
 def _contig(fn, a, b, out, m_indices, num_groups, stream):
     ac, bc, oc = _op_c(a), _op_c(b), _out_c(out)
@@ -217,6 +252,34 @@ def transform_sf(sf, mn, gran, stream=None):
     if host:
         torch.cuda.current_stream().synchronize() if stream is None else stream.synchronize()
     return SfTensor(rows, cols, SfGran(int(gran)), out)
+
+
+def transform_sf_batched(sf, batch, mn, gran, stream=None):
+    """sf: f32 [batch, mn, sf_k] powers of two (device or host, api.rs:1263-1270).  Returns the arena SfTensor
+    [batch * ceil(sf_k/4), align4(mn)]."""
+    if not (isinstance(sf, torch.Tensor) and sf.is_cuda):
+        sf = torch.as_tensor(sf, dtype=torch.float32).contiguous().cuda()
+    if batch == 0:
+        raise error_for(3, "batch must be nonzero")
+    per_batch = sf.numel() // batch
+    if per_batch == 0 or per_batch * batch != sf.numel() or per_batch % mn != 0:
+        raise error_for(3, "batched SF must hold batch * mn * sf_k values")
+    sf_k = per_batch // mn
+    rows, cols = (sf_k + 3) // 4, (mn + 3) // 4 * 4
+    out = torch.empty((batch * rows, cols), dtype=torch.int32, device=sf.device)
+    _check(_lib.load().dg_transform_sf_batched(sf.data_ptr(), batch, mn, sf_k, out.data_ptr(), _stream_ptr(stream)))
+    return SfTensor(batch * rows, cols, SfGran(int(gran)), out)
+
+
+def quantize_output_fp8(src, m, n, in_stride, stochastic=False, seed=0, stream=None):
+    """src: f32 device tensor [m, >= n] with row pitch in_stride (api.rs:1951-1959).  Returns (E4M3 codes
+    u8 [m, n], packed UE8M0 words i32 [ceil(n/32/4), align4(m)])."""
+    rows, cols = sf_shape(m, n, 32)
+    data = torch.empty((m, n), dtype=torch.uint8, device=src.device)
+    sf = torch.empty((rows, cols), dtype=torch.int32, device=src.device)
+    _check(_lib.load().dg_quantize_output_fp8(src.data_ptr(), m, n, in_stride, 1 if stochastic else 0, seed, data.data_ptr(),
+                                              sf.data_ptr(), _stream_ptr(stream)))
+    return data, sf
 
 
 # ---- MQA logits ------------------------------------------------------------------------

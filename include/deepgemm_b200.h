@@ -102,6 +102,29 @@ DG_API int32_t dg_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_outpu
 DG_API int32_t dg_fp8_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
 DG_API int32_t dg_fp4_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
 DG_API int32_t dg_bf16_gemm_nt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
+/* Operands may individually be K-major or MN-major (dg_operand_t.major; the general entry
+ * api::gemm_nt_layout, deepgemm/src/api.rs:679-715, which dg_gemm_nt implements).  An MN-major operand
+ * is a [K, rows] buffer: element (r, k) at r + k * outer_stride (deepgemm/src/types.rs:128-137); FP8 and
+ * BF16 only -- FP4 operands must be K-major (api.rs:176-180).  The scale-factor layout does not depend
+ * on the major.  FP8 x FP4 and FP4 x FP8 operand pairs are accepted (the FP4 side is unpacked to one
+ * code per byte on its way into shared memory, api.rs:264-265).
+ * replaces api::gemm_nt_alpha (api.rs:663-673): D = alpha * (A . B^T) (+ D); alpha scales the f32
+ * accumulator before the output cast, the accumulated D is not scaled. */
+DG_API int32_t dg_gemm_nt_alpha(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate,
+                                float alpha, void* stream);
+/* replace api::gemm_nn / gemm_tn / gemm_tt (api.rs:720-759): the BLAS layouts over zero-copy MN-major
+ * views.  nn: B is MN-major ([K, N] buffer); tn: A is MN-major ([K, M] buffer); tt: both.  They check
+ * the orientation of the views and run dg_gemm_nt. */
+DG_API int32_t dg_gemm_nn(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
+DG_API int32_t dg_gemm_tn(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
+DG_API int32_t dg_gemm_tt(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int32_t accumulate, void* stream);
+/* replaces api::fp8_bmm (api.rs:966-993): `batch` independent GEMMs.  a, b and out describe ONE batch
+ * (rows = M / N, out.rows = M); the buffers hold the batches stacked along the rows ([batch * M, K],
+ * [batch * N, K], [batch * M, N]; MN-major operands: [batch * K, rows]) and the scale-factor tensors are
+ * the arenas of dg_transform_sf_batched: [batch * ceil(K/(4 gran)), align4(rows)], batch b's word rows
+ * starting at b * ceil(K/(4 gran)).  dg_bmm takes any operand dtype, dg_fp8_bmm insists on FP8. */
+DG_API int32_t dg_bmm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, uint32_t batch, int32_t accumulate, void* stream);
+DG_API int32_t dg_fp8_bmm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, uint32_t batch, int32_t accumulate, void* stream);
 
 /* ---- grouped GEMM (MoE) ----------------------------------------------------------------
  * replaces api::m_grouped_gemm_nt_contiguous (deepgemm/src/api.rs:859-903).  a.rows must be
@@ -182,13 +205,28 @@ DG_API int32_t dg_dequant_mx(const void* data, const dg_sf_tensor_t* sf, uint32_
  * [mn, sf_k] row-major -> packed words [ceil(sf_k/4), align4(mn)]. */
 DG_API int32_t dg_transform_sf(const float* sf, uint32_t mn, uint32_t sf_k, uint32_t* out, void* stream);
 DG_API int32_t dg_transform_sf_host(const float* sf_host, uint32_t mn, uint32_t sf_k, uint32_t* out, void* stream);
+/* replaces api::transform_sf_batched (deepgemm/src/api.rs:1263-1311): sf f32 [batch, mn, sf_k] (device) ->
+ * one arena [batch * ceil(sf_k/4), align4(mn)], batch b's rows starting at b * ceil(sf_k/4): the SF
+ * operand layout of dg_bmm. */
+DG_API int32_t dg_transform_sf_batched(const float* sf, uint32_t batch, uint32_t mn, uint32_t sf_k, uint32_t* out, void* stream);
+/* replaces api::quantize_output_fp8 (deepgemm/src/api.rs:1951-2011; device side
+ * deepgemm/kernels/layout_quant.cu:318-361): src f32 [m, n] (device) with row pitch in_stride elements ->
+ * E4M3 codes [m, n] and packed UE8M0 words [ceil(n/32/4), align4(m)], one scale per (row, 32 columns),
+ * so that a GEMM's f32 output can feed the next FP8 GEMM.  n % 32 == 0.  stochastic == 0: round to
+ * nearest, bit-identical to dg_quant_mx at granularity 32 (exponent rule of deepgemm/src/golden.rs:211-224).
+ * stochastic != 0: a value between two neighbouring E4M3 values goes up with probability equal to its
+ * relative position between them, the draw being a hash of (element index, seed): unbiased, and
+ * reproducible for a given seed. */
+DG_API int32_t dg_quantize_output_fp8(const float* src, uint32_t m, uint32_t n, uint32_t in_stride, int32_t stochastic,
+                                      uint32_t seed, void* data_out, uint32_t* sf_out, void* stream);
 
 /* ---- MQA logits (lightning indexer) ----------------------------------------------------
  * logits[i, j] = sum_h w[i,h] * relu(<q[i,h,:], kv[j,:]>) for j in [ks[i], min(ke[i], S)).
  * fp32 contract (deepgemm/src/api_sm90_mqa.rs:5-31): q raw E4M3 [T,H,D]; kv E4M3 [S,D]
  * with one f32 scale per kv token applied after the head sum; weights f32 [T,H]; logits f32
- * with row pitch `logits_stride` elements, written at the absolute column j; columns outside
- * the range are not written. */
+ * with row pitch `logits_stride` elements, stored compressed: the value for kv token j of query i
+ * goes to column j - ks[i] of row i (absolute columns when ks = 0); columns outside the range are not
+ * written.  q and kv are dense ([T*H, D] and [S, D] bytes, row pitch D). */
 DG_API int32_t dg_mqa_logits_f32(const void* q, const void* kv, const float* kv_scale, const float* weights,
                           const uint32_t* cu_k_start, const uint32_t* cu_k_end,
                           uint32_t num_tokens, uint32_t num_kv_tokens, uint32_t num_heads, uint32_t head_dim,

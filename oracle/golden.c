@@ -384,15 +384,119 @@ void dgo_quant_fp8_block128_host(const float* x, uint32_t n, uint32_t k, uint8_t
  * the fused path (golden.rs:569-577) both factors are the bf16-rounded GEMM outputs and the product
  * silu(g) * u, silu(g) = g / (1 + exp(-g)), is formed in f32; there is no clamp and the routing weight is
  * applied later, when the copies of a token are combined.  out: f32 [m, inter], the input of the
- * re-quantisation (dgo_quant_mx_host). */
+ * re-quantisation (dgo_quant_mx_host).
+ * The golden model calls the platform's exp; platforms differ in its last bit, which would make the
+ * E4M3 codes after re-quantisation platform dependent.  The exponential is therefore spelled out here
+ * (range reduction by ln 2, degree-6 Taylor polynomial, fused multiply-adds; within about 1 ulp of expf,
+ * asserted by the tests), and the device code evaluates the same sequence of correctly rounded operations. */
+static float exp_taylor6(float x) {
+    if (x < -87.0f) x = -87.0f;
+    if (x > 87.0f) x = 87.0f;
+    float n = rintf(x * 1.44269502162933349609375f);
+    float f = fmaf(n, -0.693145751953125f, x);
+    f = fmaf(n, -1.428606765330187045037746429443359375e-06f, f);
+    float p = fmaf(f, 1.0f / 720.0f, 1.0f / 120.0f);
+    p = fmaf(p, f, 1.0f / 24.0f);
+    p = fmaf(p, f, 1.0f / 6.0f);
+    p = fmaf(p, f, 0.5f);
+    p = fmaf(p, f, 1.0f);
+    p = fmaf(p, f, 1.0f);
+    return p * u2f((uint32_t)((int)n + 127) << 23);
+}
+float dgo_exp_taylor6(float x) { return exp_taylor6(x); }
+
 void dgo_swiglu_f32(const uint16_t* inter_bf16, uint32_t m, uint32_t inter, uint32_t ld, float* out) {
 #pragma omp parallel for schedule(static)
     for (uint32_t r = 0; r < m; ++r) {
         const uint16_t* row = inter_bf16 + (size_t)r * ld;
         for (uint32_t c = 0; c < inter; ++c) {
             float g = u2f((uint32_t)row[c] << 16), u = u2f((uint32_t)row[inter + c] << 16);
-            float sig = g / (1.0f + expf(-g));
+            float sig = g / (1.0f + exp_taylor6(-g));
             out[(size_t)r * inter + c] = sig * u;
         }
     }
 }
+
+/* api::quantize_output_fp8 (deepgemm/src/api.rs:1951-2011): f32 [m, n] with row pitch in_stride -> E4M3
+ * codes [m, n] + packed UE8M0 words [ceil(n/32/4), align4(m)], one scale per (row, 32 columns).
+ * Round-to-nearest mode: the exponent rule and cast of the golden model (golden.rs:211-224, 299-363),
+ * i.e. quant_mx at granularity 32 on a pitched input.  (The reference's device kernel shifts the 8-bit
+ * exponent field where the golden model shifts the float's bits, deepgemm/kernels/layout_quant.cu:339-341;
+ * the golden model is the contract.)
+ * Stochastic mode (no golden model exists for it; the reference's device code draws from an xorshift
+ * stream per group, layout_quant.cu:343-353): defined here as a pure function of (x, seed) -- a scaled
+ * value v between neighbouring grid values lo < hi becomes hi when the top 24 bits of
+ * hash(element index, seed), read as a fraction in [0, 1), lie below (|v| - lo) / (hi - lo). */
+static uint32_t hash_u32(uint64_t idx, uint32_t seed) {
+    uint32_t x = (uint32_t)idx * 0x9E3779B9u + (uint32_t)(idx >> 32) * 0x7F4A7C15u + seed;
+    x ^= x >> 16; x *= 0x85EBCA6Bu;
+    x ^= x >> 13; x *= 0xC2B2AE35u;
+    x ^= x >> 16;
+    return x;
+}
+uint32_t dgo_hash_u32(uint64_t idx, uint32_t seed) { return hash_u32(idx, seed); }
+
+static float stochastic_e4m3_value(float v, uint32_t rnd) {
+    uint32_t bits = f2u(v), sign = bits & 0x80000000u, mag = bits & 0x7fffffffu;
+    if (mag > 0x7f800000u) return v;
+    float a = u2f(mag);
+    if (a >= 448.0f) return u2f(sign | f2u(448.0f));
+    uint32_t e = mag >> 23;
+    if (e < 121u) e = 121u;
+    float step = u2f((e - 3u) << 23), inv_step = u2f((257u - e) << 23);
+    float units = a * inv_step;
+    float fl = floorf(units);
+    float frac = units - fl;
+    float u = (float)(rnd >> 8) * (1.0f / 16777216.0f);
+    float r = (u < frac ? fl + 1.0f : fl) * step;
+    return u2f(f2u(r) | sign);
+}
+
+void dgo_quantize_output_fp8(const float* in, uint32_t m, uint32_t n, uint32_t in_stride, int stochastic, uint32_t seed,
+                             uint8_t* data, uint32_t* sf) {
+    grids_init();
+    uint32_t num_groups = n / 32;
+    uint32_t sf_cols = dgo_tma_aligned(m, 4), sf_rows = dgo_ceil_div(num_groups, 4);
+    memset(sf, 0, (size_t)sf_rows * sf_cols * 4);
+#pragma omp parallel for schedule(static)
+    for (uint32_t row = 0; row < m; ++row) {
+        for (uint32_t gi = 0; gi < num_groups; ++gi) {
+            const float* px = in + (size_t)row * in_stride + (size_t)gi * 32;
+            float amax = 0.0f;
+            for (uint32_t i = 0; i < 32; ++i) {
+                float v = fabsf(px[i]);
+                if (v > amax) amax = v;
+            }
+            if (amax < 1e-30f) amax = 1e-30f;
+            uint8_t e = dgo_ue8m0_exp_fp8(amax);
+            float inv_sf = u2f((254u - (uint32_t)e) << 23);
+            for (uint32_t i = 0; i < 32; ++i) {
+                float v = px[i] * inv_sf;
+                uint64_t idx = (uint64_t)row * n + gi * 32 + i;
+                if (stochastic) v = stochastic_e4m3_value(v, hash_u32(idx, seed));
+                data[idx] = dgo_quant_e4m3(v);
+            }
+            sf[(size_t)(gi / 4) * sf_cols + row] |= (uint32_t)e << (8 * (gi % 4));
+        }
+    }
+}
+
+/* api::transform_sf_batched (deepgemm/src/api.rs:1263-1311): [batch, mn, sf_k] scales -> one arena
+ * [batch * ceil(sf_k/4), align4(mn)]; batch b's rows start at b * ceil(sf_k/4), each batch packed as by
+ * transform_sf_host. */
+void dgo_transform_sf_batched_host(const float* sf, uint32_t batch, uint32_t mn, uint32_t sf_k, uint32_t* out) {
+    uint32_t cols = dgo_tma_aligned(mn, 4), rows = dgo_ceil_div(sf_k, 4);
+    for (uint32_t b = 0; b < batch; ++b)
+        dgo_transform_sf_host(sf + (size_t)b * mn * sf_k, mn, sf_k, out + (size_t)b * rows * cols);
+}
+
+/* Thread count of the OpenMP loops above (the benchmark's CPU arm sets it to the host's cores explicitly:
+ * launchers such as torch.distributed.run export OMP_NUM_THREADS=1). */
+#ifdef _OPENMP
+#include <omp.h>
+void dgo_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int dgo_get_threads(void) { return omp_get_max_threads(); }
+#else
+void dgo_set_threads(int n) { (void)n; }
+int dgo_get_threads(void) { return 1; }
+#endif

@@ -61,6 +61,14 @@ def lib():
         L.dgo_gemm_f32_ref.argtypes = [f32p, f32p, u32, u32, u32, f32p]
         L.dgo_mqa_logits_ref.argtypes = [f32p, f32p, f32p, u32, u32, u32, u32p, u32p, u32p, u32, f32p]
         L.dgo_swiglu_f32.argtypes = [C.POINTER(C.c_uint16), u32, u32, u32, f32p]
+        L.dgo_exp_taylor6.restype = C.c_float
+        L.dgo_exp_taylor6.argtypes = [C.c_float]
+        L.dgo_hash_u32.restype = u32
+        L.dgo_hash_u32.argtypes = [C.c_uint64, u32]
+        L.dgo_quantize_output_fp8.argtypes = [f32p, u32, u32, u32, C.c_int, u32, u8p, u32p]
+        L.dgo_transform_sf_batched_host.argtypes = [f32p, u32, u32, u32, u32p]
+        L.dgo_set_threads.argtypes = [C.c_int]
+        L.dgo_get_threads.restype = C.c_int
         L.dgo_calc_diff.restype = C.c_double
         L.dgo_calc_diff.argtypes = [f32p, f32p, C.c_size_t]
         _lib = L
@@ -194,6 +202,35 @@ def swiglu_f32(inter_bf16_bits, inter):
     out = np.zeros((m, inter), dtype=np.float32)
     lib().dgo_swiglu_f32(_p(a, C.c_uint16), m, inter, a.shape[1], _p(out, C.c_float))
     return out
+
+
+def quantize_output_fp8(x, n, stochastic=False, seed=0):
+    """x f32 [m, in_stride >= n] -> (codes u8 [m, n], sf u32 [ceil(n/32/4), align4(m)]) (api.rs:1951-2011)."""
+    x = _c(x, np.float32)
+    m, in_stride = x.shape
+    data = np.zeros((m, n), dtype=np.uint8)
+    sf = np.zeros(sf_shape(m, n, 32), dtype=np.uint32)
+    lib().dgo_quantize_output_fp8(_p(x, C.c_float), m, n, in_stride, 1 if stochastic else 0, seed, _p(data, C.c_uint8),
+                                  _p(sf, C.c_uint32))
+    return data, sf
+
+
+def transform_sf_batched_host(sf, batch, mn):
+    sf = _c(sf, np.float32).reshape(batch, mn, -1)
+    sf_k = sf.shape[2]
+    out = np.zeros((batch * ceil_div(sf_k, 4), tma_aligned(mn)), dtype=np.uint32)
+    lib().dgo_transform_sf_batched_host(_p(sf, C.c_float), batch, mn, sf_k, _p(out, C.c_uint32))
+    return out
+
+
+def exp_taylor6(x): return float(lib().dgo_exp_taylor6(C.c_float(x)))
+def hash_u32(idx, seed): return int(lib().dgo_hash_u32(int(idx), int(seed)))
+
+
+def set_threads(n):
+    """Thread count of the oracle's OpenMP loops (returns the count in effect)."""
+    lib().dgo_set_threads(int(n))
+    return int(lib().dgo_get_threads())
 
 
 def calc_diff(x, y):
