@@ -92,9 +92,12 @@ class ClockSampler:
 # ------------------------------------------------------------------------------ reference arm
 def cpu_gemm_sample(rows, cols, k, seed=0):
     """Times the oracle's gemm_ref (quantised inputs prepared outside the timed region) on a
-    rows x cols x k sample of the grouped workload; returns (TFLOPS, seconds, threads)."""
+    rows x cols x k sample of the grouped workload; returns (TFLOPS, seconds, threads).  The OpenMP
+    thread count is set to the host's cores explicitly: launchers such as torch.distributed.run
+    export OMP_NUM_THREADS=1, and the CPU arm must run alike under every launch."""
     import numpy as np
     import oracle as o
+    threads = o.set_threads(os.cpu_count() or 1)
     rng = np.random.default_rng(seed)
     xa = rng.standard_normal((rows, k)).astype(np.float32)
     xb = rng.standard_normal((cols, k)).astype(np.float32)
@@ -104,7 +107,7 @@ def cpu_gemm_sample(rows, cols, k, seed=0):
     t0 = time.perf_counter()
     o.gemm_ref(a, b, m=rows, n=cols)
     dt = time.perf_counter() - t0
-    return 2.0 * rows * cols * k / dt / 1e12, dt, os.cpu_count()
+    return 2.0 * rows * cols * k / dt / 1e12, dt, threads
 
 
 def run_reference(args):
@@ -114,18 +117,16 @@ def run_reference(args):
     rows, cols, k = 512, 512, CFG["hidden"]
     for _ in range(args.warmup):
         cpu_gemm_sample(rows, cols, k)
-    t0 = time.perf_counter()
-    for s in range(args.steps):
-        cpu_gemm_sample(rows, cols, k, seed=s)
     # only the gemm_ref calls count: re-time them precisely
-    times = [cpu_gemm_sample(rows, cols, k, seed=s)[1] for s in range(args.steps)]
+    samples = [cpu_gemm_sample(rows, cols, k, seed=s) for s in range(args.steps)]
+    times, threads = [t[1] for t in samples], samples[0][2]
     dt = sum(times) / len(times)
     val = 2.0 * rows * cols * k / dt / 1e12
     sample = f"{rows} token rows x {cols} weight rows x K={k} of one expert (gemm_ref, f64 accumulation), per step"
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOPS", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "fp8_e4m3 (f64 accumulate on CPU)", "data": "synthetic", "config": workload_config(args.gpus),
-            "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": os.cpu_count(), "kind": "port", "sample": sample},
+            "cpu_baseline": {"value": val, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -136,6 +137,69 @@ def workload_config(n):
             "tokens_per_gpu": c["tokens_per_gpu"], "hidden_k": c["hidden"], "n": c["n_out"], "sf_granularity": c["gran"],
             "experts_per_gpu": c["num_experts"] // n, "parallelism": f"ep{n}",
             "l2": "inputs (>= 1 GB of weights touched per step) exceed the 126 MB L2; no flush needed"}
+
+
+# ------------------------------------------------------------------------------ parity of what is timed
+PARITY_TOL = {"fp8": 1e-3, "fp4": 2e-3}
+PARITY_MAX_ERR = 0.05      # largest element error allowed, in units of the sample's RMS
+
+
+def parity_ok(par, kind="fp8"):
+    return par is not None and par["calc_diff"] <= PARITY_TOL[kind] and par["max_err"] <= PARITY_MAX_ERR
+
+
+def parity_moe_step(torch, synth, out, x8, x_sf, topk_idx, topk_w, e_local, n_out, k, seed_of_rank, tokens=8, cols=256):
+    """Checks the output of one whole step (dispatch, grouped GEMM, return, combine; every GPU's share of it)
+    for a sample of this rank's tokens: for each of their top-k experts the oracle multiplies the token's
+    codes by the expert's weights, regenerated here from the owner rank's seed, rounds to bf16 like the GEMM,
+    and the copies are combined in f32 in top-k order like dg_moe_combine."""
+    import numpy as np
+    import oracle as o
+    from oracle import sampled
+    T = x8.shape[0]
+    ts = sampled.pick(T, tokens, 21, [0, T - 1])
+    cs = sampled.pick(n_out, cols, 22, sampled.edges(n_out, 224))
+    ci = torch.as_tensor(cs, device=x8.device)
+    idx = topk_idx[torch.as_tensor(ts, device=x8.device)].cpu().numpy()
+    tw = topk_w[torch.as_tensor(ts, device=x8.device)].cpu().numpy().astype(np.float32)
+    want = np.zeros((len(ts), len(cs)), dtype=np.float32)
+    for i, t in enumerate(ts):
+        ga = sampled.golden_rows(x8, x_sf.buf, [int(t)], o.FP8, 128, k)
+        acc = np.zeros(len(cs), dtype=np.float32)
+        for j, g in enumerate(idx[i]):
+            codes, words = synth.expert_weight(seed_of_rank(int(g) // e_local), int(g) % e_local, n_out, k, x8.device)
+            gb = sampled.golden_rows(codes, words, cs, o.FP8, 128, k)
+            y = o.bf16_bits_to_f32(o.f32_to_bf16_bits_np(o.gemm_ref(ga, gb, m=1, n=len(cs))))[0]
+            acc = acc + np.float32(tw[i, j]) * y
+        want[i] = acc
+    got = out[torch.as_tensor(ts, device=x8.device)][:, ci].float().cpu().numpy()
+    d, e = sampled.compare(got, want)
+    return {"calc_diff": d, "max_err": e, "sample": f"{len(ts)} tokens x {len(cs)} output columns x top-{idx.shape[1]} experts at full K"}
+
+
+def ep_check(torch, dist, moe, synth, group, rank, world, dev):
+    """Before the timed steps at N > 1: a small expert-parallel case in which every rank also holds all the
+    experts and runs the single-GPU step on its own tokens; the expert-parallel output must equal it bit
+    for bit (same weights, same combination order), over two steps through the reused buffers."""
+    from deepgemm import Dtype, Operand, SfGran, SfTensor, quant_mx
+    E, topk, T, K, N = 4 * world, 2, 256, 512, 256
+    full = synth.random_expert_weights(E, N, K, seed=70, device=dev)
+    e_local = E // world
+    rows = slice(rank * e_local * N, (rank + 1) * e_local * N)
+    local = Operand.k_major(Dtype.Fp8, N, K, K, SfTensor(full.sf.rows, e_local * N, SfGran.G128, full.sf.buf[:, rows].contiguous()),
+                            full.data[rows].contiguous())
+    ep = moe.ExpertParallelMoE(local, E, group)
+    single = moe.ExpertParallelMoE(full, E, None)
+    same = True
+    for step in range(2):
+        g = torch.Generator(device=dev).manual_seed(50 + rank + 100 * step)
+        x8, x_sf = quant_mx(torch.randn((T, K), device=dev, generator=g), T, K, Dtype.Fp8, 128)
+        idx, w = synth.random_topk_routing(T, E, topk, seed=60 + rank + 100 * step, device=dev)
+        same = same and torch.equal(ep.forward(x8, x_sf, idx, w), single.forward(x8, x_sf, idx, w))
+    ep.close()
+    flag = torch.tensor([1 if same else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return "bit-identical" if flag.item() == 1 else "MISMATCH"
 
 
 # ------------------------------------------------------------------------------ our arm
@@ -182,6 +246,7 @@ def main():
 
     E, topk, T, K, N = CFG["num_experts"], CFG["topk"], CFG["tokens_per_gpu"], CFG["hidden"], CFG["n_out"]
     e_local = E // world
+    ep_verdict = ep_check(torch, dist, moe, synth, group, rank, world, dev) if world > 1 else None
     weights = synth.random_expert_weights(e_local, N, K, seed=1000 + rank, device=dev)
     layer = moe.ExpertParallelMoE(weights, E, group)
     gx = torch.Generator(device=dev).manual_seed(rank)
@@ -302,10 +367,21 @@ def main():
         dist.all_reduce(ms_t, op=dist.ReduceOp.MAX)
     ms_e2e = ms_t.item() / e2e_steps
 
+    # parity of what was timed: one more resident step, sampled tokens of rank 0 against the oracle
+    parity = None
+    if rank == 0 or world > 1:
+        out_check = step_resident()
+        dg.poll_device_status()
+        if rank == 0:
+            parity = parity_moe_step(torch, synth, out_check, x8, x_sf, topk_idx, topk_w, e_local, N, K, lambda r: 1000 + r)
+        del out_check
     value = flops_per_step / (ms_step * 1e-3) / 1e12
     e2e_value = flops_per_step / (ms_e2e * 1e-3) / 1e12
     gemm_tflops = 2.0 * T * topk * N * K / (gemm_ms * 1e-3) / 1e12       # this rank's launch
-    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    # the timed region lasts a fraction of a second at boost clocks: the burst figure is the denominator
+    # (the sustained one was measured over seconds under the power cap)
+    fp8_peak = 2.0 * peaks["bf16_tflops"]
+    h2d_bytes = x_host.numel() * 4 + idx_host.numel() * 4 + w_host.numel() * 4
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
@@ -313,8 +389,10 @@ def main():
                                                                          "expert_slices": len(layer._slice_bounds()) - 1}
                                                                         if world > 1 else {})),
         "e2e": {"value": e2e_value, "unit": "TFLOPS", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": x_host.numel() * 4 + idx_host.numel() * 4 + w_host.numel() * 4,
+                "h2d_bytes_per_step": h2d_bytes,
                 "d2h_bytes_per_step": T * N * 2,
+                # every rank uploads its own tokens: bytes of one rank over the step time all ranks share
+                "h2d_gbs_per_rank": h2d_bytes / (ms_e2e * 1e-3) / 1e9,
                 "steps": e2e_steps,
                 "path": "pinned host f32 tokens -> quant_mx -> expert-parallel grouped GEMM -> combine -> pinned host bf16; "
                         "upload, compute and download of consecutive steps overlap on three streams"},
@@ -326,10 +404,22 @@ def main():
                      "traffic": 10.07e9 * (T / 16384.0) if CFG["num_experts"] == 256 else None,
                      "traffic_source": "profiles/gemm_fp8_grouped_contiguous__moe_prefill.md",
                      "algorithmic_bytes_per_launch": float(T * topk * 1.125 * K + e_local * N * K + T * topk * 1.125 * N * 2),
-                     "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peak_kind}); FP8 runs at twice the bf16 rate",
+                     "peak_source": f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({peak_kind}); FP8 runs at twice the bf16 rate; "
+                                    "the timed region is shorter than a second",
                      "frac_of_nominal_4500": gemm_tflops / NOMINAL_FP8_TFLOPS, "launch_ms": gemm_ms,
                      "algorithmic_flops_per_launch": 2.0 * T * topk * N * K},
     }
+    if rank == 0:
+        line["parity"] = parity
+        if not parity_ok(parity):
+            # a step whose sampled outputs disagree with the oracle has no throughput to report
+            line["error"] = "parity check failed"
+            line["value"], line["e2e"]["value"], line["roofline"]["achieved"], line["roofline"]["frac"] = None, None, None, None
+        if world > 1:
+            line["ep_check"] = ep_verdict
+            if ep_verdict != "bit-identical":
+                line["error"] = "expert-parallel check failed"
+                line["value"], line["e2e"]["value"] = None, None
     if rank == 0 and world == 1:
         v, dt, cores = cpu_gemm_sample(1024, 1024, K)
         line["cpu_baseline"] = {"value": v, "unit": "TFLOPS", "cores": cores, "kind": "port", "seconds": dt,
@@ -383,9 +473,18 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
 
     g = torch.Generator(device=dev).manual_seed(0)
     res = {}
+    import numpy as np
+    import oracle as o
+    from oracle import sampled
 
     def want(name):
         return only is None or name.startswith(only)
+
+    def gated(entry, kind="fp8"):
+        """A workload whose sampled outputs disagree with the oracle reports its parity figures and no throughput."""
+        if parity_ok(entry.get("parity"), kind):
+            return entry
+        return {"parity": entry.get("parity"), "error": "parity check failed"}
 
     def dense(kind, m, n, k):
         if kind == "fp8":
@@ -408,8 +507,15 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
         ms = timeit(lambda: dg.gemm_nt(a, b, out))
         tf = 2.0 * m * n * k / ms / 1e9
         byts = (m * k + n * k) * (1 if kind == "fp8" else 0.5) + m * n * 2
-        return {"ms": ms, "tflops": tf, "frac_of_measured_tensor_peak": tf / peak, "hbm_gbs": byts / ms / 1e6,
-                "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
+        # the output of the last timed call, sampled: 128 rows x 256 columns over the full K against gemm_ref
+        odt, gran = (o.FP8, 128) if kind == "fp8" else (o.FP4, 32)
+        cfg = dg.get_gemm_config(Dtype.Fp8 if kind == "fp8" else Dtype.Fp4, 0, m, n, k)
+        rows = sampled.pick(m, 128, 31, sampled.edges(m, cfg["block_m"]))
+        cols = sampled.pick(n, 256, 32, sampled.edges(n, cfg["block_n"]))
+        par = sampled.check_gemm_sample(a.data, a.sf.buf, b.data, b.sf.buf, out.data, rows, cols, odt, gran, odt, b.sf.gran.k(), k)
+        return gated({"ms": ms, "tflops": tf, "frac_of_measured_tensor_peak": tf / peak, "hbm_gbs": byts / ms / 1e6,
+                      "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"],
+                      "tile": f"{cfg['block_m']}x{cfg['block_n']}", "parity": par}, kind)
 
     for m in (128, 4096):
         for n, k in ((24576, 1536), (7168, 16384), (4096, 7168)):
@@ -431,9 +537,16 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
         ms = timeit(lambda: dg.m_grouped_fp8_gemm_nt_masked(a, w, out, masked, G, 128))
         sm = int(masked.sum().item())
         byts = sm * k + G * n * k + sm * n * 2
-        res["m_grouped_fp8_gemm_nt_masked_G32"] = {"ms": ms, "sum_masked_m": sm, "tflops": 2.0 * sm * n * k / ms / 1e9,
-                                                   "hbm_gbs": byts / ms / 1e6,
-                                                   "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
+        mm = masked.cpu().numpy()
+        cols = sampled.pick(n, 256, 33, sampled.edges(n, 224))
+        worst = {"calc_diff": 0.0, "max_err": 0.0}
+        for gi in [int(x) for x in np.nonzero(mm > 0)[0][[0, len(np.nonzero(mm > 0)[0]) // 2, -1]]]:
+            rows = gi * max_m + sampled.pick(int(mm[gi]), 24, gi, [0, int(mm[gi]) - 1, 127, 128])
+            par = sampled.check_gemm_sample(da, sa.buf, w.data, w.sf.buf, out.data, rows, cols, o.FP8, 128, o.FP8, 128, k, b_row_offset=gi * n)
+            worst = {key: max(worst[key], par[key]) for key in worst}
+        res["m_grouped_fp8_gemm_nt_masked_G32"] = gated({"ms": ms, "sum_masked_m": sm, "tflops": 2.0 * sm * n * k / ms / 1e9,
+                                                         "hbm_gbs": byts / ms / 1e6,
+                                                         "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"], "parity": worst})
 
     # whole MoE feed-forward layer (gate/up GEMM -> SwiGLU + FP8 re-quantisation -> down GEMM -> combine),
     # 256 experts, top-8, 16384 tokens, hidden 7168, intermediate 2048: the layer around the headline GEMM
@@ -466,8 +579,19 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
         ms = timeit(lambda: dg.mqa_logits_f32(q, kv, scale, wq, ks, ke, T, S, H, D, logits, S), iters=5)
         pairs = int(ke.sum().item())
         tf = 2.0 * H * D * pairs / ms / 1e9
-        res["mqa_logits_T4096_S32768_H64_D128"] = {"ms": ms, "tflops": tf,
-                                                   "frac_of_measured_tensor_peak": tf / (2 * peaks["bf16_tflops"])}
+        qs = sampled.pick(T, 32, 34, [0, 1, T - 1, 2047, 2048])
+        ends = S - T + qs + 1
+        js = sampled.pick(S, 2048, 35, [0, 127, 128, S - 1] + [int(e) - 1 for e in ends])
+        qi, ji = torch.as_tensor(qs, device=dev), torch.as_tensor(js, device=dev)
+        ref = o.mqa_logits_ref(q.view(torch.float8_e4m3fn)[qi].float().cpu().numpy(),
+                               (kv.view(torch.float8_e4m3fn)[ji].float() * scale[ji][:, None]).cpu().numpy(), wq[qi].cpu().numpy(),
+                               np.zeros(len(qs), np.uint32), np.full(len(qs), len(js), np.uint32))
+        got = logits[qi][:, ji].cpu().numpy()
+        valid = js[None, :] < ends[:, None]
+        dq, eq = sampled.compare(got[valid], ref[valid], out_is_bf16=False)
+        res["mqa_logits_T4096_S32768_H64_D128"] = gated({"ms": ms, "tflops": tf,
+                                                         "frac_of_measured_tensor_peak": tf / (2 * peaks["bf16_tflops"]),
+                                                         "parity": {"calc_diff": dq, "max_err": eq}})
 
     # quant_mx bandwidth
     for (m, k, dt, gran, name) in ((16384, 7168, Dtype.Fp8, 128, "fp8_g128"), (16384, 7168, Dtype.Fp8, 32, "fp8_g32"),
@@ -477,7 +601,16 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
         x = torch.randn((m, k), device=dev, generator=g)
         ms = timeit(lambda: dg.quant_mx(x, m, k, dt, gran))
         byts = 4 * m * k + (m * k if dt == Dtype.Fp8 else m * k // 2) + 4 * (-(-(k // gran) // 4)) * m
-        res[f"quant_mx_{name}_{m}x{k}"] = {"ms": ms, "gbs": byts / ms / 1e6, "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"]}
+        # bytes of 64 sampled rows (codes and their scale-factor columns) against the oracle's quantiser
+        rs = sampled.pick(m, 64, 36, [0, 1, 31, 32, m - 1])
+        ri = torch.as_tensor(rs, device=dev)
+        codes, sft = dg.quant_mx(x, m, k, dt, gran)
+        wc, ws = o.quant_mx_host(x[ri].cpu().numpy(), o.FP8 if dt == Dtype.Fp8 else o.FP4, gran)
+        same = bool(np.array_equal(codes[ri].cpu().numpy(), wc) and
+                    np.array_equal(sft.buf[:, ri].cpu().numpy().view(np.uint32), ws[:, :len(rs)]))
+        entry = {"ms": ms, "gbs": byts / ms / 1e6, "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"],
+                 "parity": "bytes equal on 64 sampled rows" if same else "MISMATCH"}
+        res[f"quant_mx_{name}_{m}x{k}"] = entry if same else {"parity": "MISMATCH", "error": "parity check failed"}
     # SwiGLU + FP8 re-quantisation between the two GEMMs of the FFN layer (HBM-bound): 139264 rows
     # (131072 copies + padding) x 2 * 2048 bf16 in, 2048 codes + scale factors out
     if want("swiglu_quant_139264x2048"):

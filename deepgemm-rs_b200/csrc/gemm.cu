@@ -73,7 +73,6 @@ struct GemmParams {
     uint32_t k_splits;          // dense GEMM with few tiles: K is cut into this many ranges (1 = off)
     uint32_t kb_per_split;      // k-blocks per range (a multiple of 4)
     float* split_ws;            // f32 partial tiles [k_splits][m][n] when k_splits > 1
-    uint32_t* split_cnt;        // arrival counters [tiles][4] of the K ranges, zero between launches
     float alpha;                // factor on the product before the output cast (1 = none)
     uint32_t idesc;             // tcgen05 instruction descriptor
     uint32_t b_group_rows;      // rows of B per group (grouped GEMMs); >= n when only a column range is computed
@@ -95,7 +94,6 @@ struct Tile {
     uint32_t b_row;     // first row in (stacked) B / SFB-column coordinates
     uint32_t kb0, kb1;  // k-block range of this work item
     uint32_t split;     // index of the K range (0 without split-K)
-    uint32_t tile;      // split-K: index of the output tile
     uint32_t mn_a;      // batched: first row of the tile inside its batch (SFA column, MN coordinate of an MN-major A)
     uint32_t batch;     // batched: index of the batch
     bool skip;
@@ -110,8 +108,6 @@ struct Tile {
 // so that a CTA that is slowed down (an SM shared with another kernel, a slow tile) simply takes
 // fewer tiles instead of holding up the whole grid.
 constexpr uint32_t kSchedRing = 4;
-constexpr uint32_t kSplitHeaderBytes = 16384;   // split-K: 4 arrival counters per output tile in front of the partial tiles
-enum : uint32_t { kWaitSched = 8 };
 constexpr uint32_t kSchedRunBytes = 4096; // dynamic schedule: room for the run list behind the barrier block
 constexpr uint32_t kSchedMaxRuns = kSchedRunBytes / 2 - 1;   // runs of equal m_indices entries the scheduler warp keeps (u16 first blocks + end)
 struct SchedRing {
@@ -193,7 +189,6 @@ struct Scheduler {
                 // work item = (tile, K range); ranges of one tile are neighbours in the order
                 if (id >= p.num_m_blocks * p.num_n_blocks * p.k_splits) return false;
                 tile = id / p.k_splits;
-                t.tile = tile;
                 t.split = id - tile * p.k_splits;
                 t.kb0 = t.split * p.kb_per_split;
                 t.kb1 = min(p.num_k_blocks, t.kb0 + p.kb_per_split);
@@ -870,48 +865,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 }
                 store_chunk(r, col0);
             }
-            if (SPLIT) {
-                // The K ranges of a tile finish in any order.  Each warp counts the arrivals for its 32
-                // rows; the warp that arrives last adds the partial tiles in range order (always the
-                // same order, so results repeat bit for bit), rounds once and writes D.  The counter
-                // goes back to zero for the next launch.
-                __threadfence();
-                __syncwarp();
-                uint32_t* cnt = p.split_cnt + t.tile * 4u + q;
-                uint32_t arrived = 0;
-                if (lane == 0) arrived = atomicAdd(cnt, 1u);
-                arrived = __shfl_sync(0xffffffffu, arrived, 0);
-                if (arrived + 1u == p.k_splits) {
-                    __threadfence();
-                    if (lane == 0) *cnt = 0u;
-                    for (uint32_t c = 0; c < chunks; ++c) {
-                        const uint32_t col0 = t.n0 + c * 32u;
-                        if (!row_ok || col0 >= p.n) continue;
-                        uint32_t r[32];
-                        float acc[32];
-#pragma unroll
-                        for (uint32_t i = 0; i < 32; ++i) acc[i] = 0.f;
-                        const bool vec = p.n % 4 == 0 && col0 + 32u <= p.n;
-                        for (uint32_t sp = 0; sp < p.k_splits; ++sp) {
-                            const float* src = p.split_ws + ((size_t)sp * p.m + row) * p.n + col0;
-                            if (vec) {
-#pragma unroll
-                                for (uint32_t i = 0; i < 8; ++i) {
-                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src) + i);
-                                    acc[4 * i] += v.x; acc[4 * i + 1] += v.y; acc[4 * i + 2] += v.z; acc[4 * i + 3] += v.w;
-                                }
-                            } else {
-#pragma unroll
-                                for (uint32_t i = 0; i < 32; ++i)
-                                    if (col0 + i < p.n) acc[i] += __ldcg(src + i);
-                            }
-                        }
-#pragma unroll
-                        for (uint32_t i = 0; i < 32; ++i) r[i] = __float_as_uint(acc[i]);
-                        store_chunk(r, col0);
-                    }
-                }
-            }
         }
     }
 
@@ -930,6 +883,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             p.tile_counter[0] = 0;
             p.tile_counter[1] = 0;
             __threadfence();
+        }
+    }
+}
+
+// Second pass of a split-K GEMM: D[r][c] (+)= alpha * sum over the K ranges, added in range order (fixed, so
+// results repeat bit for bit), rounded once to the output type.  Four columns per thread; launched with
+// the programmatic-serialization attribute, so its blocks are resident when the GEMM's last CTA leaves.
+__global__ void __launch_bounds__(256) split_reduce_kernel(const float* __restrict__ ws, uint32_t splits, uint32_t m, uint32_t n,
+                                                          void* __restrict__ d, uint64_t ldd, uint32_t out_f32, uint32_t accumulate,
+                                                          float alpha) {
+    griddep_wait();
+    const uint32_t n4 = (n + 3u) / 4u;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)m * n4) return;
+    const uint32_t r = (uint32_t)(idx / n4), c = (uint32_t)(idx % n4) * 4u;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const bool vec = n % 4u == 0;
+    for (uint32_t s = 0; s < splits; ++s) {
+        const float* src = ws + ((size_t)s * m + r) * n + c;
+        if (vec) {
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(src));
+            acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+        } else {
+            for (uint32_t i = 0; i < 4u; ++i) if (c + i < n) acc[i] += __ldcg(src + i);
+        }
+    }
+    for (uint32_t i = 0; i < 4u; ++i) {
+        if (c + i >= n) break;
+        const float v = acc[i] * alpha;
+        if (out_f32) {
+            float* o = reinterpret_cast<float*>(d) + (size_t)r * ldd + c + i;
+            *o = accumulate ? *o + v : v;
+        } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(d) + (size_t)r * ldd + c + i;
+            __nv_bfloat16 b = __float2bfloat16_rn(v);
+            if (accumulate) b = __float2bfloat16_rn(__bfloat162float(*o) + __bfloat162float(b));
+            *o = b;
         }
     }
 }
@@ -1026,7 +1016,6 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
         for (uint32_t bn = 64; bn <= 224; bn += 32) {
             if (forced_bn && bn != forced_bn) continue;
             const uint32_t tiles = ceil_div(n, bn);
-            if (tiles * 16u > kSplitHeaderBytes) continue;   // 4 counters of 4 bytes per tile
             for (uint32_t sp = 1; sp <= 16; ++sp) {
                 const uint32_t per = align_up(ceil_div(p.num_k_blocks, sp), 4);
                 if (ceil_div(p.num_k_blocks, per) != sp) continue;
@@ -1037,7 +1026,7 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
             }
         }
         const uint32_t forced_sp = env_u32("DG_SPLIT_K", 1);
-        if (forced_sp > 1 && ceil_div(n, best_bn) * 16u <= kSplitHeaderBytes) best_splits = forced_sp;
+        if (forced_sp > 1) best_splits = forced_sp;
         p.block_n = best_bn;
         p.num_n_blocks = ceil_div(n, p.block_n);
         p.kb_per_split = align_up(ceil_div(p.num_k_blocks, best_splits), 4);
@@ -1246,6 +1235,13 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     p.b_group_rows = n_full;
     p.b_row_offset = n_begin;
     p.alpha = alpha;
+    if (mixed) {
+        // The copy that unpacks FP4 codes into byte containers reports the bytes it read (two codes per
+        // byte), not the bytes it wrote, to the stage's barrier (measured: with the shared-memory size the
+        // barrier never completes).
+        const uint32_t a_b = kBlockM * 128u, b_b = p.block_n / plan.cluster * 128u;
+        p.tx_ab = (a->dtype == DG_FP4 ? a_b / 2 : a_b) + (b->dtype == DG_FP4 ? b_b / 2 : b_b);
+    }
     p.sf_rows_a = has_sf ? ceil_div(k, gran_a * 4) : 0u;
     p.sf_rows_b = has_sf ? ceil_div(k, gran_b * 4) : 0u;
     // instruction descriptor: operand formats (mxf8f6f4: E4M3 = 0, E2M1 = 5; mxf4: E2M1 = 1), tile shape, majors
@@ -1282,22 +1278,18 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
         tsa = ta; tsb = tb;
     }
     if (p.k_splits > 1) {
-        // Scratch for the partial tiles, behind a header of arrival counters (zero between launches:
-        // cleared when the buffer is allocated, put back to zero by the kernel).  One buffer per
-        // (thread, device, stream), grown on demand with stream-ordered allocation and kept for the
-        // next call (work on one stream is ordered, so consecutive calls may share it; allocating per
-        // call costs more host time than the GEMM).
-        struct SplitWs { cudaStream_t stream; int device; uint8_t* ptr; size_t bytes; };
+        // Scratch for the partial tiles: one buffer per (thread, device, stream), grown on demand with
+        // stream-ordered allocation and kept for the next call (work on one stream is ordered, so
+        // consecutive calls may share it; allocating per call costs more host time than the GEMM).
+        struct SplitWs { cudaStream_t stream; int device; float* ptr; size_t bytes; };
         static thread_local SplitWs cache[8] = {};
         static thread_local int cache_next = 0;
-        const size_t need = kSplitHeaderBytes + sizeof(float) * (size_t)p.k_splits * m * n;
-        uint8_t* graph_ws = nullptr;
-        uint8_t* ws = nullptr;
+        const size_t need = sizeof(float) * (size_t)p.k_splits * m * n;
+        float* graph_ws = nullptr;
         if (capturing != cudaStreamCaptureStatusNone) {
-            // inside a graph capture the buffer must belong to the graph: allocate, clear and free per call
+            // inside a graph capture the buffer must belong to the graph: allocate and free per call
             DG_CUDA_CHECK(cudaMallocAsync(&graph_ws, need, s));
-            DG_CUDA_CHECK(cudaMemsetAsync(graph_ws, 0, kSplitHeaderBytes, s));
-            ws = graph_ws;
+            p.split_ws = graph_ws;
         } else {
             SplitWs* slot = nullptr;
             for (auto& c : cache)
@@ -1310,19 +1302,32 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
             if (slot->bytes < need) {
                 if (slot->ptr) cudaFreeAsync(slot->ptr, s);
                 *slot = SplitWs{};
-                uint8_t* fresh = nullptr;
+                float* fresh = nullptr;
                 DG_CUDA_CHECK(cudaMallocAsync(&fresh, need, s));
-                DG_CUDA_CHECK(cudaMemsetAsync(fresh, 0, kSplitHeaderBytes, s));
                 *slot = SplitWs{s, dev->device, fresh, need};
             }
-            ws = slot->ptr;
+            p.split_ws = slot->ptr;
         }
-        p.split_cnt = reinterpret_cast<uint32_t*>(ws);
-        p.split_ws = reinterpret_cast<float*>(ws + kSplitHeaderBytes);
         int32_t lst = DG_OK;
         if (kind == kFp8) lst = launch<kFp8, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
         else if (kind == kFp4) lst = launch<kFp4, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
         else lst = launch<kBf16, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
+        if (lst == DG_OK) {
+            const size_t threads = (size_t)m * ((n + 3) / 4);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((uint32_t)((threads + 255) / 256));
+            cfg.blockDim = dim3(256);
+            cfg.stream = s;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = pdl_enabled() ? 1 : 0;
+            cudaError_t e = cudaLaunchKernelEx(&cfg, split_reduce_kernel, (const float*)p.split_ws, p.k_splits, m, n, out->data,
+                                               (uint64_t)out->stride, p.out_f32, p.accumulate, alpha);
+            if (e != cudaSuccess) lst = fail(DG_ERR_DRIVER, "split-K reduction launch failed: %s", cudaGetErrorString(e));
+            else note_launch();
+        }
         if (graph_ws) cudaFreeAsync(graph_ws, s);
         return lst;
     }

@@ -89,29 +89,6 @@ __host__ __device__ constexpr uint32_t make_idesc_f8(uint32_t m, uint32_t n) {
     return (1u << 4) /*D=f32*/ | ((n >> 3) << 17) | ((m >> 4) << 24);  // A, B = E4M3 (format 0), K-major
 }
 
-__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
-    uint64_t d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ float sum_f32x2(uint64_t v) {
-    float lo, hi;
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-    return lo + hi;
-}
-
-#ifdef DG_MQA_TRACE
-__device__ unsigned long long g_mqa_trace[8 * 256];
-#define MQA_STAMP(row, idx) do { if (blockIdx.x == 0 && lane == 0 && (idx) < 256u) g_mqa_trace[(row) * 256 + (idx)] = clock64(); } while (0)
-#else
-#define MQA_STAMP(row, idx) do { } while (0)
-#endif
-
 template <bool SCALED>
 __global__ void __launch_bounds__(kMqaMaxThreads, 1)
 mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
@@ -154,6 +131,8 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    griddep_wait();                 // the kernel before this one in the stream produced q / kv / weights
+    griddep_launch_dependents();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
     const uint32_t acc_stride = SCALED ? 192u : 256u;
     const uint32_t num_mma = p.head_dim / 32u;
@@ -216,9 +195,7 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 ++acount;
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull))) break;
                 if (SCALED && !(ok = DG_WARP_WAIT(smem_u32(&bars->kv_ready[stage]), phase, wc, kWaitSfReady))) break;
-                MQA_STAMP(0, acount - 1u);
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
-                MQA_STAMP(1, acount - 1u);
                 tc_fence_after();
                 const uint32_t kaddr = base + p.off_kv + stage * p.kv_stage_bytes;
                 const uint64_t kv_desc = make_smem_desc(kaddr, p.sbo, 0, p.layout);
@@ -311,15 +288,13 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             // the slowest one (it waits here), so a buffer is never rewritten while still read.
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->w_full[wb]));
-            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->w_full[wb]), wphase, wc, kWaitPeer));
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->w_full[wb]), wphase, wc, kWaitWeights));
             if (!ok) break;
             for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
                 const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
                 ++acount;
-                if (warp == 4 || warp == 12) MQA_STAMP(2, acount - 1u);
                 ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull));
                 if (!ok) break;
-                if (warp == 4 || warp == 12) MQA_STAMP(3, acount - 1u);
                 tc_fence_after();
                 const uint32_t j = kb * kMqaBlockKv + quarter * 32u + lane;
                 float scale = 1.f;
@@ -378,7 +353,6 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 tmem_ld_x16(taddr, va);
                 load_w(wa, 0);
                 tmem_ld_wait();
-                if (warp == 4 || warp == 12) MQA_STAMP(4, acount - 1u);
                 for (uint32_t u = 0; u < nunits; u += 2) {
                     if (u + 1 < nunits) { tmem_ld_x16(taddr + (u + 1) * 16u, vb); load_w(wb4, u + 1); } else release();
                     consume(va, wa);
@@ -389,7 +363,6 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         if (u + 2 < nunits) tmem_ld_wait();
                     }
                 }
-                if (warp == 4 || warp == 12) MQA_STAMP(5, acount - 1u);
             }
         }
     }
@@ -402,13 +375,6 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
 }
 
-#ifdef DG_MQA_TRACE
-}  // namespace dg
-extern "C" __attribute__((visibility("default"))) int dg_debug_mqa_trace(unsigned long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, dg::g_mqa_trace, sizeof(dg::g_mqa_trace));
-}
-namespace dg {
-#endif
 // ============================================================================ host side
 static int32_t check_mqa_common(uint32_t num_tokens, uint32_t num_kv, uint32_t num_heads, uint32_t head_dim,
                                 uint32_t logits_stride, const void* ks, const void* ke, const void* w, const void* logits) {
@@ -481,9 +447,18 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     DG_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     uint32_t grid = (uint32_t)dev->sm_count;
     if (p.num_q_blocks < grid) grid = p.num_q_blocks;
-    fn<<<grid, 128u + 128u * p.ep_groups, smem_bytes, static_cast<cudaStream_t>(stream)>>>(tq, tkv, tqsf, tkvsf, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(128u + 128u * p.ep_groups);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set-up overlaps the previous kernel's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p));
     dg::note_launch();
-    DG_CUDA_CHECK(cudaGetLastError());
     return DG_OK;
 }
 
@@ -520,6 +495,8 @@ int32_t dg_mqa_logits(const dg_operand_t* q, const dg_operand_t* kv, const void*
     if (q->sf.gran != 32 || kv->sf.gran != 32) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: scale granularity must be 32");
     if (q->rows != num_tokens * num_heads || q->k != head_dim || kv->rows != num_kv_tokens || kv->k != head_dim)
         return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q must be [num_tokens*num_heads, head_dim] and kv [num_kv_tokens, head_dim]");
+    if (q->major != DG_MAJOR_K || kv->major != DG_MAJOR_K || q->outer_stride != head_dim || kv->outer_stride != head_dim)
+        return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q and kv must be dense K-major rows (outer_stride == head_dim)");
     if (q->sf.cols < dg::align_up(q->rows, 4) || kv->sf.cols < dg::align_up(kv->rows, 4) || q->sf.rows < 1 || kv->sf.rows < 1)
         return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: scale-factor tensors too small");
     return dg::run_mqa<true>(q->data, kv->data, q->sf.data, q->sf.cols, kv->sf.data, kv->sf.cols, nullptr, weights_bf16,

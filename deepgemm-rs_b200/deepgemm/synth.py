@@ -27,15 +27,25 @@ def block128_quant_fp8(x):
     return codes, sf.to(torch.int32)
 
 
+def expert_seed(seed, expert):
+    """Seed of one expert's weight matrix: experts are generated independently, so that any one of them
+    can be regenerated alone (a parity check on one GPU can rebuild an expert that lives on another)."""
+    return seed * 1000003 + expert
+
+
+def expert_weight(seed, expert, n, k, device):
+    """(codes u8 [n, k], packed SF words i32 [k/512, n]) of expert `expert` of the stack seeded `seed`."""
+    g = torch.Generator(device=device).manual_seed(expert_seed(seed, expert))
+    return block128_quant_fp8(torch.randn((n, k), device=device, generator=g))
+
+
 def random_expert_weights(num_local_experts, n, k, seed, device):
     """Stacked FP8 weights [E*n, k] + SF of the stacked matrix, generated and quantised expert
     by expert so that no f32 tensor of the whole stack is ever held."""
-    g = torch.Generator(device=device).manual_seed(seed)
     codes = torch.empty((num_local_experts * n, k), dtype=torch.uint8, device=device)
     sf = torch.empty((k // 512, num_local_experts * n), dtype=torch.int32, device=device)
     for e in range(num_local_experts):
-        w = torch.randn((n, k), device=device, generator=g)
-        c, s = block128_quant_fp8(w)
+        c, s = expert_weight(seed, e, n, k, device)
         codes[e * n:(e + 1) * n] = c
         sf[:, e * n:(e + 1) * n] = s
     op = Operand.k_major(Dtype.Fp8, n, k, k, SfTensor(k // 512, num_local_experts * n, SfGran.G128, sf), codes)

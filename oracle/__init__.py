@@ -4,3 +4,4 @@ Only the tests, the smoke check and the benchmark's cpu_baseline / reference arm
 this package.  The shipped library never does.
 """
 from .oracle import *  # noqa: F401,F403
+from . import sampled  # noqa: F401,E402

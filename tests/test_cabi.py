@@ -117,3 +117,19 @@ def test_peer_and_ffn_entry_checks(L):
     assert L.dg_peer_copy(None, 0x1000, 16, None) == 3
     assert L.dg_peer_copy(0x1000, 0x2000, 0, None) == 0                                # empty copy is a no-op
     assert L.dg_m_grouped_gemm_nt_contiguous_rowptr(None, None, 0x1000, 1, 1, 0x2000, None, 0, 0, None) == 3
+
+
+def test_layout_batch_and_output_quant_checks(L):
+    a, b, o = _op(0, 128, 256), _op(0, 64, 256), _out(128, 64)
+    for fn, who in ((L.dg_gemm_nn, "B"), (L.dg_gemm_tn, "A"), (L.dg_gemm_tt, "A")):
+        assert fn(C.byref(a), C.byref(b), C.byref(o), 0, None) == 3 and f"{who} must be described as an MN-major view" in _err(L)
+    amn = _lib.OperandC(0, 1, 128, 256, 64, a.sf, 0x1000)            # MN-major pitch below its rows
+    assert L.dg_gemm_tn(C.byref(amn), C.byref(b), C.byref(o), 0, None) == 3 and "MN-major outer_stride" in _err(L)
+    a2 = _op(2, 128, 256, sf=False)
+    assert L.dg_gemm_nt(C.byref(a2), C.byref(b), C.byref(o), 0, None) == 3 and "cannot be multiplied" in _err(L)
+    assert L.dg_fp8_bmm(C.byref(a2), C.byref(a2), C.byref(o), 2, 0, None) == 3 and "must be FP8" in _err(L)
+    assert L.dg_bmm(C.byref(a), C.byref(b), C.byref(o), 0, 0, None) == 3 and "num_groups must be positive" in _err(L)
+    assert L.dg_bmm(C.byref(a), C.byref(b), C.byref(o), 2, 0, None) == 3 and "scale-factor tensor" in _err(L)   # arenas hold one batch only
+    assert L.dg_transform_sf_batched(0x1000, 0, 4, 4, 0x2000, None) == 3 and "batch must be nonzero" in _err(L)
+    assert L.dg_quantize_output_fp8(0x1000, 16, 100, 100, 0, 0, 0x2000, 0x3000, None) == 3 and "n % 32 == 0" in _err(L)
+    assert L.dg_quantize_output_fp8(0x1000, 16, 128, 64, 0, 0, 0x2000, 0x3000, None) == 3                          # pitch below n

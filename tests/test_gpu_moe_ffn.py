@@ -1,10 +1,10 @@
 """The MoE feed-forward layer beyond the reference's moe_grouped_layer (which stops after the gate/up
 GEMM, deepgemm/src/api_serving.rs:371-375): SwiGLU + FP8 re-quantisation (dg_swiglu_quant) against the
 oracle's swiglu_f32 + quant_mx_host, and the whole layer (two grouped GEMMs) against the oracle
-composed copy by copy.  Tolerances: the quantiser input passes through expf, which the GPU and the host
-library round differently in the last place, so a code may land on the neighbouring grid point:
-at most 0.2 % of the code bytes may differ and the dequantised tensors must agree to calc_diff 1e-6;
-the layer output is held to the FP8 GEMM contract, calc_diff <= 1e-3."""
+composed copy by copy.  dg_swiglu_quant is held to the oracle byte for byte: both evaluate the same
+operation-by-operation exponential (the platform expf differs between machines in its last bit; the
+oracle's own test bounds the distance of the spelled-out exponential from expf).  The layer output is
+held to the FP8 GEMM contract, calc_diff <= 1e-3."""
 import numpy as np
 import pytest
 import torch
@@ -16,10 +16,11 @@ from helpers import dev, randn
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("m,inter,gran,pad", [(200, 512, 128, 0), (37, 256, 32, 64), (129, 384, 128, 8), (5, 128, 32, 0)])
+@pytest.mark.parametrize("m,inter,gran,pad", [(200, 512, 128, 0), (37, 256, 32, 64), (129, 384, 128, 8), (5, 128, 32, 0),
+                                              (1000, 2048, 128, 0)])
 def test_swiglu_quant_matches_oracle(m, inter, gran, pad):
     x = randn((m, 2 * inter + pad), m + inter) * 2.0
-    x[0, :4] = [0.0, -0.0, 30.0, -30.0]
+    x[0, :8] = [0.0, -0.0, 30.0, -30.0, 88.0, -88.0, 100.0, -100.0]
     bits = o.f32_to_bf16_bits_np(x)
     want_f32 = o.swiglu_f32(bits[:, :2 * inter], inter)
     want_data, want_sf = o.quant_mx_host(want_f32, o.FP8, gran)
@@ -28,11 +29,9 @@ def test_swiglu_quant_matches_oracle(m, inter, gran, pad):
     poll_device_status()
     got_data, got_sf = data.cpu().numpy(), sf.buf.cpu().numpy().view(np.uint32)
     assert got_sf.shape == want_sf.shape
-    assert (got_data != want_data).mean() <= 2e-3, f"{(got_data != want_data).sum()} code bytes differ"
-    assert (got_sf != want_sf).mean() <= 2e-3
-    back_got = o.dequant_mx_host(got_data, got_sf, m, inter, o.FP8, gran)
-    back_want = o.dequant_mx_host(want_data, want_sf, m, inter, o.FP8, gran)
-    assert o.calc_diff(back_got, back_want) <= 1e-6
+    assert np.array_equal(got_sf, want_sf), f"SF words differ at {np.argwhere(got_sf != want_sf)[:4]}"
+    bad = np.argwhere(got_data != want_data)
+    assert bad.size == 0, f"{len(bad)} code bytes differ, first {bad[:4]}"
 
 
 def test_swiglu_quant_argument_checks():
