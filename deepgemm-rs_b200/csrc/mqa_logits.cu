@@ -2,23 +2,40 @@
 //   logits[i, j] = s_kv[j] * sum_h w[i,h] * relu(<q[i,h,:], kv[j,:]>),  j in [ks[i], min(ke[i], S))
 // stored compressed at column j - ks[i] of row i.
 //
-// Two contracts of the reference share this kernel:
+// Contracts of the reference that share this kernel:
 //   fp32  (deepgemm/src/api_sm90_mqa.rs:5-31): raw E4M3 q, E4M3 kv with one f32 scale per kv
 //         token, f32 weights, f32 logits           -> tcgen05.mma kind::f8f6f4
 //   ue8m0 (api::mqa_logits, deepgemm/src/api.rs:1614-1745; device side
 //         deepgemm/kernels/mqa_logits_sm100.cu:514-1084): UE8M0 scales per 32 along head_dim on
-//         q and kv, bf16 weights, bf16 logits      -> tcgen05.mma kind::mxf8f6f4.block_scale
-// Numerical contract: mqa_logits_ref of the golden model (deepgemm/src/golden.rs:469-501).
+//         q and kv, bf16 weights, bf16 logits; FP8 codes (kind::mxf8f6f4.block_scale) or packed FP4
+//         codes (kind::mxf4.block_scale.block32)
+//   paged (api::mqa_logits_paged, api.rs:1752-1941; scheduler and metadata kernel
+//         mqa_logits_sm100.cu:110-492): the ue8m0 contract over a paged KV cache for decode --
+//         query tokens carry a request id and a context length, the kv tokens of a request are
+//         found through its row of the block table
+// Numerical contract: mqa_logits_ref of the golden model (deepgemm/src/golden.rs:469-501), within
+// calc_diff <= 1e-3.
 //
 // The contraction runs with the 128 kv tokens of a block on the UMMA M side (TMEM lanes) and
 // the (query, head) pairs of a query block on the N side, so one epilogue thread owns one kv
-// token, reduces over heads with weights broadcast from shared memory and the warp stores 32
-// consecutive columns of a logits row.
-//   warp 0      TMA producer (Q tile per query block, KV tiles streamed through a ring)
-//   warp 1      MMA issuer (head_dim/32 MMAs per kv block, two accumulator stages in TMEM)
-//   warp 2      TMEM owner; ue8m0 contract: scale-factor transposer
-//   warps 4-..  two or four epilogue warpgroups, each reducing its share of the query block's
-//               columns with the next TMEM load in flight while a chunk is consumed
+// token and a warp stores 32 consecutive columns of a logits row.
+//   warp 0      TMA producer (Q tile per task, KV blocks streamed through a ring; paged: page by page)
+//   warp 1      MMA issuer (scores into accumulator stages in TMEM; with the tensor-core reduction also
+//               the second MMA of every block)
+//   warp 2      TMEM owner; ue8m0 contracts: scale factors into the layout tcgen05.cp needs
+//   warps 4-..  epilogue warpgroups
+// Head reduction, two forms:
+//   tensor-core (default where the shapes allow): scores are produced in sub-tiles of 128 columns
+//     (whole queries) that rotate through three or four TMEM stages.  The epilogue warps only apply
+//     ReLU, round to bf16 and write a sub-tile back into the tensor memory it came from (half the
+//     columns); a second MMA multiplies it, as the A operand read from tensor memory, with the
+//     block-diagonal weight matrix of the sub-tile ([16 rows, 128] bf16 in shared memory: row i = the
+//     weights of query i over its own columns, zero elsewhere; the fp32 contract adds rows 8.. with the
+//     bf16 remainders of the f32 weights, so the weights enter to 16 bits of mantissa) into 16 freed
+//     columns of the same stage.  The CUDA cores then touch 16 values per kv token and sub-tile instead
+//     of 256.  The scores enter the sum rounded to bf16 (the reference reduces in bf16x2 altogether,
+//     mqa_logits_sm100.cu:1022-1031); the sum itself is f32.
+//   CUDA-core: relu(x) * w accumulated in f32 per thread (any head count; DG_MQA_TSRED=0 selects it).
 #include "host.h"
 #include "ptx.cuh"
 
@@ -29,54 +46,127 @@ namespace dg {
 constexpr uint32_t kMqaBlockKv = 128;
 constexpr uint32_t kMqaMaxKvStages = 10;
 constexpr uint32_t kMqaMaxThreads = 640;   // 4 role warps + up to 4 epilogue warpgroups
-constexpr uint32_t kMqaSfaCol = 448;   // ue8m0 contract only: accumulators are <= 192 wide
+constexpr uint32_t kMqaSfaCol = 448;       // ue8m0 contracts only: the accumulators end at column 384
 constexpr uint32_t kMqaSfbCol = 452;
+constexpr uint32_t kMqaSub = 128;          // tensor-core reduction: score columns per sub-tile = TMEM stage width
+constexpr uint32_t kMqaW2Bytes = 8192;     // block-diagonal weight tiles of one task: [2 sub-tiles][16][128] bf16
 
 struct MqaParams {
     uint32_t num_tokens, num_kv, num_heads, head_dim;
-    uint32_t block_q, n;          // n = block_q * num_heads (UMMA N)
-    uint32_t ep_groups;           // epilogue warpgroups (2 or 4); each reduces block_q / ep_groups queries
+    uint32_t block_q, n, n_mma;   // n = block_q * num_heads score columns, n_mma = n rounded up to the MMA's granule
+    uint32_t ep_groups;           // epilogue warpgroups; CUDA-core form: each reduces block_q / ep_groups queries
+    uint32_t unit;                // CUDA-core form: columns per TMEM load (16, or 4 for head counts not divisible by 16)
+    uint32_t subs, num_acc;       // tensor-core form: sub-tiles per kv block (1 or 2), TMEM stages (3 or 4)
     uint32_t num_q_blocks;
     uint32_t kv_stages, kv_stage_bytes, q_stage_bytes;
     uint32_t off_w, off_q, off_kv;  // offsets from the 1024-aligned base
-    uint32_t kv_sf_off, q_sf_off;   // SF words inside a kv / q stage (ue8m0 contract)
+    uint32_t kv_sf_off, q_sf_off;   // SF words inside a kv / q stage (ue8m0 contracts)
+    uint32_t row_bytes;             // bytes of one q / kv row (head_dim, or head_dim / 2 for FP4)
     uint32_t sbo;                   // 8-row group pitch of the swizzled tiles
     uint32_t layout;                // UMMA layout type of the tiles
+    uint32_t num_mma;               // MMAs per kv block (and sub-tile)
+    uint32_t idesc, idesc2;         // instruction descriptors of the score MMA and of the reduction MMA
+    uint32_t acc_stride;            // TMEM columns between accumulator stages
     uint32_t logits_stride;
     const uint32_t* ks;
     const uint32_t* ke;
     const float* kv_scale;          // fp32 contract
-    const void* weights;            // f32 (fp32 contract) or bf16 (ue8m0 contract)
+    const void* weights;            // f32 (fp32 contract) or bf16 (ue8m0 contracts)
     void* logits;
     uint32_t* status;
+    // paged KV
+    uint32_t page_kv, boxes_per_block, box_rows;   // kv rows per page; TMA boxes per 128-token block and their height
+    const uint32_t* kv_sf;          // scale words of the cache, one per token in page order
+    const uint32_t* context_lens;
+    const uint32_t* block_table;
+    uint32_t block_table_stride;
+    const uint32_t* cum;            // [num_tokens + 1] kv blocks of the query blocks that start before a token
+    const uint32_t* qb_tokens;      // [num_tokens] tokens of the query block that starts here, 0 elsewhere
+    const uint32_t* req_first;      // [num_tokens] first token of the token's request
 };
 
 struct __align__(8) MqaBarriers {
     uint64_t kv_full[kMqaMaxKvStages];
-    uint64_t kv_ready[kMqaMaxKvStages];   // ue8m0: SF transposed
+    uint64_t kv_ready[kMqaMaxKvStages];   // ue8m0: scale factors in place
     uint64_t kv_empty[kMqaMaxKvStages];
     uint64_t q_full[2], q_ready[2], q_empty[2];
-    uint64_t tmem_full[2], tmem_empty[2];
-    uint64_t w_full[2];                   // weights of a query block staged by the 8 epilogue warps
+    uint64_t tmem_full[4], tmem_empty[4];
+    uint64_t relu_done[4], out_full[4];   // tensor-core reduction: scores written back / reduced sums ready
+    uint64_t w_full[2], w_empty[2];       // weights of a task staged (by the epilogue warps, or by warp 3 for the tensor-core form)
     uint32_t tmem_base;
     uint32_t abort;
 };
 
-// kv-block range [b0, b1) that a query block touches; identical in every role.
-struct QRange { uint32_t b0, b1; };
-__device__ __forceinline__ QRange q_block_range(const MqaParams& p, uint32_t qb) {
-    uint32_t lo = 0xffffffffu, hi = 0;
-    for (uint32_t i = 0; i < p.block_q; ++i) {
-        const uint32_t q = qb * p.block_q + i;
-        if (q < p.num_tokens) {
-            const uint32_t s = __ldg(p.ks + q), e = min(__ldg(p.ke + q), p.num_kv);
-            if (s < e) { lo = min(lo, s); hi = max(hi, e); }
+// One unit of work, identical in every role: `nq` queries starting at token q0 against the kv blocks
+// [kb0, kb1) (128 tokens each; paged: blocks of the request's own token order).
+struct MqaTask { uint32_t q0, nq, kb0, kb1, table_row; };
+
+// Contiguous KV: query block qb = blockIdx.x, + gridDim.x, ...; its kv range follows from the windows.
+// Paged KV: every CTA takes an equal share of all (query block, kv block) pairs, cut out of the list
+// the metadata kernel prepared; a share may begin and end in the middle of a query block's kv range.
+template <bool PAGED>
+struct MqaTasks {
+    uint32_t qb;                // contiguous
+    uint32_t t, u, u_end;       // paged: next query block's first token, next unit, end of this CTA's share
+    __device__ explicit MqaTasks(const MqaParams& p) : qb(blockIdx.x), t(0), u(0), u_end(0) {
+        if (PAGED) {
+            const uint64_t total = __ldg(p.cum + p.num_tokens);
+            u = (uint32_t)(total * blockIdx.x / gridDim.x);
+            u_end = (uint32_t)(total * (blockIdx.x + 1) / gridDim.x);
+            // the query block that holds unit u: the first token i with cum[i + 1] > u
+            uint32_t lo = 0, hi = p.num_tokens;
+            while (lo < hi) {
+                const uint32_t mid = (lo + hi) >> 1;
+                if (__ldg(p.cum + mid + 1) > u) hi = mid; else lo = mid + 1;
+            }
+            t = lo;
         }
     }
-    QRange r;
-    r.b0 = hi > lo ? lo / kMqaBlockKv : 0;
-    r.b1 = hi > lo ? (hi + kMqaBlockKv - 1) / kMqaBlockKv : 0;
-    return r;
+    __device__ bool next(const MqaParams& p, MqaTask& k) {
+        if (PAGED) {
+            while (u < u_end && t < p.num_tokens) {
+                const uint32_t c0 = __ldg(p.cum + t), c1 = __ldg(p.cum + t + 1);
+                const uint32_t nq = __ldg(p.qb_tokens + t);
+                if (c1 <= u || nq == 0) { t += nq ? nq : 1u; continue; }   // a query block without kv tokens, or not a start
+                k.q0 = t; k.nq = nq;
+                k.kb0 = u - c0;
+                k.kb1 = min(c1, u_end) - c0;
+                k.table_row = __ldg(p.req_first + t);
+                u = min(c1, u_end);
+                if (u == c1) t += nq;
+                return true;
+            }
+            return false;
+        }
+        while (qb < p.num_q_blocks) {
+            const uint32_t b = qb;
+            qb += gridDim.x;
+            uint32_t lo = 0xffffffffu, hi = 0;
+            for (uint32_t i = 0; i < p.block_q; ++i) {
+                const uint32_t q = b * p.block_q + i;
+                if (q < p.num_tokens) {
+                    const uint32_t s = __ldg(p.ks + q), e = min(__ldg(p.ke + q), p.num_kv);
+                    if (s < e) { lo = min(lo, s); hi = max(hi, e); }
+                }
+            }
+            if (hi <= lo) continue;
+            k.q0 = b * p.block_q; k.nq = min(p.block_q, p.num_tokens - k.q0);
+            k.kb0 = lo / kMqaBlockKv; k.kb1 = (hi + kMqaBlockKv - 1) / kMqaBlockKv;
+            k.table_row = 0;
+            return true;
+        }
+        return false;
+    }
+};
+
+// Row of the paged cache that holds token `tok` (request order) of the request whose table row is given;
+// tokens past the table's width or pages outside the cache read row 0 (they lie beyond every context
+// length and are masked by the epilogue).
+__device__ __forceinline__ uint32_t paged_row(const MqaParams& p, uint32_t table_row, uint32_t tok, uint32_t span) {
+    const uint32_t pg = tok / p.page_kv;
+    const uint32_t page = pg < p.block_table_stride ? __ldg(p.block_table + (size_t)table_row * p.block_table_stride + pg) : 0u;
+    const uint32_t row = page * p.page_kv + tok % p.page_kv;
+    return row + span <= p.num_kv ? row : 0u;
 }
 
 __device__ __forceinline__ void tc_mma_f8(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
@@ -85,11 +175,48 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d, uint64_t a, uint64_t b, ui
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
 }
+// A operand read from tensor memory (bf16, two K elements per 32-bit column), B from shared memory.
+__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
 __host__ __device__ constexpr uint32_t make_idesc_f8(uint32_t m, uint32_t n) {
     return (1u << 4) /*D=f32*/ | ((n >> 3) << 17) | ((m >> 4) << 24);  // A, B = E4M3 (format 0), K-major
 }
+__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// the first 16 words of a 32-word register array
+__device__ __forceinline__ void tmem_st_x16_of32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld_x4(uint32_t taddr, uint32_t (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+}
+// relu, then two f32 -> one bf16x2 word (first value in the low half)
+__device__ __forceinline__ uint32_t relu_pack_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 
-template <bool SCALED>
+// SCALED: ue8m0 contracts (scale factors on q and kv, bf16 weights and logits); FP4: packed E2M1 codes;
+// PAGED: kv through a block table, work from the metadata kernel; TSRED: tensor-core head reduction.
+template <bool SCALED, bool FP4, bool PAGED, bool TSRED>
 __global__ void __launch_bounds__(kMqaMaxThreads, 1)
 mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_qsf, const __grid_constant__ CUtensorMap tm_kvsf,
@@ -99,11 +226,13 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t base = (raw_u32 + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw_u32);
     MqaBarriers* bars = reinterpret_cast<MqaBarriers*>(base_ptr);
-    float* w_smem = reinterpret_cast<float*>(base_ptr + p.off_w);   // [2][n]
-    uint32_t* win_smem = reinterpret_cast<uint32_t*>(base_ptr + 512);  // [2][2][16]: ks / ke of the queries of a block
+    float* w_smem = reinterpret_cast<float*>(base_ptr + p.off_w);      // CUDA-core form: [2][n] halved weights
+    uint8_t* w2_smem = base_ptr + p.off_w;                             // tensor-core form: [2 tasks][2 sub-tiles][16][128] bf16, swizzled
+    uint32_t* win_smem = reinterpret_cast<uint32_t*>(base_ptr + 512);  // [2][2][16]: ks / ke of the queries of a task
     static_assert(sizeof(MqaBarriers) <= 512, "barrier block overlaps the window table");
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const WaitCtx wc{p.status, &bars->abort};
+    const uint32_t ep_warps = 4u * p.ep_groups;
 
     if (threadIdx.x == 0) {
         bars->abort = 0;
@@ -116,9 +245,14 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(smem_u32(&bars->q_full[s]), 1);
             mbar_init(smem_u32(&bars->q_ready[s]), 1);
             mbar_init(smem_u32(&bars->q_empty[s]), 1);
+            mbar_init(smem_u32(&bars->w_full[s]), TSRED ? 1u : ep_warps);
+            mbar_init(smem_u32(&bars->w_empty[s]), 1);
+        }
+        for (uint32_t s = 0; s < 4; ++s) {
             mbar_init(smem_u32(&bars->tmem_full[s]), 1);
-            mbar_init(smem_u32(&bars->tmem_empty[s]), 4 * p.ep_groups);
-            mbar_init(smem_u32(&bars->w_full[s]), 4 * p.ep_groups);
+            mbar_init(smem_u32(&bars->tmem_empty[s]), TSRED ? 4u : ep_warps);   // tensor-core form: one warpgroup owns a stage
+            mbar_init(smem_u32(&bars->relu_done[s]), 4u);
+            mbar_init(smem_u32(&bars->out_full[s]), 1);
         }
         fence_barrier_init();
         tma_prefetch_desc(&tm_q);
@@ -131,36 +265,45 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    griddep_wait();                 // the kernel before this one in the stream produced q / kv / weights
+    griddep_wait();                 // the kernel before this one in the stream produced q / kv / weights / the task list
     griddep_launch_dependents();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
-    const uint32_t acc_stride = SCALED ? 192u : 256u;
-    const uint32_t num_mma = p.head_dim / 32u;
+    const uint32_t acc_stride = p.acc_stride;
+    const uint32_t kv_tx = kMqaBlockKv * p.row_bytes + ((SCALED && !PAGED) ? kMqaBlockKv * 4u : 0u);
 
     if (warp == 0) {
         // ===================================================== producer (warp-converged, one lane issues)
         uint32_t stage = 0, phase = 0, qcount = 0;
         bool ok = true;
-        for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
-            const QRange r = q_block_range(p, qb);
-            if (r.b1 <= r.b0) continue;
+        MqaTasks<PAGED> tasks(p);
+        MqaTask k;
+        while (ok && tasks.next(p, k)) {
             const uint32_t qs = qcount & 1u, qphase = (qcount >> 1) & 1u;
             ++qcount;
             if (!(ok = DG_WARP_WAIT(smem_u32(&bars->q_empty[qs]), qphase ^ 1u, wc, kWaitEmpty))) break;
             const uint32_t qbar = smem_u32(&bars->q_full[qs]);
             const uint32_t qdst = base + p.off_q + qs * p.q_stage_bytes;
             if (elect_one()) {
-                mbar_arrive_expect_tx(qbar, p.n * p.head_dim + (SCALED ? p.n * 4u : 0u));
-                tma_load_2d(&tm_q, qbar, qdst, 0, (int32_t)(qb * p.n));
-                if (SCALED) tma_load_2d(&tm_qsf, qbar, qdst + p.q_sf_off, (int32_t)(qb * p.n), 0);
+                // the box always holds block_q queries; rows of queries beyond the task's own are never stored
+                mbar_arrive_expect_tx(qbar, p.n * p.row_bytes + (SCALED ? p.n * 4u : 0u));
+                tma_load_2d(&tm_q, qbar, qdst, 0, (int32_t)(k.q0 * p.num_heads));
+                if (SCALED) tma_load_2d(&tm_qsf, qbar, qdst + p.q_sf_off, (int32_t)(k.q0 * p.num_heads), 0);
             }
             __syncwarp();
-            for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
+            for (uint32_t kb = k.kb0; kb < k.kb1; ++kb) {
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
                 const uint32_t bar = smem_u32(&bars->kv_full[stage]);
                 const uint32_t dst = base + p.off_kv + stage * p.kv_stage_bytes;
-                if (elect_one()) {
-                    mbar_arrive_expect_tx(bar, kMqaBlockKv * p.head_dim + (SCALED ? kMqaBlockKv * 4u : 0u));
+                if (PAGED) {
+                    // a block of 128 tokens is a run of whole pages (or half / a quarter of a large page): lane i
+                    // looks up the page of box i
+                    uint32_t row = 0;
+                    if (lane < p.boxes_per_block) row = paged_row(p, k.table_row, kb * kMqaBlockKv + lane * p.box_rows, p.box_rows);
+                    if (lane == 0) mbar_arrive_expect_tx(bar, kv_tx);
+                    __syncwarp();
+                    if (lane < p.boxes_per_block) tma_load_2d(&tm_kv, bar, dst + lane * p.box_rows * p.row_bytes, 0, (int32_t)row);
+                } else if (elect_one()) {
+                    mbar_arrive_expect_tx(bar, kv_tx);
                     tma_load_2d(&tm_kv, bar, dst, 0, (int32_t)(kb * kMqaBlockKv));
                     if (SCALED) tma_load_2d(&tm_kvsf, bar, dst + p.kv_sf_off, (int32_t)(kb * kMqaBlockKv), 0);
                 }
@@ -171,54 +314,110 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     } else if (warp == 1) {
         // ===================================================== MMA issuer (warp-converged, one lane issues)
         uint32_t stage = 0, phase = 0, qcount = 0, acount = 0;
-        const uint32_t idesc = SCALED ? make_idesc_bs(0u, 0u, kMqaBlockKv, p.n) : make_idesc_f8(kMqaBlockKv, p.n);
         bool ok = true;
-        for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
-            const QRange r = q_block_range(p, qb);
-            if (r.b1 <= r.b0) continue;
+        MqaTasks<PAGED> tasks(p);
+        MqaTask k;
+        // Tensor-core reduction: the second MMA of a sub-tile is issued as soon as the warpgroup that owns its
+        // stage has rewritten the scores, checked before every score MMA; this warp blocks on it only when all
+        // other stages are in flight.  Ring of the sub-tiles whose reduction is outstanding, oldest first:
+        // stage, phase, address of the weight tile, and whether the sub-tile is the last of its task (then the
+        // reduction also hands the task's weight buffer back).
+        uint32_t n_pend = 0;
+        uint32_t pa0 = 0, pp0 = 0, pw0 = 0, pl0 = 0, pa1 = 0, pp1 = 0, pw1 = 0, pl1 = 0, pa2 = 0, pp2 = 0, pw2 = 0, pl2 = 0;
+        auto reduce_oldest = [&]() {
+            if (!DG_WARP_WAIT(smem_u32(&bars->relu_done[pa0]), pp0, wc, kWaitTmemFull)) return false;
+            tc_fence_after();
+            if (elect_one()) {
+                const uint32_t stage_col = tmem + pa0 * acc_stride;
+                const uint32_t d2 = stage_col + 16u;                           // the 16 columns freed by packing the first 32
+                for (uint32_t t16 = 0; t16 < kMqaSub / 16u; ++t16) {
+                    const uint32_t kappa = t16 * 16u;                          // first (query, head) pair of this step
+                    const uint32_t a_col = stage_col + (kappa / 32u) * 32u + (kappa % 32u) / 2u;
+                    const uint64_t b_desc = make_kmajor_sw128_desc(pw0 + (kappa / 64u) * 2048u) + ((kappa % 64u) * 2u >> 4);
+                    tc_mma_bf16_ts(d2, a_col, b_desc, p.idesc2, t16 != 0u);
+                }
+                tc_commit(smem_u32(&bars->out_full[pa0]));
+                if (pl0 & 2u) tc_commit(smem_u32(&bars->w_empty[pl0 & 1u]));
+            }
+            __syncwarp();
+            pa0 = pa1; pp0 = pp1; pw0 = pw1; pl0 = pl1;
+            pa1 = pa2; pp1 = pp2; pw1 = pw2; pl1 = pl2;
+            --n_pend;
+            return true;
+        };
+        while (ok && tasks.next(p, k)) {
             const uint32_t qs = qcount & 1u, qphase = (qcount >> 1) & 1u;
             ++qcount;
             if (!(ok = DG_WARP_WAIT(smem_u32(&bars->q_full[qs]), qphase, wc, kWaitFull))) break;
             if (SCALED && !(ok = DG_WARP_WAIT(smem_u32(&bars->q_ready[qs]), qphase, wc, kWaitSfReady))) break;
+            if (TSRED && !(ok = DG_WARP_WAIT(smem_u32(&bars->w_full[qs]), qphase, wc, kWaitWeights))) break;
             tc_fence_after();
             const uint32_t qaddr = base + p.off_q + qs * p.q_stage_bytes;
             const uint64_t q_desc = make_smem_desc(qaddr, p.sbo, 0, p.layout);
-            if (SCALED) {
-                if (elect_one()) {
-                    for (uint32_t c = 0; c < (p.n + 127u) / 128u; ++c)
-                        tc_cp_32x128b_warpx4(tmem + kMqaSfbCol + c * 4u, make_sf_desc(qaddr + p.q_sf_off + c * 512u));
-                }
-                __syncwarp();
-            }
-            for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
-                const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
-                ++acount;
+            bool q_sf_copied = false;
+            for (uint32_t kb = k.kb0; ok && kb < k.kb1; ++kb) {
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull))) break;
                 if (SCALED && !(ok = DG_WARP_WAIT(smem_u32(&bars->kv_ready[stage]), phase, wc, kWaitSfReady))) break;
-                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
-                tc_fence_after();
                 const uint32_t kaddr = base + p.off_kv + stage * p.kv_stage_bytes;
                 const uint64_t kv_desc = make_smem_desc(kaddr, p.sbo, 0, p.layout);
-                const uint32_t d_tmem = tmem + as * acc_stride;
-                if (elect_one()) {
-                if (SCALED) tc_cp_32x128b_warpx4(tmem + kMqaSfaCol, make_sf_desc(kaddr + p.kv_sf_off));
-                for (uint32_t k = 0; k < num_mma; ++k) {
-                    if (SCALED)
-                        tc_mma_mxf8(d_tmem, kv_desc + 2u * k, q_desc + 2u * k, idesc_with_sf_ids(idesc, k, k), k != 0u,
-                                    tmem + kMqaSfaCol, tmem + kMqaSfbCol);
-                    else
-                        tc_mma_f8(d_tmem, kv_desc + 2u * k, q_desc + 2u * k, idesc, k != 0u);
+                const uint32_t nsub = TSRED ? p.subs : 1u;
+                for (uint32_t sub = 0; sub < nsub; ++sub) {
+                    const uint32_t as = TSRED ? acount % p.num_acc : acount & 1u;
+                    const uint32_t aphase = TSRED ? (acount / p.num_acc) & 1u : (acount >> 1) & 1u;
+                    ++acount;
+                    if (TSRED) {
+                        while (ok && n_pend && (n_pend + 1u >= p.num_acc ||
+                                                __any_sync(0xffffffffu, mbar_test_wait(smem_u32(&bars->relu_done[pa0]), pp0))))
+                            ok = reduce_oldest();
+                        if (!ok) break;
+                    }
+                    if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem + as * acc_stride;
+                    // sub-tile `sub` = rows [128 sub, 128 sub + 128) of the Q tile
+                    const uint64_t qd = q_desc + (uint64_t)((sub * kMqaSub * p.row_bytes) >> 4);
+                    if (elect_one()) {
+                        if (SCALED) {
+                            if (!q_sf_copied)    // the q scales of this task: in order behind every MMA that used the previous task's
+                                for (uint32_t c = 0; c < (p.n + 127u) / 128u; ++c)
+                                    tc_cp_32x128b_warpx4(tmem + kMqaSfbCol + c * 4u, make_sf_desc(qaddr + p.q_sf_off + c * 512u));
+                            if (sub == 0) tc_cp_32x128b_warpx4(tmem + kMqaSfaCol, make_sf_desc(kaddr + p.kv_sf_off));
+                        }
+                        for (uint32_t m = 0; m < p.num_mma; ++m) {
+                            if (SCALED && FP4)      // 64 elements per MMA: half-word (m & 1) of the row's scale word
+                                tc_mma_mxf4(d_tmem, kv_desc + 2u * m, qd + 2u * m, idesc_with_sf_ids(p.idesc, (m & 1u) * 2u, (m & 1u) * 2u),
+                                            m != 0u, tmem + kMqaSfaCol, tmem + kMqaSfbCol + sub * 4u);
+                            else if (SCALED)
+                                tc_mma_mxf8(d_tmem, kv_desc + 2u * m, qd + 2u * m, idesc_with_sf_ids(p.idesc, m, m), m != 0u,
+                                            tmem + kMqaSfaCol, tmem + kMqaSfbCol + sub * 4u);
+                            else
+                                tc_mma_f8(d_tmem, kv_desc + 2u * m, qd + 2u * m, p.idesc, m != 0u);
+                        }
+                        if (sub + 1 == nsub) tc_commit(smem_u32(&bars->kv_empty[stage]));
+                        tc_commit(smem_u32(&bars->tmem_full[as]));
+                        if (sub + 1 == nsub && kb + 1 == k.kb1) tc_commit(smem_u32(&bars->q_empty[qs]));
+                    }
+                    __syncwarp();
+                    q_sf_copied = true;
+                    if (TSRED) {
+                        const uint32_t wt = base + p.off_w + qs * kMqaW2Bytes + sub * (kMqaW2Bytes / 2u);
+                        const uint32_t last = (sub + 1 == nsub && kb + 1 == k.kb1) ? 2u : 0u;
+                        if (n_pend == 0u) { pa0 = as; pp0 = aphase; pw0 = wt; pl0 = last | qs; }
+                        else if (n_pend == 1u) { pa1 = as; pp1 = aphase; pw1 = wt; pl1 = last | qs; }
+                        else { pa2 = as; pp2 = aphase; pw2 = wt; pl2 = last | qs; }
+                        ++n_pend;
+                    }
                 }
-                tc_commit(smem_u32(&bars->kv_empty[stage]));
-                tc_commit(smem_u32(&bars->tmem_full[as]));
-                if (kb + 1 == r.b1) tc_commit(smem_u32(&bars->q_empty[qs]));
-                }
-                __syncwarp();
                 if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
             }
         }
+        while (TSRED && ok && n_pend) ok = reduce_oldest();
     } else if (warp == 2 && SCALED) {
-        // ===================================================== SF transposer (ue8m0 contract)
+        // ===================================================== scale factors (ue8m0 contracts)
+        // tcgen05.cp wants the word of row 32 i + l at position 4 l + i.  Contiguous kv: the TMA load
+        // brought the 128 words in row order, rewrite them in place.  Paged kv: the words are fetched
+        // here, page by page with plain loads (a page's words may be fewer than a TMA box can address),
+        // as soon as the stage is free, and stored in the final order directly.
         uint32_t stage = 0, phase = 0, qcount = 0;
         bool ok = true;
         auto transpose128 = [&](uint32_t* q) {
@@ -226,9 +425,9 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             __syncwarp();
             *reinterpret_cast<uint4*>(q + lane * 4u) = make_uint4(v0, v1, v2, v3);
         };
-        for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
-            const QRange r = q_block_range(p, qb);
-            if (r.b1 <= r.b0) continue;
+        MqaTasks<PAGED> tasks(p);
+        MqaTask k;
+        while (ok && tasks.next(p, k)) {
             const uint32_t qs = qcount & 1u, qphase = (qcount >> 1) & 1u;
             ++qcount;
             ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->q_full[qs]), qphase, wc, kWaitFull));
@@ -238,129 +437,301 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->q_ready[qs]));
-            for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
-                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull));
-                if (!ok) break;
-                transpose128(reinterpret_cast<uint32_t*>(base_ptr + p.off_kv + stage * p.kv_stage_bytes + p.kv_sf_off));
+            for (uint32_t kb = k.kb0; kb < k.kb1; ++kb) {
+                uint32_t* sf = reinterpret_cast<uint32_t*>(base_ptr + p.off_kv + stage * p.kv_stage_bytes + p.kv_sf_off);
+                if (PAGED) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, wc, kWaitEmpty));
+                    if (!ok) break;
+                    uint32_t v[4];
+#pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i)
+                        v[i] = __ldg(p.kv_sf + paged_row(p, k.table_row, kb * kMqaBlockKv + 32u * i + lane, 1u));
+                    *reinterpret_cast<uint4*>(sf + lane * 4u) = make_uint4(v[0], v[1], v[2], v[3]);
+                } else {
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull));
+                    if (!ok) break;
+                    transpose128(sf);
+                }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars->kv_ready[stage]));
                 if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
             }
         }
-    } else if (warp >= 4) {
-        // ===================================================== epilogue (2 or 4 warpgroups)
-        const uint32_t et = threadIdx.x - 128u;
-        const uint32_t wg = et >> 7;                  // which share of the query block
-        const uint32_t quarter = warp & 3u;           // TMEM lane quarter of this warp
-        const uint32_t q_per_wg = p.block_q / p.ep_groups;
-        const uint32_t units_per_q = p.num_heads / 16u;
-        const uint32_t nunits = q_per_wg * units_per_q;        // 16-column TMEM loads per kv block
-        const uint32_t q_first = wg * q_per_wg;
-        const uint32_t col_base = q_first * p.num_heads;
-        uint32_t qcount = 0, acount = 0;
+    } else if (warp == 3 && TSRED) {
+        // ===================================================== weight tiles of the tensor-core reduction
+        // Per task and sub-tile a K-major [16 rows][128] bf16 tile with 128-byte swizzle (atoms of 64 K elements;
+        // the 16-byte pieces of a row XOR-ed with the row's index inside its group of 8).  Row i < 8: the bf16
+        // weights of the sub-tile's query i over its own heads' columns, zero elsewhere; row 8 + i: the bf16
+        // remainders of the f32 weights (fp32 contract).  512 pieces of 16 bytes = (sub-tile, row, 8 consecutive
+        // K elements), 16 per lane.  A buffer is rewritten once the reductions of the task before the previous
+        // one have all run.
+        const uint32_t qps = kMqaSub / p.num_heads;          // queries per sub-tile (1, 2, 4 or 8)
+        uint32_t qcount = 0;
         bool ok = true;
-        for (uint32_t qb = blockIdx.x; ok && qb < p.num_q_blocks; qb += gridDim.x) {
-            const QRange r = q_block_range(p, qb);
-            if (r.b1 <= r.b0) continue;
+        MqaTasks<PAGED> tasks(p);
+        MqaTask k;
+        while (ok && tasks.next(p, k)) {
             const uint32_t wb = qcount & 1u, wphase = (qcount >> 1) & 1u;
-            float* w = w_smem + wb * p.n;
             ++qcount;
-            if (et < p.n) {
-                const uint32_t q = qb * p.block_q + et / p.num_heads;
-                float v = 0.f;
-                if (q < p.num_tokens) {
-                    const size_t idx = (size_t)q * p.num_heads + et % p.num_heads;
-                    v = SCALED ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.weights)[idx])
-                               : reinterpret_cast<const float*>(p.weights)[idx];
-                }
-                w[et] = 0.5f * v;      // see the epilogue loop: relu(x) * w = (x + |x|) * (w / 2)
-            }
-            // the kv windows of the block's queries travel with the weights: the reduction loop reads
-            // them from shared memory instead of waiting on two global loads per query and kv block
-            uint32_t* win = win_smem + wb * 32u;
-            if (et < p.block_q) {
-                const uint32_t q = qb * p.block_q + et;
-                win[et] = q < p.num_tokens ? __ldg(p.ks + q) : 0u;
-                win[16u + et] = q < p.num_tokens ? min(__ldg(p.ke + q), p.num_kv) : 0u;
-            }
-            // The two buffers alternate, and no warp can run more than one query block ahead of
-            // the slowest one (it waits here), so a buffer is never rewritten while still read.
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars->w_full[wb]));
-            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->w_full[wb]), wphase, wc, kWaitWeights));
-            if (!ok) break;
-            for (uint32_t kb = r.b0; kb < r.b1; ++kb) {
-                const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
-                ++acount;
-                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull));
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t j = kb * kMqaBlockKv + quarter * 32u + lane;
-                float scale = 1.f;
-                if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
-                const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride + col_base;
-                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;    // four partial sums of the current query
-                uint32_t unit_in_q = 0, q_done = 0;              // position inside this warp's share of the query block
-
-                // The reduction runs in units of 16 columns.  relu(x) * w is computed as
-                // (x + |x|) * (w / 2): the addition takes |x| as a source modifier and runs on the FMA
-                // pipe at full rate, where a max would go through the half-rate ALU pipe; both
-                // scalings are by powers of two, so the result is the same bit for bit (the weights in
-                // shared memory are already halved).  The TMEM load and the four weight vectors of
-                // unit u + 1 are requested before the arithmetic of unit u starts, so that neither the
-                // tensor-memory latency nor the shared-memory latency sits between dependent
-                // instructions; 16-column units keep both register sets inside the 102 registers a
-                // 640-thread block leaves per thread.
-                auto load_w = [&](float4 (&dst)[4], uint32_t u) {
-                    const float4* w4 = reinterpret_cast<const float4*>(w + col_base + u * 16u);
-#pragma unroll
-                    for (uint32_t i = 0; i < 4; ++i) dst[i] = w4[i];
-                };
-                auto consume = [&](const uint32_t (&v)[16], const float4 (&ww)[4]) {
+            if (!(ok = DG_WARP_WAIT(smem_u32(&bars->w_empty[wb]), wphase ^ 1u, wc, kWaitWeights))) break;
+            uint8_t* w2 = w2_smem + wb * kMqaW2Bytes;
+            for (uint32_t piece = lane; piece < 512u; piece += 32u) {
+                const uint32_t sub = piece >> 8, r = (piece >> 4) & 15u, c = piece & 15u;
+                const uint32_t qs_ = r & 7u;                                  // query inside the sub-tile this row belongs to
+                const uint32_t qi = sub * qps + qs_, q = k.q0 + qi;
+                const bool lo_row = r >= 8u;
+                uint32_t words[4] = {0u, 0u, 0u, 0u};
+                const bool live = sub < p.subs && qs_ < qps && qi < k.nq && q < p.num_tokens && (c * 8u) / p.num_heads == qs_ &&
+                                  !(lo_row && SCALED);
+                if (live) {
+                    const uint32_t h0 = (c * 8u) % p.num_heads;
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
-                        const float x0 = __uint_as_float(v[4 * i]), x1 = __uint_as_float(v[4 * i + 1]);
-                        const float x2 = __uint_as_float(v[4 * i + 2]), x3 = __uint_as_float(v[4 * i + 3]);
-                        a0 = fmaf(x0 + fabsf(x0), ww[i].x, a0);
-                        a1 = fmaf(x1 + fabsf(x1), ww[i].y, a1);
-                        a2 = fmaf(x2 + fabsf(x2), ww[i].z, a2);
-                        a3 = fmaf(x3 + fabsf(x3), ww[i].w, a3);
+                        float w0, w1;
+                        const size_t idx = (size_t)q * p.num_heads + h0 + 2 * i;
+                        if (SCALED) {
+                            w0 = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.weights)[idx]);
+                            w1 = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.weights)[idx + 1]);
+                        } else {
+                            w0 = reinterpret_cast<const float*>(p.weights)[idx];
+                            w1 = reinterpret_cast<const float*>(p.weights)[idx + 1];
+                        }
+                        __nv_bfloat16 b0 = __float2bfloat16_rn(w0), b1 = __float2bfloat16_rn(w1);
+                        if (lo_row) {
+                            b0 = __float2bfloat16_rn(w0 - __bfloat162float(b0));
+                            b1 = __float2bfloat16_rn(w1 - __bfloat162float(b1));
+                        }
+                        words[i] = (uint32_t)__bfloat16_as_ushort(b0) | ((uint32_t)__bfloat16_as_ushort(b1) << 16);
                     }
-                    if (++unit_in_q == units_per_q) {
+                }
+                const uint32_t off = sub * (kMqaW2Bytes / 2u) + (c / 8u) * 2048u + r * 128u + (((c & 7u) ^ (r & 7u)) * 16u);
+                *reinterpret_cast<uint4*>(w2 + off) = make_uint4(words[0], words[1], words[2], words[3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->w_full[wb]));
+        }
+    } else if (warp >= 4) {
+        // ===================================================== epilogue warpgroups
+        const uint32_t et = threadIdx.x - 128u;
+        const uint32_t wg = et >> 7;                  // warpgroup index
+        const uint32_t quarter = warp & 3u;           // TMEM lane quarter of this warp
+        uint32_t qcount = 0, acount = 0;
+        bool ok = true;
+        MqaTasks<PAGED> tasks(p);
+        MqaTask k;
+
+        // windows of a task's queries into shared memory (the first block_q epilogue threads)
+        auto stage_windows = [&](uint32_t wb) {
+            uint32_t* win = win_smem + wb * 32u;
+            if (et < p.block_q) {
+                const uint32_t q = k.q0 + et;
+                const bool live = et < k.nq && q < p.num_tokens;
+                uint32_t s = 0, e = 0;
+                if (live) {
+                    if (PAGED) e = min(__ldg(p.context_lens + q), p.block_table_stride * p.page_kv);
+                    else { s = __ldg(p.ks + q); e = min(__ldg(p.ke + q), p.num_kv); }
+                }
+                win[et] = s;
+                win[16u + et] = e;       // e = 0: nothing of this query is stored
+            }
+        };
+        auto load_weight = [&](uint32_t q, uint32_t h) -> float {
+            const size_t idx = (size_t)q * p.num_heads + h;
+            return SCALED ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.weights)[idx])
+                          : reinterpret_cast<const float*>(p.weights)[idx];
+        };
+
+        if (TSRED) {
+            // ---- tensor-core reduction.  Warpgroup g owns TMEM stage g and the sub-tiles that pass through it:
+            // (A) ReLU + bf16 write-back of the 128 score columns: every 32 columns shrink into their first 16;
+            // (B) after the reduction MMA, the sums from columns [16, 32) of the stage: column i = query i of the
+            //     sub-tile (bf16 part of the weights), 8 + i = the remainders.
+            const uint32_t qps = kMqaSub / p.num_heads;          // queries per sub-tile (1, 2, 4 or 8)
+            while (ok && wg < p.num_acc && tasks.next(p, k)) {
+                for (uint32_t kb = k.kb0; ok && kb < k.kb1; ++kb) {
+                    for (uint32_t sub = 0; sub < p.subs; ++sub) {
+                        const uint32_t as = acount % p.num_acc, aphase = (acount / p.num_acc) & 1u;
+                        ++acount;
+                        if (as != wg) continue;
+                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull));
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride;
+#pragma unroll
+                        for (uint32_t half = 0; half < 2; ++half) {
+                            uint32_t x[32], y[32];
+                            tmem_ld_x32(taddr + half * 64u, x);
+                            tmem_ld_x32(taddr + half * 64u + 32u, y);
+                            tmem_ld_wait();
+                            // packed in place: word i takes elements 2i and 2i + 1, both at or above position i
+#pragma unroll
+                            for (uint32_t i = 0; i < 16; ++i) {
+                                x[i] = relu_pack_bf16x2(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
+                                y[i] = relu_pack_bf16x2(__uint_as_float(y[2 * i]), __uint_as_float(y[2 * i + 1]));
+                            }
+                            tmem_st_x16_of32(taddr + half * 64u, x);
+                            tmem_st_x16_of32(taddr + half * 64u + 32u, y);
+                        }
+                        tmem_st_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->relu_done[as]));
+                        // this thread's kv token and the windows of the sub-tile's queries, fetched while the reduction runs
+                        const uint32_t j = kb * kMqaBlockKv + quarter * 32u + lane;
+                        float scale = 1.f;
+                        if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
+                        uint32_t ws[8], we[8];
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) {
+                            const uint32_t qi = sub * qps + i, q = k.q0 + qi;
+                            ws[i] = 0; we[i] = 0;
+                            if (i < qps && qi < k.nq && q < p.num_tokens) {
+                                if (PAGED) we[i] = min(__ldg(p.context_lens + q), p.block_table_stride * p.page_kv);
+                                else { ws[i] = __ldg(p.ks + q); we[i] = min(__ldg(p.ke + q), p.num_kv); }
+                            }
+                        }
+                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->out_full[as]), aphase, wc, kWaitTmemFull));
+                        if (!ok) break;
+                        tc_fence_after();
+                        uint32_t v[16];
+                        tmem_ld_x16(taddr + 16u, v);
+                        tmem_ld_wait();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+#pragma unroll
+                        for (uint32_t i = 0; i < 8; ++i) {
+                            if (j >= ws[i] && j < we[i]) {
+                                float val = __uint_as_float(v[i]);
+                                if (!SCALED) val = (val + __uint_as_float(v[8 + i])) * scale;
+                                const size_t o = (size_t)(k.q0 + sub * qps + i) * p.logits_stride + (j - ws[i]);
+                                if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
+                                else reinterpret_cast<float*>(p.logits)[o] = val;
+                            }
+                        }
+                    }
+                }
+            }
+        } else {
+            // ---- CUDA-core reduction
+            const uint32_t q_per_wg = p.block_q / p.ep_groups;
+            const uint32_t units_per_q = p.num_heads / p.unit;
+            const uint32_t nunits = q_per_wg * units_per_q;        // TMEM loads per kv block
+            const uint32_t q_first = wg * q_per_wg;
+            const uint32_t col_base = q_first * p.num_heads;
+            while (ok && tasks.next(p, k)) {
+                const uint32_t wb = qcount & 1u, wphase = (qcount >> 1) & 1u;
+                float* w = w_smem + wb * p.n;
+                ++qcount;
+                for (uint32_t c = et; c < p.n; c += 128u * p.ep_groups) {
+                    const uint32_t qi = c / p.num_heads, q = k.q0 + qi;
+                    float v = 0.f;
+                    if (qi < k.nq && q < p.num_tokens) v = load_weight(q, c % p.num_heads);
+                    w[c] = 0.5f * v;       // see the reduction loop: relu(x) * w = (x + |x|) * (w / 2)
+                }
+                // the kv windows of the task's queries travel with the weights: the reduction loop reads
+                // them from shared memory instead of waiting on two global loads per query and kv block
+                stage_windows(wb);
+                const uint32_t* win = win_smem + wb * 32u;
+                // The two buffers alternate, and no warp can run more than one task ahead of
+                // the slowest one (it waits here), so a buffer is never rewritten while still read.
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->w_full[wb]));
+                ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->w_full[wb]), wphase, wc, kWaitWeights));
+                if (!ok) break;
+                for (uint32_t kb = k.kb0; kb < k.kb1; ++kb) {
+                    const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
+                    ++acount;
+                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull));
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t j = kb * kMqaBlockKv + quarter * 32u + lane;
+                    float scale = 1.f;
+                    if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
+                    const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride + col_base;
+                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;    // four partial sums of the current query
+                    uint32_t unit_in_q = 0, q_done = 0;              // position inside this warp's share of the query block
+                    auto store_query = [&]() {
                         const uint32_t qi = q_first + q_done;        // index inside the query block
                         const uint32_t s = win[qi], e = win[16u + qi];   // e = 0 for queries past the end
                         if (j >= s && j < e) {
                             const float val = ((a0 + a1) + (a2 + a3)) * scale;
-                            const size_t o = (size_t)(qb * p.block_q + qi) * p.logits_stride + (j - s);
+                            const size_t o = (size_t)(k.q0 + qi) * p.logits_stride + (j - s);
                             if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
                             else reinterpret_cast<float*>(p.logits)[o] = val;
                         }
                         a0 = a1 = a2 = a3 = 0.f;
                         unit_in_q = 0;
                         ++q_done;
+                    };
+                    auto release = [&]() {
+                        // every column of this stage is in registers: hand the TMEM stage back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
+                    };
+                    if (p.unit == 4u) {
+                        // head counts that are not a multiple of 16: four columns at a time, no software pipeline
+                        for (uint32_t u = 0; u < nunits; ++u) {
+                            uint32_t v[4];
+                            __syncwarp();
+                            tmem_ld_x4(taddr + u * 4u, v);
+                            tmem_ld_wait();
+                            if (u + 1 == nunits) release();
+                            const float4 ww = *reinterpret_cast<const float4*>(w + col_base + u * 4u);
+                            const float x0 = __uint_as_float(v[0]), x1 = __uint_as_float(v[1]);
+                            const float x2 = __uint_as_float(v[2]), x3 = __uint_as_float(v[3]);
+                            a0 = fmaf(x0 + fabsf(x0), ww.x, a0);
+                            a1 = fmaf(x1 + fabsf(x1), ww.y, a1);
+                            a2 = fmaf(x2 + fabsf(x2), ww.z, a2);
+                            a3 = fmaf(x3 + fabsf(x3), ww.w, a3);
+                            if (++unit_in_q == units_per_q) store_query();
+                        }
+                        continue;
                     }
-                };
-                auto release = [&]() {
-                    // every column of this stage is in registers: hand the TMEM stage back
-                    tc_fence_before();
+                    // The reduction runs in units of 16 columns.  relu(x) * w is computed as
+                    // (x + |x|) * (w / 2): the addition takes |x| as a source modifier and runs on the FMA
+                    // pipe at full rate, where a max would go through the half-rate ALU pipe; both
+                    // scalings are by powers of two, so the result is the same bit for bit (the weights in
+                    // shared memory are already halved).  The TMEM load and the four weight vectors of
+                    // unit u + 1 are requested before the arithmetic of unit u starts, so that neither the
+                    // tensor-memory latency nor the shared-memory latency sits between dependent
+                    // instructions; 16-column units keep both register sets inside the 102 registers a
+                    // 640-thread block leaves per thread.
+                    auto load_w = [&](float4 (&dst)[4], uint32_t u) {
+                        const float4* w4 = reinterpret_cast<const float4*>(w + col_base + u * 16u);
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) dst[i] = w4[i];
+                    };
+                    auto consume = [&](const uint32_t (&v)[16], const float4 (&ww)[4]) {
+#pragma unroll
+                        for (uint32_t i = 0; i < 4; ++i) {
+                            const float x0 = __uint_as_float(v[4 * i]), x1 = __uint_as_float(v[4 * i + 1]);
+                            const float x2 = __uint_as_float(v[4 * i + 2]), x3 = __uint_as_float(v[4 * i + 3]);
+                            a0 = fmaf(x0 + fabsf(x0), ww[i].x, a0);
+                            a1 = fmaf(x1 + fabsf(x1), ww[i].y, a1);
+                            a2 = fmaf(x2 + fabsf(x2), ww[i].z, a2);
+                            a3 = fmaf(x3 + fabsf(x3), ww[i].w, a3);
+                        }
+                        if (++unit_in_q == units_per_q) store_query();
+                    };
+                    uint32_t va[16], vb[16];
+                    float4 wa[4], wb4[4];
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
-                };
-                uint32_t va[16], vb[16];
-                float4 wa[4], wb4[4];
-                __syncwarp();
-                tmem_ld_x16(taddr, va);
-                load_w(wa, 0);
-                tmem_ld_wait();
-                for (uint32_t u = 0; u < nunits; u += 2) {
-                    if (u + 1 < nunits) { tmem_ld_x16(taddr + (u + 1) * 16u, vb); load_w(wb4, u + 1); } else release();
-                    consume(va, wa);
-                    if (u + 1 < nunits) {
-                        tmem_ld_wait();
-                        if (u + 2 < nunits) { tmem_ld_x16(taddr + (u + 2) * 16u, va); load_w(wa, u + 2); } else release();
-                        consume(vb, wb4);
-                        if (u + 2 < nunits) tmem_ld_wait();
+                    tmem_ld_x16(taddr, va);
+                    load_w(wa, 0);
+                    tmem_ld_wait();
+                    for (uint32_t u = 0; u < nunits; u += 2) {
+                        if (u + 1 < nunits) { tmem_ld_x16(taddr + (u + 1) * 16u, vb); load_w(wb4, u + 1); } else release();
+                        consume(va, wa);
+                        if (u + 1 < nunits) {
+                            tmem_ld_wait();
+                            if (u + 2 < nunits) { tmem_ld_x16(taddr + (u + 2) * 16u, va); load_w(wa, u + 2); } else release();
+                            consume(vb, wb4);
+                            if (u + 2 < nunits) tmem_ld_wait();
+                        }
                     }
                 }
             }
@@ -373,6 +744,67 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
+}
+
+// ---------------------------------------------------------------------------- paged metadata
+// Counterpart of mqa_paged_metadata_impl (deepgemm/kernels/mqa_logits_sm100.cu:359-492): one block turns the
+// sorted request ids and the context lengths into the list the main kernel cuts its shares from.
+//   req_first[t]  first token of t's request (runs of equal ids)
+//   qb_tokens[t]  a query block starts at every block_q-th token of a request: its token count, else 0
+//   cum[t]        kv blocks (128 tokens) of all query blocks that start before t; cum[T] = all work
+// A query block needs the kv tokens [0, context length of its last token): context lengths grow inside a
+// request (deepgemm/kernels/mqa_logits_sm100.cu:207-216), so that is the longest of its own.
+constexpr uint32_t kMetaThreads = 1024;
+__device__ __forceinline__ uint32_t block_scan_excl(uint32_t v, uint32_t* sh, bool use_max) {
+    // exclusive scan (sum or max) of one value per thread over the block; identity 0
+    const uint32_t tid = threadIdx.x;
+    sh[tid] = v;
+    __syncthreads();
+    for (uint32_t d = 1; d < kMetaThreads; d <<= 1) {
+        const uint32_t other = tid >= d ? sh[tid - d] : 0u;
+        __syncthreads();
+        sh[tid] = use_max ? max(sh[tid], other) : sh[tid] + other;
+        __syncthreads();
+    }
+    const uint32_t r = tid ? sh[tid - 1] : 0u;
+    __syncthreads();
+    return r;
+}
+__global__ void __launch_bounds__(kMetaThreads) mqa_paged_metadata_kernel(const uint32_t* __restrict__ context_lens,
+                                                                         const uint32_t* __restrict__ indices, uint32_t num_tokens,
+                                                                         uint32_t block_q, uint32_t max_ctx, uint32_t* cum,
+                                                                         uint32_t* qb_tokens, uint32_t* req_first) {
+    __shared__ uint32_t sh[kMetaThreads];
+    const uint32_t per = (num_tokens + kMetaThreads - 1) / kMetaThreads;
+    const uint32_t t0 = min(threadIdx.x * per, num_tokens), t1 = min(t0 + per, num_tokens);
+    // request starts: running maximum of (start position + 1)
+    uint32_t run = 0;
+    for (uint32_t t = t0; t < t1; ++t)
+        if (t == 0 || indices[t] != indices[t - 1]) run = t + 1;
+    uint32_t carry = block_scan_excl(run, sh, true);
+    for (uint32_t t = t0; t < t1; ++t) {
+        if (t == 0 || indices[t] != indices[t - 1]) carry = t + 1;
+        req_first[t] = carry - 1u;
+    }
+    // query blocks and their kv blocks
+    uint32_t local = 0;
+    for (uint32_t t = t0; t < t1; ++t) {
+        const uint32_t first = req_first[t];
+        uint32_t nq = 0;
+        if ((t - first) % block_q == 0) {
+            nq = 1;
+            while (nq < block_q && t + nq < num_tokens && indices[t + nq] == indices[t]) ++nq;
+        }
+        qb_tokens[t] = nq;
+        if (nq) local += (min(context_lens[t + nq - 1], max_ctx) + kMqaBlockKv - 1) / kMqaBlockKv;
+    }
+    uint32_t acc = block_scan_excl(local, sh, false);
+    for (uint32_t t = t0; t < t1; ++t) {
+        cum[t] = acc;
+        const uint32_t nq = qb_tokens[t];
+        if (nq) acc += (min(context_lens[t + nq - 1], max_ctx) + kMqaBlockKv - 1) / kMqaBlockKv;
+    }
+    if (threadIdx.x == kMetaThreads - 1) cum[num_tokens] = acc;
 }
 
 // ============================================================================ host side
@@ -389,36 +821,71 @@ static int32_t check_mqa_common(uint32_t num_tokens, uint32_t num_kv, uint32_t n
     return DG_OK;
 }
 
-template <bool SCALED>
+struct MqaPaged {
+    uint32_t page_kv = 0, num_pages = 0, block_table_stride = 0;
+    const uint32_t* context_lens = nullptr;
+    const uint32_t* indices = nullptr;
+    const uint32_t* block_table = nullptr;
+};
+
+static uint32_t mqa_env(const char* name, uint32_t dflt) {
+    const char* v = getenv(name);
+    return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
+}
+
+template <bool SCALED, bool FP4, bool PAGED>
 static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint32_t q_sf_cols, const uint32_t* kv_sf,
                        uint32_t kv_sf_cols, const float* kv_scale, const void* weights, const uint32_t* ks,
                        const uint32_t* ke, uint32_t num_tokens, uint32_t num_kv, uint32_t num_heads, uint32_t head_dim,
-                       void* logits, uint32_t logits_stride, void* stream) {
-    // Tiling: the query block holds an even number of queries so that the two epilogue
-    // warpgroups split it; heads must come in whole 32-column TMEM loads.
-    const uint32_t max_n = SCALED ? 192u : 256u;
-    if (num_heads % 32 != 0 || 2 * num_heads > max_n)
-        return fail(DG_ERR_UNSUPPORTED, "mqa_logits: this build handles num_heads in {32, 64%s}, got %u",
-                    SCALED ? ", 96" : ", 96, 128", num_heads);
+                       void* logits, uint32_t logits_stride, const MqaPaged& pg, void* stream) {
     const DeviceInfo* dev;
     int32_t st = current_device(&dev);
     if (st != DG_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
     MqaParams p{};
     p.num_tokens = num_tokens; p.num_kv = num_kv; p.num_heads = num_heads; p.head_dim = head_dim;
-    p.block_q = 2 * (max_n / 2 / num_heads);
-    p.n = p.block_q * num_heads;
-    p.ep_groups = p.block_q % 4 == 0 ? 4u : 2u;
-    p.num_q_blocks = ceil_div(num_tokens, p.block_q);
-    p.sbo = 8 * head_dim;
-    p.layout = head_dim == 128 ? 2u : head_dim == 64 ? 4u : 6u;
-    const CUtensorMapSwizzle sw = head_dim == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
-                                : head_dim == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    // Tiling: n = block_q * num_heads score columns per kv block, at most 256 (192 beside the scale-factor
+    // columns of the ue8m0 contracts); the MMA wants a multiple of 16 columns and computes a few unused ones
+    // when n is not.  The tensor-core reduction works on sub-tiles of 128 columns holding whole queries
+    // (16, 32, 64 or 128 heads): two per kv block for the fp32 contract, one for the ue8m0 contracts.
+    const uint32_t max_n = SCALED ? 192u : 256u;
+    const bool tsred = mqa_env("DG_MQA_TSRED", 1) != 0 && num_heads >= 16 && kMqaSub % num_heads == 0;
+    uint32_t block_q;
+    if (tsred) {
+        p.subs = SCALED ? 1u : 2u;
+        p.num_acc = SCALED ? 3u : 4u;
+        block_q = p.subs * (kMqaSub / num_heads);
+        p.acc_stride = kMqaSub;
+    } else {
+        block_q = max_n / num_heads;
+        if (block_q > 16) block_q = 16;
+        if (block_q >= 4) block_q &= ~3u; else if (block_q == 3) block_q = 2;
+        if (block_q == 0) return fail(DG_ERR_UNSUPPORTED, "mqa_logits: %u heads do not fit the %u score columns of this contract", num_heads, max_n);
+        p.subs = 1; p.num_acc = 2;
+        p.acc_stride = SCALED ? 192u : 256u;
+    }
+    p.block_q = block_q;
+    p.n = block_q * num_heads;
+    p.n_mma = tsred ? kMqaSub : align_up(p.n, 16);
+    p.ep_groups = tsred ? 4u : (block_q % 4 == 0 ? 4u : block_q % 2 == 0 ? 2u : 1u);
+    p.unit = num_heads % 16 == 0 ? 16u : 4u;
+    p.num_q_blocks = ceil_div(num_tokens, block_q);
+    p.row_bytes = FP4 ? head_dim / 2 : head_dim;
+    p.sbo = 8 * p.row_bytes;
+    p.layout = p.row_bytes == 128 ? 2u : p.row_bytes == 64 ? 4u : p.row_bytes == 32 ? 6u : 0u;
+    if (p.layout == 0) return fail(DG_ERR_INVALID_ARG, "MXFP4 requires head_dim 64/128");
+    const CUtensorMapSwizzle sw = p.row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : p.row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    p.num_mma = p.row_bytes / 32u;
+    p.idesc = SCALED ? make_idesc_bs(FP4 ? 1u : 0u, FP4 ? 1u : 0u, kMqaBlockKv, p.n_mma) : make_idesc_f8(kMqaBlockKv, p.n_mma);
+    p.idesc2 = make_idesc_bf16(kMqaBlockKv, 16);
     p.off_w = 1024;
-    p.off_q = 1024 + 2048;
-    p.q_sf_off = align_up(p.n * head_dim, 1024);
+    p.off_q = 1024 + (tsred ? 2 * kMqaW2Bytes : 2048u);
+    const uint32_t q_rows = tsred ? p.n : p.n_mma;      // the MMA of the last rows may read a few rows past the box
+    p.q_sf_off = align_up(q_rows * p.row_bytes, 1024);
     p.q_stage_bytes = p.q_sf_off + (SCALED ? 1024u : 0u);
     p.off_kv = p.off_q + 2 * p.q_stage_bytes;
-    p.kv_sf_off = kMqaBlockKv * head_dim;
+    p.kv_sf_off = kMqaBlockKv * p.row_bytes;
     p.kv_stage_bytes = align_up(p.kv_sf_off + (SCALED ? 512u : 0u), 1024);
     const uint32_t budget = (uint32_t)dev->smem_optin - 1024u;
     uint32_t stages = (budget - p.off_kv) / p.kv_stage_bytes;
@@ -430,35 +897,82 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     p.ks = ks; p.ke = ke; p.kv_scale = kv_scale; p.weights = weights; p.logits = logits;
     p.status = dev->status;
 
+    uint32_t* meta = nullptr;
+    if (PAGED) {
+        p.page_kv = pg.page_kv;
+        p.box_rows = pg.page_kv < kMqaBlockKv ? pg.page_kv : kMqaBlockKv;
+        p.boxes_per_block = kMqaBlockKv / p.box_rows;
+        p.kv_sf = kv_sf;
+        p.context_lens = pg.context_lens;
+        p.block_table = pg.block_table;
+        p.block_table_stride = pg.block_table_stride;
+        // scratch of the metadata kernel: three arrays of one word per token, stream-ordered
+        const size_t words = 3 * (size_t)num_tokens + 4;
+        DG_CUDA_CHECK(cudaMallocAsync(&meta, words * sizeof(uint32_t), s));
+        uint32_t* cum = meta;
+        uint32_t* qb_tokens = meta + num_tokens + 1;
+        uint32_t* req_first = qb_tokens + num_tokens;
+        p.cum = cum; p.qb_tokens = qb_tokens; p.req_first = req_first;
+        const uint64_t max_ctx64 = (uint64_t)pg.block_table_stride * pg.page_kv;
+        mqa_paged_metadata_kernel<<<1, kMetaThreads, 0, s>>>(pg.context_lens, pg.indices, num_tokens, block_q,
+                                                             (uint32_t)(max_ctx64 > 0xffffff00ull ? 0xffffff00ull : max_ctx64), cum,
+                                                             qb_tokens, req_first);
+        note_launch();
+    }
+
     CUtensorMap tq, tkv, tqsf, tkvsf;
-    if ((st = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, head_dim, (uint64_t)num_tokens * num_heads, head_dim,
-                           head_dim, p.n, sw, "q")) != DG_OK) return st;
-    if ((st = make_tmap_2d(&tkv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, kv, head_dim, num_kv, head_dim, head_dim, kMqaBlockKv,
-                           sw, "kv")) != DG_OK) return st;
+    auto fail_free = [&](int32_t code) { if (meta) cudaFreeAsync(meta, s); return code; };
+    if ((st = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, p.row_bytes, (uint64_t)num_tokens * num_heads, p.row_bytes,
+                           p.row_bytes, p.n, sw, "q")) != DG_OK) return fail_free(st);
+    if ((st = make_tmap_2d(&tkv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, kv, p.row_bytes, num_kv, p.row_bytes, p.row_bytes,
+                           PAGED ? p.box_rows : kMqaBlockKv, sw, "kv")) != DG_OK) return fail_free(st);
+    tqsf = tq; tkvsf = tkv;
     if (SCALED) {
         if ((st = make_tmap_2d(&tqsf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, q_sf, q_sf_cols, 1, (uint64_t)q_sf_cols * 4, p.n, 1,
-                               CU_TENSOR_MAP_SWIZZLE_NONE, "q_sf")) != DG_OK) return st;
-        if ((st = make_tmap_2d(&tkvsf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, kv_sf, kv_sf_cols, 1, (uint64_t)kv_sf_cols * 4,
-                               kMqaBlockKv, 1, CU_TENSOR_MAP_SWIZZLE_NONE, "kv_sf")) != DG_OK) return st;
-    } else {
-        tqsf = tq; tkvsf = tkv;
+                               CU_TENSOR_MAP_SWIZZLE_NONE, "q_sf")) != DG_OK) return fail_free(st);
+        if (!PAGED && (st = make_tmap_2d(&tkvsf, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, kv_sf, kv_sf_cols, 1, (uint64_t)kv_sf_cols * 4,
+                                         kMqaBlockKv, 1, CU_TENSOR_MAP_SWIZZLE_NONE, "kv_sf")) != DG_OK) return fail_free(st);
     }
-    auto* fn = mqa_logits_kernel<SCALED>;
-    DG_CUDA_CHECK(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     uint32_t grid = (uint32_t)dev->sm_count;
-    if (p.num_q_blocks < grid) grid = p.num_q_blocks;
+    if (!PAGED && p.num_q_blocks < grid) grid = p.num_q_blocks;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(128u + 128u * p.ep_groups);
     cfg.dynamicSmemBytes = smem_bytes;
-    cfg.stream = static_cast<cudaStream_t>(stream);
+    cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // set-up overlaps the previous kernel's tail
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p));
+    cudaError_t e;
+    if (tsred) {
+        auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, true>;
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
+    } else {
+        auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false>;
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
+    }
+    if (meta) cudaFreeAsync(meta, s);
+    if (e != cudaSuccess) return fail(DG_ERR_DRIVER, "mqa_logits launch failed: %s", cudaGetErrorString(e));
     dg::note_launch();
+    return DG_OK;
+}
+
+// q operand checks shared by the contiguous and the paged ue8m0 entries
+static int32_t check_mqa_q(const dg_operand_t* q, uint32_t num_tokens, uint32_t num_heads, uint32_t head_dim) {
+    if (!q || !q->data) return fail(DG_ERR_INVALID_ARG, "mqa_logits: null operand");
+    if (q->dtype != DG_FP8 && q->dtype != DG_FP4) return fail(DG_ERR_INVALID_ARG, "mqa_logits: q/kv must be FP8 or FP4");
+    if (q->dtype == DG_FP4 && head_dim != 64 && head_dim != 128) return fail(DG_ERR_INVALID_ARG, "MXFP4 requires head_dim 64/128");
+    if (!q->sf.data) return fail(DG_ERR_INVALID_ARG, "mqa_logits: q and kv require scale factors");
+    if (q->sf.gran != 32) return fail(DG_ERR_INVALID_ARG, "mqa_logits: scale granularity must be 32");
+    if (q->rows != num_tokens * num_heads || q->k != head_dim)
+        return fail(DG_ERR_INVALID_ARG, "mqa_logits: q must be [num_tokens*num_heads, head_dim] and kv [num_kv_tokens, head_dim]");
+    if (q->major != DG_MAJOR_K || q->outer_stride != head_dim)
+        return fail(DG_ERR_INVALID_ARG, "mqa_logits: q and kv must be dense K-major rows (outer_stride == head_dim)");
+    if (q->sf.cols < align_up(q->rows, 4) || q->sf.rows < 1) return fail(DG_ERR_INVALID_ARG, "mqa_logits: scale-factor tensors too small");
     return DG_OK;
 }
 
@@ -474,8 +988,8 @@ int32_t dg_mqa_logits_f32(const void* q, const void* kv, const float* kv_scale, 
     int32_t st = dg::check_mqa_common(num_tokens, num_kv_tokens, num_heads, head_dim, logits_stride, cu_k_start, cu_k_end,
                                       weights, logits);
     if (st != DG_OK) return st;
-    return dg::run_mqa<false>(q, kv, nullptr, 0, nullptr, 0, kv_scale, weights, cu_k_start, cu_k_end, num_tokens,
-                              num_kv_tokens, num_heads, head_dim, logits, logits_stride, stream);
+    return dg::run_mqa<false, false, false>(q, kv, nullptr, 0, nullptr, 0, kv_scale, weights, cu_k_start, cu_k_end, num_tokens,
+                                            num_kv_tokens, num_heads, head_dim, logits, logits_stride, dg::MqaPaged{}, stream);
 }
 
 int32_t dg_mqa_logits(const dg_operand_t* q, const dg_operand_t* kv, const void* weights_bf16, const uint32_t* cu_k_start,
@@ -486,22 +1000,51 @@ int32_t dg_mqa_logits(const dg_operand_t* q, const dg_operand_t* kv, const void*
     int32_t st = dg::check_mqa_common(num_tokens, num_kv_tokens, num_heads, head_dim, logits_stride, cu_k_start, cu_k_end,
                                       weights_bf16, logits_bf16);
     if (st != DG_OK) return st;
-    if (q->dtype == DG_FP4) {
-        if (head_dim != 64 && head_dim != 128) return dg::fail(DG_ERR_INVALID_ARG, "MXFP4 requires head_dim 64/128");
-        return dg::fail(DG_ERR_UNSUPPORTED, "mqa_logits: the MXFP4 flavour is not built");
-    }
-    if (q->dtype != DG_FP8) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q/kv must be FP8 or FP4");
-    if (!q->sf.data || !kv->sf.data) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q and kv require scale factors");
-    if (q->sf.gran != 32 || kv->sf.gran != 32) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: scale granularity must be 32");
-    if (q->rows != num_tokens * num_heads || q->k != head_dim || kv->rows != num_kv_tokens || kv->k != head_dim)
+    if ((st = dg::check_mqa_q(q, num_tokens, num_heads, head_dim)) != DG_OK) return st;
+    if (!kv->sf.data || kv->sf.gran != 32) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q and kv require scale factors of granularity 32");
+    if (kv->rows != num_kv_tokens || kv->k != head_dim)
         return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q must be [num_tokens*num_heads, head_dim] and kv [num_kv_tokens, head_dim]");
-    if (q->major != DG_MAJOR_K || kv->major != DG_MAJOR_K || q->outer_stride != head_dim || kv->outer_stride != head_dim)
+    if (kv->major != DG_MAJOR_K || kv->outer_stride != head_dim)
         return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: q and kv must be dense K-major rows (outer_stride == head_dim)");
-    if (q->sf.cols < dg::align_up(q->rows, 4) || kv->sf.cols < dg::align_up(kv->rows, 4) || q->sf.rows < 1 || kv->sf.rows < 1)
+    if (kv->sf.cols < dg::align_up(kv->rows, 4) || kv->sf.rows < 1)
         return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits: scale-factor tensors too small");
-    return dg::run_mqa<true>(q->data, kv->data, q->sf.data, q->sf.cols, kv->sf.data, kv->sf.cols, nullptr, weights_bf16,
-                             cu_k_start, cu_k_end, num_tokens, num_kv_tokens, num_heads, head_dim, logits_bf16,
-                             logits_stride, stream);
+    if (q->dtype == DG_FP4)
+        return dg::run_mqa<true, true, false>(q->data, kv->data, q->sf.data, q->sf.cols, kv->sf.data, kv->sf.cols, nullptr, weights_bf16,
+                                              cu_k_start, cu_k_end, num_tokens, num_kv_tokens, num_heads, head_dim, logits_bf16,
+                                              logits_stride, dg::MqaPaged{}, stream);
+    return dg::run_mqa<true, false, false>(q->data, kv->data, q->sf.data, q->sf.cols, kv->sf.data, kv->sf.cols, nullptr, weights_bf16,
+                                           cu_k_start, cu_k_end, num_tokens, num_kv_tokens, num_heads, head_dim, logits_bf16,
+                                           logits_stride, dg::MqaPaged{}, stream);
+}
+
+int32_t dg_mqa_logits_paged(const dg_operand_t* q, const void* kv_pages, const uint32_t* kv_sf_pages, const void* weights_bf16,
+                            uint32_t page_kv, uint32_t num_pages, const uint32_t* context_lens, const uint32_t* indices,
+                            const uint32_t* block_table, uint32_t block_table_stride, uint32_t num_tokens, uint32_t num_heads,
+                            uint32_t head_dim, void* logits_bf16, uint32_t logits_stride, void* stream) {
+    if (!kv_pages || !kv_sf_pages || !context_lens || !indices || !block_table)
+        return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits_paged: null buffer");
+    // deepgemm/src/api.rs:1778-1795
+    if (head_dim % 32 != 0 || head_dim > 128 || head_dim == 96 || head_dim == 0)
+        return dg::fail(DG_ERR_INVALID_ARG, "head_dim must be 32/64/128");
+    if (num_heads % 4 != 0 || num_heads > 256 || num_heads == 0)
+        return dg::fail(DG_ERR_INVALID_ARG, "num_heads must be a multiple of 4 (<= 256)");
+    if (page_kv == 0 || page_kv % 4 != 0 || 256 % page_kv != 0)
+        return dg::fail(DG_ERR_INVALID_ARG, "page_kv must divide 256 (multiple of 4)");
+    if (!q || (q->dtype != DG_FP8 && q->dtype != DG_FP4)) return dg::fail(DG_ERR_INVALID_ARG, "paged MQA needs FP8 or FP4 Q");
+    if (num_tokens == 0 || num_pages == 0 || block_table_stride == 0 || logits_stride == 0 || !weights_bf16 || !logits_bf16)
+        return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits_paged: empty problem");
+    if ((uint64_t)num_pages * page_kv >= (1ull << 31)) return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits_paged: the cache exceeds 2^31 tokens");
+    int32_t st = dg::check_mqa_q(q, num_tokens, num_heads, head_dim);
+    if (st != DG_OK) return st;
+    dg::MqaPaged pg;
+    pg.page_kv = page_kv; pg.num_pages = num_pages; pg.block_table_stride = block_table_stride;
+    pg.context_lens = context_lens; pg.indices = indices; pg.block_table = block_table;
+    const uint32_t num_kv = num_pages * page_kv;
+    if (q->dtype == DG_FP4)
+        return dg::run_mqa<true, true, true>(q->data, kv_pages, q->sf.data, q->sf.cols, kv_sf_pages, num_kv, nullptr, weights_bf16, nullptr,
+                                             nullptr, num_tokens, num_kv, num_heads, head_dim, logits_bf16, logits_stride, pg, stream);
+    return dg::run_mqa<true, false, true>(q->data, kv_pages, q->sf.data, q->sf.cols, kv_sf_pages, num_kv, nullptr, weights_bf16, nullptr,
+                                          nullptr, num_tokens, num_kv, num_heads, head_dim, logits_bf16, logits_stride, pg, stream);
 }
 
 }  // extern "C"

@@ -93,6 +93,7 @@ def load(build_if_missing=True):
         L.dg_mqa_logits_f32.argtypes = [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, vp, u32, vp]
     if hasattr(L, "dg_mqa_logits"):
         L.dg_mqa_logits.argtypes = [opp, opp, vp, vp, vp, u32, u32, u32, u32, vp, u32, vp]
+    L.dg_mqa_logits_paged.argtypes = [opp, vp, vp, vp, u32, u32, vp, vp, vp, u32, u32, u32, u32, vp, u32, vp]
     L.dg_gather_rows.argtypes = [vp, u64, vp, vp, u64, u32, u32, vp]
     L.dg_gather_sf.argtypes = [vp, u64, u64, vp, vp, u64, u64, u32, u32, vp]
     L.dg_moe_plan.argtypes = [vp, u32, u32, u32, u32, u32, vp, vp, vp, vp, vp, vp, vp]

@@ -298,6 +298,18 @@ def mqa_logits(q, kv, weights, cu_k_start, cu_k_end, num_tokens, num_kv_tokens, 
                                      logits.data_ptr(), logits_stride, _stream_ptr(stream)))
 
 
+def mqa_logits_paged(q, kv_pages, kv_sf_pages, weights, page_kv, num_pages, context_lens, indices, block_table,
+                     block_table_stride, num_tokens, num_heads, head_dim, logits, logits_stride, stream=None):
+    """Paged-KV mqa_logits for decode (api.rs:1752-1775): q Operand with its scale factors, kv_pages
+    [num_pages, page_kv, head_dim] codes, kv_sf_pages [num_pages, page_kv] int32, weights bf16 [T, H],
+    context_lens / indices int32 [T], block_table int32 [T, block_table_stride], logits bf16."""
+    qc = _op_c(q)
+    _check(_lib.load().dg_mqa_logits_paged(C.byref(qc), kv_pages.data_ptr(), kv_sf_pages.data_ptr(), weights.data_ptr(), page_kv,
+                                           num_pages, context_lens.data_ptr(), indices.data_ptr(), block_table.data_ptr(),
+                                           block_table_stride, num_tokens, num_heads, head_dim, logits.data_ptr(), logits_stride,
+                                           _stream_ptr(stream)))
+
+
 def get_gemm_config(dtype, kind, m, n, k, num_groups=1):
     cfg = _lib.GemmConfigC()
     _check(_lib.load().dg_get_gemm_config(int(dtype), kind, m, n, k, num_groups, C.byref(cfg)))

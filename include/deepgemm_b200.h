@@ -232,12 +232,30 @@ DG_API int32_t dg_mqa_logits_f32(const void* q, const void* kv, const float* kv_
                           uint32_t num_tokens, uint32_t num_kv_tokens, uint32_t num_heads, uint32_t head_dim,
                           float* logits, uint32_t logits_stride, void* stream);
 /* reference SM100 contract, api::mqa_logits (deepgemm/src/api.rs:1614-1745): q and kv carry
- * packed UE8M0 per-32 scales, weights are bf16 [T,H], logits are bf16 and stored compressed
- * at column j - ks[i] (deepgemm/kernels/mqa_logits_sm100.cu:1014-1020). */
+ * packed UE8M0 per-32 scales (the reference passes them as separate SfTensors, here they ride in
+ * q.sf / kv.sf), FP8 or packed FP4 codes (head_dim 64 / 128), weights are bf16 [T,H], logits are bf16 and
+ * stored compressed at column j - ks[i] (deepgemm/kernels/mqa_logits_sm100.cu:1014-1020).  num_heads: any
+ * multiple of 4 whose query block fits 192 score columns (up to 192 heads). */
 DG_API int32_t dg_mqa_logits(const dg_operand_t* q, const dg_operand_t* kv, const void* weights_bf16,
                       const uint32_t* cu_k_start, const uint32_t* cu_k_end,
                       uint32_t num_tokens, uint32_t num_kv_tokens, uint32_t num_heads, uint32_t head_dim,
                       void* logits_bf16, uint32_t logits_stride, void* stream);
+
+/* replaces api::mqa_logits_paged (deepgemm/src/api.rs:1752-1941) and its metadata kernel
+ * (deepgemm/kernels/mqa_logits_sm100.cu:359-492): the ue8m0 contract over a paged KV cache, for decode.
+ * q as in dg_mqa_logits ([num_tokens * num_heads, head_dim], FP8 or FP4, per-32 scales); kv_pages
+ * [num_pages, page_kv, head_dim] codes and kv_sf_pages [num_pages, page_kv] one scale word per token;
+ * weights bf16 [num_tokens, num_heads].  indices[t] = request of query token t (sorted: tokens of a request
+ * are neighbours), context_lens[t] = kv tokens visible to token t (growing inside a request),
+ * block_table[first token of the request][i] = page holding the request's kv tokens [i * page_kv, (i+1) *
+ * page_kv).  logits[t, j] (bf16, row pitch logits_stride) for j in [0, context_lens[t]); other columns are
+ * not written.  page_kv divides 256 and is a multiple of 4.  The call takes a few words of stream-ordered
+ * scratch per query token for its work list (cudaMallocAsync on `stream`). */
+DG_API int32_t dg_mqa_logits_paged(const dg_operand_t* q, const void* kv_pages, const uint32_t* kv_sf_pages,
+                                   const void* weights_bf16, uint32_t page_kv, uint32_t num_pages,
+                                   const uint32_t* context_lens, const uint32_t* indices, const uint32_t* block_table,
+                                   uint32_t block_table_stride, uint32_t num_tokens, uint32_t num_heads, uint32_t head_dim,
+                                   void* logits_bf16, uint32_t logits_stride, void* stream);
 
 /* ---- MoE row movement around the grouped GEMM -----------------------------------------------
  * The steps the reference leaves to the caller of Serving::moe_grouped_layer

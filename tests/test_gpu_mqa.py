@@ -85,3 +85,116 @@ def test_mqa_logits_ue8m0_contract(T, S, H, D):
     poll_device_status()
     got = logits.float().cpu().numpy()
     _check(got, o.bf16_bits_to_f32(o.f32_to_bf16_bits_np(ref)), ks, ke, S, fill)
+
+
+@pytest.mark.parametrize("H,D", [(16, 128), (36, 128), (100, 64), (128, 128), (256, 128), (4, 32), (96, 128)])
+def test_mqa_logits_f32_head_counts(H, D):
+    """Any multiple of 4 up to 256 (deepgemm/src/api.rs:1639-1650); counts that divide 128 take the tensor-core
+    reduction, the others the CUDA-core one."""
+    T, S = 21, 640
+    q8, kv8, scale, w = _inputs_f32(T, S, H, D, H + D)
+    rng = np.random.default_rng(H)
+    ks = rng.integers(0, S // 2, T).astype(np.uint32)
+    ke = (ks + rng.integers(0, S, T)).astype(np.uint32)
+    ref = o.mqa_logits_ref(E4M3[q8], E4M3[kv8] * scale[:, None], w, ks, ke)
+    fill = -3.0
+    logits = torch.full((T, S), fill, dtype=torch.float32, device="cuda")
+    mqa_logits_f32(dev(q8), dev(kv8), dev(scale), dev(w), dev(ks.view(np.int32)), dev(ke.view(np.int32)), T, S, H, D, logits, S)
+    poll_device_status()
+    _check(logits.cpu().numpy(), ref, ks, ke, S, fill)
+
+
+@pytest.mark.parametrize("reduction", ["tensor", "cuda"])
+def test_mqa_logits_both_reductions_agree_with_the_oracle(reduction, monkeypatch):
+    monkeypatch.setenv("DG_MQA_TSRED", "1" if reduction == "tensor" else "0")
+    T, S, H, D = 70, 1500, 64, 128
+    q8, kv8, scale, w = _inputs_f32(T, S, H, D, 99)
+    ks, ke = np.zeros(T, np.uint32), (S - T + np.arange(T) + 1).astype(np.uint32)
+    ref = o.mqa_logits_ref(E4M3[q8], E4M3[kv8] * scale[:, None], w, ks, ke)
+    logits = torch.full((T, S), -1.0, dtype=torch.float32, device="cuda")
+    mqa_logits_f32(dev(q8), dev(kv8), dev(scale), dev(w), dev(ks.view(np.int32)), dev(ke.view(np.int32)), T, S, H, D, logits, S)
+    poll_device_status()
+    _check(logits.cpu().numpy(), ref, ks, ke, S, -1.0)
+
+
+@pytest.mark.parametrize("T,S,H,D", [(8, 256, 64, 128), (40, 700, 64, 128), (24, 512, 32, 64), (10, 300, 96, 128)])
+def test_mqa_logits_mxfp4(T, S, H, D):
+    """The reference accepts packed FP4 q / kv with head_dim 64 / 128 (deepgemm/src/api.rs:1639-1650)."""
+    qf, kvf = randn((T * H, D), 13), randn((S, D), 14) * 2.0
+    q4, qsf = o.quant_mx_host(qf, o.FP4, 32)
+    kv4, kvsf = o.quant_mx_host(kvf, o.FP4, 32)
+    wb = torch.from_numpy(randn((T, H), 15)).to(torch.bfloat16)
+    rng = np.random.default_rng(T + 1)
+    ks = rng.integers(0, S // 2, T).astype(np.uint32)
+    ke = (ks + rng.integers(1, S, T)).astype(np.uint32)
+    qd = o.dequant_mx_host(q4, qsf, T * H, D, o.FP4, 32).reshape(T, H, D)
+    kvd = o.dequant_mx_host(kv4, kvsf, S, D, o.FP4, 32)
+    ref = o.mqa_logits_ref(qd, kvd, wb.float().numpy(), ks, ke)
+    qop = Operand.k_major(Dtype.Fp4, T * H, D, D, sf_tensor(qsf, 32), dev(q4))
+    kvop = Operand.k_major(Dtype.Fp4, S, D, D, sf_tensor(kvsf, 32), dev(kv4))
+    fill = -9.0
+    logits = torch.full((T, S), fill, dtype=torch.bfloat16, device="cuda")
+    mqa_logits(qop, kvop, wb.cuda(), dev(ks.view(np.int32)), dev(ke.view(np.int32)), T, S, H, D, logits, S)
+    poll_device_status()
+    _check(logits.float().cpu().numpy(), o.bf16_bits_to_f32(o.f32_to_bf16_bits_np(ref)), ks, ke, S, fill)
+
+
+@pytest.mark.parametrize("kind,H,D,page_kv", [("fp8", 64, 128, 64), ("fp8", 64, 128, 4), ("fp8", 32, 64, 16), ("fp8", 64, 128, 256),
+                                              ("fp8", 36, 128, 32), ("fp4", 64, 128, 64), ("fp4", 32, 64, 8), ("fp8", 64, 128, 128)])
+def test_mqa_logits_paged(kind, H, D, page_kv):
+    """Decode over a paged cache (deepgemm/src/api.rs:1752-1941): requests of 1..5 query tokens with growing
+    context lengths, pages scattered over the cache, every request checked against the oracle on its own
+    gathered kv tokens; columns at and beyond a token's context length stay untouched."""
+    from deepgemm import mqa_logits_paged
+    rng = np.random.default_rng(H + page_kv)
+    odt, dt = (o.FP8, Dtype.Fp8) if kind == "fp8" else (o.FP4, Dtype.Fp4)
+    reqs = [(1, 700), (3, 1300), (5, 260), (2, 1), (4, 2049), (1, 128), (2, 0)]        # (query tokens, context of the last token)
+    T = sum(n for n, _ in reqs)
+    indices, ctx = [], []
+    for r, (n, c) in enumerate(reqs):
+        indices += [7 * r + 3] * n
+        ctx += [max(0, c - (n - 1 - i)) for i in range(n)]
+    max_ctx = max(c for _, c in reqs)
+    stride = -(-max_ctx // page_kv) + 2
+    num_pages = sum(-(-c // page_kv) for _, c in reqs) + 5
+    perm = rng.permutation(num_pages)
+    table = np.zeros((T, stride), dtype=np.int32)
+    table[:] = 10 ** 6          # entries nobody may follow: beyond a request's context, or rows of non-first tokens
+    bytes_per = D if kind == "fp8" else D // 2
+    kv_pages = np.zeros((num_pages * page_kv, bytes_per), dtype=np.uint8)
+    kv_sf_pages = np.zeros(num_pages * page_kv, dtype=np.uint32)
+    per_req, used, t0 = [], 0, 0
+    for n, c in reqs:
+        kvf = randn((max(c, 1), D), 100 + t0) * 2.0
+        codes, words = o.quant_mx_host(kvf, odt, 32)
+        pages = perm[used:used + -(-c // page_kv)]
+        used += len(pages)
+        table[t0, :len(pages)] = pages
+        for i, pgid in enumerate(pages):
+            lo, hi = i * page_kv, min(c, (i + 1) * page_kv)
+            kv_pages[pgid * page_kv:pgid * page_kv + hi - lo] = codes[lo:hi]
+            kv_sf_pages[pgid * page_kv:pgid * page_kv + hi - lo] = words[0, lo:hi]
+        per_req.append((t0, n, c, o.dequant_mx_host(codes, words, max(c, 1), D, odt, 32)))
+        t0 += n
+    qf = randn((T * H, D), 5)
+    qc, qsf = o.quant_mx_host(qf, odt, 32)
+    qd = o.dequant_mx_host(qc, qsf, T * H, D, odt, 32).reshape(T, H, D)
+    wb = torch.from_numpy(randn((T, H), 6)).to(torch.bfloat16)
+    fill = -5.0
+    width = max_ctx + 8
+    logits = torch.full((T, width), fill, dtype=torch.bfloat16, device="cuda")
+    qop = Operand.k_major(dt, T * H, D, D, sf_tensor(qsf, 32), dev(qc))
+    mqa_logits_paged(qop, dev(kv_pages), dev(kv_sf_pages.view(np.int32)), wb.cuda(), page_kv, num_pages,
+                     dev(np.array(ctx, dtype=np.int32)), dev(np.array(indices, dtype=np.int32)), dev(table), stride, T, H, D,
+                     logits, width)
+    poll_device_status()
+    got = logits.float().cpu().numpy()
+    for t0, n, c, kvd in per_req:
+        ke = np.array(ctx[t0:t0 + n], dtype=np.uint32)
+        ks = np.zeros(n, np.uint32)
+        ref = o.mqa_logits_ref(qd[t0:t0 + n], kvd[:max(c, 1)], wb.float().numpy()[t0:t0 + n], ks, ke)
+        ref = np.pad(ref, ((0, 0), (0, width - ref.shape[1])))
+        if ke.max() == 0:
+            assert (got[t0:t0 + n] == fill).all()
+            continue
+        _check(got[t0:t0 + n], o.bf16_bits_to_f32(o.f32_to_bf16_bits_np(ref)), ks, ke, width, fill)
