@@ -133,3 +133,14 @@ def test_layout_batch_and_output_quant_checks(L):
     assert L.dg_transform_sf_batched(0x1000, 0, 4, 4, 0x2000, None) == 3 and "batch must be nonzero" in _err(L)
     assert L.dg_quantize_output_fp8(0x1000, 16, 100, 100, 0, 0, 0x2000, 0x3000, None) == 3 and "n % 32 == 0" in _err(L)
     assert L.dg_quantize_output_fp8(0x1000, 16, 128, 64, 0, 0, 0x2000, 0x3000, None) == 3                          # pitch below n
+
+
+def test_rust_binding_declares_every_entry():
+    """deepgemm-rs_b200/rust/ffi_b200.rs (the binding a maintainer of the reference adds) lists exactly the
+    functions of the public header."""
+    import os
+    import re
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(_lib.__file__))), "rust", "ffi_b200.rs")
+    with open(path) as f:
+        rust = set(re.findall(r"pub fn (dg_\w+)\s*\(", f.read()))
+    assert rust == set(_lib.declared_symbols()), (sorted(set(_lib.declared_symbols()) - rust), sorted(rust - set(_lib.declared_symbols())))
