@@ -20,22 +20,14 @@
 // the (query, head) pairs of a query block on the N side, so one epilogue thread owns one kv
 // token and a warp stores 32 consecutive columns of a logits row.
 //   warp 0      TMA producer (Q tile per task, KV blocks streamed through a ring; paged: page by page)
-//   warp 1      MMA issuer (scores into accumulator stages in TMEM; with the tensor-core reduction also
-//               the second MMA of every block)
+//   warp 1      MMA issuer (scores into one of two accumulator stages in TMEM)
 //   warp 2      TMEM owner; ue8m0 contracts: scale factors into the layout tcgen05.cp needs
-//   warps 4-..  epilogue warpgroups
-// Head reduction, two forms:
-//   tensor-core (default where the shapes allow): scores are produced in sub-tiles of 128 columns
-//     (whole queries) that rotate through three or four TMEM stages.  The epilogue warps only apply
-//     ReLU, round to bf16 and write a sub-tile back into the tensor memory it came from (half the
-//     columns); a second MMA multiplies it, as the A operand read from tensor memory, with the
-//     block-diagonal weight matrix of the sub-tile ([16 rows, 128] bf16 in shared memory: row i = the
-//     weights of query i over its own columns, zero elsewhere; the fp32 contract adds rows 8.. with the
-//     bf16 remainders of the f32 weights, so the weights enter to 16 bits of mantissa) into 16 freed
-//     columns of the same stage.  The CUDA cores then touch 16 values per kv token and sub-tile instead
-//     of 256.  The scores enter the sum rounded to bf16 (the reference reduces in bf16x2 altogether,
-//     mqa_logits_sm100.cu:1022-1031); the sum itself is f32.
-//   CUDA-core: relu(x) * w accumulated in f32 per thread (any head count; DG_MQA_TSRED=0 selects it).
+//   warps 4-..  epilogue warpgroups: relu(x) * w accumulated in f32 per thread, every warpgroup reducing its
+//               share of the query block's columns with the next TMEM load in flight while a chunk is consumed
+// (A head reduction on the tensor cores -- ReLU'd scores written back to tensor memory as bf16 and multiplied
+// with a block-diagonal weight tile by a second MMA whose A operand is read from tensor memory -- was built
+// and measured on this kernel: correct, but twice as slow, because the 16 narrow MMAs it adds per kv block cost
+// more tensor-pipe time than the reduction costs the CUDA cores.)
 #include "host.h"
 #include "ptx.cuh"
 
@@ -46,17 +38,14 @@ namespace dg {
 constexpr uint32_t kMqaBlockKv = 128;
 constexpr uint32_t kMqaMaxKvStages = 10;
 constexpr uint32_t kMqaMaxThreads = 640;   // 4 role warps + up to 4 epilogue warpgroups
-constexpr uint32_t kMqaSfaCol = 448;       // ue8m0 contracts only: the accumulators end at column 384
+constexpr uint32_t kMqaSfaCol = 448;       // ue8m0 contracts only: the accumulators are <= 192 wide
 constexpr uint32_t kMqaSfbCol = 452;
-constexpr uint32_t kMqaSub = 128;          // tensor-core reduction: score columns per sub-tile = TMEM stage width
-constexpr uint32_t kMqaW2Bytes = 8192;     // block-diagonal weight tiles of one task: [2 sub-tiles][16][128] bf16
 
 struct MqaParams {
     uint32_t num_tokens, num_kv, num_heads, head_dim;
     uint32_t block_q, n, n_mma;   // n = block_q * num_heads score columns, n_mma = n rounded up to the MMA's granule
-    uint32_t ep_groups;           // epilogue warpgroups; CUDA-core form: each reduces block_q / ep_groups queries
-    uint32_t unit;                // CUDA-core form: columns per TMEM load (16, or 4 for head counts not divisible by 16)
-    uint32_t subs, num_acc;       // tensor-core form: sub-tiles per kv block (1 or 2), TMEM stages (3 or 4)
+    uint32_t ep_groups;           // epilogue warpgroups; each reduces block_q / ep_groups queries
+    uint32_t unit;                // columns per TMEM load (16, or 4 for head counts not divisible by 16)
     uint32_t num_q_blocks;
     uint32_t kv_stages, kv_stage_bytes, q_stage_bytes;
     uint32_t off_w, off_q, off_kv;  // offsets from the 1024-aligned base
@@ -64,9 +53,9 @@ struct MqaParams {
     uint32_t row_bytes;             // bytes of one q / kv row (head_dim, or head_dim / 2 for FP4)
     uint32_t sbo;                   // 8-row group pitch of the swizzled tiles
     uint32_t layout;                // UMMA layout type of the tiles
-    uint32_t num_mma;               // MMAs per kv block (and sub-tile)
-    uint32_t idesc, idesc2;         // instruction descriptors of the score MMA and of the reduction MMA
-    uint32_t acc_stride;            // TMEM columns between accumulator stages
+    uint32_t num_mma;               // MMAs per kv block
+    uint32_t idesc;                 // instruction descriptor of the score MMA
+    uint32_t acc_stride;            // TMEM columns between the two accumulator stages
     uint32_t logits_stride;
     const uint32_t* ks;
     const uint32_t* ke;
@@ -90,9 +79,8 @@ struct __align__(8) MqaBarriers {
     uint64_t kv_ready[kMqaMaxKvStages];   // ue8m0: scale factors in place
     uint64_t kv_empty[kMqaMaxKvStages];
     uint64_t q_full[2], q_ready[2], q_empty[2];
-    uint64_t tmem_full[4], tmem_empty[4];
-    uint64_t relu_done[4], out_full[4];   // tensor-core reduction: scores written back / reduced sums ready
-    uint64_t w_full[2], w_empty[2];       // weights of a task staged (by the epilogue warps, or by warp 3 for the tensor-core form)
+    uint64_t tmem_full[2], tmem_empty[2];
+    uint64_t w_full[2];                   // weights of a task staged by the epilogue warps
     uint32_t tmem_base;
     uint32_t abort;
 };
@@ -175,48 +163,16 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d, uint64_t a, uint64_t b, ui
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
 }
-// A operand read from tensor memory (bf16, two K elements per 32-bit column), B from shared memory.
-__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
-}
 __host__ __device__ constexpr uint32_t make_idesc_f8(uint32_t m, uint32_t n) {
     return (1u << 4) /*D=f32*/ | ((n >> 3) << 17) | ((m >> 4) << 24);  // A, B = E4M3 (format 0), K-major
 }
-__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-// the first 16 words of a 32-word register array
-__device__ __forceinline__ void tmem_st_x16_of32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_x4(uint32_t taddr, uint32_t (&r)[4]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
 }
-// relu, then two f32 -> one bf16x2 word (first value in the low half)
-__device__ __forceinline__ uint32_t relu_pack_bf16x2(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-
 // SCALED: ue8m0 contracts (scale factors on q and kv, bf16 weights and logits); FP4: packed E2M1 codes;
-// PAGED: kv through a block table, work from the metadata kernel; TSRED: tensor-core head reduction.
-template <bool SCALED, bool FP4, bool PAGED, bool TSRED>
+// PAGED: kv through a block table, work from the metadata kernel.
+template <bool SCALED, bool FP4, bool PAGED>
 __global__ void __launch_bounds__(kMqaMaxThreads, 1)
 mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_qsf, const __grid_constant__ CUtensorMap tm_kvsf,
@@ -226,8 +182,7 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t base = (raw_u32 + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw_u32);
     MqaBarriers* bars = reinterpret_cast<MqaBarriers*>(base_ptr);
-    float* w_smem = reinterpret_cast<float*>(base_ptr + p.off_w);      // CUDA-core form: [2][n] halved weights
-    uint8_t* w2_smem = base_ptr + p.off_w;                             // tensor-core form: [2 tasks][2 sub-tiles][16][128] bf16, swizzled
+    float* w_smem = reinterpret_cast<float*>(base_ptr + p.off_w);      // [2][n] halved weights
     uint32_t* win_smem = reinterpret_cast<uint32_t*>(base_ptr + 512);  // [2][2][16]: ks / ke of the queries of a task
     static_assert(sizeof(MqaBarriers) <= 512, "barrier block overlaps the window table");
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -245,14 +200,9 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             mbar_init(smem_u32(&bars->q_full[s]), 1);
             mbar_init(smem_u32(&bars->q_ready[s]), 1);
             mbar_init(smem_u32(&bars->q_empty[s]), 1);
-            mbar_init(smem_u32(&bars->w_full[s]), TSRED ? 1u : ep_warps);
-            mbar_init(smem_u32(&bars->w_empty[s]), 1);
-        }
-        for (uint32_t s = 0; s < 4; ++s) {
+            mbar_init(smem_u32(&bars->w_full[s]), ep_warps);
             mbar_init(smem_u32(&bars->tmem_full[s]), 1);
-            mbar_init(smem_u32(&bars->tmem_empty[s]), TSRED ? 4u : ep_warps);   // tensor-core form: one warpgroup owns a stage
-            mbar_init(smem_u32(&bars->relu_done[s]), 4u);
-            mbar_init(smem_u32(&bars->out_full[s]), 1);
+            mbar_init(smem_u32(&bars->tmem_empty[s]), ep_warps);
         }
         fence_barrier_init();
         tma_prefetch_desc(&tm_q);
@@ -317,40 +267,11 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         bool ok = true;
         MqaTasks<PAGED> tasks(p);
         MqaTask k;
-        // Tensor-core reduction: the second MMA of a sub-tile is issued as soon as the warpgroup that owns its
-        // stage has rewritten the scores, checked before every score MMA; this warp blocks on it only when all
-        // other stages are in flight.  Ring of the sub-tiles whose reduction is outstanding, oldest first:
-        // stage, phase, address of the weight tile, and whether the sub-tile is the last of its task (then the
-        // reduction also hands the task's weight buffer back).
-        uint32_t n_pend = 0;
-        uint32_t pa0 = 0, pp0 = 0, pw0 = 0, pl0 = 0, pa1 = 0, pp1 = 0, pw1 = 0, pl1 = 0, pa2 = 0, pp2 = 0, pw2 = 0, pl2 = 0;
-        auto reduce_oldest = [&]() {
-            if (!DG_WARP_WAIT(smem_u32(&bars->relu_done[pa0]), pp0, wc, kWaitTmemFull)) return false;
-            tc_fence_after();
-            if (elect_one()) {
-                const uint32_t stage_col = tmem + pa0 * acc_stride;
-                const uint32_t d2 = stage_col + 16u;                           // the 16 columns freed by packing the first 32
-                for (uint32_t t16 = 0; t16 < kMqaSub / 16u; ++t16) {
-                    const uint32_t kappa = t16 * 16u;                          // first (query, head) pair of this step
-                    const uint32_t a_col = stage_col + (kappa / 32u) * 32u + (kappa % 32u) / 2u;
-                    const uint64_t b_desc = make_kmajor_sw128_desc(pw0 + (kappa / 64u) * 2048u) + ((kappa % 64u) * 2u >> 4);
-                    tc_mma_bf16_ts(d2, a_col, b_desc, p.idesc2, t16 != 0u);
-                }
-                tc_commit(smem_u32(&bars->out_full[pa0]));
-                if (pl0 & 2u) tc_commit(smem_u32(&bars->w_empty[pl0 & 1u]));
-            }
-            __syncwarp();
-            pa0 = pa1; pp0 = pp1; pw0 = pw1; pl0 = pl1;
-            pa1 = pa2; pp1 = pp2; pw1 = pw2; pl1 = pl2;
-            --n_pend;
-            return true;
-        };
         while (ok && tasks.next(p, k)) {
             const uint32_t qs = qcount & 1u, qphase = (qcount >> 1) & 1u;
             ++qcount;
             if (!(ok = DG_WARP_WAIT(smem_u32(&bars->q_full[qs]), qphase, wc, kWaitFull))) break;
             if (SCALED && !(ok = DG_WARP_WAIT(smem_u32(&bars->q_ready[qs]), qphase, wc, kWaitSfReady))) break;
-            if (TSRED && !(ok = DG_WARP_WAIT(smem_u32(&bars->w_full[qs]), qphase, wc, kWaitWeights))) break;
             tc_fence_after();
             const uint32_t qaddr = base + p.off_q + qs * p.q_stage_bytes;
             const uint64_t q_desc = make_smem_desc(qaddr, p.sbo, 0, p.layout);
@@ -360,58 +281,37 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (SCALED && !(ok = DG_WARP_WAIT(smem_u32(&bars->kv_ready[stage]), phase, wc, kWaitSfReady))) break;
                 const uint32_t kaddr = base + p.off_kv + stage * p.kv_stage_bytes;
                 const uint64_t kv_desc = make_smem_desc(kaddr, p.sbo, 0, p.layout);
-                const uint32_t nsub = TSRED ? p.subs : 1u;
-                for (uint32_t sub = 0; sub < nsub; ++sub) {
-                    const uint32_t as = TSRED ? acount % p.num_acc : acount & 1u;
-                    const uint32_t aphase = TSRED ? (acount / p.num_acc) & 1u : (acount >> 1) & 1u;
-                    ++acount;
-                    if (TSRED) {
-                        while (ok && n_pend && (n_pend + 1u >= p.num_acc ||
-                                                __any_sync(0xffffffffu, mbar_test_wait(smem_u32(&bars->relu_done[pa0]), pp0))))
-                            ok = reduce_oldest();
-                        if (!ok) break;
+                const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
+                ++acount;
+                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + as * acc_stride;
+                if (elect_one()) {
+                    if (SCALED) {
+                        if (!q_sf_copied)    // the q scales of this task: in order behind every MMA that used the previous task's
+                            for (uint32_t c = 0; c < (p.n + 127u) / 128u; ++c)
+                                tc_cp_32x128b_warpx4(tmem + kMqaSfbCol + c * 4u, make_sf_desc(qaddr + p.q_sf_off + c * 512u));
+                        tc_cp_32x128b_warpx4(tmem + kMqaSfaCol, make_sf_desc(kaddr + p.kv_sf_off));
                     }
-                    if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
-                    tc_fence_after();
-                    const uint32_t d_tmem = tmem + as * acc_stride;
-                    // sub-tile `sub` = rows [128 sub, 128 sub + 128) of the Q tile
-                    const uint64_t qd = q_desc + (uint64_t)((sub * kMqaSub * p.row_bytes) >> 4);
-                    if (elect_one()) {
-                        if (SCALED) {
-                            if (!q_sf_copied)    // the q scales of this task: in order behind every MMA that used the previous task's
-                                for (uint32_t c = 0; c < (p.n + 127u) / 128u; ++c)
-                                    tc_cp_32x128b_warpx4(tmem + kMqaSfbCol + c * 4u, make_sf_desc(qaddr + p.q_sf_off + c * 512u));
-                            if (sub == 0) tc_cp_32x128b_warpx4(tmem + kMqaSfaCol, make_sf_desc(kaddr + p.kv_sf_off));
-                        }
-                        for (uint32_t m = 0; m < p.num_mma; ++m) {
-                            if (SCALED && FP4)      // 64 elements per MMA: half-word (m & 1) of the row's scale word
-                                tc_mma_mxf4(d_tmem, kv_desc + 2u * m, qd + 2u * m, idesc_with_sf_ids(p.idesc, (m & 1u) * 2u, (m & 1u) * 2u),
-                                            m != 0u, tmem + kMqaSfaCol, tmem + kMqaSfbCol + sub * 4u);
-                            else if (SCALED)
-                                tc_mma_mxf8(d_tmem, kv_desc + 2u * m, qd + 2u * m, idesc_with_sf_ids(p.idesc, m, m), m != 0u,
-                                            tmem + kMqaSfaCol, tmem + kMqaSfbCol + sub * 4u);
-                            else
-                                tc_mma_f8(d_tmem, kv_desc + 2u * m, qd + 2u * m, p.idesc, m != 0u);
-                        }
-                        if (sub + 1 == nsub) tc_commit(smem_u32(&bars->kv_empty[stage]));
-                        tc_commit(smem_u32(&bars->tmem_full[as]));
-                        if (sub + 1 == nsub && kb + 1 == k.kb1) tc_commit(smem_u32(&bars->q_empty[qs]));
+                    for (uint32_t m = 0; m < p.num_mma; ++m) {
+                        if (SCALED && FP4)      // 64 elements per MMA: half-word (m & 1) of the row's scale word
+                            tc_mma_mxf4(d_tmem, kv_desc + 2u * m, q_desc + 2u * m, idesc_with_sf_ids(p.idesc, (m & 1u) * 2u, (m & 1u) * 2u),
+                                        m != 0u, tmem + kMqaSfaCol, tmem + kMqaSfbCol);
+                        else if (SCALED)
+                            tc_mma_mxf8(d_tmem, kv_desc + 2u * m, q_desc + 2u * m, idesc_with_sf_ids(p.idesc, m, m), m != 0u,
+                                        tmem + kMqaSfaCol, tmem + kMqaSfbCol);
+                        else
+                            tc_mma_f8(d_tmem, kv_desc + 2u * m, q_desc + 2u * m, p.idesc, m != 0u);
                     }
-                    __syncwarp();
-                    q_sf_copied = true;
-                    if (TSRED) {
-                        const uint32_t wt = base + p.off_w + qs * kMqaW2Bytes + sub * (kMqaW2Bytes / 2u);
-                        const uint32_t last = (sub + 1 == nsub && kb + 1 == k.kb1) ? 2u : 0u;
-                        if (n_pend == 0u) { pa0 = as; pp0 = aphase; pw0 = wt; pl0 = last | qs; }
-                        else if (n_pend == 1u) { pa1 = as; pp1 = aphase; pw1 = wt; pl1 = last | qs; }
-                        else { pa2 = as; pp2 = aphase; pw2 = wt; pl2 = last | qs; }
-                        ++n_pend;
-                    }
+                    tc_commit(smem_u32(&bars->kv_empty[stage]));
+                    tc_commit(smem_u32(&bars->tmem_full[as]));
+                    if (kb + 1 == k.kb1) tc_commit(smem_u32(&bars->q_empty[qs]));
                 }
+                __syncwarp();
+                q_sf_copied = true;
                 if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
             }
         }
-        while (TSRED && ok && n_pend) ok = reduce_oldest();
     } else if (warp == 2 && SCALED) {
         // ===================================================== scale factors (ue8m0 contracts)
         // tcgen05.cp wants the word of row 32 i + l at position 4 l + i.  Contiguous kv: the TMA load
@@ -458,60 +358,6 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
             }
         }
-    } else if (warp == 3 && TSRED) {
-        // ===================================================== weight tiles of the tensor-core reduction
-        // Per task and sub-tile a K-major [16 rows][128] bf16 tile with 128-byte swizzle (atoms of 64 K elements;
-        // the 16-byte pieces of a row XOR-ed with the row's index inside its group of 8).  Row i < 8: the bf16
-        // weights of the sub-tile's query i over its own heads' columns, zero elsewhere; row 8 + i: the bf16
-        // remainders of the f32 weights (fp32 contract).  512 pieces of 16 bytes = (sub-tile, row, 8 consecutive
-        // K elements), 16 per lane.  A buffer is rewritten once the reductions of the task before the previous
-        // one have all run.
-        const uint32_t qps = kMqaSub / p.num_heads;          // queries per sub-tile (1, 2, 4 or 8)
-        uint32_t qcount = 0;
-        bool ok = true;
-        MqaTasks<PAGED> tasks(p);
-        MqaTask k;
-        while (ok && tasks.next(p, k)) {
-            const uint32_t wb = qcount & 1u, wphase = (qcount >> 1) & 1u;
-            ++qcount;
-            if (!(ok = DG_WARP_WAIT(smem_u32(&bars->w_empty[wb]), wphase ^ 1u, wc, kWaitWeights))) break;
-            uint8_t* w2 = w2_smem + wb * kMqaW2Bytes;
-            for (uint32_t piece = lane; piece < 512u; piece += 32u) {
-                const uint32_t sub = piece >> 8, r = (piece >> 4) & 15u, c = piece & 15u;
-                const uint32_t qs_ = r & 7u;                                  // query inside the sub-tile this row belongs to
-                const uint32_t qi = sub * qps + qs_, q = k.q0 + qi;
-                const bool lo_row = r >= 8u;
-                uint32_t words[4] = {0u, 0u, 0u, 0u};
-                const bool live = sub < p.subs && qs_ < qps && qi < k.nq && q < p.num_tokens && (c * 8u) / p.num_heads == qs_ &&
-                                  !(lo_row && SCALED);
-                if (live) {
-                    const uint32_t h0 = (c * 8u) % p.num_heads;
-#pragma unroll
-                    for (uint32_t i = 0; i < 4; ++i) {
-                        float w0, w1;
-                        const size_t idx = (size_t)q * p.num_heads + h0 + 2 * i;
-                        if (SCALED) {
-                            w0 = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.weights)[idx]);
-                            w1 = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.weights)[idx + 1]);
-                        } else {
-                            w0 = reinterpret_cast<const float*>(p.weights)[idx];
-                            w1 = reinterpret_cast<const float*>(p.weights)[idx + 1];
-                        }
-                        __nv_bfloat16 b0 = __float2bfloat16_rn(w0), b1 = __float2bfloat16_rn(w1);
-                        if (lo_row) {
-                            b0 = __float2bfloat16_rn(w0 - __bfloat162float(b0));
-                            b1 = __float2bfloat16_rn(w1 - __bfloat162float(b1));
-                        }
-                        words[i] = (uint32_t)__bfloat16_as_ushort(b0) | ((uint32_t)__bfloat16_as_ushort(b1) << 16);
-                    }
-                }
-                const uint32_t off = sub * (kMqaW2Bytes / 2u) + (c / 8u) * 2048u + r * 128u + (((c & 7u) ^ (r & 7u)) * 16u);
-                *reinterpret_cast<uint4*>(w2 + off) = make_uint4(words[0], words[1], words[2], words[3]);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bars->w_full[wb]));
-        }
     } else if (warp >= 4) {
         // ===================================================== epilogue warpgroups
         const uint32_t et = threadIdx.x - 128u;
@@ -543,79 +389,7 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                           : reinterpret_cast<const float*>(p.weights)[idx];
         };
 
-        if (TSRED) {
-            // ---- tensor-core reduction.  Warpgroup g owns TMEM stage g and the sub-tiles that pass through it:
-            // (A) ReLU + bf16 write-back of the 128 score columns: every 32 columns shrink into their first 16;
-            // (B) after the reduction MMA, the sums from columns [16, 32) of the stage: column i = query i of the
-            //     sub-tile (bf16 part of the weights), 8 + i = the remainders.
-            const uint32_t qps = kMqaSub / p.num_heads;          // queries per sub-tile (1, 2, 4 or 8)
-            while (ok && wg < p.num_acc && tasks.next(p, k)) {
-                for (uint32_t kb = k.kb0; ok && kb < k.kb1; ++kb) {
-                    for (uint32_t sub = 0; sub < p.subs; ++sub) {
-                        const uint32_t as = acount % p.num_acc, aphase = (acount / p.num_acc) & 1u;
-                        ++acount;
-                        if (as != wg) continue;
-                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->tmem_full[as]), aphase, wc, kWaitTmemFull));
-                        if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride;
-#pragma unroll
-                        for (uint32_t half = 0; half < 2; ++half) {
-                            uint32_t x[32], y[32];
-                            tmem_ld_x32(taddr + half * 64u, x);
-                            tmem_ld_x32(taddr + half * 64u + 32u, y);
-                            tmem_ld_wait();
-                            // packed in place: word i takes elements 2i and 2i + 1, both at or above position i
-#pragma unroll
-                            for (uint32_t i = 0; i < 16; ++i) {
-                                x[i] = relu_pack_bf16x2(__uint_as_float(x[2 * i]), __uint_as_float(x[2 * i + 1]));
-                                y[i] = relu_pack_bf16x2(__uint_as_float(y[2 * i]), __uint_as_float(y[2 * i + 1]));
-                            }
-                            tmem_st_x16_of32(taddr + half * 64u, x);
-                            tmem_st_x16_of32(taddr + half * 64u + 32u, y);
-                        }
-                        tmem_st_wait();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bars->relu_done[as]));
-                        // this thread's kv token and the windows of the sub-tile's queries, fetched while the reduction runs
-                        const uint32_t j = kb * kMqaBlockKv + quarter * 32u + lane;
-                        float scale = 1.f;
-                        if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
-                        uint32_t ws[8], we[8];
-#pragma unroll
-                        for (uint32_t i = 0; i < 8; ++i) {
-                            const uint32_t qi = sub * qps + i, q = k.q0 + qi;
-                            ws[i] = 0; we[i] = 0;
-                            if (i < qps && qi < k.nq && q < p.num_tokens) {
-                                if (PAGED) we[i] = min(__ldg(p.context_lens + q), p.block_table_stride * p.page_kv);
-                                else { ws[i] = __ldg(p.ks + q); we[i] = min(__ldg(p.ke + q), p.num_kv); }
-                            }
-                        }
-                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->out_full[as]), aphase, wc, kWaitTmemFull));
-                        if (!ok) break;
-                        tc_fence_after();
-                        uint32_t v[16];
-                        tmem_ld_x16(taddr + 16u, v);
-                        tmem_ld_wait();
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
-#pragma unroll
-                        for (uint32_t i = 0; i < 8; ++i) {
-                            if (j >= ws[i] && j < we[i]) {
-                                float val = __uint_as_float(v[i]);
-                                if (!SCALED) val = (val + __uint_as_float(v[8 + i])) * scale;
-                                const size_t o = (size_t)(k.q0 + sub * qps + i) * p.logits_stride + (j - ws[i]);
-                                if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
-                                else reinterpret_cast<float*>(p.logits)[o] = val;
-                            }
-                        }
-                    }
-                }
-            }
-        } else {
-            // ---- CUDA-core reduction
+        {
             const uint32_t q_per_wg = p.block_q / p.ep_groups;
             const uint32_t units_per_q = p.num_heads / p.unit;
             const uint32_t nunits = q_per_wg * units_per_q;        // TMEM loads per kv block
@@ -828,11 +602,6 @@ struct MqaPaged {
     const uint32_t* block_table = nullptr;
 };
 
-static uint32_t mqa_env(const char* name, uint32_t dflt) {
-    const char* v = getenv(name);
-    return v && *v ? (uint32_t)strtoul(v, nullptr, 10) : dflt;
-}
-
 template <bool SCALED, bool FP4, bool PAGED>
 static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint32_t q_sf_cols, const uint32_t* kv_sf,
                        uint32_t kv_sf_cols, const float* kv_scale, const void* weights, const uint32_t* ks,
@@ -846,28 +615,17 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     p.num_tokens = num_tokens; p.num_kv = num_kv; p.num_heads = num_heads; p.head_dim = head_dim;
     // Tiling: n = block_q * num_heads score columns per kv block, at most 256 (192 beside the scale-factor
     // columns of the ue8m0 contracts); the MMA wants a multiple of 16 columns and computes a few unused ones
-    // when n is not.  The tensor-core reduction works on sub-tiles of 128 columns holding whole queries
-    // (16, 32, 64 or 128 heads): two per kv block for the fp32 contract, one for the ue8m0 contracts.
+    // when n is not.
     const uint32_t max_n = SCALED ? 192u : 256u;
-    const bool tsred = mqa_env("DG_MQA_TSRED", 1) != 0 && num_heads >= 16 && kMqaSub % num_heads == 0;
-    uint32_t block_q;
-    if (tsred) {
-        p.subs = SCALED ? 1u : 2u;
-        p.num_acc = SCALED ? 3u : 4u;
-        block_q = p.subs * (kMqaSub / num_heads);
-        p.acc_stride = kMqaSub;
-    } else {
-        block_q = max_n / num_heads;
-        if (block_q > 16) block_q = 16;
-        if (block_q >= 4) block_q &= ~3u; else if (block_q == 3) block_q = 2;
-        if (block_q == 0) return fail(DG_ERR_UNSUPPORTED, "mqa_logits: %u heads do not fit the %u score columns of this contract", num_heads, max_n);
-        p.subs = 1; p.num_acc = 2;
-        p.acc_stride = SCALED ? 192u : 256u;
-    }
+    uint32_t block_q = max_n / num_heads;
+    if (block_q > 16) block_q = 16;
+    if (block_q >= 4) block_q &= ~3u; else if (block_q == 3) block_q = 2;
+    if (block_q == 0) return fail(DG_ERR_UNSUPPORTED, "mqa_logits: %u heads do not fit the %u score columns of this contract", num_heads, max_n);
+    p.acc_stride = SCALED ? 192u : 256u;
     p.block_q = block_q;
     p.n = block_q * num_heads;
-    p.n_mma = tsred ? kMqaSub : align_up(p.n, 16);
-    p.ep_groups = tsred ? 4u : (block_q % 4 == 0 ? 4u : block_q % 2 == 0 ? 2u : 1u);
+    p.n_mma = align_up(p.n, 16);
+    p.ep_groups = block_q % 4 == 0 ? 4u : block_q % 2 == 0 ? 2u : 1u;
     p.unit = num_heads % 16 == 0 ? 16u : 4u;
     p.num_q_blocks = ceil_div(num_tokens, block_q);
     p.row_bytes = FP4 ? head_dim / 2 : head_dim;
@@ -878,11 +636,9 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
                                 : p.row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
     p.num_mma = p.row_bytes / 32u;
     p.idesc = SCALED ? make_idesc_bs(FP4 ? 1u : 0u, FP4 ? 1u : 0u, kMqaBlockKv, p.n_mma) : make_idesc_f8(kMqaBlockKv, p.n_mma);
-    p.idesc2 = make_idesc_bf16(kMqaBlockKv, 16);
     p.off_w = 1024;
-    p.off_q = 1024 + (tsred ? 2 * kMqaW2Bytes : 2048u);
-    const uint32_t q_rows = tsred ? p.n : p.n_mma;      // the MMA of the last rows may read a few rows past the box
-    p.q_sf_off = align_up(q_rows * p.row_bytes, 1024);
+    p.off_q = 1024 + 2048u;
+    p.q_sf_off = align_up(p.n_mma * p.row_bytes, 1024);   // the MMA of the last rows may read a few rows past the box
     p.q_stage_bytes = p.q_sf_off + (SCALED ? 1024u : 0u);
     p.off_kv = p.off_q + 2 * p.q_stage_bytes;
     p.kv_sf_off = kMqaBlockKv * p.row_bytes;
@@ -945,16 +701,9 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e;
-    if (tsred) {
-        auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, true>;
-        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
-    } else {
-        auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false>;
-        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
-    }
+    auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED>;
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     if (meta) cudaFreeAsync(meta, s);
     if (e != cudaSuccess) return fail(DG_ERR_DRIVER, "mqa_logits launch failed: %s", cudaGetErrorString(e));
     dg::note_launch();

@@ -89,8 +89,7 @@ def test_mqa_logits_ue8m0_contract(T, S, H, D):
 
 @pytest.mark.parametrize("H,D", [(16, 128), (36, 128), (100, 64), (128, 128), (256, 128), (4, 32), (96, 128)])
 def test_mqa_logits_f32_head_counts(H, D):
-    """Any multiple of 4 up to 256 (deepgemm/src/api.rs:1639-1650); counts that divide 128 take the tensor-core
-    reduction, the others the CUDA-core one."""
+    """Any multiple of 4 up to 256 (deepgemm/src/api.rs:1639-1650)."""
     T, S = 21, 640
     q8, kv8, scale, w = _inputs_f32(T, S, H, D, H + D)
     rng = np.random.default_rng(H)
@@ -102,19 +101,6 @@ def test_mqa_logits_f32_head_counts(H, D):
     mqa_logits_f32(dev(q8), dev(kv8), dev(scale), dev(w), dev(ks.view(np.int32)), dev(ke.view(np.int32)), T, S, H, D, logits, S)
     poll_device_status()
     _check(logits.cpu().numpy(), ref, ks, ke, S, fill)
-
-
-@pytest.mark.parametrize("reduction", ["tensor", "cuda"])
-def test_mqa_logits_both_reductions_agree_with_the_oracle(reduction, monkeypatch):
-    monkeypatch.setenv("DG_MQA_TSRED", "1" if reduction == "tensor" else "0")
-    T, S, H, D = 70, 1500, 64, 128
-    q8, kv8, scale, w = _inputs_f32(T, S, H, D, 99)
-    ks, ke = np.zeros(T, np.uint32), (S - T + np.arange(T) + 1).astype(np.uint32)
-    ref = o.mqa_logits_ref(E4M3[q8], E4M3[kv8] * scale[:, None], w, ks, ke)
-    logits = torch.full((T, S), -1.0, dtype=torch.float32, device="cuda")
-    mqa_logits_f32(dev(q8), dev(kv8), dev(scale), dev(w), dev(ks.view(np.int32)), dev(ke.view(np.int32)), T, S, H, D, logits, S)
-    poll_device_status()
-    _check(logits.cpu().numpy(), ref, ks, ke, S, -1.0)
 
 
 @pytest.mark.parametrize("T,S,H,D", [(8, 256, 64, 128), (40, 700, 64, 128), (24, 512, 32, 64), (10, 300, 96, 128)])
