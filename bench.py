@@ -504,7 +504,20 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
             a, b = Operand.k_major(Dtype.Fp4, m, k, k, sa, da), Operand.k_major(Dtype.Fp4, n, k, k, sb, db)
             peak = 4 * peaks["bf16_tflops"]
         out = Output(Dtype.Bf16, m, n, n, torch.empty((m, n), dtype=torch.bfloat16, device=dev))
-        ms = timeit(lambda: dg.gemm_nt(a, b, out))
+        # A weight-streaming shape (M = 128) re-reads its weights on every call: consecutive calls take copies of B in
+        # turn, enough of them to exceed the 126 MB L2, so that every call streams its weights from HBM.
+        bs = [b]
+        if m <= 128:
+            per = n * k * (1 if kind == "fp8" else 0.5)
+            for _ in range(int(-(-300e6 // per)) - 1):
+                bs.append(Operand.k_major(b.dtype, n, k, k, type(b.sf)(b.sf.rows, b.sf.cols, b.sf.gran, b.sf.buf.clone()), b.data.clone()))
+        turn = [0]
+
+        def call():
+            dg.gemm_nt(a, bs[turn[0] % len(bs)], out)
+            turn[0] += 1
+        ms = timeit(call, iters=max(10, len(bs)))
+        b = bs[(turn[0] - 1) % len(bs)]          # the operand of the last call: the parity check below reads its output
         tf = 2.0 * m * n * k / ms / 1e9
         byts = (m * k + n * k) * (1 if kind == "fp8" else 0.5) + m * n * 2
         # the output of the last timed call, sampled: 128 rows x 256 columns over the full K against gemm_ref
@@ -515,7 +528,8 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
         par = sampled.check_gemm_sample(a.data, a.sf.buf, b.data, b.sf.buf, out.data, rows, cols, odt, gran, odt, b.sf.gran.k(), k)
         return gated({"ms": ms, "tflops": tf, "frac_of_measured_tensor_peak": tf / peak, "hbm_gbs": byts / ms / 1e6,
                       "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"],
-                      "tile": f"{cfg['block_m']}x{cfg['block_n']}", "parity": par}, kind)
+                      "tile": f"{cfg['block_m']}x{cfg['block_n']}", "parity": par,
+                      **({"l2": f"{len(bs)} copies of B in turn ({len(bs) * n * k / 1e6:.0f} MB > L2)"} if len(bs) > 1 else {})}, kind)
 
     for m in (128, 4096):
         for n, k in ((24576, 1536), (7168, 16384), (4096, 7168)):

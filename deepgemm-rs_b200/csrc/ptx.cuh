@@ -109,6 +109,18 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking probe: has the phase with this parity completed?  (try_wait may suspend the thread for a
+// while before it answers; test_wait answers at once.)
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
 // Shared by all roles of a CTA: where to report, and the CTA-wide abort flag.
 struct WaitCtx {
     uint32_t* status;            // global; 0 = healthy
@@ -251,6 +263,13 @@ template <int CL = 1>
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     if (CL == 1) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
     else asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// One commit whose completion signal arrives on the barrier at the same shared-memory offset in both CTAs
+// of a pair (the multicast here is of the signal only; no data moves).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_local) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar_local), "h"(mask) : "memory");
 }
 // 32 rows x 128 bit from shared memory, broadcast to the four 32-lane quarters of TMEM
 // (CL = 2: each CTA of the pair copies from its own shared memory into its own TMEM).
