@@ -895,6 +895,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 __global__ void __launch_bounds__(256) split_reduce_kernel(const float* __restrict__ ws, uint32_t splits, uint32_t m, uint32_t n,
                                                           void* __restrict__ d, uint64_t ldd, uint32_t out_f32, uint32_t accumulate,
                                                           float alpha) {
+    // lets the next kernel of the stream become resident (its set-up runs) as soon as this one is
+    griddep_launch_dependents();
     griddep_wait();
     const uint32_t n4 = (n + 3u) / 4u;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1480,7 +1482,7 @@ int32_t dg_get_gemm_config(int32_t dtype, int32_t kind, uint32_t m, uint32_t n, 
     if (!cfg || kind < 0 || kind > 2 || dtype < 0 || dtype > 2) return dg::fail(DG_ERR_INVALID_ARG, "get_gemm_config: bad argument");
     dg::Plan plan;
     st = dg::make_plan(dtype == DG_FP8 ? dg::kFp8 : dtype == DG_FP4 ? dg::kFp4 : dg::kBf16, kind, m, n, k,
-                       num_groups ? num_groups : 1, m, 32, 32, dev, &plan);
+                       num_groups ? num_groups : 1, m, dtype == DG_FP8 ? 128 : 32, dtype == DG_FP8 ? 128 : 32, dev, &plan);   // FP8: per-128 scales assumed
     if (st != DG_OK) return st;
     cfg->block_m = dg::kBlockM;
     cfg->block_n = plan.p.block_n;

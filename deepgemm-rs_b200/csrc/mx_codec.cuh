@@ -85,7 +85,7 @@ __host__ __device__ __forceinline__ float stochastic_e4m3_value(float v, uint32_
 // checker can state the same function and the re-quantised codes agree bit for bit:
 //   exp(x), x = -g clamped to [-87, 87]:  n = rint(x * log2 e), f = x - n * ln 2 (two-step Cody-Waite),
 //   degree-6 Taylor polynomial of exp(f) in Horner form with fused multiply-adds, times 2^n;
-//   silu(g) = g / (1 + exp(-g)) with the IEEE division.
+//   silu(g) = g * (1 / (1 + exp(-g))) with the correctly rounded reciprocal.
 // About 1 ulp from the exact exponential; 20 FMA-pipe instructions instead of two special-function
 // ones, which cost as many issue slots (the special-function unit has an eighth of the lanes).
 __device__ __forceinline__ float swiglu_value(float g, float u) {
@@ -100,7 +100,7 @@ __device__ __forceinline__ float swiglu_value(float g, float u) {
     p = fmaf(p, f, 1.0f);
     p = fmaf(p, f, 1.0f);
     const float e = p * __uint_as_float((uint32_t)((int)n + 127) << 23);
-    return __fdiv_rn(g, 1.0f + e) * u;
+    return g * __frcp_rn(1.0f + e) * u;
 }
 
 __device__ __forceinline__ float amax4(const float4& v) {

@@ -382,7 +382,7 @@ void dgo_quant_fp8_block128_host(const float* x, uint32_t n, uint32_t k, uint8_t
  * gate/up projection (row pitch ld elements): gate = columns [0, inter), up = columns
  * [inter, 2 * inter) ("the two halves", deepgemm/src/api_serving.rs:371-373).  As in the golden model of
  * the fused path (golden.rs:569-577) both factors are the bf16-rounded GEMM outputs and the product
- * silu(g) * u, silu(g) = g / (1 + exp(-g)), is formed in f32; there is no clamp and the routing weight is
+ * silu(g) * u, silu(g) = g * (1 / (1 + exp(-g))) (a rounded reciprocal, then a product), is formed in f32; there is no clamp and the routing weight is
  * applied later, when the copies of a token are combined.  out: f32 [m, inter], the input of the
  * re-quantisation (dgo_quant_mx_host).
  * The golden model calls the platform's exp; platforms differ in its last bit, which would make the
@@ -411,7 +411,7 @@ void dgo_swiglu_f32(const uint16_t* inter_bf16, uint32_t m, uint32_t inter, uint
         const uint16_t* row = inter_bf16 + (size_t)r * ld;
         for (uint32_t c = 0; c < inter; ++c) {
             float g = u2f((uint32_t)row[c] << 16), u = u2f((uint32_t)row[inter + c] << 16);
-            float sig = g / (1.0f + exp_taylor6(-g));
+            float sig = g * (1.0f / (1.0f + exp_taylor6(-g)));
             out[(size_t)r * inter + c] = sig * u;
         }
     }
