@@ -35,9 +35,12 @@ constexpr uint32_t kBlockM = 128;
 constexpr uint32_t kMaxStages = 10;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccStageCols = 256;   // accumulator stage s starts at column s * 256
-constexpr uint32_t kSfaCol = 224;         // SF columns live above a <=224-wide accumulator
-constexpr uint32_t kSfbCol = 232;
-constexpr uint32_t kSmemBarrierBytes = 512;
+// Scale factors live above the <=224-wide accumulators, in two sets that take turns: set 0 in columns
+// 224..255, set 1 in 480..511; inside a set A's rows start at +0 (<= 8 columns), B's at +8 (<= 24).
+__host__ __device__ constexpr uint32_t sf_set_col(uint32_t set) { return set ? 480u : 224u; }
+constexpr uint32_t kSfaOff = 0;
+constexpr uint32_t kSfbOff = 8;
+constexpr uint32_t kSmemBarrierBytes = 1024;
 constexpr uint32_t kMaxPairedBlocks = 4096;   // contiguous layout on CTA pairs: m_indices entries the in-kernel tile list holds
 constexpr uint32_t kPairedListBytes = 17 * 1024;  // tile list + run list (u16 each), 1024-aligned
 
@@ -56,7 +59,9 @@ struct GemmParams {
     uint32_t num_stages;
     uint32_t stage_bytes;  // A + B + SFA + SFB, 1024-aligned
     uint32_t off_b, off_sfa, off_sfb;
-    uint32_t sfa_period, sfb_period;  // k-blocks per SF row: 1 (gran 32) or 4 (gran 128)
+    uint32_t sf_cp_by_mma;            // 1 = the MMA issuer copies the SF rows into tensor memory itself (SF on every k-block), 0 = the SF warp does
+    uint32_t sf_load_mask;            // SF rows of both operands are loaded on k-blocks with (kb & mask) == 0: every k-block, or every fourth when both operands carry per-128 scales
+    uint32_t sfa_shift, sfb_shift;    // log2 of the k-blocks per packed SF row: 0 (gran 32) or 2 (gran 128); shifts and masks, no run-time division in the k-loops
     uint32_t sfb_chunks;   // 128-row chunks of the B scale factors per tile
     uint32_t sf_sub;       // SF rows per k-block: 1 (FP8) or 2 (FP4)
     uint32_t tx_ab, tx_sfa, tx_sfb;
@@ -251,7 +256,9 @@ struct Scheduler {
 struct __align__(8) Barriers {
     uint64_t full[kMaxStages];      // A and B tiles landed (pair: both CTAs' tiles, on the leader's barrier)
     uint64_t sf_full[kMaxStages];   // this CTA's SF rows landed (only on k-blocks that load SF)
-    uint64_t sf_ready[kMaxStages];  // SF rows transposed (pair: both CTAs arrive on the leader's barrier)
+    uint64_t sf_ready[kMaxStages];  // SF rows copied into tensor memory (commit of the copies; pair: on the leader)
+    uint64_t sf_peer[kMaxStages];   // pair, on the leader: the second CTA has transposed its SF rows
+    uint64_t sf_free[2];            // the MMAs that read SF set s have completed (commit of the MMA issuer)
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];         // pair: the leader's barrier collects both CTAs' epilogue warps
@@ -268,11 +275,16 @@ static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 // SPLIT (dense, single CTA only): a work item is a K range of a tile and the epilogue stores f32
 // partial tiles.  It is a separate instantiation because a k-loop that starts at a run-time
 // block measurably slows the common case (the k-block index feeds every role's bookkeeping).
-template <int KIND, int GTYPE, int CL, bool SPLIT, bool DYN, bool MNM = false>
+template <int KIND, int GTYPE, int CL, bool SPLIT, bool DYN, bool MNM = false, bool SFW = false>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
     constexpr bool kHasSf = KIND != kBf16;
+    // Whether one elected lane runs the MMA issuer's k-loop alone (no warp-wide vote and re-convergence per
+    // k-block).  Measured on one B200, warp-wide -> single lane: FP4 3470 -> 4200 TFLOPS, masked FP8 1009 -> 1052,
+    // split-K FP8 at M = 128 2 to 7 % faster; but the dynamic contiguous schedule 1826 -> 1780 and dense FP8
+    // on CTA pairs 1950 -> 1925, so those keep the warp-wide loop.
+    constexpr bool kConsLane = KIND == kFp4 || SPLIT || GTYPE == kMasked || (GTYPE == kNormal && CL == 1);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // Dynamic shared memory: [barriers (512 B, padded to 1024)] [stage 0] [stage 1] ...
     // (identical offsets in both CTAs of a pair: the launch gives every CTA the same window offset)
@@ -295,10 +307,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         for (uint32_t s = 0; s < p.num_stages; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
             mbar_init(smem_u32(&bars->sf_full[s]), 1);
-            mbar_init(smem_u32(&bars->sf_ready[s]), CL);
+            mbar_init(smem_u32(&bars->sf_ready[s]), SFW ? 1 : CL);
+            mbar_init(smem_u32(&bars->sf_peer[s]), 1);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         for (uint32_t s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&bars->sf_free[s]), 1);
             mbar_init(smem_u32(&bars->tmem_full[s]), 1);
             mbar_init(smem_u32(&bars->tmem_empty[s]), 4 * CL);
         }
@@ -395,8 +409,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 const uint32_t kb = kb_first + ki;
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
                 const uint32_t sa = stage_addr(stage);
-                const bool ld_sfa = kHasSf && (kb % p.sfa_period == 0);
-                const bool ld_sfb = kHasSf && (kb % p.sfb_period == 0);
+                const bool ld_sfa = kHasSf && (kb & p.sf_load_mask) == 0, ld_sfb = ld_sfa;
                 // Inner coordinate kx in elements: 128 bytes per k-block (128 FP8, 256 FP4 = 128 B, 64 BF16).
                 const int32_t kx = (int32_t)(kb * (KIND == kBf16 ? 64u : 128u));
                 if (elect_one()) {
@@ -407,8 +420,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         mbar_arrive_expect_tx(sbar, (ld_sfa ? p.tx_sfa : 0u) + (ld_sfb ? p.tx_sfb : 0u));
                         // batched: the SF rows of batch b start at b * (packed rows per batch), columns count inside the batch
                         const uint32_t sfa_x = GTYPE == kBatched ? t.mn_a : t.a_row, sfb_x = GTYPE == kBatched ? t.n0 : t.b_row;
-                        const uint32_t sfa_y = (GTYPE == kBatched ? t.batch * p.sf_rows_a : 0u) + (kb / p.sfa_period) * p.sf_sub;
-                        const uint32_t sfb_y = (GTYPE == kBatched ? t.batch * p.sf_rows_b : 0u) + (kb / p.sfb_period) * p.sf_sub;
+                        const uint32_t sfa_y = (GTYPE == kBatched ? t.batch * p.sf_rows_a : 0u) + (kb >> p.sfa_shift) * p.sf_sub;
+                        const uint32_t sfb_y = (GTYPE == kBatched ? t.batch * p.sf_rows_b : 0u) + (kb >> p.sfb_shift) * p.sf_sub;
                         if (ld_sfa) tma_load_2d(&tm_sfa, sbar, sa + p.off_sfa, (int32_t)sfa_x, (int32_t)sfa_y);
                         if (ld_sfb) tma_load_2d(&tm_sfb, sbar, sa + p.off_sfb, (int32_t)sfb_x, (int32_t)sfb_y);
                     }
@@ -450,14 +463,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             }
         }
     } else if (warp == 1 && leader) {
-        // ===================================================== MMA issuer (warp-converged, one lane issues)
+        // ===================================================== MMA issuer (the warp walks the tiles, one lane issues)
         Scheduler<GTYPE, CL, SPLIT, DYN> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         sched.attach(&bars->sched, &wc);
         Tile t;
         uint32_t stage = 0, phase = 0, tile_count = 0;
         uint32_t sf_bits = 0;  // per-stage parity of sf_ready (it completes only on SF k-blocks)
+        uint32_t sf_set = 1;   // SF set the MMAs read; it changes at every SF k-block (the first one takes set 0)
         const uint32_t idesc = p.idesc;   // operand formats, tile shape and majors, built by the host
-        bool ok = true;
+        // The tile walk is done by the whole warp, the k-loop of a tile by one elected lane alone: warp-wide votes
+        // and re-convergence on every k-block cost the issuer more than the MMAs of a k-block take to execute.
+        const bool issuer = elect_one();
+        const uint32_t issuer_lane = (uint32_t)__ffs(__ballot_sync(0xffffffffu, issuer)) - 1u;
+        uint32_t ok = 1;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
             const uint32_t as = tile_count & 1u, aphase = (tile_count >> 1) & 1u;
@@ -466,27 +484,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             tc_fence_after();
             const uint32_t d_tmem = tmem + as * kAccStageCols;
             const uint32_t kb_first = SPLIT ? t.kb0 : 0u, kb_count = SPLIT ? t.kb1 - t.kb0 : p.num_k_blocks;
+            if (!kConsLane || issuer) {
             for (uint32_t ki = 0; ki < kb_count; ++ki) {
                 const uint32_t kb = kb_first + ki;
-                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->full[stage]), phase, wc, kWaitFull))) break;
-                if (kHasSf && (kb % p.sfa_period == 0 || kb % p.sfb_period == 0)) {
-                    if (!(ok = DG_WARP_WAIT(smem_u32(&bars->sf_ready[stage]), (sf_bits >> stage) & 1u, wc, kWaitSfReady))) break;
+                if (!(ok = kConsLane ? (uint32_t)mbar_wait(smem_u32(&bars->full[stage]), phase, wc, kWaitFull)
+                                     : (uint32_t)DG_WARP_WAIT(smem_u32(&bars->full[stage]), phase, wc, kWaitFull))) break;
+                if (kHasSf && (kb & p.sf_load_mask) == 0) {
+                    // the SF warp has copied this k-block's scale factors into the other set (its commit arrives here)
+                    if (!(ok = kConsLane ? (uint32_t)mbar_wait(smem_u32(&bars->sf_ready[stage]), (sf_bits >> stage) & 1u, wc, kWaitSfReady)
+                                         : (uint32_t)DG_WARP_WAIT(smem_u32(&bars->sf_ready[stage]), (sf_bits >> stage) & 1u, wc, kWaitSfReady))) break;
                     sf_bits ^= 1u << stage;
+                    if (SFW) sf_set ^= 1u;
                 }
                 tc_fence_after();
                 const uint32_t sa = stage_addr(stage);
-                if (elect_one()) {
-                    if (kHasSf) {
-                        if (kb % p.sfa_period == 0) {
-                            for (uint32_t j = 0; j < p.sf_sub; ++j)
-                                tc_cp_32x128b_warpx4<CL>(tmem + kSfaCol + j * 4u, make_sf_desc(sa + p.off_sfa + j * 512u));
-                        }
-                        if (kb % p.sfb_period == 0) {
-                            for (uint32_t j = 0; j < p.sf_sub; ++j)
-                                for (uint32_t c = 0; c < p.sfb_chunks; ++c)
-                                    tc_cp_32x128b_warpx4<CL>(tmem + kSfbCol + (j * p.sfb_chunks + c) * 4u,
-                                                             make_sf_desc(sa + p.off_sfb + (j * p.sfb_chunks + c) * 512u));
-                        }
+                const uint32_t sfa_col = tmem + sf_set_col(sf_set) + kSfaOff, sfb_col = tmem + sf_set_col(sf_set) + kSfbOff;
+                if (kConsLane || elect_one()) {
+                    if (kHasSf && !SFW && (kb & p.sf_load_mask) == 0) {
+                        // in order with the MMAs in the tensor pipe: the copy may overwrite the set the MMAs before it read
+                        const uint32_t na = p.sf_sub, nb = p.sf_sub * p.sfb_chunks;
+                        for (uint32_t c = 0; c < na; ++c) tc_cp_32x128b_warpx4<CL>(sfa_col + c * 4u, make_sf_desc(sa + p.off_sfa + c * 512u));
+                        for (uint32_t c = 0; c < nb; ++c) tc_cp_32x128b_warpx4<CL>(sfb_col + c * 4u, make_sf_desc(sa + p.off_sfb + c * 512u));
                     }
                     // K-major tile: 8-row groups 1024 B apart.  MN-major tile: 8 K rows of an atom are 1024 B
                     // apart (SBO), atoms along MN box_bytes apart (LBO).
@@ -505,14 +523,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         } else if (KIND == kFp8) {
                             // one SF byte per row per MMA: byte k of the word (gran 32), or the
                             // byte of this k-block within its 512-wide SF row (gran 128)
-                            const uint32_t ida = p.sfa_period == 1 ? k : (kb & 3u);
-                            const uint32_t idb = p.sfb_period == 1 ? k : (kb & 3u);
-                            tc_mma_mxf8<CL>(d_tmem, ad, bd, idesc_with_sf_ids(idesc, ida, idb), acc, tmem + kSfaCol, tmem + kSfbCol);
+                            const uint32_t ida = p.sfa_shift == 0 ? k : (kb & 3u);
+                            const uint32_t idb = p.sfb_shift == 0 ? k : (kb & 3u);
+                            tc_mma_mxf8<CL>(d_tmem, ad, bd, idesc_with_sf_ids(idesc, ida, idb), acc, sfa_col, sfb_col);
                         } else {
                             // two SF bytes per row per MMA (64 elements): half-word (k & 1) of SF row (k >> 1)
                             const uint32_t sub = k >> 1, id = (k & 1u) * 2u;
                             tc_mma_mxf4<CL>(d_tmem, ad, bd, idesc_with_sf_ids(idesc, id, id), acc,
-                                            tmem + kSfaCol + sub * 4u, tmem + kSfbCol + sub * p.sfb_chunks * 4u);
+                                            sfa_col + sub * 4u, sfb_col + sub * p.sfb_chunks * 4u);
                         }
                     }
                     // free the stage in both CTAs / publish the accumulator to both epilogues (a pair: one commit
@@ -524,32 +542,48 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         tc_commit<CL>(smem_u32(&bars->empty[stage]));
                         if (ki + 1 == kb_count) tc_commit<CL>(smem_u32(&bars->tmem_full[as]));
                     }
+                    // last k-block that reads this SF set: once its MMAs are through, the SF warp may overwrite the set
+                    if (kHasSf && SFW && (ki + 1 == kb_count || ((kb + 1u) & p.sf_load_mask) == 0)) tc_commit<CL>(smem_u32(&bars->sf_free[sf_set]));
                 }
-                __syncwarp();
+                if (!kConsLane) __syncwarp();
                 if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+            }
+            }
+            __syncwarp();
+            if (kConsLane) {
+                ok = __shfl_sync(0xffffffffu, ok, issuer_lane);
+                stage = __shfl_sync(0xffffffffu, stage, issuer_lane);
+                phase = __shfl_sync(0xffffffffu, phase, issuer_lane);
+                sf_bits = __shfl_sync(0xffffffffu, sf_bits, issuer_lane);
+                sf_set = __shfl_sync(0xffffffffu, sf_set, issuer_lane);
             }
         }
     } else if (warp == 2 && kHasSf) {
-        // ===================================================== SF transposer
+        // ===================================================== SF warp: transposes the SF rows in shared memory and copies them into tensor memory
+        // With SFW the copies (tcgen05.cp) are issued here, not by the MMA issuer: each costs the issuing thread
+        // some 200 cycles, and the MMA issuer's loop, not the tensor pipe, bounded the single-CTA kernel.  Two sets of SF columns
+        // take turns; the set written for SF k-block n was last read by the MMAs of SF k-block n - 2, whose
+        // completion the MMA issuer reports on sf_free.  Pair: the copy reads both CTAs' shared memory, so the
+        // leader's warp issues it once the second CTA has reported its rows transposed.
         Scheduler<GTYPE, CL, SPLIT, DYN> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         sched.attach(&bars->sched, &wc);
         Tile t;
-        uint32_t stage = 0, sf_bits = 0;
+        uint32_t stage = 0, sf_bits = 0, n_sf = 0;
         bool ok = true;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
             const uint32_t kb_first = SPLIT ? t.kb0 : 0u, kb_count = SPLIT ? t.kb1 - t.kb0 : p.num_k_blocks;
             for (uint32_t ki = 0; ki < kb_count; ++ki) {
                 const uint32_t kb = kb_first + ki;
-                const bool has_a = kb % p.sfa_period == 0, has_b = kb % p.sfb_period == 0;
-                if (has_a || has_b) {
+                if ((kb & p.sf_load_mask) == 0) {
                     const uint32_t parity = (sf_bits >> stage) & 1u;
                     sf_bits ^= 1u << stage;
                     ok = DG_WARP_WAIT(smem_u32(&bars->sf_full[stage]), parity, wc, kWaitFull);
                     if (!ok) break;
-                    uint32_t* sfa = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfa - smem_u32(smem_raw)));
-                    uint32_t* sfb = reinterpret_cast<uint32_t*>(smem_raw + (stage_addr(stage) + p.off_sfb - smem_u32(smem_raw)));
-                    const uint32_t na = has_a ? p.sf_sub : 0u, nb = has_b ? p.sf_sub * p.sfb_chunks : 0u;
+                    const uint32_t sa = stage_addr(stage);
+                    uint32_t* sfa = reinterpret_cast<uint32_t*>(smem_raw + (sa + p.off_sfa - smem_u32(smem_raw)));
+                    uint32_t* sfb = reinterpret_cast<uint32_t*>(smem_raw + (sa + p.off_sfb - smem_u32(smem_raw)));
+                    const uint32_t na = p.sf_sub, nb = p.sf_sub * p.sfb_chunks;
                     // Up to 6 chunks of 128 words: word of row 32*i + lane -> position lane*4 + i.
                     // All loads are issued before the first store.
                     uint4 v[6];
@@ -570,10 +604,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                     fence_proxy_async_smem();
                     __syncwarp();
-                    if (lane == 0) {
-                        if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
-                        else mbar_arrive_cluster(mapa(smem_u32(&bars->sf_ready[stage]), 0));
+                    if (!SFW) {
+                        if (lane == 0) {
+                            if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
+                            else mbar_arrive_cluster(mapa(smem_u32(&bars->sf_ready[stage]), 0));
+                        }
+                    } else if (CL == 2 && !leader) {
+                        if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bars->sf_peer[stage]), 0));
+                    } else {
+                        if (CL == 2 && !(ok = DG_WARP_WAIT(smem_u32(&bars->sf_peer[stage]), parity, wc, kWaitSfReady))) break;
+                        const uint32_t set = n_sf & 1u;
+                        if (n_sf >= 2u && !(ok = DG_WARP_WAIT(smem_u32(&bars->sf_free[set]), ((n_sf >> 1) - 1u) & 1u, wc, kWaitSfFree))) break;
+                        tc_fence_after();
+                        if (elect_one()) {
+                            const uint32_t sfa_col = tmem + sf_set_col(set) + kSfaOff, sfb_col = tmem + sf_set_col(set) + kSfbOff;
+                            for (uint32_t c = 0; c < na; ++c) tc_cp_32x128b_warpx4<CL>(sfa_col + c * 4u, make_sf_desc(sa + p.off_sfa + c * 512u));
+                            for (uint32_t c = 0; c < nb; ++c) tc_cp_32x128b_warpx4<CL>(sfb_col + c * 4u, make_sf_desc(sa + p.off_sfb + c * 512u));
+                            tc_commit<CL>(smem_u32(&bars->sf_ready[stage]));
+                        }
+                        __syncwarp();
                     }
+                    ++n_sf;
                 }
                 if (++stage == p.num_stages) stage = 0;
             }
@@ -1044,8 +1095,16 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     const bool has_sf = kind != kBf16;
     p.sf_sub = kind == kFp4 ? 2u : 1u;
     p.sfb_chunks = ceil_div(p.block_n, 128u);
-    p.sfa_period = gran_a == 128 ? 4u : 1u;
-    p.sfb_period = gran_b == 128 ? 4u : 1u;
+    p.sfa_shift = gran_a == 128 ? 2u : 0u;
+    p.sfb_shift = gran_b == 128 ? 2u : 0u;
+    p.sf_load_mask = (gran_a == 128 && gran_b == 128) ? 3u : 0u;
+    // Who copies the SF rows into tensor memory (tcgen05.cp, some 200 cycles of issue time each).  FP8 with per-128
+    // scales on single CTAs: the SF warp, which takes the copies off the MMA issuer's loop (grouped GEMM 1710 ->
+    // 1776 TFLOPS, M = 128 shapes 2 to 4 % faster).  SF on every k-block (FP4, per-32 FP8): the SF warp's own loop
+    // (transposition + up to six copies) then becomes the limit, the MMA issuer keeps the copies.  CTA pairs: the
+    // MMA issuer as well (dense FP8 2411 against 2317 TFLOPS).  The choice is a template parameter: as a run-time
+    // branch in the k-loop it cost the pair kernel 13 %.
+    p.sf_cp_by_mma = env_u32("DG_SF_CP_BY_MMA", p.sf_load_mask == 0 ? 1u : 0u);
     // per CTA; a K-major tile holds its rows x 128 bytes of K, an MN-major one whole atoms of 128 bytes x BLOCK_K rows
     const uint32_t block_k_rows = kind == kBf16 ? 64u : 128u;
     p.a_mn = a_mn; p.b_mn = b_mn;
@@ -1098,10 +1157,10 @@ static bool pdl_enabled() {
     return on;
 }
 
-template <int KIND, int GTYPE, int CL, bool SPLIT = false, bool DYN = false, bool MNM = false>
+template <int KIND, int GTYPE, int CL, bool SPLIT = false, bool DYN = false, bool MNM = false, bool SFW = false>
 static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                       const CUtensorMap& tsb, cudaStream_t s) {
-    auto* fn = gemm_kernel<KIND, GTYPE, CL, SPLIT, DYN, MNM>;
+    auto* fn = gemm_kernel<KIND, GTYPE, CL, SPLIT, DYN, MNM, SFW>;
     static thread_local uint32_t configured[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1124,6 +1183,12 @@ static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    if (env_u32("DG_PRINT_CONFIGS", 0)) {
+        int clusters = -1;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg);
+        fprintf(stderr, "[deepgemm_b200] launch: grid %u, cluster %d, smem %u: %d clusters can be resident (%s)\n", plan.grid, CL,
+                plan.smem_bytes, clusters, cudaGetErrorString(e));
+    }
     DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, ta, tb, tsa, tsb, plan.p));
     note_launch();
     return DG_OK;
@@ -1284,6 +1349,8 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     } else {
         tsa = ta; tsb = tb;
     }
+    // FP8 with per-128 scales on both operands: the instantiation whose SF warp copies the scale factors into tensor memory
+    const bool sfw = kind == kFp8 && plan.cluster == 1 && !a_mn && !b_mn && gtype != kBatched && p.sf_cp_by_mma == 0;
     if (p.k_splits > 1) {
         // Scratch for the partial tiles: one buffer per (thread, device, stream), grown on demand with
         // stream-ordered allocation and kept for the next call (work on one stream is ordered, so
@@ -1316,7 +1383,8 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
             p.split_ws = slot->ptr;
         }
         int32_t lst = DG_OK;
-        if (kind == kFp8) lst = launch<kFp8, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
+        if (kind == kFp8 && sfw) lst = launch<kFp8, kNormal, 1, true, false, false, true>(plan, ta, tb, tsa, tsb, s);
+        else if (kind == kFp8) lst = launch<kFp8, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
         else if (kind == kFp4) lst = launch<kFp4, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
         else lst = launch<kBf16, kNormal, 1, true>(plan, ta, tb, tsa, tsb, s);
         if (lst == DG_OK) {
@@ -1340,6 +1408,7 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     }
     if (plan.dynamic) {
         p.tile_counter = tile_counters(dev);
+        if (kind == kFp8 && sfw) return launch<kFp8, kContiguous, 1, false, true, false, true>(plan, ta, tb, tsa, tsb, s);
         if (kind == kFp8) return launch<kFp8, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, s);
         if (kind == kFp4) return launch<kFp4, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, s);
         return launch<kBf16, kContiguous, 1, false, true>(plan, ta, tb, tsa, tsb, s);
@@ -1350,6 +1419,12 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
         if (kind == kBf16 && gtype == kNormal) return launch<kBf16, kNormal, 1, false, false, true>(plan, ta, tb, tsa, tsb, s);
         if (kind == kBf16 && gtype == kBatched) return launch<kBf16, kBatched, 1, false, false, true>(plan, ta, tb, tsa, tsb, s);
     }
+#define DG_DISPATCH_SFW(G)                                                                               \
+    if (kind == kFp8 && gtype == G && sfw) {                                                             \
+        return launch<kFp8, G, 1, false, false, false, true>(plan, ta, tb, tsa, tsb, s);                 \
+    }
+    DG_DISPATCH_SFW(kNormal) DG_DISPATCH_SFW(kContiguous) DG_DISPATCH_SFW(kMasked)
+#undef DG_DISPATCH_SFW
 #define DG_DISPATCH(K, G)                                                            \
     if (kind == K && gtype == G) {                                                   \
         if (plan.cluster == 2) return launch<K, G, 2>(plan, ta, tb, tsa, tsb, s);    \

@@ -21,7 +21,7 @@ constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
 // Status word layout: low byte = which wait gave up, bits 8.. = blockIdx.x.
 enum WaitSite : uint32_t {
     kWaitEmpty = 1, kWaitFull = 2, kWaitSfReady = 3, kWaitTmemFull = 4, kWaitTmemEmpty = 5,
-    kWaitStore = 6, kWaitPeer = 7, kWaitSched = 8, kWaitWeights = 9,
+    kWaitStore = 6, kWaitPeer = 7, kWaitSched = 8, kWaitWeights = 9, kWaitSfFree = 10,
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
