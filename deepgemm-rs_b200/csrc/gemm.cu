@@ -1027,6 +1027,25 @@ static uint32_t pick_block_n(int kind, uint32_t m_tiles_total, uint32_t n, uint3
     return best;
 }
 
+// Dense FP8 with per-128 scales: tile shape from measured tile times.  A tile of kb k-blocks takes about
+// fixed + kb * per_kb nanoseconds (B200, 4096 x 7168 x {2048, 16384}, every width, both modes; the 224-wide
+// single-CTA tile has four pipeline stages where 192 has five, hence its jump; a CTA pair takes the same
+// time per k-block at every width), and a launch takes waves x tile time.
+static void pick_dense_fp8_tile(uint32_t m, uint32_t n, uint32_t kb, uint32_t sms, uint32_t* cl_out, uint32_t* bn_out) {
+    static const double single_kb[7] = {214, 214, 233, 273, 331, 361, 537};   // 32 (as 64), 64, 96, ..., 224
+    static const double pair_kb[7] = {423, 423, 417, 414, 392, 442, 447};
+    double best = 1e30;
+    for (uint32_t cl = 1; cl <= (m > kBlockM ? 2u : 1u); ++cl) {
+        for (uint32_t i = 1; i < 7; ++i) {
+            const uint32_t bn = 32u * (i + 1u);
+            const uint64_t tiles = (uint64_t)ceil_div(m, kBlockM * cl) * ceil_div(n, bn);
+            const uint64_t waves = (tiles + sms / cl - 1) / (sms / cl);
+            const double cost = (double)waves * (cl == 1 ? 1300.0 + kb * single_kb[i] : 400.0 + kb * pair_kb[i]);
+            if (cost < best) { best = cost; *cl_out = cl; *bn_out = bn; }
+        }
+    }
+}
+
 static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k, uint32_t num_groups,
                          uint32_t expected_m, uint32_t gran_a, uint32_t gran_b, const DeviceInfo* dev, Plan* plan,
                          bool allow_dynamic = true, bool a_mn = false, bool b_mn = false) {
@@ -1051,6 +1070,10 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     if (forced_cl == 1 || forced_cl == 2) cl = forced_cl;
     if (gtype == kContiguous && m / kBlockM > kMaxPairedBlocks) cl = 1;   // the in-kernel tile list is bounded
     if (a_mn || b_mn) cl = 1;   // MN-major tiles are loaded atom by atom by one CTA
+    uint32_t dense_bn = 0;
+    if (kind == kFp8 && gtype == kNormal && gran_a == 128 && gran_b == 128 && !a_mn && !b_mn && m > kBlockM && forced_cl == 0 &&
+        env_u32("DG_BLOCK_N", 0) == 0)
+        pick_dense_fp8_tile(m, n, p.num_k_blocks, sms, &cl, &dense_bn);
     plan->cluster = cl;
     const uint32_t tile_m = kBlockM * cl;
     const uint32_t units = sms / cl;
@@ -1059,7 +1082,7 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     else if (gtype == kBatched) m_tiles_total = num_groups * ceil_div(m, tile_m);
     else m_tiles_total = ceil_div(m, tile_m);
     // an MN-major B is loaded in whole swizzle atoms of 128 bytes along N: 128 columns of FP8, 64 of BF16
-    p.block_n = pick_block_n(kind, m_tiles_total, n, units, b_mn ? (kind == kBf16 ? 64u : 128u) : 32u);
+    p.block_n = dense_bn ? dense_bn : pick_block_n(kind, m_tiles_total, n, units, b_mn ? (kind == kBf16 ? 64u : 128u) : 32u);
     p.num_m_blocks = ceil_div(m, tile_m);
     p.num_n_blocks = ceil_div(n, p.block_n);
     // Split-K for weight-streaming shapes (a single row block, long K): with one tile per SM at
