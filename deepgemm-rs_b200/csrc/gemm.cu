@@ -726,7 +726,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 row = (uint32_t)mapped;
             }
             const uint32_t taddr = tmem + ((q * 32u) << 16) + as * kAccStageCols;
-            const uint32_t chunks = p.block_n / 32u;
+            const uint32_t chunks = (p.block_n + 31u) / 32u;   // the last chunk of a 16-column-granular tile is half used
+            const uint32_t n_end = min(p.n, t.n0 + p.block_n);   // columns from here on belong to the next tile (or to nobody)
             if (!SPLIT && !p.out_f32 && !p.accumulate && (vec_ok || by_ptr) && p.n % 8u == 0) {
                 // BF16 rows leave the SM in runs of 128 contiguous bytes.  A lane holds 32 columns of
                 // its own row after the TMEM load; the lanes of a group of 8 exchange 16-byte pieces
@@ -754,7 +755,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             else mbar_arrive_cluster(mapa(smem_u32(&bars->tmem_empty[as]), 0));
                         }
                     }
-                    if (col0 >= p.n) continue;
+                    if (col0 >= n_end) continue;
                     uint4 a[8];
 #pragma unroll
                     for (uint32_t i = 0; i < 4; ++i) {
@@ -768,7 +769,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                                               pack_bf16x2(__uint_as_float(r1[8 * i + 4]) * al, __uint_as_float(r1[8 * i + 5]) * al),
                                               pack_bf16x2(__uint_as_float(r1[8 * i + 6]) * al, __uint_as_float(r1[8 * i + 7]) * al));
                     }
-                    if (two && col0 + 64u <= p.n) {
+                    if (two && col0 + 64u <= n_end) {
 #pragma unroll
                         for (uint32_t sft = 4; sft >= 1; sft >>= 1) {
                             const bool up = (lane & sft) != 0;
@@ -796,8 +797,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
 #pragma unroll
                         for (uint32_t h = 0; h < 2; ++h) {
                             const uint32_t cc = col0 + 32u * h;
-                            if ((h == 1 && !two) || cc >= p.n) break;
-                            if (cc + 32u <= p.n) {
+                            if ((h == 1 && !two) || cc >= n_end) break;
+                            if (cc + 32u <= n_end) {
 #pragma unroll
                                 for (uint32_t sft = 2; sft >= 1; sft >>= 1) {
                                     const bool up = (lane & sft) != 0;
@@ -821,7 +822,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             } else if (my_row) {
 #pragma unroll
                                 for (uint32_t i = 0; i < 4; ++i)
-                                    if (cc + 8u * i + 8u <= p.n) *reinterpret_cast<uint4*>(my_row + (cc + 8u * i) * 2ull) = a[4 * h + i];
+                                    if (cc + 8u * i + 8u <= n_end) *reinterpret_cast<uint4*>(my_row + (cc + 8u * i) * 2ull) = a[4 * h + i];
                             }
                         }
                     }
@@ -833,7 +834,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             auto store_chunk = [&](const uint32_t (&r)[32], uint32_t col0) {
                 if (p.out_f32) {
                     float* dst = reinterpret_cast<float*>(p.d) + (size_t)row * p.ldd + col0;
-                    if (vec_ok && col0 + 32u <= p.n) {
+                    if (vec_ok && col0 + 32u <= n_end) {
 #pragma unroll
                         for (uint32_t i = 0; i < 8; ++i) {
                             float4 v = make_float4(__uint_as_float(r[4 * i]) * p.alpha, __uint_as_float(r[4 * i + 1]) * p.alpha,
@@ -847,12 +848,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else {
 #pragma unroll
                         for (uint32_t i = 0; i < 32; ++i)
-                            if (col0 + i < p.n) dst[i] = __uint_as_float(r[i]) * p.alpha + (p.accumulate ? dst[i] : 0.f);
+                            if (col0 + i < n_end) dst[i] = __uint_as_float(r[i]) * p.alpha + (p.accumulate ? dst[i] : 0.f);
                     }
                 } else {
                     __nv_bfloat16* dst = by_ptr ? reinterpret_cast<__nv_bfloat16*>(row_addr) + col0
                                                 : reinterpret_cast<__nv_bfloat16*>(p.d) + (size_t)row * p.ldd + col0;
-                    if ((vec_ok || by_ptr) && col0 + 32u <= p.n) {
+                    if ((vec_ok || by_ptr) && col0 + 32u <= n_end) {
 #pragma unroll
                         for (uint32_t i = 0; i < 4; ++i) {
                             uint32_t w[4];
@@ -876,7 +877,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else {
 #pragma unroll
                         for (uint32_t i = 0; i < 32; ++i) {
-                            if (col0 + i < p.n) {
+                            if (col0 + i < n_end) {
                                 __nv_bfloat16 v = __float2bfloat16_rn(__uint_as_float(r[i]) * p.alpha);
                                 if (p.accumulate) v = __float2bfloat16_rn(__bfloat162float(dst[i]) + __bfloat162float(v));
                                 dst[i] = v;
@@ -900,11 +901,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                 }
                 const uint32_t col0 = t.n0 + c * 32u;
-                if (!row_ok || col0 >= p.n) continue;
+                if (!row_ok || col0 >= n_end) continue;
                 if (SPLIT) {
                     // partial sum of this K range
                     float* dst = p.split_ws + ((size_t)t.split * p.m + row) * p.n + col0;
-                    if (p.n % 4 == 0 && col0 + 32u <= p.n) {
+                    if (p.n % 4 == 0 && col0 + 32u <= n_end) {
 #pragma unroll
                         for (uint32_t i = 0; i < 8; ++i)
                             *reinterpret_cast<float4*>(dst + 4 * i) = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
@@ -912,7 +913,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else {
 #pragma unroll
                         for (uint32_t i = 0; i < 32; ++i)
-                            if (col0 + i < p.n) dst[i] = __uint_as_float(r[i]);
+                            if (col0 + i < n_end) dst[i] = __uint_as_float(r[i]);
                     }
                     continue;
                 }
@@ -1014,7 +1015,7 @@ static uint32_t env_u32(const char* name, uint32_t dflt) {
 static uint32_t pick_block_n(int kind, uint32_t m_tiles_total, uint32_t n, uint32_t units, uint32_t step = 32) {
     const uint32_t max_bn = kind == kBf16 ? 256u : 224u;
     const uint32_t forced = env_u32("DG_BLOCK_N", 0);
-    if (forced >= step && forced <= max_bn && forced % step == 0) return forced;
+    if (forced >= step && forced <= max_bn && forced % (step == 32 ? 16u : step) == 0) return forced;   // K-major B: any multiple of 16
     uint32_t best = step;
     double best_cost = 1e30;
     for (uint32_t bn = step; bn <= max_bn; bn += step) {
@@ -1028,17 +1029,19 @@ static uint32_t pick_block_n(int kind, uint32_t m_tiles_total, uint32_t n, uint3
 }
 
 // Dense FP8 with per-128 scales: tile shape from measured tile times.  A tile of kb k-blocks takes about
-// fixed + kb * per_kb nanoseconds (B200, 4096 x 7168 x {2048, 16384}, every width, both modes; the 224-wide
+// fixed + kb * per_kb nanoseconds (B200, 4096 x 7168 x {2048, 16384}, both modes; widths are multiples of 16, the 224-wide
 // single-CTA tile has four pipeline stages where 192 has five, hence its jump; a CTA pair takes the same
 // time per k-block at every width), and a launch takes waves x tile time.
-static void pick_dense_fp8_tile(uint32_t m, uint32_t n, uint32_t kb, uint32_t sms, uint32_t* cl_out, uint32_t* bn_out) {
-    static const double single_kb[7] = {214, 214, 233, 273, 331, 361, 537};   // 32 (as 64), 64, 96, ..., 224
-    static const double pair_kb[7] = {423, 423, 417, 414, 392, 442, 447};
+static void pick_dense_fp8_tile(uint32_t m, uint32_t groups, uint32_t n, uint32_t kb, uint32_t sms, uint32_t* cl_out, uint32_t* bn_out) {
+    static const uint32_t widths[8] = {64, 96, 128, 160, 176, 192, 208, 224};
+    static const double single_kb[8] = {214, 233, 273, 331, 355, 361, 394, 537};
+    static const double pair_kb[8] = {423, 417, 414, 392, 0, 442, 0, 447};   // 0: not measured, not offered
     double best = 1e30;
     for (uint32_t cl = 1; cl <= (m > kBlockM ? 2u : 1u); ++cl) {
-        for (uint32_t i = 1; i < 7; ++i) {
-            const uint32_t bn = 32u * (i + 1u);
-            const uint64_t tiles = (uint64_t)ceil_div(m, kBlockM * cl) * ceil_div(n, bn);
+        for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t bn = widths[i];
+            if (cl == 2 && pair_kb[i] == 0) continue;
+            const uint64_t tiles = (uint64_t)groups * ceil_div(m, kBlockM * cl) * ceil_div(n, bn);
             const uint64_t waves = (tiles + sms / cl - 1) / (sms / cl);
             const double cost = (double)waves * (cl == 1 ? 1300.0 + kb * single_kb[i] : 400.0 + kb * pair_kb[i]);
             if (cost < best) { best = cost; *cl_out = cl; *bn_out = bn; }
@@ -1071,9 +1074,9 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     if (gtype == kContiguous && m / kBlockM > kMaxPairedBlocks) cl = 1;   // the in-kernel tile list is bounded
     if (a_mn || b_mn) cl = 1;   // MN-major tiles are loaded atom by atom by one CTA
     uint32_t dense_bn = 0;
-    if (kind == kFp8 && gtype == kNormal && gran_a == 128 && gran_b == 128 && !a_mn && !b_mn && m > kBlockM && forced_cl == 0 &&
-        env_u32("DG_BLOCK_N", 0) == 0)
-        pick_dense_fp8_tile(m, n, p.num_k_blocks, sms, &cl, &dense_bn);
+    if (kind == kFp8 && (gtype == kNormal || gtype == kMasked) && gran_a == 128 && gran_b == 128 && !a_mn && !b_mn &&
+        (gtype == kMasked || m > kBlockM) && forced_cl == 0 && env_u32("DG_BLOCK_N", 0) == 0)
+        pick_dense_fp8_tile(rows_per_group, gtype == kMasked ? num_groups : 1u, n, p.num_k_blocks, sms, &cl, &dense_bn);   // masked: expected rows per group
     plan->cluster = cl;
     const uint32_t tile_m = kBlockM * cl;
     const uint32_t units = sms / cl;
