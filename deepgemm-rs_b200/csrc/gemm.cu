@@ -1094,18 +1094,26 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     p.k_splits = 1;
     p.kb_per_split = p.num_k_blocks;
     if (gtype == kNormal && cl == 1 && !a_mn && !b_mn && m <= kBlockM && p.num_k_blocks >= 16 && env_u32("DG_SPLIT_K", 1)) {
+        // Cost of a (tile width, K ranges) choice in nanoseconds, fitted to a sweep on B200 (M = 128, rotating
+        // weights): the longer of the busiest CTA's k-loop (its k-blocks x the measured time per k-block of that
+        // width) and the weight stream from DRAM, a fixed part per wave, and the second kernel: a fixed part plus
+        // one pass over the f32 partial tiles per range.  Few ranges on narrow tiles beat many on wide ones.
         const uint32_t forced_bn = env_u32("DG_BLOCK_N", 0);
         uint32_t best_bn = p.block_n, best_splits = 1;
         double best_cost = 1e30;
-        for (uint32_t bn = 64; bn <= 224; bn += 32) {
+        static const uint32_t widths[6] = {96, 128, 160, 192, 208, 224};
+        static const double kb_ns[6] = {233, 273, 331, 361, 394, 537};
+        const double stream_ns = (double)n * k * (kind == kBf16 ? 2.0 : (kind == kFp4 ? 0.5 : 1.0)) / 5.5e3;
+        for (uint32_t i = 0; i < 6; ++i) {
+            const uint32_t bn = widths[i];
             if (forced_bn && bn != forced_bn) continue;
             const uint32_t tiles = ceil_div(n, bn);
             for (uint32_t sp = 1; sp <= 16; ++sp) {
                 const uint32_t per = align_up(ceil_div(p.num_k_blocks, sp), 4);
                 if (ceil_div(p.num_k_blocks, per) != sp) continue;
                 const uint32_t waves = ceil_div(tiles * sp, sms);
-                // k-blocks of the longest chain + a fixed cost per work item + the reduce traffic
-                const double cost = (double)waves * (per * (0.35 + bn / 640.0) + 6.0) + (sp > 1 ? 2.0 + sp * 0.5 : 0.0);
+                const double cost = std::max((double)waves * per * kb_ns[i], stream_ns) + waves * 1000.0 +
+                                    (sp > 1 ? 2500.0 + sp * ((double)m * n * 4.0 / 3.5e3) : 0.0);
                 if (cost < best_cost) { best_cost = cost; best_bn = bn; best_splits = sp; }
             }
         }
