@@ -172,7 +172,9 @@ __device__ __forceinline__ void tmem_ld_x4(uint32_t taddr, uint32_t (&r)[4]) {
 }
 // SCALED: ue8m0 contracts (scale factors on q and kv, bf16 weights and logits); FP4: packed E2M1 codes;
 // PAGED: kv through a block table, work from the metadata kernel.
-template <bool SCALED, bool FP4, bool PAGED>
+// U4: head counts that are not a multiple of 16 (their 4-column reduction loop is a variant of its own: as a
+// run-time branch beside the 16-column loop it cost the common case 4 %).
+template <bool SCALED, bool FP4, bool PAGED, bool U4 = false>
 __global__ void __launch_bounds__(kMqaMaxThreads, 1)
 mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_qsf, const __grid_constant__ CUtensorMap tm_kvsf,
@@ -391,7 +393,7 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
         {
             const uint32_t q_per_wg = p.block_q / p.ep_groups;
-            const uint32_t units_per_q = p.num_heads / p.unit;
+            const uint32_t units_per_q = p.num_heads / (U4 ? 4u : 16u);
             const uint32_t nunits = q_per_wg * units_per_q;        // TMEM loads per kv block
             const uint32_t q_first = wg * q_per_wg;
             const uint32_t col_base = q_first * p.num_heads;
@@ -446,7 +448,7 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(&bars->tmem_empty[as]));
                     };
-                    if (p.unit == 4u) {
+                    if (U4) {
                         // head counts that are not a multiple of 16: four columns at a time, no software pipeline
                         for (uint32_t u = 0; u < nunits; ++u) {
                             uint32_t v[4];
@@ -701,9 +703,16 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED>;
-    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
-    if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
+    cudaError_t e;
+    if (p.unit == 4u) {
+        auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, true>;
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
+    } else {
+        auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false>;
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
+    }
     if (meta) cudaFreeAsync(meta, s);
     if (e != cudaSuccess) return fail(DG_ERR_DRIVER, "mqa_logits launch failed: %s", cudaGetErrorString(e));
     dg::note_launch();
