@@ -71,6 +71,21 @@ def test_fp8_every_block_n(block_n):
     run_dense("fp8", 256, 512, 1024, gran_a=128, gran_b=128, seed=block_n, block_n=block_n)
 
 
+@pytest.mark.parametrize("kind,cluster,block_n,n", [
+    ("fp8", 1, 48, 520), ("fp8", 1, 176, 1000), ("fp8", 1, 208, 1040), ("fp8", 2, 208, 1344), ("fp8", 2, 80, 400),
+    ("fp4", 1, 208, 624), ("bf16", 1, 144, 440), ("bf16", 2, 240, 720),
+])
+def test_tile_widths_that_are_multiples_of_16(kind, cluster, block_n, n):
+    """Tile widths need not be multiples of 32: the last 32-column chunk of a tile is then half used and the
+    epilogue must stop at the tile's end, not at the chunk's (the columns behind it belong to the next tile)."""
+    run_dense(kind, 300, n, 1024, gran_a=128 if kind == "fp8" else 32, gran_b=128 if kind == "fp8" else 32, seed=block_n,
+              block_n=block_n, cluster=cluster)
+
+
+def test_tile_width_208_with_f32_output():
+    run_dense("fp8", 260, 1040, 512, gran_a=128, gran_b=128, seed=9, block_n=208, f32=True)
+
+
 @pytest.mark.parametrize("block_n", [32, 128, 224])
 def test_fp4_block_n(block_n):
     run_dense("fp4", 256, 512, 1024, seed=block_n, block_n=block_n)
