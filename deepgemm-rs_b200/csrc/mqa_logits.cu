@@ -170,6 +170,25 @@ __device__ __forceinline__ void tmem_ld_x4(uint32_t taddr, uint32_t (&r)[4]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
 }
+// Packed pairs of f32 (sm_100: one instruction, two FMAs).
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ float lo_f32(uint64_t v) { return __uint_as_float((uint32_t)v); }
+__device__ __forceinline__ float hi_f32(uint64_t v) { return __uint_as_float((uint32_t)(v >> 32)); }
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+// max(x, 0) that keeps a NaN (as x + |x| would)
+__device__ __forceinline__ float relu_nan(float x) {
+    float r;
+    asm("max.NaN.f32 %0, %1, 0f00000000;" : "=f"(r) : "f"(x));
+    return r;
+}
 // SCALED: ue8m0 contracts (scale factors on q and kv, bf16 weights and logits); FP4: packed E2M1 codes;
 // PAGED: kv through a block table, work from the metadata kernel.
 // U4: head counts that are not a multiple of 16 (their 4-column reduction loop is a variant of its own: as a
@@ -407,7 +426,7 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     const uint32_t qi = c / p.num_heads, q = k.q0 + qi;
                     float v = 0.f;
                     if (qi < k.nq && q < p.num_tokens) v = load_weight(q, c % p.num_heads);
-                    w[c] = 0.5f * v;       // see the reduction loop: relu(x) * w = (x + |x|) * (w / 2)
+                    w[c] = v;
                 }
                 // the kv windows of the task's queries travel with the weights: the reduction loop reads
                 // them from shared memory instead of waiting on two global loads per query and kv block
@@ -429,18 +448,18 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     float scale = 1.f;
                     if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
                     const uint32_t taddr = tmem + ((quarter * 32u) << 16) + as * acc_stride + col_base;
-                    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;    // four partial sums of the current query
+                    uint64_t a01 = 0ull, a23 = 0ull;                 // four f32 partial sums of the current query, as two packed pairs
                     uint32_t unit_in_q = 0, q_done = 0;              // position inside this warp's share of the query block
                     auto store_query = [&]() {
                         const uint32_t qi = q_first + q_done;        // index inside the query block
                         const uint32_t s = win[qi], e = win[16u + qi];   // e = 0 for queries past the end
                         if (j >= s && j < e) {
-                            const float val = ((a0 + a1) + (a2 + a3)) * scale;
+                            const float val = ((lo_f32(a01) + hi_f32(a01)) + (lo_f32(a23) + hi_f32(a23))) * scale;
                             const size_t o = (size_t)(k.q0 + qi) * p.logits_stride + (j - s);
                             if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
                             else reinterpret_cast<float*>(p.logits)[o] = val;
                         }
-                        a0 = a1 = a2 = a3 = 0.f;
+                        a01 = a23 = 0ull;
                         unit_in_q = 0;
                         ++q_done;
                     };
@@ -461,19 +480,16 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             const float4 ww = *reinterpret_cast<const float4*>(w + col_base + u * 4u);
                             const float x0 = __uint_as_float(v[0]), x1 = __uint_as_float(v[1]);
                             const float x2 = __uint_as_float(v[2]), x3 = __uint_as_float(v[3]);
-                            a0 = fmaf(x0 + fabsf(x0), ww.x, a0);
-                            a1 = fmaf(x1 + fabsf(x1), ww.y, a1);
-                            a2 = fmaf(x2 + fabsf(x2), ww.z, a2);
-                            a3 = fmaf(x3 + fabsf(x3), ww.w, a3);
+                            a01 = fma_f32x2(pack_f32x2(relu_nan(x0), relu_nan(x1)), pack_f32x2(ww.x, ww.y), a01);
+                            a23 = fma_f32x2(pack_f32x2(relu_nan(x2), relu_nan(x3)), pack_f32x2(ww.z, ww.w), a23);
                             if (++unit_in_q == units_per_q) store_query();
                         }
                         continue;
                     }
-                    // The reduction runs in units of 16 columns.  relu(x) * w is computed as
-                    // (x + |x|) * (w / 2): the addition takes |x| as a source modifier and runs on the FMA
-                    // pipe at full rate, where a max would go through the half-rate ALU pipe; both
-                    // scalings are by powers of two, so the result is the same bit for bit (the weights in
-                    // shared memory are already halved).  The TMEM load and the four weight vectors of
+                    // The reduction runs in units of 16 columns.  The kernel is bound by the instructions its epilogue
+                    // warps issue, so relu(x) * w costs 1.5 of them per element: a max on the ALU pipe and half of a
+                    // packed FMA (fma.rn.f32x2, two accumulators per instruction) on the FMA pipe; the sums are the
+                    // same bit for bit as with scalar FMAs.  The TMEM load and the four weight vectors of
                     // unit u + 1 are requested before the arithmetic of unit u starts, so that neither the
                     // tensor-memory latency nor the shared-memory latency sits between dependent
                     // instructions; 16-column units keep both register sets inside the 102 registers a
@@ -488,10 +504,8 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         for (uint32_t i = 0; i < 4; ++i) {
                             const float x0 = __uint_as_float(v[4 * i]), x1 = __uint_as_float(v[4 * i + 1]);
                             const float x2 = __uint_as_float(v[4 * i + 2]), x3 = __uint_as_float(v[4 * i + 3]);
-                            a0 = fmaf(x0 + fabsf(x0), ww[i].x, a0);
-                            a1 = fmaf(x1 + fabsf(x1), ww[i].y, a1);
-                            a2 = fmaf(x2 + fabsf(x2), ww[i].z, a2);
-                            a3 = fmaf(x3 + fabsf(x3), ww[i].w, a3);
+                            a01 = fma_f32x2(pack_f32x2(relu_nan(x0), relu_nan(x1)), pack_f32x2(ww[i].x, ww[i].y), a01);
+                            a23 = fma_f32x2(pack_f32x2(relu_nan(x2), relu_nan(x3)), pack_f32x2(ww[i].z, ww[i].w), a23);
                         }
                         if (++unit_in_q == units_per_q) store_query();
                     };
