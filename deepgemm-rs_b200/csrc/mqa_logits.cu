@@ -438,6 +438,9 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (lane == 0) mbar_arrive(smem_u32(&bars->w_full[wb]));
                 ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->w_full[wb]), wphase, wc, kWaitWeights));
                 if (!ok) break;
+                // one query per warpgroup: its window and the address of its logits row do not change over the kv blocks
+                const uint32_t s_fix = NUN ? win[q_first] : 0u, e_fix = NUN ? win[16u + q_first] : 0u;
+                const size_t row_fix = NUN ? (size_t)(k.q0 + q_first) * p.logits_stride : 0;
                 for (uint32_t kb = k.kb0; kb < k.kb1; ++kb) {
                     const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
                     ++acount;
@@ -452,10 +455,10 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     uint32_t unit_in_q = 0, q_done = 0;              // position inside this warp's share of the query block
                     auto store_query = [&]() {
                         const uint32_t qi = q_first + q_done;        // index inside the query block
-                        const uint32_t s = win[qi], e = win[16u + qi];   // e = 0 for queries past the end
+                        const uint32_t s = NUN ? s_fix : win[qi], e = NUN ? e_fix : win[16u + qi];   // e = 0 for queries past the end
                         if (j >= s && j < e) {
                             const float val = ((lo_f32(a01) + hi_f32(a01)) + (lo_f32(a23) + hi_f32(a23))) * scale;
-                            const size_t o = (size_t)(k.q0 + qi) * p.logits_stride + (j - s);
+                            const size_t o = (NUN ? row_fix : (size_t)(k.q0 + qi) * p.logits_stride) + (j - s);
                             if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
                             else reinterpret_cast<float*>(p.logits)[o] = val;
                         }
