@@ -193,8 +193,8 @@ __device__ __forceinline__ float relu_nan(float x) {
 // PAGED: kv through a block table, work from the metadata kernel.
 // U4: head counts that are not a multiple of 16 (their 4-column reduction loop is a variant of its own: as a
 // run-time branch beside the 16-column loop it cost the common case 4 %).
-// NUN: 16-column units a warpgroup reduces per kv block when that is known at compile time (4 = one query of 64
-// heads per warpgroup, the common case: the unit loop is then straight-line code without counters), 0 = any.
+// NUN: 16-column units a warpgroup reduces per kv block when that is known at compile time (4 / 8 = one query of
+// 64 / 128 heads per warpgroup: the unit loop is then straight-line code without counters), 0 = any.
 template <bool SCALED, bool FP4, bool PAGED, bool U4 = false, uint32_t NUN = 0>
 __global__ void __launch_bounds__(kMqaMaxThreads, 1)
 mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
@@ -518,7 +518,7 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tmem_ld_x16(taddr, va);
                     load_w(wa, 0);
                     tmem_ld_wait();
-#pragma unroll(NUN ? 4 : 1)
+#pragma unroll(NUN ? NUN : 1)
                     for (uint32_t u = 0; u < nunits; u += 2) {
                         if (u + 1 < nunits) { tmem_ld_x16(taddr + (u + 1) * 16u, vb); load_w(wb4, u + 1); } else release();
                         consume(va, wa);
@@ -730,6 +730,10 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else if (num_heads == 64 && p.block_q == p.ep_groups) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false, 4>;   // one query of 64 heads per warpgroup
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
+    } else if (num_heads == 128 && p.block_q == p.ep_groups) {
+        auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false, 8>;   // one query of 128 heads per warpgroup
         e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else {
