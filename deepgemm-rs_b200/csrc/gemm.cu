@@ -59,7 +59,7 @@ struct GemmParams {
     uint32_t num_stages;
     uint32_t stage_bytes;  // A + B + SFA + SFB, 1024-aligned
     uint32_t off_b, off_sfa, off_sfb;
-    uint32_t sf_cp_by_mma;            // 1 = the MMA issuer copies the SF rows into tensor memory itself (SF on every k-block), 0 = the SF warp does
+    uint32_t sf_cp_by_mma;            // host-side choice of the instantiation: 1 = the MMA issuer copies the SF rows into tensor memory itself, 0 = the SF warp does (single CTAs)
     uint32_t sf_load_mask;            // SF rows of both operands are loaded on k-blocks with (kb & mask) == 0: every k-block, or every fourth when both operands carry per-128 scales
     uint32_t sfa_shift, sfb_shift;    // log2 of the k-blocks per packed SF row: 0 (gran 32) or 2 (gran 128); shifts and masks, no run-time division in the k-loops
     uint32_t sfb_chunks;   // 128-row chunks of the B scale factors per tile
@@ -257,7 +257,6 @@ struct __align__(8) Barriers {
     uint64_t full[kMaxStages];      // A and B tiles landed (pair: both CTAs' tiles, on the leader's barrier)
     uint64_t sf_full[kMaxStages];   // this CTA's SF rows landed (only on k-blocks that load SF)
     uint64_t sf_ready[kMaxStages];  // SF rows copied into tensor memory (commit of the copies; pair: on the leader)
-    uint64_t sf_peer[kMaxStages];   // pair, on the leader: the second CTA has transposed its SF rows
     uint64_t sf_free[2];            // the MMAs that read SF set s have completed (commit of the MMA issuer)
     uint64_t empty[kMaxStages];
     uint64_t tmem_full[2];
@@ -280,6 +279,7 @@ __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
     constexpr bool kHasSf = KIND != kBf16;
+    static_assert(!(SFW && CL == 2), "the SF warp copies scale factors only on single CTAs");
     // Whether one elected lane runs the MMA issuer's k-loop alone (no warp-wide vote and re-convergence per
     // k-block).  Measured on one B200, warp-wide -> single lane: FP4 3470 -> 4200 TFLOPS, masked FP8 1009 -> 1052,
     // split-K FP8 at M = 128 2 to 7 % faster; but the dynamic contiguous schedule 1826 -> 1780 and dense FP8
@@ -308,7 +308,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             mbar_init(smem_u32(&bars->full[s]), 1);
             mbar_init(smem_u32(&bars->sf_full[s]), 1);
             mbar_init(smem_u32(&bars->sf_ready[s]), SFW ? 1 : CL);
-            mbar_init(smem_u32(&bars->sf_peer[s]), 1);
             mbar_init(smem_u32(&bars->empty[s]), 1);
         }
         for (uint32_t s = 0; s < 2; ++s) {
@@ -563,8 +562,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         // With SFW the copies (tcgen05.cp) are issued here, not by the MMA issuer: each costs the issuing thread
         // some 200 cycles, and the MMA issuer's loop, not the tensor pipe, bounded the single-CTA kernel.  Two sets of SF columns
         // take turns; the set written for SF k-block n was last read by the MMAs of SF k-block n - 2, whose
-        // completion the MMA issuer reports on sf_free.  Pair: the copy reads both CTAs' shared memory, so the
-        // leader's warp issues it once the second CTA has reported its rows transposed.
+        // completion the MMA issuer reports on sf_free.  (Single CTAs only: on a pair the copy reads both CTAs'
+        // shared memory, the leader's warp would have to wait for its partner, and that measured slower.)
         Scheduler<GTYPE, CL, SPLIT, DYN> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         sched.attach(&bars->sched, &wc);
         Tile t;
@@ -609,10 +608,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                             if (CL == 1 || leader) mbar_arrive(smem_u32(&bars->sf_ready[stage]));
                             else mbar_arrive_cluster(mapa(smem_u32(&bars->sf_ready[stage]), 0));
                         }
-                    } else if (CL == 2 && !leader) {
-                        if (lane == 0) mbar_arrive_cluster(mapa(smem_u32(&bars->sf_peer[stage]), 0));
                     } else {
-                        if (CL == 2 && !(ok = DG_WARP_WAIT(smem_u32(&bars->sf_peer[stage]), parity, wc, kWaitSfReady))) break;
                         const uint32_t set = n_sf & 1u;
                         if (n_sf >= 2u && !(ok = DG_WARP_WAIT(smem_u32(&bars->sf_free[set]), ((n_sf >> 1) - 1u) & 1u, wc, kWaitSfFree))) break;
                         tc_fence_after();
