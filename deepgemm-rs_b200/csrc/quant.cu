@@ -71,7 +71,10 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
                                             __uint_as_float(gb.y << 16), __uint_as_float(gb.y & 0xffff0000u)};
                         const float u[4] = {__uint_as_float(ub.x << 16), __uint_as_float(ub.x & 0xffff0000u),
                                             __uint_as_float(ub.y << 16), __uint_as_float(ub.y & 0xffff0000u)};
-                        v[i][j] = make_float4(swiglu_value(g[0], u[0]), swiglu_value(g[1], u[1]), swiglu_value(g[2], u[2]), swiglu_value(g[3], u[3]));
+                        float4 sv;
+                        swiglu_value2(g[0], g[1], u[0], u[1], sv.x, sv.y);
+                        swiglu_value2(g[2], g[3], u[2], u[3], sv.z, sv.w);
+                        v[i][j] = sv;
                     }
                 } else {
                     v[i][j] = ok ? __ldcs(reinterpret_cast<const float4*>(x + (size_t)row * x_pitch + col0 + j * 128u + lane * 4u))
