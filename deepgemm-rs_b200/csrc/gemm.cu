@@ -80,6 +80,9 @@ struct GemmParams {
     float* split_ws;            // f32 partial tiles [k_splits][m][n] when k_splits > 1
     float alpha;                // factor on the product before the output cast (1 = none)
     uint32_t idesc;             // tcgen05 instruction descriptor
+    uint32_t tail_n;            // width of the last column tile when it is narrower than block_n (rounded up to 16; 0 = none): that tile loads and multiplies only its own columns
+    uint32_t idesc_tail;        // instruction descriptor of that tile
+    uint32_t tx_ab_tail;        // bytes of its A and B tiles per k-block and CTA
     uint32_t b_group_rows;      // rows of B per group (grouped GEMMs); >= n when only a column range is computed
     uint32_t b_row_offset;      // first B row inside every group
     uint32_t sf_rows_a, sf_rows_b;  // batched: packed SF rows per batch
@@ -102,6 +105,7 @@ struct Tile {
     uint32_t mn_a;      // batched: first row of the tile inside its batch (SFA column, MN coordinate of an MN-major A)
     uint32_t batch;     // batched: index of the batch
     bool skip;
+    bool tail;          // the narrow last column tile
 };
 
 // Static persistent schedule: cluster c (one CTA, or a CTA pair) takes tiles c, c + C, c + 2C, ...
@@ -154,7 +158,7 @@ struct Scheduler {
             t.kb0 = 0; t.kb1 = p.num_k_blocks; t.split = 0;
             t.a_row = mb * kBlockM;
             t.row_end = p.m;
-            t.n0 = nb * p.block_n;
+            t.n0 = nb * p.block_n; t.tail = p.tail_n != 0u && nb + 1u == p.num_n_blocks;
             const int32_t e = __ldg(p.layout + mb);
             t.skip = e < 0 || (uint32_t)e >= p.num_groups;
             t.b_row = (t.skip ? 0u : (uint32_t)e * p.b_group_rows + p.b_row_offset) + t.n0;
@@ -182,7 +186,7 @@ struct Scheduler {
             const bool paired = (entry & 0x8000u) != 0;
             t.a_row = (blk + rank) * kBlockM;
             t.row_end = (rank == 0 || paired) ? p.m : 0u;
-            t.n0 = nb * p.block_n;
+            t.n0 = nb * p.block_n; t.tail = p.tail_n != 0u && nb + 1u == p.num_n_blocks;
             t.b_row = (uint32_t)__ldg(p.layout + blk) * p.b_group_rows + p.b_row_offset + t.n0;
             return true;
         } else if (GTYPE != kMasked && GTYPE != kBatched) {
@@ -207,7 +211,7 @@ struct Scheduler {
             const uint32_t nb = rem / rows, mb = mb0 + (rem - nb * rows);
             t.a_row = mb * kTileM + rank * kBlockM;
             t.row_end = p.m;
-            t.n0 = nb * p.block_n;
+            t.n0 = nb * p.block_n; t.tail = p.tail_n != 0u && nb + 1u == p.num_n_blocks;
             t.b_row = p.b_row_offset + t.n0;
             if (GTYPE == kContiguous) {
                 const int32_t e = __ldg(p.layout + mb);
@@ -227,7 +231,7 @@ struct Scheduler {
             t.mn_a = mb * kTileM + rank * kBlockM;
             t.a_row = b * p.m + t.mn_a;
             t.row_end = b * p.m + p.m;
-            t.n0 = nb * p.block_n;
+            t.n0 = nb * p.block_n; t.tail = p.tail_n != 0u && nb + 1u == p.num_n_blocks;
             t.b_row = b * p.b_group_rows + p.b_row_offset + t.n0;
             return true;
         } else {
@@ -241,7 +245,7 @@ struct Scheduler {
                     const uint32_t nb = rem / mbs, mb = rem - nb * mbs;
                     t.a_row = g * p.m + mb * kTileM + rank * kBlockM;
                     t.row_end = g * p.m + rows;
-                    t.n0 = nb * p.block_n;
+                    t.n0 = nb * p.block_n; t.tail = p.tail_n != 0u && nb + 1u == p.num_n_blocks;
                     t.b_row = g * p.b_group_rows + p.b_row_offset + t.n0;
                     return true;
                 }
@@ -276,7 +280,7 @@ static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 // block measurably slows the common case (the k-block index feeds every role's bookkeeping).
 template <int KIND, int GTYPE, int CL, bool SPLIT, bool DYN, bool MNM = false, bool SFW = false>
 __global__ void __launch_bounds__(256, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_bt,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
     constexpr bool kHasSf = KIND != kBf16;
     static_assert(!(SFW && CL == 2), "the SF warp copies scale factors only on single CTAs");
@@ -400,10 +404,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         Tile t;
         uint32_t stage = 0, phase = 0;
         bool ok = true;
-        const uint32_t b_rows_per_cta = p.block_n / CL;
         while (ok && sched.next(p, t)) {
             if (t.skip) continue;
             const uint32_t kb_first = SPLIT ? t.kb0 : 0u, kb_count = SPLIT ? t.kb1 - t.kb0 : p.num_k_blocks;
+            // the narrow last column tile has a tensor map of its own (a box of just its rows) and fewer bytes per stage
+            const CUtensorMap* bmap = t.tail ? &tm_bt : &tm_b;
+            const uint32_t tx_ab = t.tail ? p.tx_ab_tail : p.tx_ab;
+            const uint32_t b_rows_per_cta = (t.tail ? p.tail_n : p.block_n) / CL;
             for (uint32_t ki = 0; ki < kb_count; ++ki) {
                 const uint32_t kb = kb_first + ki;
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
@@ -446,15 +453,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                         }
                     } else if (CL == 1) {
                         const uint32_t bar = smem_u32(&bars->full[stage]);
-                        mbar_arrive_expect_tx(bar, p.tx_ab);
+                        mbar_arrive_expect_tx(bar, tx_ab);
                         tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
-                        tma_load_2d(&tm_b, bar, sa + p.off_b, kx, (int32_t)t.b_row);
+                        tma_load_2d(bmap, bar, sa + p.off_b, kx, (int32_t)t.b_row);
                     } else {
                         // both CTAs' tiles complete on the leader's barrier; the leader announces the bytes of both
-                        if (leader) mbar_arrive_expect_tx(smem_u32(&bars->full[stage]), 2u * p.tx_ab);
+                        if (leader) mbar_arrive_expect_tx(smem_u32(&bars->full[stage]), 2u * tx_ab);
                         const uint32_t bar = mapa(smem_u32(&bars->full[stage]), 0);
                         tma_load_2d_pair(&tm_a, bar, sa, kx, (int32_t)t.a_row);
-                        tma_load_2d_pair(&tm_b, bar, sa + p.off_b, kx, (int32_t)(t.b_row + rank * b_rows_per_cta));
+                        tma_load_2d_pair(bmap, bar, sa + p.off_b, kx, (int32_t)(t.b_row + rank * b_rows_per_cta));
                     }
                 }
                 __syncwarp();
@@ -469,7 +476,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         uint32_t stage = 0, phase = 0, tile_count = 0;
         uint32_t sf_bits = 0;  // per-stage parity of sf_ready (it completes only on SF k-blocks)
         uint32_t sf_set = 1;   // SF set the MMAs read; it changes at every SF k-block (the first one takes set 0)
-        const uint32_t idesc = p.idesc;   // operand formats, tile shape and majors, built by the host
         // The tile walk is done by the whole warp, the k-loop of a tile by one elected lane alone: warp-wide votes
         // and re-convergence on every k-block cost the issuer more than the MMAs of a k-block take to execute.
         const bool issuer = elect_one();
@@ -482,6 +488,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem + as * kAccStageCols;
+            const uint32_t idesc = t.tail ? p.idesc_tail : p.idesc;   // operand formats, tile shape and majors, built by the host
             const uint32_t kb_first = SPLIT ? t.kb0 : 0u, kb_count = SPLIT ? t.kb1 - t.kb0 : p.num_k_blocks;
             if (!kConsLane || issuer) {
             for (uint32_t ki = 0; ki < kb_count; ++ki) {
@@ -722,7 +729,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                 row = (uint32_t)mapped;
             }
             const uint32_t taddr = tmem + ((q * 32u) << 16) + as * kAccStageCols;
-            const uint32_t chunks = (p.block_n + 31u) / 32u;   // the last chunk of a 16-column-granular tile is half used
+            const uint32_t chunks = ((t.tail ? p.tail_n : p.block_n) + 31u) / 32u;   // the last chunk of a 16-column-granular tile is half used
             const uint32_t n_end = min(p.n, t.n0 + p.block_n);   // columns from here on belong to the next tile (or to nobody)
             if (!SPLIT && !p.out_f32 && !p.accumulate && (vec_ok || by_ptr) && p.n % 8u == 0) {
                 // BF16 rows leave the SM in runs of 128 contiguous bytes.  A lane holds 32 columns of
@@ -979,6 +986,7 @@ __global__ void __launch_bounds__(256) split_reduce_kernel(const float* __restri
 // ============================================================================ host side
 struct Plan {
     GemmParams p;
+    CUtensorMap tb_tail;   // B with a box of the narrow last column tile's rows (a copy of B's map when there is none)
     uint32_t smem_bytes;
     uint32_t grid;
     uint32_t num_tiles;
@@ -1219,7 +1227,7 @@ static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap
         fprintf(stderr, "[deepgemm_b200] launch: grid %u, cluster %d, smem %u: %d clusters can be resident (%s)\n", plan.grid, CL,
                 plan.smem_bytes, clusters, cudaGetErrorString(e));
     }
-    DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, ta, tb, tsa, tsb, plan.p));
+    DG_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fn, ta, tb, plan.tb_tail, tsa, tsb, plan.p));
     note_launch();
     return DG_OK;
 }
@@ -1351,6 +1359,21 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     else if (kind == kFp4) p.idesc = make_idesc_bs(1u, 1u, kBlockM * plan.cluster, p.block_n);
     else p.idesc = make_idesc_bs(a->dtype == DG_FP4 ? 5u : 0u, b->dtype == DG_FP4 ? 5u : 0u, kBlockM * plan.cluster, p.block_n);
     p.idesc |= ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16);   // bits 15 / 16: A / B is MN-major
+    // The last column tile, when narrower than the others, gets its own width (a multiple of 16), instruction
+    // descriptor and B box: it then costs its share of a tile (N = 4096 in tiles of 224: 64 columns) instead of
+    // loading and multiplying 224 rows of B of which most belong to the next expert or to nobody.
+    p.tail_n = 0; p.idesc_tail = p.idesc; p.tx_ab_tail = p.tx_ab;
+    {
+        const uint32_t last = n_count - (p.num_n_blocks - 1u) * p.block_n, tail = align_up(last, 16u);
+        if (!a_mn && !b_mn && tail < p.block_n && env_u32("DG_TAIL_TILE", 1)) {
+            p.tail_n = tail;
+            if (kind == kBf16) p.idesc_tail = make_idesc_bf16(kBlockM * plan.cluster, tail);
+            else if (kind == kFp4) p.idesc_tail = make_idesc_bs(1u, 1u, kBlockM * plan.cluster, tail);
+            else p.idesc_tail = make_idesc_bs(a->dtype == DG_FP4 ? 5u : 0u, b->dtype == DG_FP4 ? 5u : 0u, kBlockM * plan.cluster, tail);
+            const uint32_t a_b = kBlockM * 128u, b_b = tail / plan.cluster * 128u;
+            p.tx_ab_tail = mixed ? (a->dtype == DG_FP4 ? a_b / 2 : a_b) + (b->dtype == DG_FP4 ? b_b / 2 : b_b) : a_b + b_b;
+        }
+    }
 
     CUtensorMap ta, tb, tsa, tsb;
     const uint32_t ebytes = kind == kBf16 ? 2u : 1u;
@@ -1371,6 +1394,8 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     };
     if ((st = operand_map(&ta, a, a_mn, groups_a, kBlockM, "A")) != DG_OK) return st;
     if ((st = operand_map(&tb, b, b_mn, groups_b, p.block_n / plan.cluster, "B")) != DG_OK) return st;
+    plan.tb_tail = tb;
+    if (p.tail_n && (st = operand_map(&plan.tb_tail, b, false, groups_b, p.tail_n / plan.cluster, "B (last column tile)")) != DG_OK) return st;
     if (has_sf) {
         if ((st = make_tmap_2d(&tsa, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, a->sf.data, a->sf.cols, a->sf.rows,
                                (uint64_t)a->sf.cols * 4, 128u, p.sf_sub, CU_TENSOR_MAP_SWIZZLE_NONE, "SFA")) != DG_OK) return st;
