@@ -443,7 +443,11 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
     def timeit(fn, iters=10, warm=3):
         """Device time per call between CUDA events after `warm` warm-up calls.  Calls that take
         less than 0.1 ms are re-timed as a CUDA graph of `iters` calls replayed 5 times: their
-        host launch cost exceeds their GPU time, and it is the GPU time that is reported."""
+        host launch cost exceeds their GPU time, and it is the GPU time that is reported.
+        Every workload starts from an idle GPU (0.3 s pause): these are kernels timed alone against burst
+        peaks, and without the pause a workload inherits the clocks the one before it was throttled to."""
+        torch.cuda.synchronize()
+        time.sleep(0.3)
         for _ in range(warm):
             fn()
         torch.cuda.synchronize()
