@@ -286,9 +286,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     static_assert(!(SFW && CL == 2), "the SF warp copies scale factors only on single CTAs");
     // Whether one elected lane runs the MMA issuer's k-loop alone (no warp-wide vote and re-convergence per
     // k-block).  Measured on one B200, warp-wide -> single lane: FP4 3470 -> 4200 TFLOPS, masked FP8 1009 -> 1052,
-    // split-K FP8 at M = 128 2 to 7 % faster; but the dynamic contiguous schedule 1826 -> 1780 and dense FP8
-    // on CTA pairs 1950 -> 1925, so those keep the warp-wide loop.
-    constexpr bool kConsLane = KIND == kFp4 || SPLIT || GTYPE == kMasked || (GTYPE == kNormal && CL == 1);
+    // split-K FP8 at M = 128 2 to 7 % faster, the contiguous grouped GEMM on 208-wide tiles (five stages) 1842 ->
+    // 1994 (on 224-wide tiles, four stages, where the pipeline depth bounds it, 1849 -> 1809); dense FP8 on CTA
+    // pairs 1950 -> 1925, so pairs keep the warp-wide loop.
+    constexpr bool kConsLane = KIND == kFp4 || SPLIT || GTYPE == kMasked || ((GTYPE == kNormal || GTYPE == kContiguous) && CL == 1);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // Dynamic shared memory: [barriers (512 B, padded to 1024)] [stage 0] [stage 1] ...
     // (identical offsets in both CTAs of a pair: the launch gives every CTA the same window offset)
@@ -1036,12 +1037,13 @@ static uint32_t pick_block_n(int kind, uint32_t m_tiles_total, uint32_t n, uint3
 // fixed + kb * per_kb nanoseconds (B200, 4096 x 7168 x {2048, 16384}, both modes; widths are multiples of 16, the 224-wide
 // single-CTA tile has four pipeline stages where 192 has five, hence its jump; a CTA pair takes the same
 // time per k-block at every width), and a launch takes waves x tile time.
-static void pick_dense_fp8_tile(uint32_t m, uint32_t groups, uint32_t n, uint32_t kb, uint32_t sms, uint32_t* cl_out, uint32_t* bn_out) {
+static void pick_dense_fp8_tile(uint32_t m, uint32_t groups, uint32_t n, uint32_t kb, uint32_t sms, uint32_t* cl_out, uint32_t* bn_out,
+                                bool pairs_allowed = true) {
     static const uint32_t widths[8] = {64, 96, 128, 160, 176, 192, 208, 224};
     static const double single_kb[8] = {214, 233, 273, 331, 355, 361, 394, 537};
     static const double pair_kb[8] = {423, 417, 414, 392, 0, 442, 0, 447};   // 0: not measured, not offered
     double best = 1e30;
-    for (uint32_t cl = 1; cl <= (m > kBlockM ? 2u : 1u); ++cl) {
+    for (uint32_t cl = 1; cl <= ((m > kBlockM && pairs_allowed) ? 2u : 1u); ++cl) {
         for (uint32_t i = 0; i < 8; ++i) {
             const uint32_t bn = widths[i];
             if (cl == 2 && pair_kb[i] == 0) continue;
@@ -1081,6 +1083,10 @@ static int32_t make_plan(int kind, int gtype, uint32_t m, uint32_t n, uint32_t k
     if (kind == kFp8 && (gtype == kNormal || gtype == kMasked) && gran_a == 128 && gran_b == 128 && !a_mn && !b_mn &&
         (gtype == kMasked || m > kBlockM) && forced_cl == 0 && env_u32("DG_BLOCK_N", 0) == 0)
         pick_dense_fp8_tile(rows_per_group, gtype == kMasked ? num_groups : 1u, n, p.num_k_blocks, sms, &cl, &dense_bn);   // masked: expected rows per group
+    // the contiguous grouped layout on single CTAs: the same table (208 columns and five stages for N = 4096: 1994
+    // against 1849 TFLOPS on 224 columns and four)
+    if (kind == kFp8 && gtype == kContiguous && cl == 1 && gran_a == 128 && gran_b == 128 && !a_mn && !b_mn && env_u32("DG_BLOCK_N", 0) == 0)
+        pick_dense_fp8_tile(m, 1u, n, p.num_k_blocks, sms, &cl, &dense_bn, false);
     plan->cluster = cl;
     const uint32_t tile_m = kBlockM * cl;
     const uint32_t units = sms / cl;
