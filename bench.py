@@ -400,8 +400,8 @@ def main():
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "gemm_kernel<fp8, contiguous>", "achieved": gemm_tflops, "peak": fp8_peak,
                      "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
-                     # ncu DRAM traffic of one full-size launch (256 experts, 16384 tokens): 8.672 GB read + 1.197 GB written
-                     "traffic": 9.869e9 * (T / 16384.0) if CFG["num_experts"] == 256 and world == 1 else None,
+                     # ncu DRAM traffic of one full-size launch (256 experts, 16384 tokens): 8.679 GB read + 1.197 GB written
+                     "traffic": 9.876e9 * (T / 16384.0) if CFG["num_experts"] == 256 and world == 1 else None,
                      "traffic_source": "profiles/gemm_fp8_grouped_contiguous__moe_prefill.md",
                      "algorithmic_bytes_per_launch": float(T * topk * 1.125 * K + e_local * N * K + T * topk * 1.125 * N * 2),
                      "peak_source": f"2 x bf16_tflops (burst) of MEASURED_PEAKS.json ({peak_kind}); FP8 runs at twice the bf16 rate; "
