@@ -23,11 +23,18 @@
 //   warp 1      MMA issuer (scores into one of two accumulator stages in TMEM)
 //   warp 2      TMEM owner; ue8m0 contracts: scale factors into the layout tcgen05.cp needs
 //   warps 4-..  epilogue warpgroups: relu(x) * w accumulated in f32 per thread, every warpgroup reducing its
-//               share of the query block's columns with the next TMEM load in flight while a chunk is consumed
+//               share of the query block's columns.  With one query of 64 or 128 heads per warpgroup the query's
+//               weights stay in registers for all kv blocks of a task (the role warps hand registers over for
+//               that): as broadcast loads from shared memory inside the kv loop they took as much of the shared
+//               memory bandwidth as the tensor core needs for its operands, and that bandwidth, not the
+//               instruction stream, bounded the kernel
 // (A head reduction on the tensor cores -- ReLU'd scores written back to tensor memory as bf16 and multiplied
 // with a block-diagonal weight tile by a second MMA whose A operand is read from tensor memory -- was built
 // and measured on this kernel: correct, but twice as slow, because the 16 narrow MMAs it adds per kv block cost
 // more tensor-pipe time than the reduction costs the CUDA cores.)
+// The epilogue warpgroups of this file's kernels run under a register limit raised inside the kernel; code under
+// such a limit cannot call functions, so the slow path of the bounded waits is inlined here.
+#define DG_WAIT_SLOW_ATTR __forceinline__
 #include "host.h"
 #include "ptx.cuh"
 
@@ -38,6 +45,17 @@ namespace dg {
 constexpr uint32_t kMqaBlockKv = 128;
 constexpr uint32_t kMqaMaxKvStages = 10;
 constexpr uint32_t kMqaMaxThreads = 640;   // 4 role warps + up to 4 epilogue warpgroups
+// One query of 16 * NUN heads per warpgroup (NUN = 4: 4 queries, 640 threads; NUN = 8: 2 queries, 384 threads):
+// registers per thread at launch (what the block size leaves, in steps of 8), what the role warps keep, and
+// what an epilogue thread then gets (8 * NUN packed weight pairs, 16 scores, about 30 of state).
+__host__ __device__ constexpr uint32_t mqa_threads(uint32_t nun) { return nun == 8u ? 384u : kMqaMaxThreads; }
+__host__ __device__ constexpr uint32_t mqa_launch_regs(uint32_t nun) { return (65536u / mqa_threads(nun)) & ~7u; }
+constexpr uint32_t kMqaRoleRegs = 40;
+__host__ __device__ constexpr uint32_t mqa_epilogue_regs(uint32_t nun) {
+    return ((mqa_launch_regs(nun) * mqa_threads(nun) - 128u * kMqaRoleRegs) / (mqa_threads(nun) - 128u)) & ~7u;
+}
+static_assert(mqa_launch_regs(4) == 96 && mqa_epilogue_regs(4) == 104, "register budget of the 64-head variant");
+static_assert(mqa_launch_regs(8) == 168 && mqa_epilogue_regs(8) == 232, "register budget of the 128-head variant");
 constexpr uint32_t kMqaSfaCol = 448;       // ue8m0 contracts only: the accumulators are <= 192 wide
 constexpr uint32_t kMqaSfbCol = 452;
 
@@ -196,7 +214,7 @@ __device__ __forceinline__ float relu_nan(float x) {
 // NUN: 16-column units a warpgroup reduces per kv block when that is known at compile time (4 / 8 = one query of
 // 64 / 128 heads per warpgroup: the unit loop is then straight-line code without counters), 0 = any.
 template <bool SCALED, bool FP4, bool PAGED, bool U4 = false, uint32_t NUN = 0>
-__global__ void __launch_bounds__(kMqaMaxThreads, 1)
+__global__ void __launch_bounds__(mqa_threads(NUN), 1)
 mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_qsf, const __grid_constant__ CUtensorMap tm_kvsf,
                   const MqaParams p) {
@@ -244,6 +262,8 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t acc_stride = p.acc_stride;
     const uint32_t kv_tx = kMqaBlockKv * p.row_bytes + ((SCALED && !PAGED) ? kMqaBlockKv * 4u : 0u);
 
+    if (warp < 4) {
+    if (NUN) reg_release<kMqaRoleRegs>();
     if (warp == 0) {
         // ===================================================== producer (warp-converged, one lane issues)
         uint32_t stage = 0, phase = 0, qcount = 0;
@@ -381,8 +401,10 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
             }
         }
-    } else if (warp >= 4) {
+    }
+    } else {
         // ===================================================== epilogue warpgroups
+        if (NUN) reg_acquire<mqa_epilogue_regs(NUN)>();
         const uint32_t et = threadIdx.x - 128u;
         const uint32_t wg = et >> 7;                  // warpgroup index
         const uint32_t quarter = warp & 3u;           // TMEM lane quarter of this warp
@@ -438,9 +460,66 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (lane == 0) mbar_arrive(smem_u32(&bars->w_full[wb]));
                 ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->w_full[wb]), wphase, wc, kWaitWeights));
                 if (!ok) break;
-                // one query per warpgroup: its window and the address of its logits row do not change over the kv blocks
-                const uint32_t s_fix = NUN ? win[q_first] : 0u, e_fix = NUN ? win[16u + q_first] : 0u;
-                const size_t row_fix = NUN ? (size_t)(k.q0 + q_first) * p.logits_stride : 0;
+                if (NUN) {
+                    // One query of 16 * NUN heads per warpgroup.  Its window, the address of its logits row and its
+                    // weights do not change over the kv blocks of the task: the weights are read from shared memory
+                    // once, as the packed pairs the FMAs take, and stay in registers.  The kernel is bound by what
+                    // the kv loop asks of the SM, so relu(x) * w costs 1.5 instructions per element there: a max on
+                    // the ALU pipe and half of a packed FMA (fma.rn.f32x2, two accumulators per instruction; the
+                    // sums are the same bit for bit as with scalar FMAs).  One 16-column TMEM load at a time: the
+                    // other warps of the scheduler cover its latency, a second set of 16 registers would not fit.
+                    const uint32_t s_fix = win[q_first], e_fix = win[16u + q_first];
+                    const uint32_t span = e_fix > s_fix ? e_fix - s_fix : 0u;       // length of the query's window
+                    const size_t row = (size_t)(k.q0 + q_first) * p.logits_stride;
+                    __nv_bfloat16* const out_bf16 = reinterpret_cast<__nv_bfloat16*>(p.logits) + row;
+                    float* const out_f32 = reinterpret_cast<float*>(p.logits) + row;
+                    const uint32_t lane_base = tmem + ((quarter * 32u) << 16) + col_base;
+                    const uint32_t full0 = smem_u32(&bars->tmem_full[0]), empty0 = smem_u32(&bars->tmem_empty[0]);
+                    uint64_t wp[NUN ? 8u * NUN : 1u];
+#pragma unroll
+                    for (uint32_t i = 0; i < 4u * NUN; ++i) {
+                        const float4 w4 = reinterpret_cast<const float4*>(w + col_base)[i];
+                        wp[2 * i] = pack_f32x2(w4.x, w4.y);
+                        wp[2 * i + 1] = pack_f32x2(w4.z, w4.w);
+                    }
+                    uint32_t j = k.kb0 * kMqaBlockKv + quarter * 32u + lane;
+                    for (uint32_t kb = k.kb0; kb < k.kb1; ++kb, j += kMqaBlockKv) {
+                        const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
+                        ++acount;
+                        ok = __all_sync(0xffffffffu, mbar_wait(full0 + as * 8u, aphase, wc, kWaitTmemFull));
+                        if (!ok) break;
+                        tc_fence_after();
+                        float scale = 1.f;
+                        if (!SCALED) scale = j < p.num_kv ? __ldg(p.kv_scale + j) : 0.f;
+                        const uint32_t taddr = lane_base + as * acc_stride;
+                        uint64_t a01 = 0ull, a23 = 0ull;          // four f32 partial sums as two packed pairs
+                        uint32_t v[16];
+#pragma unroll
+                        for (uint32_t u = 0; u < NUN; ++u) {
+                            tmem_ld_x16(taddr + u * 16u, v);
+                            tmem_ld_wait();
+                            if (u + 1 == NUN) {
+                                // every column of this stage is in registers: hand the TMEM stage back
+                                tc_fence_before();
+                                if (lane == 0) mbar_arrive(empty0 + as * 8u);
+                            }
+#pragma unroll
+                            for (uint32_t i = 0; i < 4; ++i) {
+                                const float x0 = __uint_as_float(v[4 * i]), x1 = __uint_as_float(v[4 * i + 1]);
+                                const float x2 = __uint_as_float(v[4 * i + 2]), x3 = __uint_as_float(v[4 * i + 3]);
+                                a01 = fma_f32x2(pack_f32x2(relu_nan(x0), relu_nan(x1)), wp[8 * u + 2 * i], a01);
+                                a23 = fma_f32x2(pack_f32x2(relu_nan(x2), relu_nan(x3)), wp[8 * u + 2 * i + 1], a23);
+                            }
+                        }
+                        const uint32_t off = j - s_fix;           // a token in front of the window wraps around and fails the test
+                        if (off < span) {
+                            const float val = ((lo_f32(a01) + hi_f32(a01)) + (lo_f32(a23) + hi_f32(a23))) * scale;
+                            if (SCALED) out_bf16[off] = __float2bfloat16_rn(val);
+                            else out_f32[off] = val;
+                        }
+                    }
+                    continue;
+                }
                 for (uint32_t kb = k.kb0; kb < k.kb1; ++kb) {
                     const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
                     ++acount;
@@ -455,10 +534,10 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     uint32_t unit_in_q = 0, q_done = 0;              // position inside this warp's share of the query block
                     auto store_query = [&]() {
                         const uint32_t qi = q_first + q_done;        // index inside the query block
-                        const uint32_t s = NUN ? s_fix : win[qi], e = NUN ? e_fix : win[16u + qi];   // e = 0 for queries past the end
+                        const uint32_t s = win[qi], e = win[16u + qi];   // e = 0 for queries past the end
                         if (j >= s && j < e) {
                             const float val = ((lo_f32(a01) + hi_f32(a01)) + (lo_f32(a23) + hi_f32(a23))) * scale;
-                            const size_t o = (NUN ? row_fix : (size_t)(k.q0 + qi) * p.logits_stride) + (j - s);
+                            const size_t o = (size_t)(k.q0 + qi) * p.logits_stride + (j - s);
                             if (SCALED) reinterpret_cast<__nv_bfloat16*>(p.logits)[o] = __float2bfloat16_rn(val);
                             else reinterpret_cast<float*>(p.logits)[o] = val;
                         }
@@ -489,14 +568,9 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                         }
                         continue;
                     }
-                    // The reduction runs in units of 16 columns.  The kernel is bound by the instructions its epilogue
-                    // warps issue, so relu(x) * w costs 1.5 of them per element: a max on the ALU pipe and half of a
-                    // packed FMA (fma.rn.f32x2, two accumulators per instruction) on the FMA pipe; the sums are the
-                    // same bit for bit as with scalar FMAs.  The TMEM load and the four weight vectors of
-                    // unit u + 1 are requested before the arithmetic of unit u starts, so that neither the
-                    // tensor-memory latency nor the shared-memory latency sits between dependent
-                    // instructions; 16-column units keep both register sets inside the 102 registers a
-                    // 640-thread block leaves per thread.
+                    // Any other head count that is a multiple of 16: units of 16 columns, the TMEM load and the four
+                    // weight vectors of unit u + 1 requested before the arithmetic of unit u starts, so that neither
+                    // the tensor-memory latency nor the shared-memory latency sits between dependent instructions.
                     auto load_w = [&](float4 (&dst)[4], uint32_t u) {
                         const float4* w4 = reinterpret_cast<const float4*>(w + col_base + u * 16u);
 #pragma unroll
@@ -518,7 +592,6 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tmem_ld_x16(taddr, va);
                     load_w(wa, 0);
                     tmem_ld_wait();
-#pragma unroll(NUN ? NUN : 1)
                     for (uint32_t u = 0; u < nunits; u += 2) {
                         if (u + 1 < nunits) { tmem_ld_x16(taddr + (u + 1) * 16u, vb); load_w(wb4, u + 1); } else release();
                         consume(va, wa);
@@ -724,16 +797,27 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e;
+    // The variants that move registers from the role warps to the epilogue warpgroups block inside the kernel if the
+    // registers the block got at launch do not cover what its warpgroups ask for: refuse the launch instead.
+    auto budget_ok = [&](const void* fn, uint32_t nun) {
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, fn) != cudaSuccess) return false;
+        const uint32_t threads = cfg.blockDim.x;
+        return threads <= mqa_threads(nun) &&
+               (uint32_t)fa.numRegs * threads >= 128u * kMqaRoleRegs + (threads - 128u) * mqa_epilogue_regs(nun);
+    };
     if (p.unit == 4u) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, true>;
         e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else if (num_heads == 64 && p.block_q == p.ep_groups) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false, 4>;   // one query of 64 heads per warpgroup
+        if (!budget_ok((const void*)fn, 4)) return fail_free(fail(DG_ERR_RUNTIME, "mqa_logits: register budget of the 64-head kernel does not add up"));
         e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else if (num_heads == 128 && p.block_q == p.ep_groups) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false, 8>;   // one query of 128 heads per warpgroup
+        if (!budget_ok((const void*)fn, 8)) return fail_free(fail(DG_ERR_RUNTIME, "mqa_logits: register budget of the 128-head kernel does not add up"));
         e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else {

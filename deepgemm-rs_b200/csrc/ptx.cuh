@@ -55,6 +55,19 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---------------------------------------------------------------- register reallocation between warpgroups
+// All four warps of a warpgroup (warps 4 g .. 4 g + 3) execute the same call.  A warpgroup that gives registers
+// back lets the others raise their limit above what the launch gave every thread; the sum over the block must
+// stay within the block's allocation at launch (reg_acquire waits until the registers are there, so a budget
+// that does not add up would block for ever: the host checks it before the launch).  N: 24 .. 256, a multiple
+// of 8.  Code that runs under a changed limit cannot call functions: everything in it is inlined.
+template <uint32_t N> __device__ __forceinline__ void reg_release() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <uint32_t N> __device__ __forceinline__ void reg_acquire() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---------------------------------------------------------------- clusters (CTA pairs)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -115,7 +128,12 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
     return ok != 0;
 }
 
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t site) {
+// (a translation unit whose kernels move registers between warpgroups defines DG_WAIT_SLOW_ATTR as
+// __forceinline__ before it includes this file)
+#ifndef DG_WAIT_SLOW_ATTR
+#define DG_WAIT_SLOW_ATTR __noinline__
+#endif
+static __device__ DG_WAIT_SLOW_ATTR bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& w, uint32_t site) {
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait_parked(bar, parity, DG_PARK_NS)) {
