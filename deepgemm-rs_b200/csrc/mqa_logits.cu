@@ -211,9 +211,10 @@ __device__ __forceinline__ float relu_nan(float x) {
 // PAGED: kv through a block table, work from the metadata kernel.
 // U4: head counts that are not a multiple of 16 (their 4-column reduction loop is a variant of its own: as a
 // run-time branch beside the 16-column loop it cost the common case 4 %).
+// QPW: queries per warpgroup of the NUN variants (their NUN units are QPW queries of 16 * NUN / QPW heads).
 // NUN: 16-column units a warpgroup reduces per kv block when that is known at compile time (4 / 8 = one query of
 // 64 / 128 heads per warpgroup: the unit loop is then straight-line code without counters), 0 = any.
-template <bool SCALED, bool FP4, bool PAGED, bool U4 = false, uint32_t NUN = 0>
+template <bool SCALED, bool FP4, bool PAGED, bool U4 = false, uint32_t NUN = 0, uint32_t QPW = 1>
 __global__ void __launch_bounds__(mqa_threads(NUN), 1)
 mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv,
                   const __grid_constant__ CUtensorMap tm_qsf, const __grid_constant__ CUtensorMap tm_kvsf,
@@ -435,8 +436,8 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         };
 
         {
-            const uint32_t q_per_wg = NUN ? 1u : p.block_q / p.ep_groups;
-            const uint32_t units_per_q = NUN ? NUN : p.num_heads / (U4 ? 4u : 16u);
+            const uint32_t q_per_wg = NUN ? QPW : p.block_q / p.ep_groups;
+            const uint32_t units_per_q = NUN ? NUN / QPW : p.num_heads / (U4 ? 4u : 16u);
             const uint32_t nunits = NUN ? NUN : q_per_wg * units_per_q;        // TMEM loads per kv block
             const uint32_t q_first = wg * q_per_wg;
             const uint32_t col_base = q_first * p.num_heads;
@@ -461,15 +462,17 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->w_full[wb]), wphase, wc, kWaitWeights));
                 if (!ok) break;
                 if (NUN) {
-                    // One query of 16 * NUN heads per warpgroup.  Its window, the address of its logits row and its
-                    // weights do not change over the kv blocks of the task: the weights are read from shared memory
-                    // once, as the packed pairs the FMAs take, and stay in registers.  The kernel is bound by what
-                    // the kv loop asks of the SM, so relu(x) * w costs 1.5 instructions per element there: a max on
-                    // the ALU pipe and half of a packed FMA (fma.rn.f32x2, two accumulators per instruction; the
-                    // sums are the same bit for bit as with scalar FMAs).  One 16-column TMEM load at a time: the
-                    // other warps of the scheduler cover its latency, a second set of 16 registers would not fit.
+                    // QPW queries of 16 * NUN / QPW heads per warpgroup, NUN 16-column units per kv block.  The
+                    // weights do not change over the kv blocks of the task: they are read from shared memory once,
+                    // as the packed pairs the FMAs take, and stay in registers; with one query per warpgroup so do
+                    // its window and the address of its logits row.  The kernel is bound by what the kv loop asks
+                    // of the SM, so relu(x) * w costs 1.5 instructions per element there: a max on the ALU pipe and
+                    // half of a packed FMA (fma.rn.f32x2, two accumulators per instruction; the sums are the same
+                    // bit for bit as with scalar FMAs).  One 16-column TMEM load at a time: the other warps of the
+                    // scheduler cover its latency, a second set of 16 registers would not fit.
+                    constexpr uint32_t UPQ = NUN / QPW;       // units per query
                     const uint32_t s_fix = win[q_first], e_fix = win[16u + q_first];
-                    const uint32_t span = e_fix > s_fix ? e_fix - s_fix : 0u;       // length of the query's window
+                    const uint32_t span_fix = e_fix > s_fix ? e_fix - s_fix : 0u;       // length of the query's window
                     const size_t row = (size_t)(k.q0 + q_first) * p.logits_stride;
                     __nv_bfloat16* const out_bf16 = reinterpret_cast<__nv_bfloat16*>(p.logits) + row;
                     float* const out_f32 = reinterpret_cast<float*>(p.logits) + row;
@@ -510,12 +513,19 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                 a01 = fma_f32x2(pack_f32x2(relu_nan(x0), relu_nan(x1)), wp[8 * u + 2 * i], a01);
                                 a23 = fma_f32x2(pack_f32x2(relu_nan(x2), relu_nan(x3)), wp[8 * u + 2 * i + 1], a23);
                             }
-                        }
-                        const uint32_t off = j - s_fix;           // a token in front of the window wraps around and fails the test
-                        if (off < span) {
-                            const float val = ((lo_f32(a01) + hi_f32(a01)) + (lo_f32(a23) + hi_f32(a23))) * scale;
-                            if (SCALED) out_bf16[off] = __float2bfloat16_rn(val);
-                            else out_f32[off] = val;
+                            if ((u + 1) % UPQ == 0) {
+                                // a query is complete
+                                const uint32_t qq = u / UPQ;
+                                const uint32_t s = QPW == 1 ? s_fix : win[q_first + qq];
+                                const uint32_t span = QPW == 1 ? span_fix : (win[16u + q_first + qq] > s ? win[16u + q_first + qq] - s : 0u);
+                                const uint32_t off = j - s;       // a token in front of the window wraps around and fails the test
+                                if (off < span) {
+                                    const float val = ((lo_f32(a01) + hi_f32(a01)) + (lo_f32(a23) + hi_f32(a23))) * scale;
+                                    if (SCALED) out_bf16[(size_t)qq * p.logits_stride + off] = __float2bfloat16_rn(val);
+                                    else out_f32[(size_t)qq * p.logits_stride + off] = val;
+                                }
+                                a01 = a23 = 0ull;
+                            }
                         }
                     }
                     continue;
@@ -808,6 +818,11 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     };
     if (p.unit == 4u) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, true>;
+        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
+    } else if (num_heads == 32 && p.block_q == 2u * p.ep_groups && p.ep_groups == 4u) {
+        auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false, 4, 2>;   // two queries of 32 heads per warpgroup
+        if (!budget_ok((const void*)fn, 4)) return fail_free(fail(DG_ERR_RUNTIME, "mqa_logits: register budget of the 32-head kernel does not add up"));
         e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else if (num_heads == 64 && p.block_q == p.ep_groups) {
