@@ -81,32 +81,43 @@ __host__ __device__ __forceinline__ float stochastic_e4m3_value(float v, uint32_
     return t.f;
 }
 
-// silu(g) * u in f32 with an exponential that is defined operation by operation, so that the CPU
-// checker can state the same function and the re-quantised codes agree bit for bit:
-//   exp(x), x = -g clamped to [-87, 87]:  n = rint(x * log2 e), f = x - n * ln 2 (two-step Cody-Waite),
-//   degree-6 Taylor polynomial of exp(f) in Horner form with fused multiply-adds, times 2^n;
-//   silu(g) = g * (1 / (1 + exp(-g))) with the correctly rounded reciprocal.
-// About 1 ulp from the exact exponential; 20 FMA-pipe instructions instead of two special-function
-// ones, which cost as many issue slots (the special-function unit has an eighth of the lanes).
+// silu(g) * u in f32, defined operation by operation so that the CPU checker can state the same function
+// and the re-quantised codes agree bit for bit; every step is a correctly rounded f32 operation on the FMA
+// pipe or an integer operation, none goes through the special-function unit (an eighth of the lanes):
+//   x = -g clamped to [-87, 87]
+//   t = fma(x, log2 e, 1.5 * 2^23): the low mantissa bits of t hold n = round(x * log2 e); nf = t - 1.5 * 2^23
+//   f = x - nf * ln 2 (two-step Cody-Waite), p = degree-6 Taylor polynomial of exp(f) in Horner form
+//   2^n = bits (t << 23) + 0x3f800000;  d = fma(p, 2^n, 1) = 1 + exp(-g)   (p * 2^n is within about 1 ulp of expf)
+//   r = 1 / d by three Newton steps r += r * (1 - d * r) from the seed bits 0x7ef311c7 - bits(d)
+//       (5 % off; 4e-11 after three steps, so r is d's reciprocal to the last bit or the one beside it)
+//   result (g * r) * u
+constexpr float kSwLog2e = 1.44269502162933349609375f;
+constexpr float kSwMagic = 12582912.0f;
+constexpr float kSwLn2Hi = -0.693145751953125f;
+constexpr float kSwLn2Lo = -1.428606765330187045037746429443359375e-06f;
 __device__ __forceinline__ float swiglu_value(float g, float u) {
     const float x = fminf(fmaxf(-g, -87.0f), 87.0f);
-    const float n = rintf(x * 1.44269502162933349609375f);
-    float f = fmaf(n, -0.693145751953125f, x);
-    f = fmaf(n, -1.428606765330187045037746429443359375e-06f, f);
+    const float t = fmaf(x, kSwLog2e, kSwMagic);
+    const float n = t - kSwMagic;
+    float f = fmaf(n, kSwLn2Hi, x);
+    f = fmaf(n, kSwLn2Lo, f);
     float p = fmaf(f, 1.0f / 720.0f, 1.0f / 120.0f);
     p = fmaf(p, f, 1.0f / 24.0f);
     p = fmaf(p, f, 1.0f / 6.0f);
     p = fmaf(p, f, 0.5f);
     p = fmaf(p, f, 1.0f);
     p = fmaf(p, f, 1.0f);
-    const float e = p * __uint_as_float((uint32_t)((int)n + 127) << 23);
-    return g * __frcp_rn(1.0f + e) * u;
+    const float d = fmaf(p, __uint_as_float((__float_as_uint(t) << 23) + 0x3f800000u), 1.0f);
+    float r = __uint_as_float(0x7ef311c7u - __float_as_uint(d));
+#pragma unroll
+    for (int i = 0; i < 3; ++i) r = fmaf(r, fmaf(-d, r, 1.0f), r);
+    return g * r * u;
 }
 
 // The same function for two elements at once: every multiply, add and fused multiply-add is a packed f32x2
 // instruction (sm_100: two lanes per instruction, each rounded as its scalar counterpart, so the results are the
-// same bit for bit); clamp, rounding to integer, exponent assembly and reciprocal stay scalar.  The kernel that
-// uses this is bound by the instructions it issues, and this halves most of them.
+// same bit for bit); the clamp and the two integer steps stay scalar.  -d is formed directly (p * -2^n - 1,
+// the mirror image of d, rounding included), so that the Newton steps need no negation.
 __device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
     uint64_t r;
     asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
@@ -130,25 +141,32 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
+// a compile-time constant in both halves: an immediate 64-bit operand, no register pair to fill
+__host__ __device__ constexpr uint64_t splat2(float v) { return (uint64_t)__builtin_bit_cast(uint32_t, v) * 0x100000001ull; }
 __device__ __forceinline__ void swiglu_value2(float g0, float g1, float u0, float u1, float& r0, float& r1) {
     const float x0 = fminf(fmaxf(-g0, -87.0f), 87.0f), x1 = fminf(fmaxf(-g1, -87.0f), 87.0f);
     const uint64_t x = f32x2(x0, x1);
+    const uint64_t t = fma2(x, splat2(kSwLog2e), splat2(kSwMagic));
+    const uint64_t n = add2(t, splat2(-kSwMagic));
+    uint64_t f = fma2(n, splat2(kSwLn2Hi), x);
+    f = fma2(n, splat2(kSwLn2Lo), f);
+    uint64_t p = fma2(f, splat2(1.0f / 720.0f), splat2(1.0f / 120.0f));
+    p = fma2(p, f, splat2(1.0f / 24.0f));
+    p = fma2(p, f, splat2(1.0f / 6.0f));
+    p = fma2(p, f, splat2(0.5f));
+    p = fma2(p, f, splat2(1.0f));
+    p = fma2(p, f, splat2(1.0f));
     float t0, t1;
-    f32x2_get(mul2(x, f32x2(1.44269502162933349609375f, 1.44269502162933349609375f)), t0, t1);
-    const float n0 = rintf(t0), n1 = rintf(t1);
-    const uint64_t n = f32x2(n0, n1);
-    uint64_t f = fma2(n, f32x2(-0.693145751953125f, -0.693145751953125f), x);
-    f = fma2(n, f32x2(-1.428606765330187045037746429443359375e-06f, -1.428606765330187045037746429443359375e-06f), f);
-    uint64_t p = fma2(f, f32x2(1.0f / 720.0f, 1.0f / 720.0f), f32x2(1.0f / 120.0f, 1.0f / 120.0f));
-    p = fma2(p, f, f32x2(1.0f / 24.0f, 1.0f / 24.0f));
-    p = fma2(p, f, f32x2(1.0f / 6.0f, 1.0f / 6.0f));
-    p = fma2(p, f, f32x2(0.5f, 0.5f));
-    p = fma2(p, f, f32x2(1.0f, 1.0f));
-    p = fma2(p, f, f32x2(1.0f, 1.0f));
-    const uint64_t scale = f32x2(__uint_as_float((uint32_t)((int)n0 + 127) << 23), __uint_as_float((uint32_t)((int)n1 + 127) << 23));
-    float d0, d1;
-    f32x2_get(add2(mul2(p, scale), f32x2(1.0f, 1.0f)), d0, d1);
-    f32x2_get(mul2(mul2(f32x2(g0, g1), f32x2(__frcp_rn(d0), __frcp_rn(d1))), f32x2(u0, u1)), r0, r1);
+    f32x2_get(t, t0, t1);
+    const uint64_t nscale = f32x2(__uint_as_float((__float_as_uint(t0) << 23) + 0xbf800000u),
+                                  __uint_as_float((__float_as_uint(t1) << 23) + 0xbf800000u));      // -2^n
+    const uint64_t nd = fma2(p, nscale, splat2(-1.0f));                                             // -(1 + exp(-g))
+    float nd0, nd1;
+    f32x2_get(nd, nd0, nd1);
+    uint64_t r = f32x2(__uint_as_float(0xfef311c7u - __float_as_uint(nd0)), __uint_as_float(0xfef311c7u - __float_as_uint(nd1)));
+#pragma unroll
+    for (int i = 0; i < 3; ++i) r = fma2(r, fma2(nd, r, splat2(1.0f)), r);
+    f32x2_get(mul2(mul2(f32x2(g0, g1), r), f32x2(u0, u1)), r0, r1);
 }
 
 __device__ __forceinline__ float amax4(const float4& v) {

@@ -54,6 +54,10 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
 
     for (uint32_t rb = 0; rb < 32u; rb += kRowsPerIter) {
         float4 v[kRowsPerIter][kLoads];
+        // SWIGLU: the raw BF16 gate and up values of all rows in flight; every load is issued before the first
+        // value is formed (formed inside a branch beside its loads, each pair of loads was waited for in turn
+        // and the kernel ran at the memory latency)
+        uint2 graw[SWIGLU ? kRowsPerIter : 1][SWIGLU ? kLoads : 1], uraw[SWIGLU ? kRowsPerIter : 1][SWIGLU ? kLoads : 1];
 #pragma unroll
         for (uint32_t i = 0; i < kRowsPerIter; ++i) {
             const uint32_t row = row0 + rb + i;
@@ -62,20 +66,9 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
                 const uint32_t grp = G == 32 ? (lane >> 3) : j;
                 const bool ok = row < m && grp < groups_here;
                 if (SWIGLU) {
-                    v[i][j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (ok) {
-                        const uint16_t* src = reinterpret_cast<const uint16_t*>(x) + (size_t)row * src_pitch + col0 + j * 128u + lane * 4u;
-                        const uint2 gb = __ldcs(reinterpret_cast<const uint2*>(src));
-                        const uint2 ub = __ldcs(reinterpret_cast<const uint2*>(src + k));
-                        const float g[4] = {__uint_as_float(gb.x << 16), __uint_as_float(gb.x & 0xffff0000u),
-                                            __uint_as_float(gb.y << 16), __uint_as_float(gb.y & 0xffff0000u)};
-                        const float u[4] = {__uint_as_float(ub.x << 16), __uint_as_float(ub.x & 0xffff0000u),
-                                            __uint_as_float(ub.y << 16), __uint_as_float(ub.y & 0xffff0000u)};
-                        float4 sv;
-                        swiglu_value2(g[0], g[1], u[0], u[1], sv.x, sv.y);
-                        swiglu_value2(g[2], g[3], u[2], u[3], sv.z, sv.w);
-                        v[i][j] = sv;
-                    }
+                    const uint16_t* src = reinterpret_cast<const uint16_t*>(x) + (size_t)row * src_pitch + col0 + j * 128u + lane * 4u;
+                    graw[i][j] = ok ? __ldcs(reinterpret_cast<const uint2*>(src)) : make_uint2(0u, 0u);
+                    uraw[i][j] = ok ? __ldcs(reinterpret_cast<const uint2*>(src + k)) : make_uint2(0u, 0u);
                 } else {
                     v[i][j] = ok ? __ldcs(reinterpret_cast<const float4*>(x + (size_t)row * x_pitch + col0 + j * 128u + lane * 4u))
                                  : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -88,6 +81,16 @@ __global__ void __launch_bounds__(256) quant_mx_kernel(const float* __restrict__
             uint32_t word = 0;
 #pragma unroll
             for (uint32_t j = 0; j < kLoads; ++j) {
+                if (SWIGLU) {
+                    // rows and groups outside the tensor were loaded as zeros and give zeros
+                    const uint2 gb = graw[i][j], ub = uraw[i][j];
+                    float4 sv;
+                    swiglu_value2(__uint_as_float(gb.x << 16), __uint_as_float(gb.x & 0xffff0000u),
+                                  __uint_as_float(ub.x << 16), __uint_as_float(ub.x & 0xffff0000u), sv.x, sv.y);
+                    swiglu_value2(__uint_as_float(gb.y << 16), __uint_as_float(gb.y & 0xffff0000u),
+                                  __uint_as_float(ub.y << 16), __uint_as_float(ub.y & 0xffff0000u), sv.z, sv.w);
+                    v[i][j] = sv;
+                }
                 float a = amax4(v[i][j]);
                 if (G == 32) {
 #pragma unroll

@@ -382,17 +382,22 @@ void dgo_quant_fp8_block128_host(const float* x, uint32_t n, uint32_t k, uint8_t
  * gate/up projection (row pitch ld elements): gate = columns [0, inter), up = columns
  * [inter, 2 * inter) ("the two halves", deepgemm/src/api_serving.rs:371-373).  As in the golden model of
  * the fused path (golden.rs:569-577) both factors are the bf16-rounded GEMM outputs and the product
- * silu(g) * u, silu(g) = g * (1 / (1 + exp(-g))) (a rounded reciprocal, then a product), is formed in f32; there is no clamp and the routing weight is
+ * silu(g) * u, silu(g) = g * (1 / (1 + exp(-g))) (a reciprocal, then a product), is formed in f32; there is no clamp and the routing weight is
  * applied later, when the copies of a token are combined.  out: f32 [m, inter], the input of the
  * re-quantisation (dgo_quant_mx_host).
  * The golden model calls the platform's exp; platforms differ in its last bit, which would make the
- * E4M3 codes after re-quantisation platform dependent.  The exponential is therefore spelled out here
- * (range reduction by ln 2, degree-6 Taylor polynomial, fused multiply-adds; within about 1 ulp of expf,
- * asserted by the tests), and the device code evaluates the same sequence of correctly rounded operations. */
-static float exp_taylor6(float x) {
+ * E4M3 codes after re-quantisation platform dependent.  The function is therefore spelled out here as a
+ * sequence of correctly rounded f32 operations, and the device code evaluates the same sequence:
+ *   x = -g clamped to [-87, 87];  t = fma(x, log2 e, 1.5 * 2^23), whose low mantissa bits hold
+ *   n = round(x * log2 e);  f = x - n * ln 2 in two steps;  p = degree-6 Taylor polynomial of exp(f), Horner,
+ *   fused multiply-adds;  2^n from the bits of t;  p * 2^n is within about 1 ulp of expf (asserted by the tests);
+ *   d = fma(p, 2^n, 1);  r = 1 / d by three Newton steps from the seed bits 0x7ef311c7 - bits(d);
+ *   silu(g) * u = (g * r) * u. */
+static float exp_parts(float x, float* scale) {
     if (x < -87.0f) x = -87.0f;
     if (x > 87.0f) x = 87.0f;
-    float n = rintf(x * 1.44269502162933349609375f);
+    float t = fmaf(x, 1.44269502162933349609375f, 12582912.0f);
+    float n = t - 12582912.0f;
     float f = fmaf(n, -0.693145751953125f, x);
     f = fmaf(n, -1.428606765330187045037746429443359375e-06f, f);
     float p = fmaf(f, 1.0f / 720.0f, 1.0f / 120.0f);
@@ -401,9 +406,22 @@ static float exp_taylor6(float x) {
     p = fmaf(p, f, 0.5f);
     p = fmaf(p, f, 1.0f);
     p = fmaf(p, f, 1.0f);
-    return p * u2f((uint32_t)((int)n + 127) << 23);
+    *scale = u2f((f2u(t) << 23) + 0x3f800000u);
+    return p;
+}
+static float exp_taylor6(float x) {
+    float s;
+    float p = exp_parts(x, &s);
+    return p * s;
 }
 float dgo_exp_taylor6(float x) { return exp_taylor6(x); }
+
+static float recip_newton3(float d) {
+    float r = u2f(0x7ef311c7u - f2u(d));
+    for (int i = 0; i < 3; ++i) r = fmaf(r, fmaf(-d, r, 1.0f), r);
+    return r;
+}
+float dgo_recip_newton3(float d) { return recip_newton3(d); }
 
 void dgo_swiglu_f32(const uint16_t* inter_bf16, uint32_t m, uint32_t inter, uint32_t ld, float* out) {
 #pragma omp parallel for schedule(static)
@@ -411,7 +429,9 @@ void dgo_swiglu_f32(const uint16_t* inter_bf16, uint32_t m, uint32_t inter, uint
         const uint16_t* row = inter_bf16 + (size_t)r * ld;
         for (uint32_t c = 0; c < inter; ++c) {
             float g = u2f((uint32_t)row[c] << 16), u = u2f((uint32_t)row[inter + c] << 16);
-            float sig = g * (1.0f / (1.0f + exp_taylor6(-g)));
+            float s;
+            float p = exp_parts(-g, &s);
+            float sig = g * recip_newton3(fmaf(p, s, 1.0f));
             out[(size_t)r * inter + c] = sig * u;
         }
     }
