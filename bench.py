@@ -177,6 +177,38 @@ def parity_moe_step(torch, synth, out, x8, x_sf, topk_idx, topk_w, e_local, n_ou
     return {"calc_diff": d, "max_err": e, "sample": f"{len(ts)} tokens x {len(cs)} output columns x top-{idx.shape[1]} experts at full K"}
 
 
+def parity_ffn_layer(torch, out, x8, x_sf, w13, w2, idx, tw, inter, hidden, tokens=4, cols=256):
+    """Checks the output of the whole feed-forward layer for a sample of tokens and output columns: for each of a
+    token's experts the oracle runs the gate/up GEMM row at full K, rounds to bf16, applies its SwiGLU and the
+    FP8 re-quantisation, multiplies by the sampled rows of the down projection, rounds to bf16, and the copies are
+    combined in f32 in top-k order."""
+    import numpy as np
+    import oracle as o
+    from oracle import sampled
+    T = x8.shape[0]
+    ts = sampled.pick(T, tokens, 31, [0, T - 1])
+    cs = sampled.pick(hidden, cols, 32, sampled.edges(hidden, 208))
+    ti = torch.as_tensor(ts, device=x8.device)
+    ex = idx[ti].cpu().numpy()
+    wt = tw[ti].cpu().numpy().astype(np.float32)
+    want = np.zeros((len(ts), len(cs)), dtype=np.float32)
+    for i, t in enumerate(ts):
+        ga = sampled.golden_rows(x8, x_sf.buf, [int(t)], o.FP8, 128, hidden)
+        acc = np.zeros(len(cs), dtype=np.float32)
+        for j, e in enumerate(ex[i]):
+            g13 = sampled.golden_rows(w13.data, w13.sf.buf, np.arange(2 * inter), o.FP8, 128, hidden, row_offset=int(e) * 2 * inter)
+            up = o.f32_to_bf16_bits_np(o.gemm_ref(ga, g13, m=1, n=2 * inter))
+            hd, hsf = o.quant_mx_host(o.swiglu_f32(up, inter), o.FP8, 128)
+            g2 = sampled.golden_rows(w2.data, w2.sf.buf, cs, o.FP8, 128, inter, row_offset=int(e) * hidden)
+            y = o.bf16_bits_to_f32(o.f32_to_bf16_bits_np(o.gemm_ref(o.GoldenOperand(hd, hsf, o.FP8, 128, inter), g2, m=1, n=len(cs))))[0]
+            acc = acc + np.float32(wt[i, j]) * y
+        want[i] = acc
+    got = out[ti][:, torch.as_tensor(cs, device=x8.device)].float().cpu().numpy()
+    d, e = sampled.compare(got, want)
+    return {"calc_diff": d, "max_err": e,
+            "sample": f"{len(ts)} tokens x {len(cs)} output columns x top-{ex.shape[1]} experts, both GEMMs at full K"}
+
+
 def ep_check(torch, dist, moe, synth, group, rank, world, dev):
     """Before the timed steps at N > 1: a small expert-parallel case in which every rank also holds all the
     experts and runs the single-GPU step on its own tokens; the expert-parallel output must equal it bit
@@ -578,9 +610,13 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
         layer = moe.GroupedMoEFfn(w13, w2, E)
         ms = timeit(lambda: layer.forward(x8, x_sf, idx, tw), iters=5, warm=2)
         flops = 2.0 * T * topk * (2 * I * H + H * I)
-        res["moe_ffn_layer_T16384_E256_top8_H7168_I2048"] = {"ms": ms, "tflops": flops / ms / 1e9,
-                                                             "frac_of_measured_tensor_peak": flops / ms / 1e9 / (2 * peaks["bf16_tflops_sustained"])}
-        del layer, w13, w2
+        out = layer.forward(x8, x_sf, idx, tw)
+        dg.poll_device_status()
+        res["moe_ffn_layer_T16384_E256_top8_H7168_I2048"] = gated(
+            {"ms": ms, "tflops": flops / ms / 1e9,
+             "frac_of_measured_tensor_peak": flops / ms / 1e9 / (2 * peaks["bf16_tflops_sustained"]),
+             "parity": parity_ffn_layer(torch, out, x8, x_sf, w13, w2, idx, tw, I, H)})
+        del layer, w13, w2, out
         torch.cuda.empty_cache()
 
     # mqa_logits, fp32 contract
