@@ -291,7 +291,8 @@ def main():
     x8, x_sf = synth.quantised_tokens(x_dev)
 
     gemm_events = []
-    gemm_names = ("m_grouped_gemm_nt_contiguous", "m_grouped_gemm_nt_contiguous_scatter", "m_grouped_gemm_nt_contiguous_rowptr")
+    gemm_names = ("m_grouped_gemm_nt_contiguous", "m_grouped_gemm_nt_contiguous_gather", "m_grouped_gemm_nt_contiguous_scatter",
+                  "m_grouped_gemm_nt_contiguous_rowptr")
     orig_gemms = {n: getattr(moe, n) for n in gemm_names}
 
     def timed_variant(fn):

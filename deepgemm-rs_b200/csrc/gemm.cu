@@ -71,6 +71,7 @@ struct GemmParams {
     const int32_t* layout; // m_indices (contiguous) or masked_m (masked)
     const int32_t* d_row_map;  // optional: D row of every A row (negative = drop the row); NULL = identity
     const uint64_t* d_row_ptr; // optional (contiguous, bf16): address of every A row's D row, this or a peer GPU's (0 = drop)
+    const int32_t* a_row_src;  // GA kernels: row of the A buffer that holds row r of the (never materialised) grouped matrix
     const int32_t* m_blocks_dev;  // optional (contiguous, single CTA): device-side count of leading 128-row blocks to visit
     uint32_t* tile_counter;       // dynamic schedule: [0] next tile id, [1] CTAs that have finished; both zero at launch
     uint32_t sched_runs;          // dynamic schedule: bands restart at every run of equal m_indices entries (0 = plain bands)
@@ -278,12 +279,17 @@ static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 // SPLIT (dense, single CTA only): a work item is a K range of a tile and the epilogue stores f32
 // partial tiles.  It is a separate instantiation because a k-loop that starts at a run-time
 // block measurably slows the common case (the k-block index feeds every role's bookkeeping).
-template <int KIND, int GTYPE, int CL, bool SPLIT, bool DYN, bool MNM = false, bool SFW = false>
+// GA (contiguous layout, single CTA, K-major FP8): the rows of A are gathered by the producer itself -- row r of
+// the grouped matrix is row p.a_row_src[r] of the buffer behind tm_a (a map whose box is one row), fetched four
+// rows per TMA instruction (tile::gather4), one instruction per lane and k-block -- so the caller need not
+// write a permuted copy of its rows first.
+template <int KIND, int GTYPE, int CL, bool SPLIT, bool DYN, bool MNM = false, bool SFW = false, bool GA = false>
 __global__ void __launch_bounds__(256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_bt,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
     constexpr bool kHasSf = KIND != kBf16;
     static_assert(!(SFW && CL == 2), "the SF warp copies scale factors only on single CTAs");
+    static_assert(!GA || (GTYPE == kContiguous && CL == 1 && !SPLIT && !MNM && KIND == kFp8), "gathered A rows: contiguous FP8, single CTAs");
     // Whether one elected lane runs the MMA issuer's k-loop alone (no warp-wide vote and re-convergence per
     // k-block).  Measured on one B200, warp-wide -> single lane: FP4 3470 -> 4200 TFLOPS, masked FP8 1009 -> 1052,
     // split-K FP8 at M = 128 2 to 7 % faster, the contiguous grouped GEMM on 208-wide tiles (five stages) 1842 ->
@@ -412,6 +418,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const CUtensorMap* bmap = t.tail ? &tm_bt : &tm_b;
             const uint32_t tx_ab = t.tail ? p.tx_ab_tail : p.tx_ab;
             const uint32_t b_rows_per_cta = (t.tail ? p.tail_n : p.block_n) / CL;
+            // GA: lane l fetches rows 4 l .. 4 l + 3 of the tile; padding rows (negative entries) read row 0, their
+            // scale factors are zero and their outputs belong to nobody
+            int4 src_rows = make_int4(0, 0, 0, 0);
+            if (GA) {
+                src_rows = __ldg(reinterpret_cast<const int4*>(p.a_row_src + t.a_row) + lane);
+                src_rows.x = max(src_rows.x, 0); src_rows.y = max(src_rows.y, 0);
+                src_rows.z = max(src_rows.z, 0); src_rows.w = max(src_rows.w, 0);
+            }
             for (uint32_t ki = 0; ki < kb_count; ++ki) {
                 const uint32_t kb = kb_first + ki;
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
@@ -455,7 +469,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     } else if (CL == 1) {
                         const uint32_t bar = smem_u32(&bars->full[stage]);
                         mbar_arrive_expect_tx(bar, tx_ab);
-                        tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
+                        if (!GA) tma_load_2d(&tm_a, bar, sa, kx, (int32_t)t.a_row);
                         tma_load_2d(bmap, bar, sa + p.off_b, kx, (int32_t)t.b_row);
                     } else {
                         // both CTAs' tiles complete on the leader's barrier; the leader announces the bytes of both
@@ -466,6 +480,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                 }
                 __syncwarp();
+                // the bytes were announced by the elected lane above: 32 x 4 rows x 128 bytes make up the A tile
+                if (GA) tma_gather4_2d(&tm_a, smem_u32(&bars->full[stage]), sa + lane * 512u, kx, src_rows.x, src_rows.y, src_rows.z, src_rows.w);
                 if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -1201,10 +1217,10 @@ static bool pdl_enabled() {
     return on;
 }
 
-template <int KIND, int GTYPE, int CL, bool SPLIT = false, bool DYN = false, bool MNM = false, bool SFW = false>
+template <int KIND, int GTYPE, int CL, bool SPLIT = false, bool DYN = false, bool MNM = false, bool SFW = false, bool GA = false>
 static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tsa,
                       const CUtensorMap& tsb, cudaStream_t s) {
-    auto* fn = gemm_kernel<KIND, GTYPE, CL, SPLIT, DYN, MNM, SFW>;
+    auto* fn = gemm_kernel<KIND, GTYPE, CL, SPLIT, DYN, MNM, SFW, GA>;
     static thread_local uint32_t configured[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1265,7 +1281,8 @@ static int32_t validate_operand(const dg_operand_t* op, const char* name) {
 static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_t* out, int gtype, const int32_t* layout,
                         uint32_t layout_len, uint32_t num_groups, uint32_t expected_m, int32_t accumulate, void* stream,
                         const int32_t* d_row_map = nullptr, uint32_t n_begin = 0, uint32_t n_count = 0,
-                        const uint64_t* d_row_ptr = nullptr, const int32_t* m_blocks_dev = nullptr, float alpha = 1.f) {
+                        const uint64_t* d_row_ptr = nullptr, const int32_t* m_blocks_dev = nullptr, float alpha = 1.f,
+                        const int32_t* a_row_src = nullptr, uint32_t a_src_rows = 0) {
     int32_t st;
     if ((st = validate_operand(a, "A")) != DG_OK) return st;
     if ((st = validate_operand(b, "B")) != DG_OK) return st;
@@ -1304,6 +1321,12 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
             return fail(DG_ERR_INVALID_ARG, "contiguous layout requires M (%u) to be a multiple of 128", a->rows);
         if (layout_len != a->rows / 128)
             return fail(DG_ERR_INVALID_ARG, "m_indices must hold M/128 = %u entries (one per 128-row block), got %u", a->rows / 128, layout_len);
+    }
+    if (a_row_src) {
+        if (gtype != kContiguous || mixed || a->dtype != DG_FP8 || a_mn || b_mn)
+            return fail(DG_ERR_INVALID_ARG, "gathered A rows need the contiguous layout and K-major FP8 operands");
+        if (a_src_rows == 0 || a_src_rows >= (1u << 31)) return fail(DG_ERR_INVALID_ARG, "gathered A rows: the source row count must be positive");
+        if (reinterpret_cast<uintptr_t>(a_row_src) & 15u) return fail(DG_ERR_INVALID_ARG, "gathered A rows: the row list must be 16-byte aligned");
     }
     const uint32_t m = a->rows, n = n_count, n_full = b->rows, k = a->k;
     if ((uint64_t)groups_a * m >= (1ull << 31) || (uint64_t)groups_b * n_full >= (1ull << 31))
@@ -1348,6 +1371,7 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
     p.d_row_map = d_row_map;
     p.d_row_ptr = d_row_ptr;
     p.m_blocks_dev = m_blocks_dev;
+    p.a_row_src = a_row_src;
     p.b_group_rows = n_full;
     p.b_row_offset = n_begin;
     p.alpha = alpha;
@@ -1398,7 +1422,12 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
         return make_tmap_2d(tm, kind == kBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, ebytes, op->data, k,
                             (uint64_t)groups * op->rows, (uint64_t)op->outer_stride * ebytes, box_k, box_rows, CU_TENSOR_MAP_SWIZZLE_128B, what);
     };
-    if ((st = operand_map(&ta, a, a_mn, groups_a, kBlockM, "A")) != DG_OK) return st;
+    if (a_row_src) {
+        // the un-permuted rows, one per box: tile::gather4 takes four of them per instruction
+        if (plan.cluster != 1 || p.k_splits > 1) return fail(DG_ERR_UNSUPPORTED, "gathered A rows run on single CTAs without split-K");
+        if ((st = make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a->data, k, a_src_rows, (uint64_t)a->outer_stride, box_k, 1u,
+                               CU_TENSOR_MAP_SWIZZLE_128B, "A (gathered rows)")) != DG_OK) return st;
+    } else if ((st = operand_map(&ta, a, a_mn, groups_a, kBlockM, "A")) != DG_OK) return st;
     if ((st = operand_map(&tb, b, b_mn, groups_b, p.block_n / plan.cluster, "B")) != DG_OK) return st;
     plan.tb_tail = tb;
     if (p.tail_n && (st = operand_map(&plan.tb_tail, b, false, groups_b, p.tail_n / plan.cluster, "B (last column tile)")) != DG_OK) return st;
@@ -1466,6 +1495,13 @@ static int32_t run_gemm(const dg_operand_t* a, const dg_operand_t* b, dg_output_
         }
         if (graph_ws) cudaFreeAsync(graph_ws, s);
         return lst;
+    }
+    if (a_row_src) {
+        if (plan.dynamic) p.tile_counter = tile_counters(dev);
+        if (plan.dynamic && sfw) return launch<kFp8, kContiguous, 1, false, true, false, true, true>(plan, ta, tb, tsa, tsb, s);
+        if (plan.dynamic) return launch<kFp8, kContiguous, 1, false, true, false, false, true>(plan, ta, tb, tsa, tsb, s);
+        if (sfw) return launch<kFp8, kContiguous, 1, false, false, false, true, true>(plan, ta, tb, tsa, tsb, s);
+        return launch<kFp8, kContiguous, 1, false, false, false, false, true>(plan, ta, tb, tsa, tsb, s);
     }
     if (plan.dynamic) {
         p.tile_counter = tile_counters(dev);
@@ -1576,6 +1612,14 @@ int32_t dg_m_grouped_gemm_nt_contiguous_scatter(const dg_operand_t* a, const dg_
     return dg::run_gemm(a, b, out, dg::kContiguous, m_indices, m_indices_len, num_groups, a->rows, 0, stream, d_row_map,
                         n_begin, n_count);
 }
+int32_t dg_m_grouped_gemm_nt_contiguous_gather(const dg_operand_t* a, const int32_t* a_row_src, uint32_t a_src_rows,
+                                               const dg_operand_t* b, dg_output_t* out, const int32_t* m_indices,
+                                               uint32_t m_indices_len, uint32_t num_groups, void* stream) {
+    if (!a_row_src) return dg::fail(DG_ERR_INVALID_ARG, "m-grouped contiguous gather requires the row list");
+    return dg::run_gemm(a, b, out, dg::kContiguous, m_indices, m_indices_len, num_groups, 0, 0, stream, nullptr, 0, 0, nullptr,
+                        nullptr, 1.f, a_row_src, a_src_rows);
+}
+
 int32_t dg_m_grouped_gemm_nt_contiguous_rowptr(const dg_operand_t* a, const dg_operand_t* b, const int32_t* m_indices,
                                                uint32_t m_indices_len, uint32_t num_groups, const uint64_t* d_row_ptr,
                                                const int32_t* m_blocks_used, uint32_t n_begin, uint32_t n_count, void* stream) {

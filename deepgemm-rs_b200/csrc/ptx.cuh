@@ -174,6 +174,16 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* m, uint32_t bar, 
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// Four rows of a 2-D tensor, picked by their row coordinates y0..y3, at inner coordinate x: the four boxes (the
+// map's box is one row high) land one after the other at `dst`, swizzled by their shared-memory address like
+// the rows of an ordinary tile, so a tile can be assembled from arbitrary rows, four per instruction.
+__device__ __forceinline__ void tma_gather4_2d(const CUtensorMap* m, uint32_t bar, uint32_t dst, int32_t x, int32_t y0, int32_t y1,
+                                               int32_t y2, int32_t y3) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::1 "
+        "[%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3) : "memory");
+}
 // The same load issued by either CTA of a pair: `bar` is a shared::cluster address (the leader
 // CTA's barrier), the destination is this CTA's own shared memory.  No multicast.
 __device__ __forceinline__ void tma_load_2d_pair(const CUtensorMap* m, uint32_t bar, uint32_t dst, int32_t x, int32_t y) {

@@ -79,6 +79,7 @@ def load(build_if_missing=True):
               "dg_m_grouped_fp4_gemm_nt_contiguous", "dg_m_grouped_bf16_gemm_nt_contiguous"):
         getattr(L, n).argtypes = [opp, opp, outp, vp, u32, u32, vp]
     L.dg_m_grouped_gemm_nt_contiguous_scatter.argtypes = [opp, opp, outp, vp, u32, u32, vp, u32, u32, vp]
+    L.dg_m_grouped_gemm_nt_contiguous_gather.argtypes = [opp, vp, u32, opp, outp, vp, u32, u32, vp]
     for n in ("dg_m_grouped_gemm_nt_masked", "dg_m_grouped_fp8_gemm_nt_masked",
               "dg_m_grouped_fp4_gemm_nt_masked", "dg_m_grouped_bf16_gemm_nt_masked"):
         getattr(L, n).argtypes = [opp, opp, outp, vp, u32, u32, vp]

@@ -152,6 +152,15 @@ def m_grouped_gemm_nt_contiguous_scatter(a, b, out, m_indices, num_groups, d_row
                                                                n_begin, n_count, _stream_ptr(stream)))
 
 
+def m_grouped_gemm_nt_contiguous_gather(a, a_row_src, a_src_rows, b, out, m_indices, num_groups, stream=None):
+    """Extension: `a.data` holds `a_src_rows` un-permuted FP8 rows; row r of the grouped matrix (a.rows rows, never
+    written out) is row a_row_src[r] of it (int32 device tensor, negative = padding).  a.sf is in the grouped order."""
+    ac, bc, oc = _op_c(a), _op_c(b), _out_c(out)
+    _check(_lib.load().dg_m_grouped_gemm_nt_contiguous_gather(C.byref(ac), a_row_src.data_ptr(), a_src_rows, C.byref(bc), C.byref(oc),
+                                                              m_indices.data_ptr(), m_indices.numel(), num_groups,
+                                                              _stream_ptr(stream)))
+
+
 def m_grouped_gemm_nt_contiguous_rowptr(a, b, m_indices, num_groups, d_row_ptr, n_begin=0, n_count=0, stream=None,
                                         m_blocks_used=None):
     """Extension: BF16 result row r is stored at the address d_row_ptr[r] (int64 device tensor of

@@ -24,11 +24,20 @@ import torch
 import torch.distributed as dist
 
 from . import _lib
-from .api import (_check, _stream_ptr, m_grouped_gemm_nt_contiguous, m_grouped_gemm_nt_contiguous_rowptr,
-                  m_grouped_gemm_nt_contiguous_scatter, swiglu_quant)
+from .api import (_check, _stream_ptr, m_grouped_gemm_nt_contiguous, m_grouped_gemm_nt_contiguous_gather,
+                  m_grouped_gemm_nt_contiguous_rowptr, m_grouped_gemm_nt_contiguous_scatter, swiglu_quant)
 from .types import Dtype, Operand, Output, SfGran, SfTensor
 
 BLOCK = 128  # rows per m_indices entry (heuristics::mk_alignment_for_contiguous_layout)
+
+
+def _gather_in_gemm():
+    """DG_MOE_GATHER=1 lets the grouped GEMM of the single-GPU step fetch the token rows itself
+    (dg_m_grouped_gemm_nt_contiguous_gather) instead of reading a permuted copy written by gather_rows.  Off by
+    default: it saves the 1 GB copy and its 0.28 ms, but the 32 four-row TMA instructions a k-block then needs
+    take the producer warp longer than the k-block's MMAs (measured: the step 11.4 ms against 4.5 ms)."""
+    import os
+    return os.environ.get("DG_MOE_GATHER", "0") == "1"
 
 
 @dataclass
@@ -310,12 +319,18 @@ class ExpertParallelMoE:
         if self.world == 1 and not (self.single_rank_transport and self.transport == "push"):
             # one device-side plan straight into the padded layout; no host synchronisation
             p = device_plan(topk_idx, self.num_experts, BLOCK, div=topk)
-            a = gather_rows(x, p.slot_src)
             a_sf = sf_permute(x_sf, p.slot_src)
             d = torch.empty((p.capacity, n_out), dtype=torch.bfloat16, device=x.device)
-            a_op = Operand.k_major(self.w.dtype, p.capacity, k_elems, k_elems, a_sf, a)
-            m_grouped_gemm_nt_contiguous(a_op, self.w, Output(Dtype.Bf16, p.capacity, n_out, n_out, d), p.block_expert,
-                                         self.e_local)
+            if self.w.dtype == Dtype.Fp8 and x.stride(0) == k and _gather_in_gemm():
+                # the GEMM's producer fetches the token rows itself (four per TMA instruction): no permuted copy
+                a_op = Operand.k_major(self.w.dtype, p.capacity, k_elems, k_elems, a_sf, x)
+                m_grouped_gemm_nt_contiguous_gather(a_op, p.slot_src, tokens, self.w, Output(Dtype.Bf16, p.capacity, n_out, n_out, d),
+                                                    p.block_expert, self.e_local)
+            else:
+                a = gather_rows(x, p.slot_src)
+                a_op = Operand.k_major(self.w.dtype, p.capacity, k_elems, k_elems, a_sf, a)
+                m_grouped_gemm_nt_contiguous(a_op, self.w, Output(Dtype.Bf16, p.capacity, n_out, n_out, d), p.block_expert,
+                                             self.e_local)
             self.last_m_indices = p.block_expert
             return combine(d, p.slot_of_row.view(tokens, topk), topk_w)
         if self.transport in ("push", "peer"):

@@ -106,6 +106,9 @@ extern "C" {
     pub fn dg_m_grouped_gemm_nt_contiguous_scatter(a: *const DgOperand, b: *const DgOperand, out: *mut DgOutput, m_indices: *const i32,
                                                    m_indices_len: u32, num_groups: u32, d_row_map: *const i32, n_begin: u32,
                                                    n_count: u32, stream: Stream) -> i32;
+    pub fn dg_m_grouped_gemm_nt_contiguous_gather(a: *const DgOperand, a_row_src: *const i32, a_src_rows: u32, b: *const DgOperand,
+                                                  out: *mut DgOutput, m_indices: *const i32, m_indices_len: u32, num_groups: u32,
+                                                  stream: Stream) -> i32;
     pub fn dg_m_grouped_gemm_nt_contiguous_rowptr(a: *const DgOperand, b: *const DgOperand, m_indices: *const i32, m_indices_len: u32,
                                                   num_groups: u32, d_row_ptr: *const u64, m_blocks_used: *const i32, n_begin: u32,
                                                   n_count: u32, stream: Stream) -> i32;

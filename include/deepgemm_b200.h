@@ -145,6 +145,18 @@ DG_API int32_t dg_m_grouped_gemm_nt_contiguous_scatter(const dg_operand_t* a, co
                                                        const int32_t* m_indices, uint32_t m_indices_len,
                                                        uint32_t num_groups, const int32_t* d_row_map,
                                                        uint32_t n_begin, uint32_t n_count, void* stream);
+/* Extension (no counterpart in the reference): the contiguous grouped GEMM that gathers the rows of A itself.
+ * a.data holds a_src_rows un-permuted rows (K-major FP8, pitch a.outer_stride); a.rows is the row count M of the
+ * grouped matrix (a multiple of 128) that is never written out: its row r is row a_row_src[r] of a.data (device,
+ * int32, M entries, 16-byte aligned; negative = padding row, whose result is unspecified).  a.sf holds the scale
+ * factors in the grouped order, as for dg_m_grouped_gemm_nt_contiguous.  The producer warp fetches four rows per
+ * TMA instruction (tile::gather4), so a MoE layer needs no permuted copy of its tokens (the caller of
+ * Serving::moe_grouped_layer, deepgemm/src/api_serving.rs:308-370, builds one).  It trades time for that memory:
+ * a k-block needs 32 such instructions, which the producer warp issues more slowly than the tensor core consumes
+ * the tile (about a third of the throughput of dg_m_grouped_gemm_nt_contiguous on 16384 tokens x top-8). */
+DG_API int32_t dg_m_grouped_gemm_nt_contiguous_gather(const dg_operand_t* a, const int32_t* a_row_src, uint32_t a_src_rows,
+                                                      const dg_operand_t* b, dg_output_t* out, const int32_t* m_indices,
+                                                      uint32_t m_indices_len, uint32_t num_groups, void* stream);
 /* replaces api::m_grouped_gemm_nt_masked (deepgemm/src/api.rs:930-963).  a, b and out are
  * stacked per group ([num_groups * rows, ...]); masked_m (device, int32, num_groups entries)
  * holds the valid rows of each group; rows beyond it are neither computed nor written.

@@ -8,9 +8,9 @@ import pytest
 import torch
 
 import oracle as o
-from deepgemm import (Dtype, Operand, Output, m_grouped_gemm_nt_contiguous_scatter, bf16_gemm_nt, fp4_gemm_nt, fp8_gemm_nt, gemm_nt, get_gemm_config,
+from deepgemm import (Dtype, Operand, Output, m_grouped_gemm_nt_contiguous_gather, m_grouped_gemm_nt_contiguous_scatter, bf16_gemm_nt, fp4_gemm_nt, fp8_gemm_nt, gemm_nt, get_gemm_config,
                       m_grouped_fp8_gemm_nt_contiguous, m_grouped_fp8_gemm_nt_masked, m_grouped_gemm_nt_contiguous,
-                      m_grouped_gemm_nt_masked, poll_device_status)
+                      m_grouped_gemm_nt_masked, poll_device_status, SfGran, SfTensor)
 from helpers import (assert_close_to_oracle, bf16_operand, bf16_round, dev, new_output, quantised_operand, randn,
                      to_f32)
 
@@ -282,6 +282,53 @@ def test_m_grouped_contiguous_many_blocks_random_runs():
             assert (got[rows] == 3.0).all()
         else:
             assert_close_to_oracle(got[rows], bf16_round(o.gemm_ref(ga, gb, rows=rows, n=n, b_row0=e * n)), "fp8", f"block {i}")
+
+
+@pytest.mark.parametrize("groups,n,k,tokens,blocks", [
+    (3, 384, 512, 200, [2, 0, 0, -1, 1]),
+    (4, 416, 1024, 77, [3, 3, 1, 0, 2, 2]),          # 416 = two 208-wide tiles; sources repeat (fewer tokens than rows)
+    (2, 4096, 7168, 300, [1, 0, 1]),                  # the shape of the MoE step: K = 7168, twenty column tiles
+])
+def test_m_grouped_contiguous_gather_equals_the_permuted_copy(groups, n, k, tokens, blocks):
+    """Extension entry: the producer gathers the rows of A from an un-permuted matrix through a row list
+    (tile::gather4).  Every non-padding row must equal, bit for bit, the plain grouped GEMM on the permuted copy."""
+    m = 128 * len(blocks)
+    rng = np.random.default_rng(k + tokens)
+    src = randn((tokens, k), 5)
+    codes, sf = o.quant_mx_host(src, o.FP8, 128)                     # [tokens, k] codes, packed SF [k/512, align4(tokens)]
+    row_src = rng.integers(0, tokens, m).astype(np.int32)
+    row_src[rng.random(m) < 0.1] = -1                                 # padding rows anywhere
+    take = np.maximum(row_src, 0)
+    a_codes = codes[take].copy()
+    a_codes[row_src < 0] = 0
+    a_sf = sf[:, take].copy()
+    a_sf[:, row_src < 0] = 0
+    sft = lambda w: SfTensor(w.shape[0], w.shape[1], SfGran.G128, dev(np.ascontiguousarray(w).view(np.int32)))
+    b, _ = _stacked_b("fp8", groups, n, k, 4, gran=128)
+    mi = dev(np.array(blocks, dtype=np.int32))
+    want = new_output(m, n, fill=0.0)
+    m_grouped_gemm_nt_contiguous(Operand.k_major(Dtype.Fp8, m, k, k, sft(a_sf), dev(a_codes)), b, want, mi, groups)
+    got = new_output(m, n, fill=0.0)
+    m_grouped_gemm_nt_contiguous_gather(Operand.k_major(Dtype.Fp8, m, k, k, sft(a_sf), dev(codes)), dev(row_src), tokens, b, got, mi, groups)
+    poll_device_status()
+    g, w = to_f32(got), to_f32(want)
+    for r in range(m):
+        if blocks[r // 128] >= 0 and row_src[r] >= 0:
+            assert np.array_equal(g[r], w[r]), f"row {r}"
+
+
+def test_m_grouped_contiguous_gather_argument_checks():
+    m, n, k = 128, 256, 512
+    a, _ = quantised_operand(randn((m, k), 3), "fp8", 128)
+    b, _ = _stacked_b("fp8", 1, n, k, 4, gran=128)
+    mi = dev(np.zeros(1, dtype=np.int32))
+    rows = dev(np.arange(m, dtype=np.int32))
+    with pytest.raises(Exception):
+        m_grouped_gemm_nt_contiguous_gather(a, rows, 0, b, new_output(m, n), mi, 1)            # no source rows
+    a4, _ = quantised_operand(randn((m, k), 3), "fp4", 32)
+    b4, _ = _stacked_b("fp4", 1, n, k, 4, gran=32)
+    with pytest.raises(Exception):
+        m_grouped_gemm_nt_contiguous_gather(a4, rows, m, b4, new_output(m, n), mi, 1)          # FP8 only
 
 
 def test_m_grouped_contiguous_scatter_and_column_range():
