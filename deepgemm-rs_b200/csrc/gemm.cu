@@ -279,12 +279,16 @@ static_assert(sizeof(Barriers) <= kSmemBarrierBytes, "barrier block too large");
 // SPLIT (dense, single CTA only): a work item is a K range of a tile and the epilogue stores f32
 // partial tiles.  It is a separate instantiation because a k-loop that starts at a run-time
 // block measurably slows the common case (the k-block index feeds every role's bookkeeping).
-// GA (contiguous layout, single CTA, K-major FP8): the rows of A are gathered by the producer itself -- row r of
-// the grouped matrix is row p.a_row_src[r] of the buffer behind tm_a (a map whose box is one row), fetched four
-// rows per TMA instruction (tile::gather4), one instruction per lane and k-block -- so the caller need not
-// write a permuted copy of its rows first.
+// GA (contiguous layout, single CTA, K-major FP8): the rows of A are gathered inside the kernel -- row r of the
+// grouped matrix is row p.a_row_src[r] of the buffer behind tm_a (a map whose box is one row), fetched four rows
+// per TMA instruction (tile::gather4) -- so the caller need not write a permuted copy of its rows first.  A
+// k-block needs 32 such instructions and a warp issues them one lane after the other (22 ns each), so extra
+// warps (8 ..) share them; warp 0 still announces the bytes and loads B and the scale factors.  Measured on the
+// grouped GEMM of the MoE step (2018 TFLOPS from a permuted copy): issued by warp 0 alone 695 TFLOPS, by 4 / 8 /
+// 16 extra warps 1598 / 1713 / 1811.
+constexpr uint32_t kGatherWarps = 16;
 template <int KIND, int GTYPE, int CL, bool SPLIT, bool DYN, bool MNM = false, bool SFW = false, bool GA = false>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(GA ? 256 + 32 * kGatherWarps : 256, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_bt,
             const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb, const GemmParams p) {
     constexpr bool kHasSf = KIND != kBf16;
@@ -330,7 +334,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             // readers of a tile id: producer, MMA issuer, (SF transposer,) four epilogue warps
             for (uint32_t s = 0; s < kSchedRing; ++s) {
                 mbar_init(smem_u32(&bars->sched.full[s]), 1);
-                mbar_init(smem_u32(&bars->sched.empty[s]), kHasSf ? 7 : 6);
+                mbar_init(smem_u32(&bars->sched.empty[s]), (kHasSf ? 7 : 6) + (GA ? kGatherWarps : 0u));
             }
         }
         fence_barrier_init();
@@ -418,14 +422,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             const CUtensorMap* bmap = t.tail ? &tm_bt : &tm_b;
             const uint32_t tx_ab = t.tail ? p.tx_ab_tail : p.tx_ab;
             const uint32_t b_rows_per_cta = (t.tail ? p.tail_n : p.block_n) / CL;
-            // GA: lane l fetches rows 4 l .. 4 l + 3 of the tile; padding rows (negative entries) read row 0, their
-            // scale factors are zero and their outputs belong to nobody
-            int4 src_rows = make_int4(0, 0, 0, 0);
-            if (GA) {
-                src_rows = __ldg(reinterpret_cast<const int4*>(p.a_row_src + t.a_row) + lane);
-                src_rows.x = max(src_rows.x, 0); src_rows.y = max(src_rows.y, 0);
-                src_rows.z = max(src_rows.z, 0); src_rows.w = max(src_rows.w, 0);
-            }
             for (uint32_t ki = 0; ki < kb_count; ++ki) {
                 const uint32_t kb = kb_first + ki;
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
@@ -480,8 +476,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                     }
                 }
                 __syncwarp();
-                // the bytes were announced by the elected lane above: 32 x 4 rows x 128 bytes make up the A tile
-                if (GA) tma_gather4_2d(&tm_a, smem_u32(&bars->full[stage]), sa + lane * 512u, kx, src_rows.x, src_rows.y, src_rows.z, src_rows.w);
                 if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
             }
         }
@@ -716,7 +710,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             if (id >= total) break;                               // the roles read the end marker and stop as well
             if (++slot == kSchedRing) { slot = 0; phase ^= 1u; }
         }
-    } else if (warp >= 4) {
+    } else if (GA && warp >= 8) {
+        // ===================================================== A rows gathered through the row list
+        // Gather warp g assembles rows 32 g .. 32 g + 31 of every A tile: lanes 0 .. 7 hold four source rows each
+        // (read once per tile; padding rows, negative entries, read row 0: their scale factors are zero and their
+        // outputs belong to nobody) and issue one four-row load per k-block into the stage the producer announced.
+        Scheduler<GTYPE, CL, SPLIT, DYN> sched(rank, mtiles, n_mtiles, run_first, n_runs);
+        sched.attach(&bars->sched, &wc);
+        Tile t;
+        constexpr uint32_t kLanes = 32u / kGatherWarps;      // lanes of a gather warp that issue loads
+        const uint32_t row0 = (warp - 8u) * (128u / kGatherWarps) + lane * 4u;
+        uint32_t stage = 0, phase = 0;
+        bool ok = true;
+        while (ok && sched.next(p, t)) {
+            if (t.skip) continue;
+            int4 src = make_int4(0, 0, 0, 0);
+            if (lane < kLanes) {
+                src = __ldg(reinterpret_cast<const int4*>(p.a_row_src + t.a_row + row0));
+                src.x = max(src.x, 0); src.y = max(src.y, 0); src.z = max(src.z, 0); src.w = max(src.w, 0);
+            }
+            for (uint32_t kb = 0; kb < p.num_k_blocks; ++kb) {
+                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
+                if (lane < kLanes)
+                    tma_gather4_2d(&tm_a, smem_u32(&bars->full[stage]), stage_addr(stage) + row0 * 128u, (int32_t)(kb * 128u),
+                                   src.x, src.y, src.z, src.w);
+                __syncwarp();
+                if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
         // ===================================================== epilogue
         Scheduler<GTYPE, CL, SPLIT, DYN> sched(rank, mtiles, n_mtiles, run_first, n_runs);
         sched.attach(&bars->sched, &wc);
@@ -1230,7 +1252,7 @@ static int32_t launch(const Plan& plan, const CUtensorMap& ta, const CUtensorMap
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(plan.grid);
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(GA ? 256 + 32 * kGatherWarps : 256);
     cfg.dynamicSmemBytes = plan.smem_bytes;
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
