@@ -648,6 +648,38 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
                                                          "frac_of_measured_tensor_peak": tf / (2 * peaks["bf16_tflops"]),
                                                          "parity": {"calc_diff": dq, "max_err": eq}})
 
+    # mqa_logits, the reference's own SM100 contract: UE8M0 scales per 32 along head_dim on q and kv, bf16 weights and logits
+    if want("mqa_logits_ue8m0_T4096_S32768_H64_D128"):
+        from deepgemm import Operand
+        T, S, H, D = 4096, 32768, 64, 128
+        q8, qsf = dg.quant_mx(torch.randn((T * H, D), device=dev, generator=g), T * H, D, Dtype.Fp8, 32)
+        kv8, kvsf = dg.quant_mx(torch.randn((S, D), device=dev, generator=g) * 3.0, S, D, Dtype.Fp8, 32)
+        wq = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+        ks = torch.zeros(T, dtype=torch.int32, device=dev)
+        ke = (S - T + torch.arange(T, device=dev) + 1).to(torch.int32)
+        logits = torch.empty((T, S), dtype=torch.bfloat16, device=dev)
+        qop = Operand.k_major(Dtype.Fp8, T * H, D, D, qsf, q8)
+        kvop = Operand.k_major(Dtype.Fp8, S, D, D, kvsf, kv8)
+        ms = timeit(lambda: dg.mqa_logits(qop, kvop, wq, ks, ke, T, S, H, D, logits, S), iters=5)
+        pairs = int(ke.sum().item())
+        tf = 2.0 * H * D * pairs / ms / 1e9
+        qs = sampled.pick(T, 16, 36, [0, 1, T - 1, 2047, 2048])
+        ends = S - T + qs + 1
+        js = sampled.pick(S, 1024, 37, [0, 127, 128, S - 1] + [int(e) - 1 for e in ends])
+        qrows = (np.asarray(qs)[:, None] * H + np.arange(H)[None, :]).reshape(-1)
+        qg = sampled.golden_rows(q8, qsf.buf, qrows, o.FP8, 32, D)
+        kg = sampled.golden_rows(kv8, kvsf.buf, js, o.FP8, 32, D)
+        qd = o.dequant_mx_host(qg.data, qg.sf, len(qrows), D, o.FP8, 32).reshape(len(qs), H, D)
+        kd = o.dequant_mx_host(kg.data, kg.sf, len(js), D, o.FP8, 32)
+        ref = o.mqa_logits_ref(qd, kd, wq[torch.as_tensor(qs, device=dev)].float().cpu().numpy(),
+                               np.zeros(len(qs), np.uint32), np.full(len(qs), len(js), np.uint32))
+        got = logits[torch.as_tensor(qs, device=dev)][:, torch.as_tensor(js, device=dev)].float().cpu().numpy()
+        valid = js[None, :] < ends[:, None]
+        dq, eq = sampled.compare(got[valid], ref[valid], out_is_bf16=True)
+        res["mqa_logits_ue8m0_T4096_S32768_H64_D128"] = gated({"ms": ms, "tflops": tf,
+                                                               "frac_of_measured_tensor_peak": tf / (2 * peaks["bf16_tflops"]),
+                                                               "parity": {"calc_diff": dq, "max_err": eq}})
+
     # quant_mx bandwidth
     for (m, k, dt, gran, name) in ((16384, 7168, Dtype.Fp8, 128, "fp8_g128"), (16384, 7168, Dtype.Fp8, 32, "fp8_g32"),
                                    (16384, 7168, Dtype.Fp4, 32, "fp4_g32"), (4096, 16384, Dtype.Fp8, 128, "fp8_g128")):

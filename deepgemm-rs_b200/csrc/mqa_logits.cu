@@ -724,13 +724,19 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     const uint32_t max_n = SCALED ? 192u : 256u;
     uint32_t block_q = max_n / num_heads;
     if (block_q > 16) block_q = 16;
-    if (block_q >= 4) block_q &= ~3u; else if (block_q == 3) block_q = 2;
+    // The epilogue warpgroups split the query block evenly: 1, 2, 3 or 4 of them.  64 and 32 heads under the 192
+    // columns of the ue8m0 contracts keep all three (six) queries that fit, on three warpgroups (one query of 64
+    // heads or two of 32 each): with two queries the MMAs are 128 columns wide and only eight warps reduce.
+    const bool three_groups = SCALED && ((num_heads == 64 && block_q == 3) || (num_heads == 32 && block_q == 6));
+    if (three_groups) { /* keep */ }
+    else if (block_q >= 4) block_q &= ~3u;
+    else if (block_q == 3) block_q = 2;
     if (block_q == 0) return fail(DG_ERR_UNSUPPORTED, "mqa_logits: %u heads do not fit the %u score columns of this contract", num_heads, max_n);
     p.acc_stride = SCALED ? 192u : 256u;
     p.block_q = block_q;
     p.n = block_q * num_heads;
     p.n_mma = align_up(p.n, 16);
-    p.ep_groups = block_q % 4 == 0 ? 4u : block_q % 2 == 0 ? 2u : 1u;
+    p.ep_groups = three_groups ? 3u : block_q % 4 == 0 ? 4u : block_q % 2 == 0 ? 2u : 1u;
     p.unit = num_heads % 16 == 0 ? 16u : 4u;
     p.num_q_blocks = ceil_div(num_tokens, block_q);
     p.row_bytes = FP4 ? head_dim / 2 : head_dim;
@@ -820,7 +826,7 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, true>;
         e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
-    } else if (num_heads == 32 && p.block_q == 2u * p.ep_groups && p.ep_groups == 4u) {
+    } else if (num_heads == 32 && p.block_q == 2u * p.ep_groups && p.ep_groups >= 3u) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false, 4, 2>;   // two queries of 32 heads per warpgroup
         if (!budget_ok((const void*)fn, 4)) return fail_free(fail(DG_ERR_RUNTIME, "mqa_logits: register budget of the 32-head kernel does not add up"));
         e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
