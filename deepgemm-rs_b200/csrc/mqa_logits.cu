@@ -284,19 +284,48 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                 if (SCALED) tma_load_2d(&tm_qsf, qbar, qdst + p.q_sf_off, (int32_t)(k.q0 * p.num_heads), 0);
             }
             __syncwarp();
+            if (PAGED) {
+                // A block of 128 tokens is a run of whole pages (or half / a quarter of a large page): lane i looks up
+                // the page of box i in the block table.  The look-ups run four blocks ahead of the loads, and the
+                // loop is unrolled by four so that an entry stays in its register, untouched, until its block comes
+                // up: looked up inside the loop, each block cost the producer a trip to memory, and decode ran at
+                // that latency instead of the cache's bandwidth.
+                const uint32_t* trow = p.block_table + (size_t)k.table_row * p.block_table_stride;
+                const uint32_t page_shift = (uint32_t)__ffs((int)p.page_kv) - 1u;      // the page size is a power of two
+                auto tok_of = [&](uint32_t kbx) { return kbx * kMqaBlockKv + lane * p.box_rows; };
+                auto page_of = [&](uint32_t kbx) -> uint32_t {
+                    const uint32_t pg = tok_of(kbx) >> page_shift;
+                    return (kbx < k.kb1 && lane < p.boxes_per_block && pg < p.block_table_stride) ? __ldg(trow + pg) : 0u;
+                };
+                uint32_t pq[4];
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) pq[j] = page_of(k.kb0 + j);
+                for (uint32_t kb4 = k.kb0; ok && kb4 < k.kb1; kb4 += 4u) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        const uint32_t kb = kb4 + j;
+                        if (kb >= k.kb1) break;
+                        if (!(ok = DG_WARP_WAIT(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
+                        const uint32_t bar = smem_u32(&bars->kv_full[stage]);
+                        const uint32_t dst = base + p.off_kv + stage * p.kv_stage_bytes;
+                        // rows past the table's width or pages outside the cache read row 0 (paged_row)
+                        uint32_t row = pq[j] * p.page_kv + (tok_of(kb) & (p.page_kv - 1u));
+                        if (row + p.box_rows > p.num_kv) row = 0u;
+                        pq[j] = page_of(kb + 4u);
+                        if (lane == 0) mbar_arrive_expect_tx(bar, kv_tx);
+                        __syncwarp();
+                        if (lane < p.boxes_per_block) tma_load_2d(&tm_kv, bar, dst + lane * p.box_rows * p.row_bytes, 0, (int32_t)row);
+                        __syncwarp();
+                        if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+                continue;
+            }
             for (uint32_t kb = k.kb0; kb < k.kb1; ++kb) {
                 if (!(ok = DG_WARP_WAIT(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, wc, kWaitEmpty))) break;
                 const uint32_t bar = smem_u32(&bars->kv_full[stage]);
                 const uint32_t dst = base + p.off_kv + stage * p.kv_stage_bytes;
-                if (PAGED) {
-                    // a block of 128 tokens is a run of whole pages (or half / a quarter of a large page): lane i
-                    // looks up the page of box i
-                    uint32_t row = 0;
-                    if (lane < p.boxes_per_block) row = paged_row(p, k.table_row, kb * kMqaBlockKv + lane * p.box_rows, p.box_rows);
-                    if (lane == 0) mbar_arrive_expect_tx(bar, kv_tx);
-                    __syncwarp();
-                    if (lane < p.boxes_per_block) tma_load_2d(&tm_kv, bar, dst + lane * p.box_rows * p.row_bytes, 0, (int32_t)row);
-                } else if (elect_one()) {
+                if (elect_one()) {
                     mbar_arrive_expect_tx(bar, kv_tx);
                     tma_load_2d(&tm_kv, bar, dst, 0, (int32_t)(kb * kMqaBlockKv));
                     if (SCALED) tma_load_2d(&tm_kvsf, bar, dst + p.kv_sf_off, (int32_t)(kb * kMqaBlockKv), 0);
@@ -381,17 +410,57 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->q_ready[qs]));
+            if (PAGED) {
+                // Lane l fetches the words of tokens 4 l .. 4 l + 3 of a block: they lie in one page (pages hold a
+                // multiple of four tokens), so it is one block-table entry and one 16-byte load.  Both run ahead
+                // of the block that is written -- entries four blocks, words two -- in registers that are not touched
+                // before their block comes up (the loop is unrolled by four for that): fetched inside the loop, one
+                // after the other, they cost two trips to memory per block, and decode ran at that latency.
+                const uint32_t* trow = p.block_table + (size_t)k.table_row * p.block_table_stride;
+                const uint32_t page_shift = (uint32_t)__ffs((int)p.page_kv) - 1u;
+                auto page_of = [&](uint32_t kbx) -> uint32_t {
+                    const uint32_t pg = (kbx * kMqaBlockKv + 4u * lane) >> page_shift;
+                    return (kbx < k.kb1 && pg < p.block_table_stride) ? __ldg(trow + pg) : 0u;
+                };
+                auto words_of = [&](uint32_t kbx, uint32_t page) -> uint4 {
+                    uint32_t row = page * p.page_kv + ((kbx * kMqaBlockKv + 4u * lane) & (p.page_kv - 1u));
+                    if (row + 4u > p.num_kv) row = 0u;       // tokens past the table or the cache: masked by the epilogue
+                    return __ldg(reinterpret_cast<const uint4*>(p.kv_sf + row));
+                };
+                uint32_t pq[4];
+                uint4 wq2[2];
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) pq[j] = page_of(k.kb0 + j);
+                wq2[0] = words_of(k.kb0, pq[0]);
+                wq2[1] = words_of(k.kb0 + 1u, pq[1]);
+                for (uint32_t kb4 = k.kb0; ok && kb4 < k.kb1; kb4 += 4u) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        const uint32_t kb = kb4 + j;
+                        if (kb >= k.kb1) break;
+                        const uint4 cur = wq2[j & 1u];
+                        wq2[j & 1u] = words_of(kb + 2u, pq[(j + 2u) & 3u]);
+                        pq[j] = page_of(kb + 4u);
+                        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, wc, kWaitEmpty));
+                        if (!ok) break;
+                        uint32_t* sf = reinterpret_cast<uint32_t*>(base_ptr + p.off_kv + stage * p.kv_stage_bytes + p.kv_sf_off);
+                        // row r = 4 l + i of the block goes to position 4 (r % 32) + r / 32
+                        const uint32_t hi = lane >> 3;
+                        sf[4u * ((4u * lane + 0u) & 31u) + hi] = cur.x;
+                        sf[4u * ((4u * lane + 1u) & 31u) + hi] = cur.y;
+                        sf[4u * ((4u * lane + 2u) & 31u) + hi] = cur.z;
+                        sf[4u * ((4u * lane + 3u) & 31u) + hi] = cur.w;
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars->kv_ready[stage]));
+                        if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
+                    }
+                }
+                continue;
+            }
             for (uint32_t kb = k.kb0; kb < k.kb1; ++kb) {
                 uint32_t* sf = reinterpret_cast<uint32_t*>(base_ptr + p.off_kv + stage * p.kv_stage_bytes + p.kv_sf_off);
-                if (PAGED) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->kv_empty[stage]), phase ^ 1u, wc, kWaitEmpty));
-                    if (!ok) break;
-                    uint32_t v[4];
-#pragma unroll
-                    for (uint32_t i = 0; i < 4; ++i)
-                        v[i] = __ldg(p.kv_sf + paged_row(p, k.table_row, kb * kMqaBlockKv + 32u * i + lane, 1u));
-                    *reinterpret_cast<uint4*>(sf + lane * 4u) = make_uint4(v[0], v[1], v[2], v[3]);
-                } else {
+                {
                     ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull));
                     if (!ok) break;
                     transpose128(sf);
@@ -914,6 +983,8 @@ int32_t dg_mqa_logits_paged(const dg_operand_t* q, const void* kv_pages, const u
                             uint32_t head_dim, void* logits_bf16, uint32_t logits_stride, void* stream) {
     if (!kv_pages || !kv_sf_pages || !context_lens || !indices || !block_table)
         return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits_paged: null buffer");
+    if (reinterpret_cast<uintptr_t>(kv_sf_pages) & 15u)
+        return dg::fail(DG_ERR_INVALID_ARG, "mqa_logits_paged: the scale words of the cache must be 16-byte aligned (they are read four tokens at a time)");
     // deepgemm/src/api.rs:1778-1795
     if (head_dim % 32 != 0 || head_dim > 128 || head_dim == 96 || head_dim == 0)
         return dg::fail(DG_ERR_INVALID_ARG, "head_dim must be 32/64/128");

@@ -256,7 +256,7 @@ DG_API int32_t dg_mqa_logits(const dg_operand_t* q, const dg_operand_t* kv, cons
 /* replaces api::mqa_logits_paged (deepgemm/src/api.rs:1752-1941) and its metadata kernel
  * (deepgemm/kernels/mqa_logits_sm100.cu:359-492): the ue8m0 contract over a paged KV cache, for decode.
  * q as in dg_mqa_logits ([num_tokens * num_heads, head_dim], FP8 or FP4, per-32 scales); kv_pages
- * [num_pages, page_kv, head_dim] codes and kv_sf_pages [num_pages, page_kv] one scale word per token;
+ * [num_pages, page_kv, head_dim] codes and kv_sf_pages [num_pages, page_kv] one scale word per token (16-byte aligned);
  * weights bf16 [num_tokens, num_heads].  indices[t] = request of query token t (sorted: tokens of a request
  * are neighbours), context_lens[t] = kv tokens visible to token t (growing inside a request),
  * block_table[first token of the request][i] = page holding the request's kv tokens [i * page_kv, (i+1) *
