@@ -680,6 +680,47 @@ def extra_workloads(torch, dg, synth, dev, peaks, only=None):
                                                                "frac_of_measured_tensor_peak": tf / (2 * peaks["bf16_tflops"]),
                                                                "parity": {"calc_diff": dq, "max_err": eq}})
 
+    # mqa_logits over a paged KV cache (decode): 128 requests of 32768 tokens, two query tokens each, pages of 64 tokens
+    if want("mqa_logits_paged_B128_ctx32768_n2_H64_D128"):
+        from deepgemm import Operand, mqa_logits_paged
+        B, CTX, NN, PAGE, H, D = 128, 32768, 2, 64, 64, 128
+        T, pages_per = B * NN, CTX // PAGE
+        num_pages = B * pages_per + 3
+        q8, qsf = dg.quant_mx(torch.randn((T * H, D), device=dev, generator=g), T * H, D, Dtype.Fp8, 32)
+        kv8, kvsf = dg.quant_mx(torch.randn((num_pages * PAGE, D), device=dev, generator=g) * 2.0, num_pages * PAGE, D, Dtype.Fp8, 32)
+        kv_words = kvsf.buf[0, :num_pages * PAGE].contiguous()            # head_dim 128: one packed word per token
+        wq = torch.randn((T, H), device=dev, generator=g).to(torch.bfloat16)
+        perm = torch.randperm(num_pages, device=dev, generator=g).to(torch.int32)
+        stride = pages_per + 1
+        table = torch.full((T, stride), 10 ** 6, dtype=torch.int32, device=dev)       # only a request's first row is read
+        table[::NN, :pages_per] = perm[:B * pages_per].view(B, pages_per)
+        req = torch.arange(B, device=dev, dtype=torch.int32).repeat_interleave(NN)
+        ctx = (CTX - (NN - 1) + torch.arange(NN, device=dev)).repeat(B).to(torch.int32)
+        width = CTX + 8
+        logits = torch.full((T, width), -7.0, dtype=torch.bfloat16, device=dev)
+        qop = Operand.k_major(Dtype.Fp8, T * H, D, D, qsf, q8)
+        ms = timeit(lambda: mqa_logits_paged(qop, kv8, kv_words, wq, PAGE, num_pages, ctx, req, table, stride, T, H, D, logits, width), iters=5)
+        byts = B * CTX * (D + 4) + T * CTX * 2
+        worst = {"calc_diff": 0.0, "max_err": 0.0}
+        for b in (0, B // 2, B - 1):                                                   # three whole requests against the oracle
+            rows = (table[b * NN, :pages_per].long()[:, None] * PAGE + torch.arange(PAGE, device=dev)[None, :]).reshape(-1)
+            kg = sampled.golden_rows(kv8, kvsf.buf, rows.cpu().numpy(), o.FP8, 32, D)
+            kd = o.dequant_mx_host(kg.data, kg.sf, CTX, D, o.FP8, 32)
+            qrows = np.arange(b * NN * H, (b + 1) * NN * H)
+            qg = sampled.golden_rows(q8, qsf.buf, qrows, o.FP8, 32, D)
+            qd = o.dequant_mx_host(qg.data, qg.sf, NN * H, D, o.FP8, 32).reshape(NN, H, D)
+            ends = ctx[b * NN:(b + 1) * NN].cpu().numpy().astype(np.uint32)
+            ref = o.mqa_logits_ref(qd, kd, wq[b * NN:(b + 1) * NN].float().cpu().numpy(), np.zeros(NN, np.uint32), ends)
+            got = logits[b * NN:(b + 1) * NN, :CTX].float().cpu().numpy()
+            valid = np.arange(CTX)[None, :] < ends[:, None]
+            dq, eq = sampled.compare(got[valid], ref[valid], out_is_bf16=True)
+            worst = {"calc_diff": max(worst["calc_diff"], dq), "max_err": max(worst["max_err"], eq)}
+            if not (got[~valid] == -7.0).all():
+                worst["max_err"] = float("inf")                                        # something was written past a context length
+        res["mqa_logits_paged_B128_ctx32768_n2_H64_D128"] = gated({"ms": ms, "gbs": byts / ms / 1e6,
+                                                                    "frac_of_measured_hbm": byts / ms / 1e6 / peaks["hbm_gbs"],
+                                                                    "tflops": 2.0 * H * D * T * CTX / ms / 1e9, "parity": worst})
+
     # quant_mx bandwidth
     for (m, k, dt, gran, name) in ((16384, 7168, Dtype.Fp8, 128, "fp8_g128"), (16384, 7168, Dtype.Fp8, 32, "fp8_g32"),
                                    (16384, 7168, Dtype.Fp4, 32, "fp4_g32"), (4096, 16384, Dtype.Fp8, 128, "fp8_g128")):
