@@ -349,17 +349,28 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const uint32_t qaddr = base + p.off_q + qs * p.q_stage_bytes;
             const uint64_t q_desc = make_smem_desc(qaddr, p.sbo, 0, p.layout);
             bool q_sf_copied = false;
+            // ue8m0 contracts: the kv loop of a task is run by one elected lane alone.  Warp-wide waits (a vote and a
+            // re-convergence per barrier, three barriers per kv block, then the scale-factor copy) cost the issuer
+            // more than the MMAs of a block take: 1380 -> 1690 TFLOPS on 4096 x 64 heads x 32768.  The fp32 contract
+            // (two barriers, no copy) is 1.5 % faster with the warp-wide loop and keeps it.
+            constexpr bool kLaneLoop = SCALED;
+            const bool issuer = elect_one();
+            const uint32_t issuer_lane = (uint32_t)__ffs(__ballot_sync(0xffffffffu, issuer)) - 1u;
+            auto wait_on = [&](uint32_t bar, uint32_t parity, uint32_t site) -> bool {
+                return kLaneLoop ? mbar_wait(bar, parity, wc, site) : (bool)DG_WARP_WAIT(bar, parity, wc, site);
+            };
+            if (!kLaneLoop || issuer) {
             for (uint32_t kb = k.kb0; ok && kb < k.kb1; ++kb) {
-                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->kv_full[stage]), phase, wc, kWaitFull))) break;
-                if (SCALED && !(ok = DG_WARP_WAIT(smem_u32(&bars->kv_ready[stage]), phase, wc, kWaitSfReady))) break;
+                if (!(ok = wait_on(smem_u32(&bars->kv_full[stage]), phase, kWaitFull))) break;
+                if (SCALED && !(ok = wait_on(smem_u32(&bars->kv_ready[stage]), phase, kWaitSfReady))) break;
                 const uint32_t kaddr = base + p.off_kv + stage * p.kv_stage_bytes;
                 const uint64_t kv_desc = make_smem_desc(kaddr, p.sbo, 0, p.layout);
                 const uint32_t as = acount & 1u, aphase = (acount >> 1) & 1u;
                 ++acount;
-                if (!(ok = DG_WARP_WAIT(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, wc, kWaitTmemEmpty))) break;
+                if (!(ok = wait_on(smem_u32(&bars->tmem_empty[as]), aphase ^ 1u, kWaitTmemEmpty))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem + as * acc_stride;
-                if (elect_one()) {
+                if (kLaneLoop || elect_one()) {
                     if (SCALED) {
                         if (!q_sf_copied)    // the q scales of this task: in order behind every MMA that used the previous task's
                             for (uint32_t c = 0; c < (p.n + 127u) / 128u; ++c)
@@ -380,9 +391,18 @@ mqa_logits_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                     tc_commit(smem_u32(&bars->tmem_full[as]));
                     if (kb + 1 == k.kb1) tc_commit(smem_u32(&bars->q_empty[qs]));
                 }
-                __syncwarp();
+                if (!kLaneLoop) __syncwarp();
                 q_sf_copied = true;
                 if (++stage == p.kv_stages) { stage = 0; phase ^= 1u; }
+            }
+            }
+            if (kLaneLoop) {
+                // the other lanes take over the issuer's position in the rings
+                __syncwarp();
+                stage = __shfl_sync(0xffffffffu, stage, issuer_lane);
+                phase = __shfl_sync(0xffffffffu, phase, issuer_lane);
+                acount = __shfl_sync(0xffffffffu, acount, issuer_lane);
+                ok = __shfl_sync(0xffffffffu, (uint32_t)ok, issuer_lane) != 0u;
             }
         }
     } else if (warp == 2 && SCALED) {
@@ -849,6 +869,7 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     p.status = dev->status;
 
     uint32_t* meta = nullptr;
+    bool meta_owned = false;        // allocated for this call alone (graph capture): freed behind the launch
     if (PAGED) {
         p.page_kv = pg.page_kv;
         p.box_rows = pg.page_kv < kMqaBlockKv ? pg.page_kv : kMqaBlockKv;
@@ -857,9 +878,39 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
         p.context_lens = pg.context_lens;
         p.block_table = pg.block_table;
         p.block_table_stride = pg.block_table_stride;
-        // scratch of the metadata kernel: three arrays of one word per token, stream-ordered
+        // Scratch of the metadata kernel: three arrays of one word per token.  One buffer per (thread, device,
+        // stream), grown on demand with stream-ordered allocation and kept for the next call: work on one stream is
+        // ordered, so consecutive calls may share it, and an allocation per call costs a decode step more than its
+        // kernels (after a synchronisation the pool has given its memory back and the next call waits for the
+        // driver).  Inside a graph capture the buffer must belong to the graph: allocated and freed per call.
         const size_t words = 3 * (size_t)num_tokens + 4;
-        DG_CUDA_CHECK(cudaMallocAsync(&meta, words * sizeof(uint32_t), s));
+        struct MetaWs { cudaStream_t stream; int device; uint32_t* ptr; size_t bytes; };
+        static thread_local MetaWs cache[8] = {};
+        static thread_local int cache_next = 0;
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        DG_CUDA_CHECK(cudaStreamIsCapturing(s, &capturing));
+        if (capturing != cudaStreamCaptureStatusNone) {
+            DG_CUDA_CHECK(cudaMallocAsync(&meta, words * sizeof(uint32_t), s));
+            meta_owned = true;
+        } else {
+            MetaWs* slot = nullptr;
+            for (auto& c : cache)
+                if (c.ptr && c.stream == s && c.device == dev->device) { slot = &c; break; }
+            if (!slot) {
+                slot = &cache[cache_next];
+                cache_next = (cache_next + 1) % 8;
+                if (slot->ptr) { cudaFreeAsync(slot->ptr, slot->stream); *slot = MetaWs{}; }
+            }
+            if (slot->bytes < words * sizeof(uint32_t)) {
+                if (slot->ptr) cudaFreeAsync(slot->ptr, s);
+                *slot = MetaWs{};
+                uint32_t* fresh = nullptr;
+                const size_t bytes = align_up((uint32_t)(words * sizeof(uint32_t)), 65536u);
+                DG_CUDA_CHECK(cudaMallocAsync(&fresh, bytes, s));
+                *slot = MetaWs{s, dev->device, fresh, bytes};
+            }
+            meta = slot->ptr;
+        }
         uint32_t* cum = meta;
         uint32_t* qb_tokens = meta + num_tokens + 1;
         uint32_t* req_first = qb_tokens + num_tokens;
@@ -872,7 +923,7 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     }
 
     CUtensorMap tq, tkv, tqsf, tkvsf;
-    auto fail_free = [&](int32_t code) { if (meta) cudaFreeAsync(meta, s); return code; };
+    auto fail_free = [&](int32_t code) { if (meta_owned) cudaFreeAsync(meta, s); return code; };
     if ((st = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, p.row_bytes, (uint64_t)num_tokens * num_heads, p.row_bytes,
                            p.row_bytes, p.n, sw, "q")) != DG_OK) return fail_free(st);
     if ((st = make_tmap_2d(&tkv, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, kv, p.row_bytes, num_kv, p.row_bytes, p.row_bytes,
@@ -930,7 +981,7 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
         e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     }
-    if (meta) cudaFreeAsync(meta, s);
+    if (meta_owned) cudaFreeAsync(meta, s);
     if (e != cudaSuccess) return fail(DG_ERR_DRIVER, "mqa_logits launch failed: %s", cudaGetErrorString(e));
     dg::note_launch();
     return DG_OK;
