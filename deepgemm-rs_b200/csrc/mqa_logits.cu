@@ -950,35 +950,60 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     cudaError_t e;
     // The variants that move registers from the role warps to the epilogue warpgroups block inside the kernel if the
     // registers the block got at launch do not cover what its warpgroups ask for: refuse the launch instead.
+    // the dynamic shared memory limit of a kernel is raised once per thread and device, not on every call
+    auto set_smem = [&](const void* fn) -> cudaError_t {
+        static thread_local const void* done_fn[8] = {};
+        static thread_local uint32_t done_bytes[8] = {};
+        static thread_local int done_dev[8] = {};
+        for (int i = 0; i < 8; ++i)
+            if (done_fn[i] == fn && done_dev[i] == dev->device && done_bytes[i] >= smem_bytes) return cudaSuccess;
+        const cudaError_t err = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        if (err == cudaSuccess) {
+            static thread_local int next = 0;
+            done_fn[next] = fn; done_bytes[next] = smem_bytes; done_dev[next] = dev->device;
+            next = (next + 1) % 8;
+        }
+        return err;
+    };
     auto budget_ok = [&](const void* fn, uint32_t nun) {
-        cudaFuncAttributes fa;
-        if (cudaFuncGetAttributes(&fa, fn) != cudaSuccess) return false;
+        // registers per thread of the (at most four) kernels this instantiation launches, looked up once per thread
+        static thread_local const void* seen_fn[4] = {nullptr, nullptr, nullptr, nullptr};
+        static thread_local uint32_t seen_regs[4] = {0, 0, 0, 0};
+        uint32_t regs = 0;
+        for (int i = 0; i < 4 && !regs; ++i)
+            if (seen_fn[i] == fn) regs = seen_regs[i];
+        if (!regs) {
+            cudaFuncAttributes fa;
+            if (cudaFuncGetAttributes(&fa, fn) != cudaSuccess) return false;
+            regs = (uint32_t)fa.numRegs;
+            for (int i = 0; i < 4; ++i)
+                if (!seen_fn[i]) { seen_fn[i] = fn; seen_regs[i] = regs; break; }
+        }
         const uint32_t threads = cfg.blockDim.x;
-        return threads <= mqa_threads(nun) &&
-               (uint32_t)fa.numRegs * threads >= 128u * kMqaRoleRegs + (threads - 128u) * mqa_epilogue_regs(nun);
+        return threads <= mqa_threads(nun) && regs * threads >= 128u * kMqaRoleRegs + (threads - 128u) * mqa_epilogue_regs(nun);
     };
     if (p.unit == 4u) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, true>;
-        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        e = set_smem((const void*)fn);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else if (num_heads == 32 && p.block_q == 2u * p.ep_groups && p.ep_groups >= 3u) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false, 4, 2>;   // two queries of 32 heads per warpgroup
         if (!budget_ok((const void*)fn, 4)) return fail_free(fail(DG_ERR_RUNTIME, "mqa_logits: register budget of the 32-head kernel does not add up"));
-        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        e = set_smem((const void*)fn);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else if (num_heads == 64 && p.block_q == p.ep_groups) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false, 4>;   // one query of 64 heads per warpgroup
         if (!budget_ok((const void*)fn, 4)) return fail_free(fail(DG_ERR_RUNTIME, "mqa_logits: register budget of the 64-head kernel does not add up"));
-        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        e = set_smem((const void*)fn);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else if (num_heads == 128 && p.block_q == p.ep_groups) {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false, 8>;   // one query of 128 heads per warpgroup
         if (!budget_ok((const void*)fn, 8)) return fail_free(fail(DG_ERR_RUNTIME, "mqa_logits: register budget of the 128-head kernel does not add up"));
-        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        e = set_smem((const void*)fn);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     } else {
         auto* fn = mqa_logits_kernel<SCALED, FP4, PAGED, false>;
-        e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes);
+        e = set_smem((const void*)fn);
         if (e == cudaSuccess) e = cudaLaunchKernelEx(&cfg, fn, tq, tkv, tqsf, tkvsf, p);
     }
     if (meta_owned) cudaFreeAsync(meta, s);
