@@ -83,6 +83,25 @@ def test_grouped_checks(L):
     assert "K-major" in _err(L)
 
 
+def test_gathered_rows_checks(L):
+    """The grouped GEMM that gathers the rows of A: row list, dtype and source row count are checked on any machine."""
+    a, b, o = _op(0, 256, 256), _op(0, 64, 256), _out(256, 64)
+    f = L.dg_m_grouped_gemm_nt_contiguous_gather
+    assert f(C.byref(a), None, 300, C.byref(b), C.byref(o), 0x4000, 2, 2, None) == 3 and "row list" in _err(L)
+    assert f(C.byref(a), 0x5000, 0, C.byref(b), C.byref(o), 0x4000, 2, 2, None) == 3 and "source row count" in _err(L)
+    assert f(C.byref(a), 0x5004, 300, C.byref(b), C.byref(o), 0x4000, 2, 2, None) == 3 and "16-byte aligned" in _err(L)
+    a4, b4 = _op(1, 256, 256), _op(1, 64, 256)
+    assert f(C.byref(a4), 0x5000, 300, C.byref(b4), C.byref(o), 0x4000, 2, 2, None) == 3 and "K-major FP8" in _err(L)
+
+
+def test_paged_mqa_checks(L):
+    """dg_mqa_logits_paged reads the cache's scale words four tokens at a time: they must be 16-byte aligned."""
+    q = _op(0, 2 * 64, 128)
+    args = lambda kv_sf: (C.byref(q), 0x10000, kv_sf, 0x20000, 64, 8, 0x30000, 0x40000, 0x50000, 4, 2, 64, 128, 0x60000, 256, None)
+    assert L.dg_mqa_logits_paged(*args(0x70004)) == 3 and "16-byte aligned" in _err(L)
+    assert L.dg_mqa_logits_paged(*args(None)) == 3 and "null buffer" in _err(L)
+
+
 def test_quant_checks(L):
     assert L.dg_quant_mx(0x1000, 16, 100, 0, 32, 0x2000, 0x3000, None) == 3      # K % gran
     assert L.dg_quant_mx(0x1000, 16, 256, 1, 128, 0x2000, 0x3000, None) == 3     # FP4 needs gran 32
