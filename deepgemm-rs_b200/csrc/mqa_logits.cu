@@ -65,6 +65,7 @@ struct MqaParams {
     uint32_t ep_groups;           // epilogue warpgroups; each reduces block_q / ep_groups queries
     uint32_t unit;                // columns per TMEM load (16, or 4 for head counts not divisible by 16)
     uint32_t num_q_blocks;
+    uint32_t kv_splits;           // contiguous kv: pieces a query block's kv range is cut into (few query blocks, many SMs)
     uint32_t kv_stages, kv_stage_bytes, q_stage_bytes;
     uint32_t off_w, off_q, off_kv;  // offsets from the 1024-aligned base
     uint32_t kv_sf_off, q_sf_off;   // SF words inside a kv / q stage (ue8m0 contracts)
@@ -144,8 +145,8 @@ struct MqaTasks {
             }
             return false;
         }
-        while (qb < p.num_q_blocks) {
-            const uint32_t b = qb;
+        while (qb < p.num_q_blocks * p.kv_splits) {
+            const uint32_t b = qb / p.kv_splits, piece = qb - b * p.kv_splits;
             qb += gridDim.x;
             uint32_t lo = 0xffffffffu, hi = 0;
             for (uint32_t i = 0; i < p.block_q; ++i) {
@@ -159,6 +160,13 @@ struct MqaTasks {
             k.q0 = b * p.block_q; k.nq = min(p.block_q, p.num_tokens - k.q0);
             k.kb0 = lo / kMqaBlockKv; k.kb1 = (hi + kMqaBlockKv - 1) / kMqaBlockKv;
             k.table_row = 0;
+            if (p.kv_splits > 1u) {
+                // the pieces of a query block write disjoint columns of its logits rows: no reduction between them
+                const uint32_t len = (k.kb1 - k.kb0 + p.kv_splits - 1u) / p.kv_splits;
+                k.kb0 += piece * len;
+                k.kb1 = min(k.kb1, k.kb0 + len);
+                if (k.kb0 >= k.kb1) continue;
+            }
             return true;
         }
         return false;
@@ -843,6 +851,16 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
     p.ep_groups = three_groups ? 3u : block_q % 4 == 0 ? 4u : block_q % 2 == 0 ? 2u : 1u;
     p.unit = num_heads % 16 == 0 ? 16u : 4u;
     p.num_q_blocks = ceil_div(num_tokens, block_q);
+    // Contiguous kv: the work items are query blocks, each over its whole kv range.  With fewer query blocks than
+    // twice the SMs (a short prefill chunk, a handful of queries) the range is cut into pieces of at least eight
+    // kv blocks, so that every SM gets work.
+    p.kv_splits = 1;
+    if (!PAGED && p.num_q_blocks < 2u * (uint32_t)dev->sm_count) {
+        const uint32_t kv_blocks = ceil_div(num_kv, kMqaBlockKv);
+        const uint32_t want = ceil_div(2u * (uint32_t)dev->sm_count, p.num_q_blocks);
+        const uint32_t most = kv_blocks / 8u > 1u ? kv_blocks / 8u : 1u;
+        p.kv_splits = want < most ? want : most;
+    }
     p.row_bytes = FP4 ? head_dim / 2 : head_dim;
     p.sbo = 8 * p.row_bytes;
     p.layout = p.row_bytes == 128 ? 2u : p.row_bytes == 64 ? 4u : p.row_bytes == 32 ? 6u : 0u;
@@ -936,7 +954,7 @@ static int32_t run_mqa(const void* q, const void* kv, const uint32_t* q_sf, uint
                                          kMqaBlockKv, 1, CU_TENSOR_MAP_SWIZZLE_NONE, "kv_sf")) != DG_OK) return fail_free(st);
     }
     uint32_t grid = (uint32_t)dev->sm_count;
-    if (!PAGED && p.num_q_blocks < grid) grid = p.num_q_blocks;
+    if (!PAGED && p.num_q_blocks * p.kv_splits < grid) grid = p.num_q_blocks * p.kv_splits;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(128u + 128u * p.ep_groups);
